@@ -1,0 +1,197 @@
+/*
+ * pink_b200.h -- C ABI of the B200-native implementation of PINK's
+ * rotation/flip-invariant SOM hot path (rotate/flip -> distance matrix ->
+ * minimum over rotations -> best matching unit -> neighbourhood update, and
+ * the mapping variant).
+ *
+ * The reference has no FFI layer for this path: its boundary is the C++
+ * template specialisation Trainer<..., UseGPU=true> / Mapper<..., UseGPU=true>
+ * (src/SelfOrganizingMapLib/Trainer.h:198-333, Mapper.h:126-229), which owns
+ * device buffers and calls three CudaLib entry points that take
+ * thrust::device_vector arguments.  The functions below are what a binding of
+ * that boundary needs: plain pointers and sizes, an opaque context in place of
+ * the Trainer/Mapper object's device state, and an int status in place of
+ * exceptions and exit().  Each entry names the reference code it stands for.
+ *
+ * Conventions
+ *   - every function returns PINK_B200_OK (0) or a negative PINK_B200_E* code;
+ *     nothing throws, nothing calls exit().  pink_b200_last_error() returns a
+ *     message for the calling thread's most recent failure.
+ *   - "host" pointers are ordinary (pageable or pinned) host memory, "dev"
+ *     pointers are device memory of the context's device.
+ *   - images are float32 [C][id][id] (C == 1 for 2-D data), SOMs are float32
+ *     [N][C][nd][nd], both row-major without padding.
+ *   - a context is used from one host thread at a time.
+ *   - there is no CPU fallback: every compute entry runs CUDA kernels and
+ *     fails with PINK_B200_ECUDA where no sm_100 device is present.
+ */
+#ifndef PINK_B200_H
+#define PINK_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PINK_B200_OK          0
+#define PINK_B200_EINVAL     -1   /* bad argument or unsupported configuration      */
+#define PINK_B200_ECUDA      -2   /* CUDA runtime / driver error                    */
+#define PINK_B200_ENCCL      -3   /* NCCL error or NCCL library not loadable        */
+#define PINK_B200_ETIMEOUT   -4   /* a bounded device-side wait expired             */
+#define PINK_B200_ESTATE     -5   /* call not valid in the context's current state  */
+
+/* Distance modes; numbering of pink::DataType (src/UtilitiesLib/DataType.h:17-22). */
+#define PINK_B200_FLOAT   0
+#define PINK_B200_UINT16  1
+#define PINK_B200_UINT8   2
+
+/* Shape of the distance region (src/UtilitiesLib/EuclideanDistanceShape.h:15-19). */
+#define PINK_B200_QUADRATIC 0
+#define PINK_B200_CIRCULAR  1
+
+/* Interpolation (src/UtilitiesLib/Interpolation.h:15-19); only BILINEAR exists
+ * on the reference's GPU path (src/CudaLib/generate_rotated_images.h:119-121). */
+#define PINK_B200_NEAREST_NEIGHBOR 0
+#define PINK_B200_BILINEAR         1
+
+typedef struct pink_b200_ctx pink_b200_ctx;
+
+/* Everything the Trainer / Mapper constructors take that shapes device state
+ * (src/SelfOrganizingMapLib/Trainer.h:211-215, Mapper.h:134-137). */
+typedef struct pink_b200_config {
+    uint32_t n_neurons;        /* N: neurons of the whole SOM                                  */
+    uint32_t channels;         /* C: 1 for 2-D images, dimension 0 of 3-D images ("spacing")   */
+    uint32_t image_dim;        /* id: images are square                                        */
+    uint32_t neuron_dim;       /* nd                                                           */
+    uint32_t ed_dim;           /* euclidean_distance_dim                                       */
+    uint32_t ed_shape;         /* PINK_B200_QUADRATIC                                          */
+    uint32_t n_rotations;      /* number_of_rotations: 1 or a multiple of 4                    */
+    uint32_t use_flip;         /* 0 / 1                                                        */
+    uint32_t dist_type;        /* PINK_B200_FLOAT / UINT16 / UINT8                             */
+    uint32_t interpolation;    /* PINK_B200_BILINEAR                                           */
+    int32_t  device;           /* CUDA device ordinal                                          */
+    uint32_t rank;             /* this process's index among the neuron shards                 */
+    uint32_t world_size;       /* number of neuron shards (1 = whole SOM on this device)       */
+    uint32_t max_batch;        /* images staged per internal batch (0 = default)               */
+} pink_b200_config;
+
+/* Message of the calling thread's most recent failing call ("" if none). */
+const char* pink_b200_last_error(void);
+
+/* Library version string. */
+const char* pink_b200_version(void);
+
+/* ---- context life cycle ---------------------------------------------------- */
+
+/* Validates the configuration (errors of TrainerCommon / MapperCommon,
+ * src/SelfOrganizingMapLib/Trainer.h:66-67, Mapper.h:59-66, and "Images must
+ * be quadratic" is implied by image_dim) and allocates the device state the
+ * reference allocates in the Trainer / Mapper constructors
+ * (Trainer.h:216-260, Mapper.h:138-178), including the cos/sin tables. */
+int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out);
+int pink_b200_destroy(pink_b200_ctx* ctx);
+
+/* Neurons [first, first+count) of the SOM live on this context's device:
+ * N/world (+1 for the first N % world ranks), contiguous, as the reference's
+ * multi-GPU split (src/CudaLib/generate_euclidean_distance_matrix_first_step_multi_gpu.h:65-77). */
+int pink_b200_shard(const pink_b200_ctx* ctx, uint32_t* first, uint32_t* count);
+
+/* ---- multi-GPU: one process per GPU, neuron shards, NCCL for the BMU exchange
+ * (replaces the per-image cudaMemcpyPeer traffic of
+ *  src/CudaLib/generate_euclidean_distance_matrix_first_step_multi_gpu.h:87-104,184-193). */
+
+/* Rank 0 fills a 128-byte NCCL unique id; the caller distributes it. */
+int pink_b200_comm_unique_id(void* id128);
+/* Collective over all ranks of the job; required before training when world_size > 1. */
+int pink_b200_comm_init(pink_b200_ctx* ctx, const void* id128);
+
+/* ---- SOM and neighbourhood table ------------------------------------------- */
+
+/* Upload the SOM (host, [N][P] float, the WHOLE map: each rank keeps its
+ * shard) and build the distance operand.  Stands for the device copy taken at
+ * construction, Trainer.h:219 / Mapper.h:140. */
+int pink_b200_set_som(pink_b200_ctx* ctx, const float* host_som);
+/* Write this rank's shard into rows [first, first+count) of host_som ([N][P]);
+ * other rows are left untouched.  Stands for Trainer::update_som(), Trainer.h:306-309. */
+int pink_b200_get_som(pink_b200_ctx* ctx, float* host_som);
+/* Upload the N x N update-factor table F[bmu * N + n] the reference builds on
+ * the host from the layout distance and the distribution function
+ * (Trainer.h:69-76, uploaded at :243).  Each rank keeps its columns. */
+int pink_b200_set_update_factors(pink_b200_ctx* ctx, const float* host_factors);
+
+/* ---- training --------------------------------------------------------------
+ * n sequential training steps; image i+1 sees the SOM updated by image i.
+ * Stands for n calls of Trainer<...,true>::operator() (Trainer.h:263-304).
+ * Asynchronous with respect to the host except for staging of host images;
+ * results are observed through get_som / get_update_counts / synchronize. */
+int pink_b200_train(pink_b200_ctx* ctx, const float* host_images, uint64_t n);
+int pink_b200_train_device(pink_b200_ctx* ctx, const float* dev_images, uint64_t n);
+/* Per-neuron BMU hit counters, [N] (all ranks hold the same totals only for
+ * their own shard; other entries are zero).  Stands for get_update_info(),
+ * Trainer.h:79, counted at :302-303. */
+int pink_b200_get_update_counts(pink_b200_ctx* ctx, uint32_t* host_counts);
+/* Optional: global BMU index of each of the last train call's images (host, [n]);
+ * only the rank owning the BMU writes an entry, others read 0xFFFFFFFF. */
+int pink_b200_get_bmu_log(pink_b200_ctx* ctx, uint32_t* host_bmus, uint64_t n);
+
+/* ---- mapping ---------------------------------------------------------------
+ * For each of n images: dist[i][j] = sqrt(min over transforms of the scaled
+ * squared distance to local neuron j), rot[i][j] = the first transform
+ * attaining it; j runs over this rank's shard (count entries per image).
+ * Stands for n calls of Mapper<...,true>::operator() (Mapper.h:181-208). */
+int pink_b200_map(pink_b200_ctx* ctx, const float* host_images, uint64_t n, float* host_dist, uint32_t* host_rot);
+int pink_b200_map_device(pink_b200_ctx* ctx, const float* dev_images, uint64_t n, float* dev_dist, uint32_t* dev_rot);
+
+/* Wait for all queued work of the context; surfaces asynchronous errors and
+ * device-side time-outs. */
+int pink_b200_synchronize(pink_b200_ctx* ctx);
+
+/* The CUDA stream (cudaStream_t) the context launches on, for callers that
+ * time or order work against it. */
+void* pink_b200_stream(pink_b200_ctx* ctx);
+
+/* ---- single stages on device buffers (what the context calls internally) ---
+ * Exposed for kernel-level parity tests and benchmarks.  `stream` is a
+ * cudaStream_t (NULL = default stream).  Operand layout: integer modes use
+ * rows of `row_stride` bytes (a multiple of 128, zero beyond K) per plane,
+ * uint16 as two planes (high bytes, low bytes); float mode uses rows of
+ * `row_stride` floats (a multiple of 16, zero beyond K). */
+
+/* Row stride (in elements) the library uses for a distance length of K elements. */
+uint32_t pink_b200_operand_stride(uint32_t K, uint32_t dist_type);
+
+/* Rotation set of n_img images: base rotations (float, [n_img][max(R/4,1)][C][nd][nd],
+ * may be NULL when shared memory holds a base) and the distance operand rows of
+ * all T transforms with their sums of squares.  Stands for
+ * SpatialTransformerGPU (src/CudaLib/generate_rotated_images.h:56-294) plus the
+ * transform half of generate_euclidean_distance_matrix's crop/convert
+ * (src/CudaLib/generate_euclidean_distance_matrix.h:86-112). */
+int pink_b200_op_rotate(const pink_b200_config* cfg, const float* dev_images, uint32_t n_img,
+                        float* dev_base, void* dev_b0, void* dev_b1, void* dev_bnorm, void* stream);
+
+/* SOM half of the crop/convert (generate_euclidean_distance_matrix.h:64-84). */
+int pink_b200_op_quantize_som(const pink_b200_config* cfg, const float* dev_som, uint32_t n_neurons,
+                              void* dev_a0, void* dev_a1, void* dev_anorm, void* stream);
+
+/* Distance of every (neuron, transform) pair reduced to the per-neuron minimum
+ * key (code << shift | transform; shift 32, or 16 for uint16), merged into
+ * dev_keys with an unsigned minimum (fill with 0xFF bytes first).  dev_matrix
+ * (nullable) receives the full [n_img][n][T] matrix: uint32 (uint8 mode),
+ * uint64 (uint16), float (float).  Stands for
+ * generate_euclidean_distance_matrix_first_step + _second_step
+ * (src/CudaLib/generate_euclidean_distance_matrix_first_step.h:17-52,
+ *  ..._second_step.h:43-62). */
+int pink_b200_op_distance(uint32_t dist_type, uint32_t n_neurons, uint32_t n_transforms, uint32_t K,
+                          const void* dev_a0, const void* dev_a1, const void* dev_anorm,
+                          const void* dev_b0, const void* dev_b1, const void* dev_bnorm, uint32_t n_img,
+                          unsigned long long* dev_keys, void* dev_matrix, void* stream);
+
+/* Waits for the device and reports (then clears) a time-out recorded by a
+ * pink_b200_op_distance launch: PINK_B200_OK or PINK_B200_ETIMEOUT. */
+int pink_b200_op_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PINK_B200_H */

@@ -1,0 +1,87 @@
+"""ctypes binding of the C ABI declared in include/pink_b200.h.
+
+The shared library holds the CUDA kernels; there is no other implementation.
+Importing this module fails loudly when the library has not been built
+(python -m pink_b200.build), and every compute call fails with a RuntimeError
+carrying the library's message when no sm_100 device is present.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libpink_b200.so")
+
+OK, EINVAL, ECUDA, ENCCL, ETIMEOUT, ESTATE = 0, -1, -2, -3, -4, -5
+FLOAT, UINT16, UINT8 = 0, 1, 2
+QUADRATIC, CIRCULAR = 0, 1
+NEAREST_NEIGHBOR, BILINEAR = 0, 1
+
+
+class Config(C.Structure):
+    """Mirror of struct pink_b200_config."""
+    _fields_ = [("n_neurons", C.c_uint32), ("channels", C.c_uint32), ("image_dim", C.c_uint32),
+                ("neuron_dim", C.c_uint32), ("ed_dim", C.c_uint32), ("ed_shape", C.c_uint32),
+                ("n_rotations", C.c_uint32), ("use_flip", C.c_uint32), ("dist_type", C.c_uint32),
+                ("interpolation", C.c_uint32), ("device", C.c_int32), ("rank", C.c_uint32),
+                ("world_size", C.c_uint32), ("max_batch", C.c_uint32)]
+
+
+# name -> (restype, argtypes); the complete list of symbols the header declares
+SYMBOLS = {
+    "pink_b200_last_error": (C.c_char_p, []),
+    "pink_b200_version": (C.c_char_p, []),
+    "pink_b200_create": (C.c_int, [C.POINTER(Config), C.POINTER(C.c_void_p)]),
+    "pink_b200_destroy": (C.c_int, [C.c_void_p]),
+    "pink_b200_shard": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
+    "pink_b200_comm_unique_id": (C.c_int, [C.c_void_p]),
+    "pink_b200_comm_init": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "pink_b200_set_som": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "pink_b200_get_som": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "pink_b200_set_update_factors": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "pink_b200_train": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64]),
+    "pink_b200_train_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64]),
+    "pink_b200_get_update_counts": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "pink_b200_get_bmu_log": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64]),
+    "pink_b200_map": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),
+    "pink_b200_map_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),
+    "pink_b200_synchronize": (C.c_int, [C.c_void_p]),
+    "pink_b200_stream": (C.c_void_p, [C.c_void_p]),
+    "pink_b200_operand_stride": (C.c_uint32, [C.c_uint32, C.c_uint32]),
+    "pink_b200_op_rotate": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p,
+                                      C.c_void_p, C.c_void_p, C.c_void_p]),
+    "pink_b200_op_quantize_som": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p,
+                                            C.c_void_p, C.c_void_p]),
+    "pink_b200_op_distance": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p,
+                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
+                                        C.c_void_p, C.c_void_p]),
+    "pink_b200_op_status": (C.c_int, []),
+}
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError("pink_b200: %s is missing; build it with `python -m pink_b200.build` "
+                          "(there is no CPU fallback)" % LIB_PATH)
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SYMBOLS.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+class PinkError(RuntimeError):
+    """A failing C-ABI call; .code is the PINK_B200_E* value."""
+
+    def __init__(self, code, msg):
+        super().__init__(msg)
+        self.code = code
+
+
+def check(rc):
+    if rc != OK:
+        raise PinkError(rc, lib.pink_b200_last_error().decode())
+    return rc

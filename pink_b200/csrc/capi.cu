@@ -1,0 +1,692 @@
+// C ABI of the library (declared in include/pink_b200.h): context state that
+// stands for the device members of the reference's Trainer<...,true> and
+// Mapper<...,true> objects (src/SelfOrganizingMapLib/Trainer.h:311-333,
+// Mapper.h:210-229), the per-image launch sequences, host<->device staging and
+// the NCCL exchange of the per-shard best matching unit.
+#include "../../include/pink_b200.h"
+#include "kernels.cuh"
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <dlfcn.h>
+#include <nccl.h>
+#include <new>
+#include <string>
+#include <vector>
+
+using namespace pinkb;
+
+namespace {
+
+thread_local std::string g_error;
+
+int fail(int code, const std::string& msg)
+{
+    g_error = msg;
+    return code;
+}
+
+#define CU_TRY(expr)                                                                              \
+    do {                                                                                          \
+        cudaError_t e_ = (expr);                                                                  \
+        if (e_ != cudaSuccess)                                                                    \
+            return fail(PINK_B200_ECUDA, std::string(#expr) + ": " + cudaGetErrorString(e_));     \
+    } while (0)
+
+// ---- NCCL, resolved at run time so that single-GPU users need no NCCL at all ----
+struct NcclApi
+{
+    void* handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    bool ok = false;
+};
+
+NcclApi& nccl()
+{
+    static NcclApi api;
+    if (api.handle) return api;
+    api.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!api.handle) api.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!api.handle) return api;
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.handle, "ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(api.handle, "ncclAllGather"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
+    api.ok = api.GetUniqueId && api.CommInitRank && api.AllGather && api.CommDestroy && api.GetErrorString;
+    return api;
+}
+
+#define NCCL_TRY(expr)                                                                            \
+    do {                                                                                          \
+        ncclResult_t r_ = (expr);                                                                 \
+        if (r_ != ncclSuccess)                                                                    \
+            return fail(PINK_B200_ENCCL, std::string(#expr) + ": " + nccl().GetErrorString(r_)); \
+    } while (0)
+
+uint32_t round_up(uint32_t v, uint32_t m) { return (v + m - 1) / m * m; }
+
+// Validation messages follow the reference's exceptions where it has one.
+int make_geometry(const pink_b200_config& c, Geometry* g)
+{
+    if (c.n_neurons == 0 || c.channels == 0 || c.image_dim == 0 || c.neuron_dim == 0)
+        return fail(PINK_B200_EINVAL, "SOM, image and neuron dimensions must be positive");
+    if (c.n_rotations == 0 || (c.n_rotations != 1 && c.n_rotations % 4 != 0))
+        return fail(PINK_B200_EINVAL, "Number of rotations must be 1 or larger then 1 and divisible by 4");
+    if (c.ed_dim == 0) return fail(PINK_B200_EINVAL, "euclidean_distance_dim not defined");
+    if (c.ed_dim > c.neuron_dim)
+        return fail(PINK_B200_EINVAL, "Euclidean distance dimension larger than neuron dimension");
+    if (c.interpolation != PINK_B200_BILINEAR)
+        return fail(PINK_B200_EINVAL, "generate_rotated_images: unknown interpolation type");
+    if (c.ed_shape != PINK_B200_QUADRATIC)
+        return fail(PINK_B200_EINVAL, "circular euclidean distance shape is not supported by this library");
+    if (c.dist_type > PINK_B200_UINT8) return fail(PINK_B200_EINVAL, "Unknown euclidean_distance_type");
+
+    g->C = c.channels; g->id = c.image_dim; g->nd = c.neuron_dim; g->ed = c.ed_dim;
+    g->R = c.n_rotations; g->flip = c.use_flip ? 1 : 0;
+    g->T = g->R * (g->flip ? 2 : 1);
+    g->q = g->R == 1 ? 0 : g->R / 4;
+    g->off = static_cast<uint32_t>((g->nd - g->ed) * 0.5);
+    const uint64_t P = (uint64_t)g->C * g->nd * g->nd, K = (uint64_t)g->C * g->ed * g->ed;
+    if (P > (1u << 30)) return fail(PINK_B200_EINVAL, "neuron size too large");
+    g->P = (uint32_t)P; g->Pp = round_up(g->P, 4);
+    g->K = (uint32_t)K;
+    g->mode = (int)c.dist_type;
+    g->Kp = g->mode == kModeF32 ? round_up(g->K, 16) : round_up(g->K, 128);
+    // s32 accumulators: K * 255^2 (uint8) and 2 * K * 255^2 (uint16 cross term) must stay below 2^31.
+    if (g->mode == kModeU8 && g->K > 33025) return fail(PINK_B200_EINVAL, "uint8 distance supports at most 33025 elements");
+    if (g->mode == kModeU16 && g->K > 16512) return fail(PINK_B200_EINVAL, "uint16 distance supports at most 16512 elements");
+    if (g->mode == kModeU16 && g->T > 65536) return fail(PINK_B200_EINVAL, "uint16 distance supports at most 65536 transforms");
+    return PINK_B200_OK;
+}
+
+size_t operand_plane_bytes(const Geometry& g, size_t rows)
+{
+    return rows * g.Kp * (g.mode == kModeF32 ? 4 : 1);
+}
+
+size_t norm_bytes(const Geometry& g, size_t rows)
+{
+    return rows * (g.mode == kModeU16 ? 8 : 4);
+}
+
+template <typename T>
+void free_dev(T*& p)
+{
+    if (p) cudaFree(p);
+    p = nullptr;
+}
+
+} // namespace
+
+struct pink_b200_ctx
+{
+    pink_b200_config cfg{};
+    Geometry g{};
+    uint32_t first = 0, count = 0;
+    uint32_t train_batch = 0, map_batch = 0;
+    cudaStream_t stream = nullptr, copy_stream = nullptr;
+    cudaEvent_t copied[2] = { nullptr, nullptr }, consumed[2] = { nullptr, nullptr };
+
+    float* d_som = nullptr;
+    void *d_a0 = nullptr, *d_a1 = nullptr, *d_anorm = nullptr;
+    float *d_cs = nullptr, *d_sn = nullptr;
+    float* d_factors = nullptr;
+    float* d_base = nullptr;   size_t base_imgs = 0;
+    void *d_b0 = nullptr, *d_b1 = nullptr, *d_bnorm = nullptr; size_t b_imgs = 0;
+    unsigned long long* d_keys = nullptr; size_t key_imgs = 0;
+    BmuPair* d_pairs = nullptr;
+    uint32_t* d_counts = nullptr;
+    uint32_t* d_bmu_log = nullptr; size_t bmu_log_cap = 0, bmu_log_n = 0;
+    int* d_status = nullptr;
+    float* d_images[2] = { nullptr, nullptr }; size_t image_cap = 0;
+    float* d_dist = nullptr; uint32_t* d_rot = nullptr; size_t out_imgs = 0;
+    bool have_som = false, have_factors = false;
+    ncclComm_t comm = nullptr;
+
+    size_t image_size() const { return (size_t)g.C * g.id * g.id; }
+};
+
+namespace {
+
+// A base rotation is staged in shared memory when it fits; only then can the
+// float copy in global memory be skipped (mapping never reads it back).
+bool base_fits_smem(const Geometry& g) { return (size_t)g.P * sizeof(float) <= 200 * 1024; }
+
+int ensure_transform_buffers(pink_b200_ctx* c, size_t imgs, size_t base_needed)
+{
+    const Geometry& g = c->g;
+    if (c->b_imgs < imgs) {
+        free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm);
+        const size_t rows = imgs * g.T;
+        CU_TRY(cudaMalloc(&c->d_b0, operand_plane_bytes(g, rows)));
+        CU_TRY(cudaMemsetAsync(c->d_b0, 0, operand_plane_bytes(g, rows), c->stream));
+        if (g.mode == kModeU16) {
+            CU_TRY(cudaMalloc(&c->d_b1, operand_plane_bytes(g, rows)));
+            CU_TRY(cudaMemsetAsync(c->d_b1, 0, operand_plane_bytes(g, rows), c->stream));
+        }
+        CU_TRY(cudaMalloc(&c->d_bnorm, norm_bytes(g, rows)));
+        c->b_imgs = imgs;
+    }
+    if (c->base_imgs < base_needed) {
+        free_dev(c->d_base);
+        CU_TRY(cudaMalloc(&c->d_base, base_needed * (g.q ? g.q : 1) * (size_t)g.P * sizeof(float)));
+        c->base_imgs = base_needed;
+    }
+    if (c->key_imgs < imgs) {
+        free_dev(c->d_keys);
+        CU_TRY(cudaMalloc(&c->d_keys, imgs * c->count * sizeof(unsigned long long)));
+        launch_fill_keys(c->d_keys, imgs * c->count, c->stream);
+        c->key_imgs = imgs;
+    }
+    return PINK_B200_OK;
+}
+
+int ensure_image_staging(pink_b200_ctx* c, size_t imgs)
+{
+    if (c->image_cap >= imgs) return PINK_B200_OK;
+    for (int i = 0; i < 2; ++i) {
+        free_dev(c->d_images[i]);
+        CU_TRY(cudaMalloc(&c->d_images[i], imgs * c->image_size() * sizeof(float)));
+    }
+    c->image_cap = imgs;
+    return PINK_B200_OK;
+}
+
+int check_status(pink_b200_ctx* c)
+{
+    int st = 0;
+    CU_TRY(cudaMemcpyAsync(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    if (st != kDevOk) {
+        cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream);
+        return fail(PINK_B200_ETIMEOUT, "device-side wait expired in the distance kernel (code " + std::to_string(st) + ")");
+    }
+    return PINK_B200_OK;
+}
+
+// One training step on an image that is already on the device.
+int train_one(pink_b200_ctx* c, const float* d_image, uint32_t* bmu_slot)
+{
+    const Geometry& g = c->g;
+    launch_rotate(g, d_image, 1, c->d_cs, c->d_sn, c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream);
+    DistanceArgs da{};
+    da.a0 = c->d_a0; da.a1 = c->d_a1; da.anorm = c->d_anorm; da.n = c->count;
+    da.b0 = c->d_b0; da.b1 = c->d_b1; da.bnorm = c->d_bnorm; da.n_img = 1;
+    da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status;
+    const char* why = "";
+    cudaError_t e = launch_distance(g, da, c->stream, &why);
+    if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
+    launch_bmu(g, c->d_keys, c->count, c->first, c->d_pairs + c->cfg.rank, c->stream);
+    if (c->cfg.world_size > 1)
+        NCCL_TRY(nccl().AllGather(c->d_pairs + c->cfg.rank, c->d_pairs, 2, ncclUint64, c->comm, c->stream));
+    UpdateArgs ua{};
+    ua.som = c->d_som; ua.base = c->d_base; ua.keys = c->d_keys;
+    ua.pairs = c->d_pairs; ua.world = c->cfg.world_size;
+    ua.factors = c->d_factors; ua.n = c->count; ua.first_neuron = c->first;
+    ua.a0 = c->d_a0; ua.a1 = c->d_a1; ua.anorm = c->d_anorm;
+    ua.counts = c->d_counts; ua.bmu_log = bmu_slot;
+    launch_update(g, ua, c->stream);
+    return PINK_B200_OK;
+}
+
+int train_prepare(pink_b200_ctx* c, uint64_t n)
+{
+    if (!c->have_som) return fail(PINK_B200_ESTATE, "pink_b200_set_som must be called before training");
+    if (!c->have_factors) return fail(PINK_B200_ESTATE, "pink_b200_set_update_factors must be called before training");
+    if (c->cfg.world_size > 1 && !c->comm)
+        return fail(PINK_B200_ESTATE, "pink_b200_comm_init must be called before training with world_size > 1");
+    int rc = ensure_transform_buffers(c, 1, 1);
+    if (rc) return rc;
+    if (c->bmu_log_cap < n) {
+        free_dev(c->d_bmu_log);
+        CU_TRY(cudaMalloc(&c->d_bmu_log, n * sizeof(uint32_t)));
+        c->bmu_log_cap = n;
+    }
+    CU_TRY(cudaMemsetAsync(c->d_bmu_log, 0xFF, n * sizeof(uint32_t), c->stream));
+    c->bmu_log_n = n;
+    return PINK_B200_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+const char* pink_b200_last_error(void) { return g_error.c_str(); }
+
+const char* pink_b200_version(void) { return "pink_b200 0.1 (sm_100a)"; }
+
+uint32_t pink_b200_operand_stride(uint32_t K, uint32_t dist_type)
+{
+    return dist_type == PINK_B200_FLOAT ? round_up(K, 16) : round_up(K, 128);
+}
+
+int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
+{
+    if (!cfg || !out) return fail(PINK_B200_EINVAL, "null argument");
+    *out = nullptr;
+    Geometry g{};
+    int rc = make_geometry(*cfg, &g);
+    if (rc) return rc;
+    if (cfg->world_size == 0 || cfg->rank >= cfg->world_size)
+        return fail(PINK_B200_EINVAL, "rank must be smaller than world_size");
+    if (cfg->world_size > cfg->n_neurons)
+        return fail(PINK_B200_EINVAL, "more neuron shards than neurons");
+
+    CU_TRY(cudaSetDevice(cfg->device));
+    cudaDeviceProp prop{};
+    CU_TRY(cudaGetDeviceProperties(&prop, cfg->device));
+    if (prop.major != 10)
+        return fail(PINK_B200_ECUDA, std::string("device '") + prop.name + "' is not an sm_100 GPU; this library has no other code path");
+
+    pink_b200_ctx* c = new (std::nothrow) pink_b200_ctx();
+    if (!c) return fail(PINK_B200_EINVAL, "out of host memory");
+    c->cfg = *cfg;
+    c->g = g;
+    const uint32_t W = cfg->world_size, N = cfg->n_neurons;
+    const uint32_t base = N / W, extra = N % W;
+    c->count = base + (cfg->rank < extra ? 1 : 0);
+    c->first = cfg->rank * base + (cfg->rank < extra ? cfg->rank : extra);
+    c->train_batch = cfg->max_batch ? cfg->max_batch : 256;
+    {
+        // Mapping batch: bound the transform operand of one batch to about 1 GiB.
+        const size_t per_img = operand_plane_bytes(g, g.T) * (g.mode == kModeU16 ? 2 : 1);
+        size_t mb = (size_t(1) << 30) / (per_img ? per_img : 1);
+        if (mb < 1) mb = 1;
+        if (mb > 64) mb = 64;
+        if (cfg->max_batch && mb > cfg->max_batch) mb = cfg->max_batch;
+        c->map_batch = (uint32_t)mb;
+    }
+
+    auto bail = [&](int code) { pink_b200_destroy(c); return code; };
+#define CTX_TRY(expr)                                                                             \
+    do {                                                                                          \
+        cudaError_t e_ = (expr);                                                                  \
+        if (e_ != cudaSuccess) {                                                                  \
+            fail(PINK_B200_ECUDA, std::string(#expr) + ": " + cudaGetErrorString(e_));            \
+            return bail(PINK_B200_ECUDA);                                                         \
+        }                                                                                         \
+    } while (0)
+
+    CTX_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    CTX_TRY(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+        CTX_TRY(cudaEventCreateWithFlags(&c->copied[i], cudaEventDisableTiming));
+        CTX_TRY(cudaEventCreateWithFlags(&c->consumed[i], cudaEventDisableTiming));
+    }
+    CTX_TRY(cudaMalloc(&c->d_som, (size_t)c->count * g.Pp * sizeof(float)));
+    CTX_TRY(cudaMemsetAsync(c->d_som, 0, (size_t)c->count * g.Pp * sizeof(float), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_a0, operand_plane_bytes(g, c->count)));
+    CTX_TRY(cudaMemsetAsync(c->d_a0, 0, operand_plane_bytes(g, c->count), c->stream));
+    if (g.mode == kModeU16) {
+        CTX_TRY(cudaMalloc(&c->d_a1, operand_plane_bytes(g, c->count)));
+        CTX_TRY(cudaMemsetAsync(c->d_a1, 0, operand_plane_bytes(g, c->count), c->stream));
+    }
+    CTX_TRY(cudaMalloc(&c->d_anorm, norm_bytes(g, c->count)));
+    CTX_TRY(cudaMalloc(&c->d_pairs, W * sizeof(BmuPair)));
+    CTX_TRY(cudaMemsetAsync(c->d_pairs, 0xFF, W * sizeof(BmuPair), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_counts, N * sizeof(uint32_t)));
+    CTX_TRY(cudaMemsetAsync(c->d_counts, 0, N * sizeof(uint32_t), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_status, sizeof(int)));
+    CTX_TRY(cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream));
+
+    // cos/sin of t * (float(2*pi)/R), t < R/4, evaluated on the host with the
+    // reference's expressions (src/SelfOrganizingMapLib/generate_rotated_images.h:70,
+    // src/ImageProcessingLib/rotate.h:20-21).
+    {
+        const uint32_t nq = g.q ? g.q : 1;
+        std::vector<float> cs(nq), sn(nq);
+        const float step = static_cast<float>(2 * M_PI) / g.R;
+        for (uint32_t t = 0; t < nq; ++t) {
+            const float angle = t * step;
+            cs[t] = std::cos(angle);
+            sn[t] = std::sin(angle);
+        }
+        CTX_TRY(cudaMalloc(&c->d_cs, nq * sizeof(float)));
+        CTX_TRY(cudaMalloc(&c->d_sn, nq * sizeof(float)));
+        CTX_TRY(cudaMemcpy(c->d_cs, cs.data(), nq * sizeof(float), cudaMemcpyHostToDevice));
+        CTX_TRY(cudaMemcpy(c->d_sn, sn.data(), nq * sizeof(float), cudaMemcpyHostToDevice));
+    }
+    CTX_TRY(cudaStreamSynchronize(c->stream));
+#undef CTX_TRY
+    *out = c;
+    return PINK_B200_OK;
+}
+
+int pink_b200_destroy(pink_b200_ctx* c)
+{
+    if (!c) return PINK_B200_OK;
+    cudaSetDevice(c->cfg.device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->copy_stream) cudaStreamSynchronize(c->copy_stream);
+    if (c->comm && nccl().ok) nccl().CommDestroy(c->comm);
+    free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
+    free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_base);
+    free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
+    free_dev(c->d_pairs); free_dev(c->d_counts); free_dev(c->d_bmu_log); free_dev(c->d_status);
+    free_dev(c->d_images[0]); free_dev(c->d_images[1]); free_dev(c->d_dist); free_dev(c->d_rot);
+    for (int i = 0; i < 2; ++i) {
+        if (c->copied[i]) cudaEventDestroy(c->copied[i]);
+        if (c->consumed[i]) cudaEventDestroy(c->consumed[i]);
+    }
+    if (c->stream) cudaStreamDestroy(c->stream);
+    if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
+    delete c;
+    return PINK_B200_OK;
+}
+
+int pink_b200_shard(const pink_b200_ctx* c, uint32_t* first, uint32_t* count)
+{
+    if (!c) return fail(PINK_B200_EINVAL, "null context");
+    if (first) *first = c->first;
+    if (count) *count = c->count;
+    return PINK_B200_OK;
+}
+
+int pink_b200_comm_unique_id(void* id128)
+{
+    if (!id128) return fail(PINK_B200_EINVAL, "null argument");
+    if (!nccl().ok) return fail(PINK_B200_ENCCL, "libnccl.so.2 could not be loaded");
+    ncclUniqueId id;
+    NCCL_TRY(nccl().GetUniqueId(&id));
+    static_assert(sizeof(ncclUniqueId) == 128, "unique id size");
+    std::memcpy(id128, &id, 128);
+    return PINK_B200_OK;
+}
+
+int pink_b200_comm_init(pink_b200_ctx* c, const void* id128)
+{
+    if (!c || !id128) return fail(PINK_B200_EINVAL, "null argument");
+    if (c->cfg.world_size == 1) return PINK_B200_OK;
+    if (!nccl().ok) return fail(PINK_B200_ENCCL, "libnccl.so.2 could not be loaded");
+    if (c->comm) return fail(PINK_B200_ESTATE, "communicator already initialised");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    ncclUniqueId id;
+    std::memcpy(&id, id128, 128);
+    NCCL_TRY(nccl().CommInitRank(&c->comm, (int)c->cfg.world_size, id, (int)c->cfg.rank));
+    return PINK_B200_OK;
+}
+
+int pink_b200_set_som(pink_b200_ctx* c, const float* host_som)
+{
+    if (!c || !host_som) return fail(PINK_B200_EINVAL, "null argument");
+    const Geometry& g = c->g;
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    CU_TRY(cudaMemcpy2D(c->d_som, (size_t)g.Pp * sizeof(float), host_som + (size_t)c->first * g.P,
+                        (size_t)g.P * sizeof(float), (size_t)g.P * sizeof(float), c->count, cudaMemcpyHostToDevice));
+    launch_quantize_som(g, c->d_som, c->count, c->d_a0, c->d_a1, c->d_anorm, c->stream);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    c->have_som = true;
+    return PINK_B200_OK;
+}
+
+int pink_b200_get_som(pink_b200_ctx* c, float* host_som)
+{
+    if (!c || !host_som) return fail(PINK_B200_EINVAL, "null argument");
+    const Geometry& g = c->g;
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    int rc = check_status(c);
+    if (rc) return rc;
+    CU_TRY(cudaMemcpy2D(host_som + (size_t)c->first * g.P, (size_t)g.P * sizeof(float), c->d_som,
+                        (size_t)g.Pp * sizeof(float), (size_t)g.P * sizeof(float), c->count, cudaMemcpyDeviceToHost));
+    return PINK_B200_OK;
+}
+
+int pink_b200_set_update_factors(pink_b200_ctx* c, const float* host_factors)
+{
+    if (!c || !host_factors) return fail(PINK_B200_EINVAL, "null argument");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    const size_t N = c->cfg.n_neurons;
+    if (!c->d_factors) CU_TRY(cudaMalloc(&c->d_factors, N * c->count * sizeof(float)));
+    CU_TRY(cudaMemcpy2D(c->d_factors, (size_t)c->count * sizeof(float), host_factors + c->first, N * sizeof(float),
+                        (size_t)c->count * sizeof(float), N, cudaMemcpyHostToDevice));
+    c->have_factors = true;
+    return PINK_B200_OK;
+}
+
+int pink_b200_train_device(pink_b200_ctx* c, const float* dev_images, uint64_t n)
+{
+    if (!c || (!dev_images && n)) return fail(PINK_B200_EINVAL, "null argument");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    int rc = train_prepare(c, n);
+    if (rc) return rc;
+    for (uint64_t i = 0; i < n; ++i) {
+        rc = train_one(c, dev_images + i * c->image_size(), c->d_bmu_log + i);
+        if (rc) return rc;
+    }
+    CU_TRY(cudaGetLastError());
+    return PINK_B200_OK;
+}
+
+int pink_b200_train(pink_b200_ctx* c, const float* host_images, uint64_t n)
+{
+    if (!c || (!host_images && n)) return fail(PINK_B200_EINVAL, "null argument");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    int rc = train_prepare(c, n);
+    if (rc) return rc;
+    const size_t B = c->train_batch, isz = c->image_size();
+    rc = ensure_image_staging(c, B > c->map_batch ? B : c->map_batch);
+    if (rc) return rc;
+    // Double-buffered staging: the copy of batch k+1 overlaps the steps of batch k.
+    uint64_t done = 0;
+    for (uint64_t k = 0; done < n; ++k) {
+        const int buf = (int)(k & 1);
+        const uint64_t m = n - done < B ? n - done : B;
+        CU_TRY(cudaStreamWaitEvent(c->copy_stream, c->consumed[buf], 0));
+        CU_TRY(cudaMemcpyAsync(c->d_images[buf], host_images + done * isz, m * isz * sizeof(float),
+                               cudaMemcpyHostToDevice, c->copy_stream));
+        CU_TRY(cudaEventRecord(c->copied[buf], c->copy_stream));
+        CU_TRY(cudaStreamWaitEvent(c->stream, c->copied[buf], 0));
+        for (uint64_t i = 0; i < m; ++i) {
+            rc = train_one(c, c->d_images[buf] + i * isz, c->d_bmu_log + done + i);
+            if (rc) return rc;
+        }
+        CU_TRY(cudaEventRecord(c->consumed[buf], c->stream));
+        done += m;
+    }
+    CU_TRY(cudaGetLastError());
+    return PINK_B200_OK;
+}
+
+int pink_b200_get_update_counts(pink_b200_ctx* c, uint32_t* host_counts)
+{
+    if (!c || !host_counts) return fail(PINK_B200_EINVAL, "null argument");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    int rc = check_status(c);
+    if (rc) return rc;
+    CU_TRY(cudaMemcpy(host_counts, c->d_counts, (size_t)c->cfg.n_neurons * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    return PINK_B200_OK;
+}
+
+int pink_b200_get_bmu_log(pink_b200_ctx* c, uint32_t* host_bmus, uint64_t n)
+{
+    if (!c || !host_bmus) return fail(PINK_B200_EINVAL, "null argument");
+    if (n > c->bmu_log_n) return fail(PINK_B200_EINVAL, "more entries requested than the last train call produced");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    CU_TRY(cudaMemcpy(host_bmus, c->d_bmu_log, n * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    return PINK_B200_OK;
+}
+
+static int map_chunk(pink_b200_ctx* c, const float* d_images, uint32_t m, float* d_dist, uint32_t* d_rot)
+{
+    const Geometry& g = c->g;
+    launch_rotate(g, d_images, m, c->d_cs, c->d_sn, base_fits_smem(g) ? nullptr : c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream);
+    DistanceArgs da{};
+    da.a0 = c->d_a0; da.a1 = c->d_a1; da.anorm = c->d_anorm; da.n = c->count;
+    da.b0 = c->d_b0; da.b1 = c->d_b1; da.bnorm = c->d_bnorm; da.n_img = m;
+    da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status;
+    const char* why = "";
+    cudaError_t e = launch_distance(g, da, c->stream, &why);
+    if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
+    launch_map_finalize(g, c->d_keys, m, c->count, d_dist, d_rot, c->stream);
+    return PINK_B200_OK;
+}
+
+int pink_b200_map_device(pink_b200_ctx* c, const float* dev_images, uint64_t n, float* dev_dist, uint32_t* dev_rot)
+{
+    if (!c || ((!dev_images || !dev_dist || !dev_rot) && n)) return fail(PINK_B200_EINVAL, "null argument");
+    if (!c->have_som) return fail(PINK_B200_ESTATE, "pink_b200_set_som must be called before mapping");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    int rc = ensure_transform_buffers(c, c->map_batch, base_fits_smem(c->g) ? 0 : c->map_batch);
+    if (rc) return rc;
+    for (uint64_t done = 0; done < n;) {
+        const uint32_t m = (uint32_t)(n - done < c->map_batch ? n - done : c->map_batch);
+        rc = map_chunk(c, dev_images + done * c->image_size(), m, dev_dist + done * c->count, dev_rot + done * c->count);
+        if (rc) return rc;
+        done += m;
+    }
+    CU_TRY(cudaGetLastError());
+    return PINK_B200_OK;
+}
+
+int pink_b200_map(pink_b200_ctx* c, const float* host_images, uint64_t n, float* host_dist, uint32_t* host_rot)
+{
+    if (!c || ((!host_images || !host_dist || !host_rot) && n)) return fail(PINK_B200_EINVAL, "null argument");
+    if (!c->have_som) return fail(PINK_B200_ESTATE, "pink_b200_set_som must be called before mapping");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    const size_t B = c->map_batch, isz = c->image_size();
+    int rc = ensure_transform_buffers(c, B, base_fits_smem(c->g) ? 0 : B);
+    if (rc) return rc;
+    rc = ensure_image_staging(c, B > c->train_batch ? B : c->train_batch);
+    if (rc) return rc;
+    if (c->out_imgs < 2 * B) {
+        free_dev(c->d_dist); free_dev(c->d_rot);
+        CU_TRY(cudaMalloc(&c->d_dist, 2 * B * c->count * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_rot, 2 * B * c->count * sizeof(uint32_t)));
+        c->out_imgs = 2 * B;
+    }
+    // Batches alternate between two staging/result buffers: the upload of batch
+    // k+1 and the download of batch k-1 overlap the kernels of batch k.
+    uint64_t done = 0;
+    for (uint64_t k = 0; done < n; ++k) {
+        const int buf = (int)(k & 1);
+        const uint32_t m = (uint32_t)(n - done < B ? n - done : B);
+        float* dd = c->d_dist + (size_t)buf * B * c->count;
+        uint32_t* dr = c->d_rot + (size_t)buf * B * c->count;
+        CU_TRY(cudaStreamWaitEvent(c->copy_stream, c->consumed[buf], 0));
+        CU_TRY(cudaMemcpyAsync(c->d_images[buf], host_images + done * isz, m * isz * sizeof(float),
+                               cudaMemcpyHostToDevice, c->copy_stream));
+        CU_TRY(cudaEventRecord(c->copied[buf], c->copy_stream));
+        CU_TRY(cudaStreamWaitEvent(c->stream, c->copied[buf], 0));
+        rc = map_chunk(c, c->d_images[buf], m, dd, dr);
+        if (rc) return rc;
+        CU_TRY(cudaMemcpyAsync(host_dist + done * c->count, dd, (size_t)m * c->count * sizeof(float),
+                               cudaMemcpyDeviceToHost, c->stream));
+        CU_TRY(cudaMemcpyAsync(host_rot + done * c->count, dr, (size_t)m * c->count * sizeof(uint32_t),
+                               cudaMemcpyDeviceToHost, c->stream));
+        CU_TRY(cudaEventRecord(c->consumed[buf], c->stream));
+        done += m;
+    }
+    return check_status(c);
+}
+
+int pink_b200_synchronize(pink_b200_ctx* c)
+{
+    if (!c) return fail(PINK_B200_EINVAL, "null context");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    CU_TRY(cudaStreamSynchronize(c->copy_stream));
+    return check_status(c);
+}
+
+void* pink_b200_stream(pink_b200_ctx* c) { return c ? c->stream : nullptr; }
+
+// ---- single stages ---------------------------------------------------------------
+
+static int* g_op_status = nullptr;   // device status word shared by the single-stage entries
+
+static int stage_tables(const Geometry& g, float** d_cs, float** d_sn)
+{
+    const uint32_t nq = g.q ? g.q : 1;
+    std::vector<float> cs(nq), sn(nq);
+    const float step = static_cast<float>(2 * M_PI) / g.R;
+    for (uint32_t t = 0; t < nq; ++t) { const float a = t * step; cs[t] = std::cos(a); sn[t] = std::sin(a); }
+    CU_TRY(cudaMalloc(d_cs, nq * sizeof(float)));
+    CU_TRY(cudaMalloc(d_sn, nq * sizeof(float)));
+    CU_TRY(cudaMemcpy(*d_cs, cs.data(), nq * sizeof(float), cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemcpy(*d_sn, sn.data(), nq * sizeof(float), cudaMemcpyHostToDevice));
+    return PINK_B200_OK;
+}
+
+int pink_b200_op_rotate(const pink_b200_config* cfg, const float* dev_images, uint32_t n_img,
+                        float* dev_base, void* dev_b0, void* dev_b1, void* dev_bnorm, void* stream)
+{
+    if (!cfg || !dev_images || !dev_b0) return fail(PINK_B200_EINVAL, "null argument");
+    Geometry g{};
+    int rc = make_geometry(*cfg, &g);
+    if (rc) return rc;
+    if (!dev_base && (size_t)g.P * sizeof(float) > 200 * 1024)
+        return fail(PINK_B200_EINVAL, "dev_base is required when a base rotation does not fit shared memory");
+    float *d_cs = nullptr, *d_sn = nullptr;
+    rc = stage_tables(g, &d_cs, &d_sn);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    launch_rotate(g, dev_images, n_img, d_cs, d_sn, dev_base, dev_b0, dev_b1, dev_bnorm, st);
+    cudaError_t e = cudaGetLastError();
+    cudaStreamSynchronize(st);
+    cudaFree(d_cs); cudaFree(d_sn);
+    if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string("rotate_kernel launch: ") + cudaGetErrorString(e));
+    return PINK_B200_OK;
+}
+
+int pink_b200_op_quantize_som(const pink_b200_config* cfg, const float* dev_som, uint32_t n_neurons,
+                              void* dev_a0, void* dev_a1, void* dev_anorm, void* stream)
+{
+    if (!cfg || !dev_som || !dev_a0) return fail(PINK_B200_EINVAL, "null argument");
+    Geometry g{};
+    int rc = make_geometry(*cfg, &g);
+    if (rc) return rc;
+    if (g.P != g.Pp) return fail(PINK_B200_EINVAL, "this entry needs a neuron size that is a multiple of 4 floats");
+    launch_quantize_som(g, dev_som, n_neurons, dev_a0, dev_a1, dev_anorm, static_cast<cudaStream_t>(stream));
+    CU_TRY(cudaGetLastError());
+    return PINK_B200_OK;
+}
+
+int pink_b200_op_distance(uint32_t dist_type, uint32_t n_neurons, uint32_t n_transforms, uint32_t K,
+                          const void* dev_a0, const void* dev_a1, const void* dev_anorm,
+                          const void* dev_b0, const void* dev_b1, const void* dev_bnorm, uint32_t n_img,
+                          unsigned long long* dev_keys, void* dev_matrix, void* stream)
+{
+    if (!dev_a0 || !dev_b0 || !dev_keys) return fail(PINK_B200_EINVAL, "null argument");
+    if (dist_type > PINK_B200_UINT8) return fail(PINK_B200_EINVAL, "Unknown euclidean_distance_type");
+    if (dist_type != PINK_B200_FLOAT && (!dev_anorm || !dev_bnorm)) return fail(PINK_B200_EINVAL, "null norm argument");
+    if (dist_type == PINK_B200_UINT16 && (!dev_a1 || !dev_b1)) return fail(PINK_B200_EINVAL, "null low-byte plane");
+    if (dist_type == PINK_B200_UINT8 && K > 33025) return fail(PINK_B200_EINVAL, "uint8 distance supports at most 33025 elements");
+    if (dist_type == PINK_B200_UINT16 && K > 16512) return fail(PINK_B200_EINVAL, "uint16 distance supports at most 16512 elements");
+    Geometry g{};
+    g.mode = (int)dist_type;
+    g.T = n_transforms; g.K = K; g.Kp = pink_b200_operand_stride(K, dist_type);
+    if (!g_op_status) { CU_TRY(cudaMalloc(&g_op_status, sizeof(int))); CU_TRY(cudaMemset(g_op_status, 0, sizeof(int))); }
+    int* d_status = g_op_status;
+    DistanceArgs da{};
+    da.a0 = dev_a0; da.a1 = dev_a1; da.anorm = dev_anorm; da.n = n_neurons;
+    da.b0 = dev_b0; da.b1 = dev_b1; da.bnorm = dev_bnorm; da.n_img = n_img;
+    da.keys = dev_keys; da.s_out = dev_matrix; da.status = d_status;
+    const char* why = "";
+    cudaError_t e = launch_distance(g, da, static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
+    return PINK_B200_OK;
+}
+
+int pink_b200_op_status(void)
+{
+    if (!g_op_status) return PINK_B200_OK;
+    int st = 0;
+    CU_TRY(cudaDeviceSynchronize());
+    CU_TRY(cudaMemcpy(&st, g_op_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st != kDevOk) {
+        cudaMemset(g_op_status, 0, sizeof(int));
+        return fail(PINK_B200_ETIMEOUT, "device-side wait expired in the distance kernel (code " + std::to_string(st) + ")");
+    }
+    return PINK_B200_OK;
+}
+
+} // extern "C"

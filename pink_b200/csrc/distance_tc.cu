@@ -1,0 +1,308 @@
+// Integer-mode distance kernel on the 5th-generation tensor cores.
+//
+// Replaces the reference's euclidean_distance_kernel + second_step_kernel
+//   (src/CudaLib/euclidean_distance_kernel.h:61-102: one block per (transform,
+//    neuron) pair streaming both operands;
+//    src/CudaLib/generate_euclidean_distance_matrix_second_step.h:18-38: serial
+//    minimum over transforms per neuron)
+// by the Gram form  S[n][t] = |a_n|^2 + |b_t|^2 - 2 * a_n . b_t  where the dot
+// products are a dense [n x K] x [K x T] contraction run as tcgen05.mma
+// kind::i8 (u8 x u8 -> s32, accumulators in tensor memory).  All terms are
+// exact integers, so S equals the reference's sum of squared differences
+// bit for bit.  The epilogue reads the accumulators with tcgen05.ld, forms S,
+// keeps the first minimum over the tile's transforms per neuron row and merges
+// tiles with one 64-bit atomicMin per row; the N x T matrix is never written
+// (unless a debug output is requested).
+//
+// uint16 operands are split into high and low bytes (a = 256*ah + al) and the
+// dot product is assembled from three s32 accumulators
+//   hh = ah.bh,  ll = al.bl,  cross = ah.bl + al.bh,
+//   a.b = 65536*hh + 256*cross + ll        (combined in 64-bit integers).
+//
+// One CTA computes a 128-neuron x n_tile-transform tile: warp 0 streams
+// 128-byte-swizzled K slices of both operands with TMA into a multi-stage
+// shared-memory ring, warp 1 issues the MMAs, warps 2-5 run the epilogue.
+// Every mbarrier wait is bounded; on a time-out the CTA records a status code
+// and unwinds through the common exit that frees its tensor memory.
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace pinkb {
+
+namespace {
+
+constexpr uint32_t kBlockM = 128;          // neurons per tile = TMEM lanes
+constexpr uint32_t kBlockK = 128;          // bytes of K per pipeline stage = one swizzle row
+constexpr uint32_t kUmmaK = 32;            // K per kind::i8 instruction
+constexpr uint32_t kThreads = 192;
+
+template <int MODE> struct TcCfg;
+template <> struct TcCfg<kModeU8>  { static constexpr uint32_t planes = 1, max_n = 256, stages = 4, accs = 1, cols = 256; };
+template <> struct TcCfg<kModeU16> { static constexpr uint32_t planes = 2, max_n = 128, stages = 3, accs = 3, cols = 512; };
+
+template <int MODE>
+struct SmemLayout
+{
+    using Cfg = TcCfg<MODE>;
+    static constexpr uint32_t a_bytes = kBlockM * kBlockK;            // per plane
+    static constexpr uint32_t b_bytes = Cfg::max_n * kBlockK;         // per plane (capacity)
+    static constexpr uint32_t stage_bytes = Cfg::planes * (a_bytes + b_bytes);
+    static constexpr uint32_t ring_bytes = Cfg::stages * stage_bytes;
+    static constexpr uint32_t bar_off = ring_bytes;                   // full[stages], empty[stages], tmem_full
+    static constexpr uint32_t tmem_ptr_off = bar_off + (2 * Cfg::stages + 1) * 8;
+    static constexpr uint32_t nb_off = (tmem_ptr_off + 4 + 15) & ~15u; // per-column |b|^2 of this tile
+    static constexpr uint32_t total = nb_off + Cfg::max_n * 8 + 1024; // + slack for 1024-byte alignment
+};
+
+struct TcParams
+{
+    const void* anorm;
+    const void* bnorm;
+    unsigned long long* keys;
+    void* s_out;
+    int* status;
+    uint32_t n, T, num_kb, n_tile;
+};
+
+__device__ __forceinline__ void report(int* status, int code)
+{
+    if (status) atomicCAS(status, kDevOk, code);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
+                   const __grid_constant__ CUtensorMap map_b0, const __grid_constant__ CUtensorMap map_b1,
+                   const TcParams p)
+{
+    using Cfg = TcCfg<MODE>;
+    using L = SmemLayout<MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::bar_off);
+    uint64_t* empty_bar = full_bar + Cfg::stages;
+    uint64_t* tmem_full_bar = empty_bar + Cfg::stages;
+    uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(smem + L::tmem_ptr_off);
+    unsigned long long* nb_s = reinterpret_cast<unsigned long long*>(smem + L::nb_off);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t m0 = blockIdx.x * kBlockM;
+    const uint32_t t0 = blockIdx.y * p.n_tile;
+    const uint32_t img = blockIdx.z;
+    const uint32_t stage_tx = Cfg::planes * (L::a_bytes + p.n_tile * kBlockK);
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < Cfg::stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(tmem_full_bar, 1);
+        mbar_fence_init();
+        tma_prefetch_desc(&map_a0);
+        tma_prefetch_desc(&map_b0);
+        if (MODE == kModeU16) { tma_prefetch_desc(&map_a1); tma_prefetch_desc(&map_b1); }
+    }
+    if (warp == 1) { tmem_alloc(tmem_ptr_s, Cfg::cols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_s;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer --
+        if (elect_one()) {
+            const int32_t brow = (int32_t)(img * p.T + t0);
+            for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
+                const uint32_t s = kb % Cfg::stages, ph = (kb / Cfg::stages) & 1;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1)) { report(p.status, kDevTimeoutProducer); break; }
+                mbar_expect_tx(&full_bar[s], stage_tx);
+                uint8_t* st = smem + s * L::stage_bytes;
+                const int32_t kx = (int32_t)(kb * kBlockK);
+                tma_load_2d(st, &map_a0, &full_bar[s], kx, (int32_t)m0);
+                tma_load_2d(st + Cfg::planes * L::a_bytes, &map_b0, &full_bar[s], kx, brow);
+                if (MODE == kModeU16) {
+                    tma_load_2d(st + L::a_bytes, &map_a1, &full_bar[s], kx, (int32_t)m0);
+                    tma_load_2d(st + Cfg::planes * L::a_bytes + L::b_bytes, &map_b1, &full_bar[s], kx, brow);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer --
+        if (elect_one()) {
+            const uint32_t idesc = make_idesc_u8(kBlockM, p.n_tile);
+            bool ok = true;
+            for (uint32_t kb = 0; kb < p.num_kb && ok; ++kb) {
+                const uint32_t s = kb % Cfg::stages, ph = (kb / Cfg::stages) & 1;
+                if (!mbar_wait(&full_bar[s], ph)) { report(p.status, kDevTimeoutMma); ok = false; break; }
+                tc_fence_after();
+                const uint32_t st = smem_u32(smem + s * L::stage_bytes);
+                const uint64_t a_hi = make_sw128_kmajor_desc(st);
+                const uint64_t b_hi = make_sw128_kmajor_desc(st + Cfg::planes * L::a_bytes);
+#pragma unroll
+                for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k) {
+                    const uint64_t adv = (k * kUmmaK) >> 4;   // 32 bytes along K inside the swizzled row
+                    const uint32_t acc = (kb | k) != 0;
+                    if (MODE == kModeU8) {
+                        umma_i8(tmem_base, a_hi + adv, b_hi + adv, idesc, acc);
+                    } else {
+                        const uint64_t a_lo = make_sw128_kmajor_desc(st + L::a_bytes);
+                        const uint64_t b_lo = make_sw128_kmajor_desc(st + Cfg::planes * L::a_bytes + L::b_bytes);
+                        umma_i8(tmem_base, a_hi + adv, b_hi + adv, idesc, acc);                         // hh
+                        umma_i8(tmem_base + Cfg::max_n, a_lo + adv, b_lo + adv, idesc, acc);            // ll
+                        umma_i8(tmem_base + 2 * Cfg::max_n, a_hi + adv, b_lo + adv, idesc, acc);        // cross
+                        umma_i8(tmem_base + 2 * Cfg::max_n, a_lo + adv, b_hi + adv, idesc, 1u);
+                    }
+                }
+                umma_commit(&empty_bar[s]);      // frees the stage once these MMAs have read it
+            }
+            umma_commit(tmem_full_bar);          // accumulators complete
+        }
+    } else {
+        // ----------------------------------------------------------- epilogue --
+        const uint32_t et = threadIdx.x - 64;               // 0..127
+        const uint32_t quad = warp & 3;                      // TMEM lane quadrant this warp may read
+        const uint32_t row = quad * 32 + lane;
+        const uint32_t n = m0 + row;
+        for (uint32_t j = et; j < p.n_tile; j += 128) {
+            const uint32_t t = t0 + j;
+            unsigned long long v = 0;
+            if (t < p.T) {
+                v = MODE == kModeU8 ? (unsigned long long)static_cast<const uint32_t*>(p.bnorm)[(size_t)img * p.T + t]
+                                    : static_cast<const unsigned long long*>(p.bnorm)[(size_t)img * p.T + t];
+            }
+            nb_s[j] = v;
+        }
+        unsigned long long na = 0;
+        if (n < p.n) {
+            na = MODE == kModeU8 ? (unsigned long long)static_cast<const uint32_t*>(p.anorm)[n]
+                                 : static_cast<const unsigned long long*>(p.anorm)[n];
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");      // nb_s visible to the four epilogue warps
+
+        unsigned long long best_s = ~0ull;
+        uint32_t best_t = 0;
+        if (mbar_wait(tmem_full_bar, 0)) {
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
+            for (uint32_t c0 = 0; c0 < p.n_tile; c0 += 16) {
+                uint32_t v0[16], v1[16], v2[16];
+                tmem_ld_32x16(lane_addr + c0, v0);
+                if (MODE == kModeU16) {
+                    tmem_ld_32x16(lane_addr + Cfg::max_n + c0, v1);
+                    tmem_ld_32x16(lane_addr + 2 * Cfg::max_n + c0, v2);
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (uint32_t j = 0; j < 16; ++j) {
+                    const uint32_t t = t0 + c0 + j;
+                    unsigned long long s;
+                    if (MODE == kModeU8) {
+                        // exact: 0 <= S < 2^32 although the intermediate wraps modulo 2^32
+                        s = (uint32_t)((uint32_t)na + (uint32_t)nb_s[c0 + j] - 2u * v0[j]);
+                    } else {
+                        const unsigned long long dot = ((unsigned long long)v0[j] << 16)
+                                                     + ((unsigned long long)v2[j] << 8) + v1[j];
+                        s = na + nb_s[c0 + j] - 2ull * dot;
+                    }
+                    if (t < p.T) {
+                        if (s < best_s) { best_s = s; best_t = t; }
+                        if (p.s_out && n < p.n) {
+                            const size_t o = ((size_t)img * p.n + n) * p.T + t;
+                            if (MODE == kModeU8) static_cast<uint32_t*>(p.s_out)[o] = (uint32_t)s;
+                            else static_cast<unsigned long long*>(p.s_out)[o] = s;
+                        }
+                    }
+                }
+            }
+            if (n < p.n && best_s != ~0ull)
+                atomicMin(&p.keys[(size_t)img * p.n + n], (best_s << key_shift(MODE)) | best_t);
+        } else {
+            report(p.status, kDevTimeoutEpilogue);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, Cfg::cols);
+}
+
+// ------------------------------------------------------------------ host side --
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn()
+{
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess
+            && qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    }
+    return fn;
+}
+
+// rows x row_bytes matrix of bytes, K-contiguous; box = 128 bytes x box_rows, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows)
+{
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = { row_bytes, rows };
+    cuuint64_t strides[1] = { row_bytes };
+    cuuint32_t box[2] = { kBlockK, box_rows };
+    cuuint32_t estr[2] = { 1, 1 };
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int MODE>
+cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why)
+{
+    using Cfg = TcCfg<MODE>;
+    using L = SmemLayout<MODE>;
+    // Balanced transform tiles: the fewest tiles of at most max_n columns, each a multiple of 16.
+    const uint32_t tiles = (g.T + Cfg::max_n - 1) / Cfg::max_n;
+    uint32_t n_tile = ((g.T + tiles - 1) / tiles + 15) & ~15u;
+    if (n_tile > Cfg::max_n) n_tile = Cfg::max_n;
+    const uint32_t n_tiles = (g.T + n_tile - 1) / n_tile;
+
+    CUtensorMap ma0, ma1, mb0, mb1;
+    bool ok = make_map(&ma0, a.a0, a.n, g.Kp, kBlockM) && make_map(&mb0, a.b0, (uint64_t)a.n_img * g.T, g.Kp, n_tile);
+    if (MODE == kModeU16)
+        ok = ok && make_map(&ma1, a.a1, a.n, g.Kp, kBlockM) && make_map(&mb1, a.b1, (uint64_t)a.n_img * g.T, g.Kp, n_tile);
+    else { ma1 = ma0; mb1 = mb0; }
+    if (!ok) { *why = "cuTensorMapEncodeTiled failed"; return cudaErrorInvalidValue; }
+
+    static int attr_dev = -1;   // the opt-in shared-memory size is a per-device function attribute
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev != attr_dev) {
+        cudaError_t e = cudaFuncSetAttribute(distance_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)L::total);
+        if (e != cudaSuccess) { *why = "cudaFuncSetAttribute(distance_tc_kernel)"; return e; }
+        attr_dev = dev;
+    }
+    TcParams p;
+    p.anorm = a.anorm; p.bnorm = a.bnorm; p.keys = a.keys; p.s_out = a.s_out; p.status = a.status;
+    p.n = a.n; p.T = g.T; p.num_kb = g.Kp / kBlockK; p.n_tile = n_tile;
+    dim3 grid((a.n + kBlockM - 1) / kBlockM, n_tiles, a.n_img);
+    distance_tc_kernel<MODE><<<grid, kThreads, L::total, st>>>(ma0, ma1, mb0, mb1, p);
+    *why = "distance_tc_kernel launch";
+    return cudaGetLastError();
+}
+
+} // namespace
+
+cudaError_t launch_distance_f32(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why);
+
+cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why)
+{
+    *why = "";
+    if (a.n == 0 || a.n_img == 0) return cudaSuccess;
+    if (g.mode == kModeU8) return launch_tc<kModeU8>(g, a, st, why);
+    if (g.mode == kModeU16) return launch_tc<kModeU16>(g, a, st, why);
+    return launch_distance_f32(g, a, st, why);
+}
+
+} // namespace pinkb

@@ -1,0 +1,95 @@
+// Shared declarations of the hot-path kernels: geometry of one SOM/image
+// configuration, device-side operand layout, and the host launchers the C-ABI
+// layer calls.  Notation (as in the PINK sources): N neurons, R rotations,
+// T = R * (flip ? 2 : 1) transforms, C channels, nd neuron side, id image
+// side, ed side of the distance region, P = C*nd*nd, K = C*ed*ed.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace pinkb {
+
+// Distance modes; numbering follows pink::DataType (UtilitiesLib/DataType.h).
+enum : int { kModeF32 = 0, kModeU16 = 1, kModeU8 = 2 };
+
+// Status codes a kernel may leave in the device status word.
+enum : int { kDevOk = 0, kDevTimeoutProducer = 1, kDevTimeoutMma = 2, kDevTimeoutEpilogue = 3 };
+
+struct Geometry
+{
+    uint32_t C, id, nd, ed;     // channels, image side, neuron side, distance-region side
+    uint32_t R, T, q;           // rotations, transforms, rotations per quadrant (R/4, 0 when R == 1)
+    uint32_t flip;
+    uint32_t off;               // crop offset uint32((nd - ed) * 0.5)
+    uint32_t P, Pp;             // neuron size and its row stride in floats (multiple of 4)
+    uint32_t K, Kp;             // distance length and operand row stride in ELEMENTS:
+                                //   integer modes: multiple of 128 (bytes per plane row)
+                                //   float mode:    multiple of 16 floats
+    int mode;
+};
+
+// Ordering code of a per-neuron minimum.  Integer modes: the exact integer sum
+// S; float mode: the IEEE bit pattern of the non-negative float sum.  A key
+// packs (code << kKeyShift) | transform so that an unsigned 64-bit minimum
+// yields the smallest distance and, among equals, the lowest transform index
+// (the reference's first-minimum rule).
+__host__ __device__ constexpr uint32_t key_shift(int mode) { return mode == kModeU16 ? 16u : 32u; }
+constexpr unsigned long long kKeyEmpty = ~0ull;
+
+// Local-shard best-matching-unit record exchanged between ranks.
+struct BmuPair { unsigned long long code; unsigned long long neuron; };
+
+// ---- rotation set -----------------------------------------------------------
+// images: [n_img][C][id][id] float.  cs/sn: [q] cos/sin of t*2*pi/R (entry 0 unused).
+// base_out (nullable): [n_img][max(q,1)][C][nd][nd] float base rotations.
+// b0/b1: operand planes [n_img*T][Kp] (u8: b0; u16: b0 = high byte, b1 = low
+// byte; f32: b0 as float).  bnorm: [n_img*T] sum of squares (u32 for u8,
+// u64 for u16, unused for f32).
+void launch_rotate(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
+                   float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st);
+
+// ---- SOM operand ------------------------------------------------------------
+// som: [n][Pp] float.  a0/a1/anorm: as b0/b1/bnorm with one row per neuron.
+void launch_quantize_som(const Geometry& g, const float* som, uint32_t n, void* a0, void* a1, void* anorm,
+                         cudaStream_t st);
+
+// ---- distances + minimum over transforms ------------------------------------
+struct DistanceArgs
+{
+    const void* a0; const void* a1; const void* anorm; uint32_t n;          // SOM operand, n local neurons
+    const void* b0; const void* b1; const void* bnorm; uint32_t n_img;      // transform operand
+    unsigned long long* keys;   // [n_img][n], must hold kKeyEmpty on entry
+    void* s_out;                // optional full matrix [n_img][n][T]: u32 (u8), u64 (u16), f32 (f32)
+    int* status;                // device status word
+};
+// Returns cudaSuccess or the launch / tensor-map error; *why receives a static message.
+cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why);
+
+// ---- best matching unit -----------------------------------------------------
+// Reduces keys[0..n) to the local (code, first_neuron + argmin) record.
+void launch_bmu(const Geometry& g, const unsigned long long* keys, uint32_t n, uint32_t first_neuron,
+                BmuPair* out, cudaStream_t st);
+
+// ---- neighbourhood update ---------------------------------------------------
+struct UpdateArgs
+{
+    float* som;                       // [n][Pp]
+    const float* base;                // [max(q,1)][C][nd][nd] base rotations of the current image
+    unsigned long long* keys;         // [n]; read, then re-armed to kKeyEmpty
+    const BmuPair* pairs; uint32_t world;   // per-rank BMU records (world entries)
+    const float* factors;             // [N_global][n] update factors, column = local neuron
+    uint32_t n, first_neuron;
+    void* a0; void* a1; void* anorm;  // SOM operand rows to refresh
+    uint32_t* counts;                 // [N_global] BMU hit counters (incremented by the owner)
+    uint32_t* bmu_log;                // nullable: receives the global BMU index of this step
+};
+void launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st);
+
+// ---- mapping epilogue -------------------------------------------------------
+// dist[i][n] = sqrt(reported distance), rot[i][n] = transform; re-arms the keys.
+void launch_map_finalize(const Geometry& g, unsigned long long* keys, uint32_t n_img, uint32_t n,
+                         float* dist, uint32_t* rot, cudaStream_t st);
+
+void launch_fill_keys(unsigned long long* keys, size_t count, cudaStream_t st);
+
+} // namespace pinkb

@@ -1,0 +1,290 @@
+// Rotation-set generator and SOM operand quantiser.
+//
+// rotate_kernel replaces the reference's seven-launch sequence
+//   thrust::fill + resize_kernel + rotate_bilinear_kernel + 3 x rotate_90_degrees_list
+//   + flip_kernel              (src/CudaLib/generate_rotated_images.h:56-167, :170-294)
+// followed by the per-image crop/convert of every transform
+//   copy_and_transform_kernel  (src/CudaLib/copy_and_transform_kernel.h:15-29,
+//                               src/CudaLib/generate_euclidean_distance_matrix.h:86-112)
+// with ONE launch that never materialises the T x P float set: a CTA computes
+// one interpolated base rotation (all channels) into shared memory, stores it
+// once as float for the update step, and emits the distance operand rows of
+// all eight transforms that are exact index permutations of that base (four
+// quarter turns x optional flip) with packed, coalesced stores, plus each
+// row's sum of squares.
+//
+// Arithmetic: every product and sum of the interpolation is rounded
+// separately (__fmul_rn/__fadd_rn are never contracted to FMA), in the order
+// of the reference's CPU code (src/ImageProcessingLib/rotate.h:31-63), so the
+// float pixels are bit-identical to the CPU reference built without FMA.
+#include "kernels.cuh"
+
+namespace pinkb {
+
+namespace {
+
+__device__ __forceinline__ uint32_t quant_u8(float v)
+{
+    return min(__float2uint_rz(__fmul_rn(v, 255.0f)), 255u);
+}
+
+__device__ __forceinline__ uint32_t quant_u16(float v)
+{
+    return min(__float2uint_rz(__fmul_rn(v, 65535.0f)), 65535u);
+}
+
+// Centre crop / zero pad (src/CudaLib/resize_kernel.h:15-32, integer margins).
+__device__ __forceinline__ float resize_pixel(const float* __restrict__ img, uint32_t id, uint32_t nd,
+                                              uint32_t x, uint32_t y)
+{
+    if (id >= nd) {
+        uint32_t m = (id - nd) / 2;
+        return __ldg(img + (size_t)(x + m) * id + (y + m));
+    }
+    uint32_t m = (nd - id) / 2;
+    if (x < m || y < m || x >= m + id || y >= m + id) return 0.0f;
+    return __ldg(img + (size_t)(x - m) * id + (y - m));
+}
+
+// Bilinear sample of the inverse-rotated position (CPU rounding order).
+__device__ __forceinline__ float bilinear_pixel(const float* __restrict__ img, uint32_t id, float sc, float dc,
+                                                float lim, float ca, float sa, uint32_t x, uint32_t y)
+{
+    float px = __fsub_rn((float)x, dc);
+    float py = __fsub_rn((float)y, dc);
+    float sx = __fadd_rn(__fsub_rn(__fmul_rn(px, ca), __fmul_rn(py, sa)), sc);
+    float sy = __fadd_rn(__fadd_rn(__fmul_rn(px, sa), __fmul_rn(py, ca)), sc);
+    if (sx < 0.0f || sx > lim || sy < 0.0f || sy > lim) return 0.0f;
+    uint32_t ix = (uint32_t)sx, iy = (uint32_t)sy;
+    // The +1 taps carry weight 0 when they would fall outside; clamp the index.
+    uint32_t ix1 = min(ix + 1, id - 1), iy1 = min(iy + 1, id - 1);
+    float rx = __fsub_rn(sx, (float)ix), ry = __fsub_rn(sy, (float)iy);
+    float cx = __fsub_rn(1.0f, rx), cy = __fsub_rn(1.0f, ry);
+    float a = __fmul_rn(__fmul_rn(cx, cy), __ldg(img + (size_t)ix * id + iy));
+    float b = __fmul_rn(__fmul_rn(cx, ry), __ldg(img + (size_t)ix * id + iy1));
+    float c = __fmul_rn(__fmul_rn(rx, cy), __ldg(img + (size_t)ix1 * id + iy));
+    float d = __fmul_rn(__fmul_rn(rx, ry), __ldg(img + (size_t)ix1 * id + iy1));
+    return __fadd_rn(__fadd_rn(__fadd_rn(a, b), c), d);
+}
+
+template <typename Acc>
+__device__ __forceinline__ Acc block_sum(Acc v, Acc* scratch)
+{
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    Acc r = 0;
+    if (warp == 0) {
+        r = lane < nw ? scratch[lane] : Acc(0);
+        for (int o = 16; o > 0; o >>= 1) r += __shfl_down_sync(0xffffffffu, r, o);
+    }
+    return r;   // valid in thread 0
+}
+
+// Source coordinate inside the base rotation of pixel (x, y) of transform
+// (flip f, quadrant j):  flip is a row reversal applied last
+// (src/CudaLib/flip_kernel.h:28); one quarter turn maps (x, y) <- (nd-1-y, x)
+// (src/CudaLib/rotate_90_degrees_list.h:28).
+__device__ __forceinline__ void base_coord(uint32_t nd, uint32_t f, uint32_t j, uint32_t x, uint32_t y,
+                                           uint32_t& bx, uint32_t& by)
+{
+    if (f) x = nd - 1 - x;
+    switch (j) {
+        case 0: bx = x; by = y; break;
+        case 1: bx = nd - 1 - y; by = x; break;
+        case 2: bx = nd - 1 - x; by = nd - 1 - y; break;
+        default: bx = y; by = nd - 1 - x; break;
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256)
+rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem,
+              const float* __restrict__ cs, const float* __restrict__ sn, float* __restrict__ base_out,
+              void* __restrict__ b0, void* __restrict__ b1, void* __restrict__ bnorm)
+{
+    extern __shared__ __align__(16) float base_s[];
+    __shared__ unsigned long long red[8];
+
+    const uint32_t tq = blockIdx.x, img_i = blockIdx.y;
+    const uint32_t nbase = g.q ? g.q : 1;
+    const uint32_t P1 = g.nd * g.nd;
+    const float* img = images + (size_t)img_i * g.C * g.id * g.id;
+    float* gbase = base_out + ((size_t)img_i * nbase + tq) * g.P;
+    const float* stage = use_smem ? base_s : gbase;
+
+    // Phase 1: the base rotation (quadrant 0, no flip) of all channels.
+    {
+        const float sc = (g.id - 1) * 0.5f, dc = (g.nd - 1) * 0.5f, lim = (float)(g.id - 1);
+        const float ca = tq ? cs[tq] : 1.0f, sa = tq ? sn[tq] : 0.0f;
+        for (uint32_t idx = threadIdx.x; idx < g.P; idx += blockDim.x) {
+            uint32_t c = idx / P1, r = idx - c * P1;
+            uint32_t x = r / g.nd, y = r - x * g.nd;
+            const float* plane = img + (size_t)c * g.id * g.id;
+            float v = tq == 0 ? resize_pixel(plane, g.id, g.nd, x, y)
+                              : bilinear_pixel(plane, g.id, sc, dc, lim, ca, sa, x, y);
+            if (use_smem) base_s[idx] = v;
+            if (base_out) gbase[idx] = v;
+        }
+    }
+    __syncthreads();   // also orders this block's global writes before its own reads below
+
+    // Phase 2: operand rows of every transform derived from this base.
+    const uint32_t nq = g.q ? 4 : 1, nv = nq * (g.flip ? 2 : 1);
+    const uint32_t K1 = g.ed * g.ed;
+    const uint32_t groups = (g.K + 3) / 4;
+    for (uint32_t v = 0; v < nv; ++v) {
+        const uint32_t f = v / nq, j = v - f * nq;
+        const uint32_t t = f * g.R + j * g.q + tq;
+        const size_t row = (size_t)img_i * g.T + t;
+        unsigned long long acc = 0;
+        for (uint32_t k4 = threadIdx.x; k4 < groups; k4 += blockDim.x) {
+            float val[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                uint32_t k = k4 * 4 + e;
+                val[e] = 0.0f;
+                if (k < g.K) {
+                    uint32_t c = k / K1, r = k - c * K1;
+                    uint32_t i = r / g.ed, jj = r - i * g.ed;
+                    uint32_t bx, by;
+                    base_coord(g.nd, f, j, g.off + i, g.off + jj, bx, by);
+                    val[e] = stage[c * P1 + bx * g.nd + by];
+                }
+            }
+            if (MODE == kModeU8) {
+                uint32_t q0 = quant_u8(val[0]), q1 = quant_u8(val[1]), q2 = quant_u8(val[2]), q3 = quant_u8(val[3]);
+                acc += q0 * q0 + q1 * q1 + q2 * q2 + q3 * q3;
+                reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(b0) + row * g.Kp)[k4] =
+                    q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+            } else if (MODE == kModeU16) {
+                uint32_t q0 = quant_u16(val[0]), q1 = quant_u16(val[1]), q2 = quant_u16(val[2]), q3 = quant_u16(val[3]);
+                acc += (unsigned long long)q0 * q0 + (unsigned long long)q1 * q1
+                     + (unsigned long long)q2 * q2 + (unsigned long long)q3 * q3;
+                reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(b0) + row * g.Kp)[k4] =
+                    (q0 >> 8) | ((q1 >> 8) << 8) | ((q2 >> 8) << 16) | ((q3 >> 8) << 24);
+                reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(b1) + row * g.Kp)[k4] =
+                    (q0 & 255) | ((q1 & 255) << 8) | ((q2 & 255) << 16) | ((q3 & 255) << 24);
+            } else {
+                reinterpret_cast<float4*>(static_cast<float*>(b0) + row * g.Kp)[k4] =
+                    make_float4(val[0], val[1], val[2], val[3]);
+            }
+        }
+        if (MODE != kModeF32) {
+            unsigned long long s = block_sum<unsigned long long>(acc, red);
+            if (threadIdx.x == 0) {
+                if (MODE == kModeU8) static_cast<uint32_t*>(bnorm)[row] = (uint32_t)s;
+                else static_cast<unsigned long long*>(bnorm)[row] = s;
+            }
+        }
+    }
+}
+
+// One CTA per neuron: centre crop of every channel, convert, row sum of squares.
+// Replaces the per-image copy_and_transform_kernel pass over the whole SOM
+// (src/CudaLib/generate_euclidean_distance_matrix.h:64-84); here it runs once
+// when a SOM is loaded, afterwards the update kernel refreshes the rows it changes.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+quantize_som_kernel(Geometry g, const float* __restrict__ som, void* __restrict__ a0, void* __restrict__ a1,
+                    void* __restrict__ anorm)
+{
+    __shared__ unsigned long long red[8];
+    const size_t n = blockIdx.x;
+    const float* src = som + n * g.Pp;
+    const uint32_t P1 = g.nd * g.nd, K1 = g.ed * g.ed;
+    const uint32_t groups = (g.K + 3) / 4;
+    unsigned long long acc = 0;
+    for (uint32_t k4 = threadIdx.x; k4 < groups; k4 += blockDim.x) {
+        float val[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            uint32_t k = k4 * 4 + e;
+            val[e] = 0.0f;
+            if (k < g.K) {
+                uint32_t c = k / K1, r = k - c * K1;
+                uint32_t i = r / g.ed, jj = r - i * g.ed;
+                val[e] = src[c * P1 + (g.off + i) * g.nd + g.off + jj];
+            }
+        }
+        if (MODE == kModeU8) {
+            uint32_t q0 = quant_u8(val[0]), q1 = quant_u8(val[1]), q2 = quant_u8(val[2]), q3 = quant_u8(val[3]);
+            acc += q0 * q0 + q1 * q1 + q2 * q2 + q3 * q3;
+            reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(a0) + n * g.Kp)[k4] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+        } else if (MODE == kModeU16) {
+            uint32_t q0 = quant_u16(val[0]), q1 = quant_u16(val[1]), q2 = quant_u16(val[2]), q3 = quant_u16(val[3]);
+            acc += (unsigned long long)q0 * q0 + (unsigned long long)q1 * q1
+                 + (unsigned long long)q2 * q2 + (unsigned long long)q3 * q3;
+            reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(a0) + n * g.Kp)[k4] =
+                (q0 >> 8) | ((q1 >> 8) << 8) | ((q2 >> 8) << 16) | ((q3 >> 8) << 24);
+            reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(a1) + n * g.Kp)[k4] =
+                (q0 & 255) | ((q1 & 255) << 8) | ((q2 & 255) << 16) | ((q3 & 255) << 24);
+        } else {
+            reinterpret_cast<float4*>(static_cast<float*>(a0) + n * g.Kp)[k4] = make_float4(val[0], val[1], val[2], val[3]);
+        }
+    }
+    if (MODE != kModeF32) {
+        unsigned long long s = block_sum<unsigned long long>(acc, red);
+        if (threadIdx.x == 0) {
+            if (MODE == kModeU8) static_cast<uint32_t*>(anorm)[n] = (uint32_t)s;
+            else static_cast<unsigned long long*>(anorm)[n] = s;
+        }
+    }
+}
+
+__global__ void fill_keys_kernel(unsigned long long* keys, size_t count)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+        keys[i] = kKeyEmpty;
+}
+
+constexpr size_t kRotateSmemLimit = 200 * 1024;
+
+template <int MODE>
+void rotate_dispatch(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
+                     float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st)
+{
+    size_t smem = (size_t)g.P * sizeof(float);
+    uint32_t use_smem = smem <= kRotateSmemLimit;
+    if (!use_smem) smem = 0;
+    static int attr_dev = -1;   // the opt-in shared-memory size is a per-device function attribute
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev != attr_dev) {
+        cudaFuncSetAttribute(rotate_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRotateSmemLimit);
+        attr_dev = dev;
+    }
+    dim3 grid(g.q ? g.q : 1, n_img);
+    rotate_kernel<MODE><<<grid, 256, smem, st>>>(g, images, use_smem, cs, sn, base_out, b0, b1, bnorm);
+}
+
+} // namespace
+
+void launch_rotate(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
+                   float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st)
+{
+    if (g.mode == kModeU8) rotate_dispatch<kModeU8>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
+    else if (g.mode == kModeU16) rotate_dispatch<kModeU16>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
+    else rotate_dispatch<kModeF32>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
+}
+
+void launch_quantize_som(const Geometry& g, const float* som, uint32_t n, void* a0, void* a1, void* anorm,
+                         cudaStream_t st)
+{
+    if (n == 0) return;
+    if (g.mode == kModeU8) quantize_som_kernel<kModeU8><<<n, 256, 0, st>>>(g, som, a0, a1, anorm);
+    else if (g.mode == kModeU16) quantize_som_kernel<kModeU16><<<n, 256, 0, st>>>(g, som, a0, a1, anorm);
+    else quantize_som_kernel<kModeF32><<<n, 256, 0, st>>>(g, som, a0, a1, anorm);
+}
+
+void launch_fill_keys(unsigned long long* keys, size_t count, cudaStream_t st)
+{
+    if (count == 0) return;
+    unsigned blocks = (unsigned)((count + 255) / 256);
+    if (blocks > 1184) blocks = 1184;
+    fill_keys_kernel<<<blocks, 256, 0, st>>>(keys, count);
+}
+
+} // namespace pinkb

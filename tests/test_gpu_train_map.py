@@ -1,0 +1,136 @@
+"""Whole-step parity through the context entry points of the C ABI (host
+buffers in, host buffers out) against the CPU oracle."""
+import numpy as np
+import pytest
+
+import oracle as O
+from util import Context, blob_images, make_config
+
+pytestmark = pytest.mark.gpu
+
+TRAIN_CASES = [
+    # layout, s0, s1, C, id, nd, ed, R, flip, n_images
+    (0, 3, 3, 1, 16, 12, 7, 16, True, 4),
+    (0, 2, 2, 1, 64, 45, 45, 360, True, 2),
+    (1, 5, 5, 1, 20, 14, 9, 8, True, 5),
+    (0, 3, 2, 2, 15, 10, 7, 12, True, 3),
+    (0, 10, 10, 1, 64, 44, 31, 360, True, 6),
+    (0, 2, 2, 1, 4, 2, 2, 1, False, 2),
+    (0, 2, 2, 1, 2, 4, 4, 4, True, 2),
+]
+
+
+def _som_size(layout, s0, s1):
+    return s0 * s1 if layout == 0 else int(O.lib.pko_hexagonal_size(s0))
+
+
+@pytest.mark.parametrize("case", TRAIN_CASES)
+@pytest.mark.parametrize("mode", [2, 1])
+def test_train_integer_modes_bit_exact(cuda, case, mode):
+    """uint8/uint16: BMU sequence, best rotations and the trained SOM equal the oracle's bit for bit."""
+    import pink_b200.capi as capi
+    layout, s0, s1, C_, idim, nd, ed, R, flip, n = case
+    N = _som_size(layout, s0, s1)
+    rng = np.random.default_rng(abs(hash(case)) % 2**32)
+    som0 = rng.random((N, C_, nd, nd), dtype=np.float32)
+    imgs = blob_images(n, idim, C_, seed=N + R) if idim >= 15 else rng.random((n, C_, idim, idim), dtype=np.float32)
+    imgs = imgs.reshape(n, C_, idim, idim)
+    F = O.update_factors(layout, s0, s1, O.FUNC_GAUSSIAN, 1.1, 0.2)
+    want = som0.copy()
+    want_bmu = []
+    for i in range(n):
+        _, _, bmu = O.train_step(want, imgs[i], F, ed, R, flip, mode)
+        want_bmu.append(bmu)
+    with Context(capi, make_config(capi, N, C_, idim, nd, ed, R, flip, mode)) as ctx:
+        ctx.set_som(som0)
+        ctx.set_factors(F)
+        log = ctx.train(imgs)
+        got = ctx.get_som(som0)
+        counts = ctx.counts()
+    assert list(log) == want_bmu
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert counts.sum() == n and all(counts[b] > 0 for b in want_bmu)
+
+
+@pytest.mark.parametrize("case", TRAIN_CASES[:5])
+def test_train_float_mode(cuda, case):
+    """float32: one teacher-forced step at a time; the SOM must match the oracle bit for bit whenever
+    BMU and rotations agree, which they must except at float near-ties (none in these seeds)."""
+    import pink_b200.capi as capi
+    layout, s0, s1, C_, idim, nd, ed, R, flip, n = case
+    N = _som_size(layout, s0, s1)
+    rng = np.random.default_rng(abs(hash(case)) % 2**32 + 1)
+    som0 = rng.random((N, C_, nd, nd), dtype=np.float32)
+    imgs = blob_images(n, idim, C_, seed=N + R + 1) if idim >= 15 else rng.random((n, C_, idim, idim), dtype=np.float32)
+    imgs = imgs.reshape(n, C_, idim, idim)
+    F = O.update_factors(layout, s0, s1, O.FUNC_GAUSSIAN, 1.1, 0.2)
+    want = som0.copy()
+    with Context(capi, make_config(capi, N, C_, idim, nd, ed, R, flip, 0)) as ctx:
+        ctx.set_factors(F)
+        for i in range(n):
+            ctx.set_som(want)                       # teacher forcing: start every step from the oracle's state
+            _, _, bmu = O.train_step(want, imgs[i], F, ed, R, flip, 0)
+            log = ctx.train(imgs[i:i + 1])
+            got = ctx.get_som(som0)
+            assert log[0] == bmu
+            np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-7)
+
+
+MAP_CASES = [
+    (0, 3, 3, 1, 16, 12, 7, 16, True, 5),
+    (0, 4, 4, 1, 64, 44, 31, 360, True, 3),
+    (0, 3, 2, 2, 15, 10, 7, 12, False, 70),      # more images than one internal batch
+    (1, 3, 3, 1, 20, 14, 9, 8, True, 4),
+]
+
+
+@pytest.mark.parametrize("case", MAP_CASES)
+@pytest.mark.parametrize("mode", [2, 1, 0])
+def test_map(cuda, case, mode):
+    import pink_b200.capi as capi
+    layout, s0, s1, C_, idim, nd, ed, R, flip, n = case
+    N = _som_size(layout, s0, s1)
+    rng = np.random.default_rng(abs(hash(case)) % 2**32 + 2)
+    som = rng.random((N, C_, nd, nd), dtype=np.float32)
+    imgs = rng.random((n, C_, idim, idim), dtype=np.float32)
+    with Context(capi, make_config(capi, N, C_, idim, nd, ed, R, flip, mode)) as ctx:
+        ctx.set_som(som)
+        dist, rot = ctx.map(imgs)
+    for i in range(min(n, 6)):
+        d, r = O.map_image(som, imgs[i], ed, R, flip, mode)
+        if mode == 0:
+            np.testing.assert_allclose(dist[i], d, rtol=1e-5)
+            same = rot[i] == r
+            assert same.mean() > 0.9              # float near-ties may pick a neighbouring transform
+        else:
+            assert np.array_equal(dist[i].view(np.uint32), d.view(np.uint32))
+            assert np.array_equal(rot[i], r)
+
+
+@pytest.mark.parametrize("mode", [0, 2, 1])
+@pytest.mark.parametrize("case", [(1, 2, 2, 2, 1, False), (1, 3, 3, 2, 1, False), (1, 3, 3, 2, 360, False),
+                                  (2, 3, 3, 2, 360, False), (2, 3, 3, 2, 360, True)])
+def test_map_reference_known_answers(cuda, mode, case):
+    """test/CudaTest/mapper.cu:55-120: image = 0, SOM = 1 must map to exactly 2.0 in all three modes."""
+    import pink_b200.capi as capi
+    som_dim, nd, idim, ed, R, flip = case
+    N = som_dim * som_dim
+    som = np.ones((N, 1, nd, nd), np.float32)
+    img = np.zeros((1, 1, idim, idim), np.float32)
+    with Context(capi, make_config(capi, N, 1, idim, nd, ed, R, flip, mode)) as ctx:
+        ctx.set_som(som)
+        dist, _ = ctx.map(img)
+    assert np.array_equal(dist[0], np.full(N, 2.0, np.float32))
+
+
+def test_config_errors_match_reference_messages():
+    import ctypes as C
+    import pink_b200.capi as capi
+    h = C.c_void_p()
+    for R in (0, 3, 90):                        # test/SelfOrganizingMapTest/Trainer.cpp:33-38
+        cfg = make_config(capi, 4, 1, 2, 2, 2, R, False, 2)
+        assert capi.lib.pink_b200_create(C.byref(cfg), C.byref(h)) == capi.EINVAL
+        assert b"Number of rotations must be 1 or larger then 1 and divisible by 4" in capi.lib.pink_b200_last_error()
+    cfg = make_config(capi, 4, 1, 8, 4, 5, 4, False, 2)
+    assert capi.lib.pink_b200_create(C.byref(cfg), C.byref(h)) == capi.EINVAL
+    assert b"Euclidean distance dimension larger than neuron dimension" in capi.lib.pink_b200_last_error()

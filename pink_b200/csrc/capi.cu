@@ -62,6 +62,13 @@ NcclApi& nccl()
     return api;
 }
 
+#define LAUNCH_TRY(expr)                                                                          \
+    do {                                                                                          \
+        cudaError_t e_ = (expr);                                                                  \
+        if (e_ != cudaSuccess)                                                                    \
+            return fail(PINK_B200_ECUDA, std::string("kernel launch failed in " #expr ": ") + cudaGetErrorString(e_)); \
+    } while (0)
+
 #define NCCL_TRY(expr)                                                                            \
     do {                                                                                          \
         ncclResult_t r_ = (expr);                                                                 \
@@ -181,7 +188,7 @@ int ensure_transform_buffers(pink_b200_ctx* c, size_t imgs, size_t base_needed)
     if (c->key_imgs < imgs) {
         free_dev(c->d_keys);
         CU_TRY(cudaMalloc(&c->d_keys, imgs * c->count * sizeof(unsigned long long)));
-        launch_fill_keys(c->d_keys, imgs * c->count, c->stream);
+        LAUNCH_TRY(launch_fill_keys(c->d_keys, imgs * c->count, c->stream));
         c->key_imgs = imgs;
     }
     return PINK_B200_OK;
@@ -214,7 +221,7 @@ int check_status(pink_b200_ctx* c)
 int train_one(pink_b200_ctx* c, const float* d_image, uint32_t* bmu_slot)
 {
     const Geometry& g = c->g;
-    launch_rotate(g, d_image, 1, c->d_cs, c->d_sn, c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream);
+    LAUNCH_TRY(launch_rotate(g, d_image, 1, c->d_cs, c->d_sn, c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream));
     DistanceArgs da{};
     da.a0 = c->d_a0; da.a1 = c->d_a1; da.anorm = c->d_anorm; da.n = c->count;
     da.b0 = c->d_b0; da.b1 = c->d_b1; da.bnorm = c->d_bnorm; da.n_img = 1;
@@ -222,7 +229,7 @@ int train_one(pink_b200_ctx* c, const float* d_image, uint32_t* bmu_slot)
     const char* why = "";
     cudaError_t e = launch_distance(g, da, c->stream, &why);
     if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
-    launch_bmu(g, c->d_keys, c->count, c->first, c->d_pairs + c->cfg.rank, c->stream);
+    LAUNCH_TRY(launch_bmu(g, c->d_keys, c->count, c->first, c->d_pairs + c->cfg.rank, c->stream));
     if (c->cfg.world_size > 1)
         NCCL_TRY(nccl().AllGather(c->d_pairs + c->cfg.rank, c->d_pairs, 2, ncclUint64, c->comm, c->stream));
     UpdateArgs ua{};
@@ -231,7 +238,7 @@ int train_one(pink_b200_ctx* c, const float* d_image, uint32_t* bmu_slot)
     ua.factors = c->d_factors; ua.n = c->count; ua.first_neuron = c->first;
     ua.a0 = c->d_a0; ua.a1 = c->d_a1; ua.anorm = c->d_anorm;
     ua.counts = c->d_counts; ua.bmu_log = bmu_slot;
-    launch_update(g, ua, c->stream);
+    LAUNCH_TRY(launch_update(g, ua, c->stream));
     return PINK_B200_OK;
 }
 
@@ -349,10 +356,10 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
         }
         CTX_TRY(cudaMalloc(&c->d_cs, nq * sizeof(float)));
         CTX_TRY(cudaMalloc(&c->d_sn, nq * sizeof(float)));
-        CTX_TRY(cudaMemcpy(c->d_cs, cs.data(), nq * sizeof(float), cudaMemcpyHostToDevice));
-        CTX_TRY(cudaMemcpy(c->d_sn, sn.data(), nq * sizeof(float), cudaMemcpyHostToDevice));
+        CTX_TRY(cudaMemcpyAsync(c->d_cs, cs.data(), nq * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+        CTX_TRY(cudaMemcpyAsync(c->d_sn, sn.data(), nq * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+        CTX_TRY(cudaStreamSynchronize(c->stream));   // cs/sn go out of scope
     }
-    CTX_TRY(cudaStreamSynchronize(c->stream));
 #undef CTX_TRY
     *out = c;
     return PINK_B200_OK;
@@ -418,10 +425,13 @@ int pink_b200_set_som(pink_b200_ctx* c, const float* host_som)
     const Geometry& g = c->g;
     CU_TRY(cudaSetDevice(c->cfg.device));
     CU_TRY(cudaStreamSynchronize(c->stream));
-    CU_TRY(cudaMemcpy2D(c->d_som, (size_t)g.Pp * sizeof(float), host_som + (size_t)c->first * g.P,
-                        (size_t)g.P * sizeof(float), (size_t)g.P * sizeof(float), c->count, cudaMemcpyHostToDevice));
-    launch_quantize_som(g, c->d_som, c->count, c->d_a0, c->d_a1, c->d_anorm, c->stream);
-    CU_TRY(cudaGetLastError());
+    // Stream-ordered copy: a blocking cudaMemcpy from pageable memory may return
+    // while its DMA is still in flight on the legacy stream, which the
+    // context's non-blocking stream does not wait for.
+    CU_TRY(cudaMemcpy2DAsync(c->d_som, (size_t)g.Pp * sizeof(float), host_som + (size_t)c->first * g.P,
+                             (size_t)g.P * sizeof(float), (size_t)g.P * sizeof(float), c->count,
+                             cudaMemcpyHostToDevice, c->stream));
+    LAUNCH_TRY(launch_quantize_som(g, c->d_som, c->count, c->d_a0, c->d_a1, c->d_anorm, c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
     c->have_som = true;
     return PINK_B200_OK;
@@ -434,8 +444,10 @@ int pink_b200_get_som(pink_b200_ctx* c, float* host_som)
     CU_TRY(cudaSetDevice(c->cfg.device));
     int rc = check_status(c);
     if (rc) return rc;
-    CU_TRY(cudaMemcpy2D(host_som + (size_t)c->first * g.P, (size_t)g.P * sizeof(float), c->d_som,
-                        (size_t)g.Pp * sizeof(float), (size_t)g.P * sizeof(float), c->count, cudaMemcpyDeviceToHost));
+    CU_TRY(cudaMemcpy2DAsync(host_som + (size_t)c->first * g.P, (size_t)g.P * sizeof(float), c->d_som,
+                             (size_t)g.Pp * sizeof(float), (size_t)g.P * sizeof(float), c->count,
+                             cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
     return PINK_B200_OK;
 }
 
@@ -446,8 +458,9 @@ int pink_b200_set_update_factors(pink_b200_ctx* c, const float* host_factors)
     CU_TRY(cudaStreamSynchronize(c->stream));
     const size_t N = c->cfg.n_neurons;
     if (!c->d_factors) CU_TRY(cudaMalloc(&c->d_factors, N * c->count * sizeof(float)));
-    CU_TRY(cudaMemcpy2D(c->d_factors, (size_t)c->count * sizeof(float), host_factors + c->first, N * sizeof(float),
-                        (size_t)c->count * sizeof(float), N, cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemcpy2DAsync(c->d_factors, (size_t)c->count * sizeof(float), host_factors + c->first, N * sizeof(float),
+                             (size_t)c->count * sizeof(float), N, cudaMemcpyHostToDevice, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
     c->have_factors = true;
     return PINK_B200_OK;
 }
@@ -502,7 +515,9 @@ int pink_b200_get_update_counts(pink_b200_ctx* c, uint32_t* host_counts)
     CU_TRY(cudaSetDevice(c->cfg.device));
     int rc = check_status(c);
     if (rc) return rc;
-    CU_TRY(cudaMemcpy(host_counts, c->d_counts, (size_t)c->cfg.n_neurons * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    CU_TRY(cudaMemcpyAsync(host_counts, c->d_counts, (size_t)c->cfg.n_neurons * sizeof(uint32_t),
+                           cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
     return PINK_B200_OK;
 }
 
@@ -511,15 +526,15 @@ int pink_b200_get_bmu_log(pink_b200_ctx* c, uint32_t* host_bmus, uint64_t n)
     if (!c || !host_bmus) return fail(PINK_B200_EINVAL, "null argument");
     if (n > c->bmu_log_n) return fail(PINK_B200_EINVAL, "more entries requested than the last train call produced");
     CU_TRY(cudaSetDevice(c->cfg.device));
+    CU_TRY(cudaMemcpyAsync(host_bmus, c->d_bmu_log, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
-    CU_TRY(cudaMemcpy(host_bmus, c->d_bmu_log, n * sizeof(uint32_t), cudaMemcpyDeviceToHost));
     return PINK_B200_OK;
 }
 
 static int map_chunk(pink_b200_ctx* c, const float* d_images, uint32_t m, float* d_dist, uint32_t* d_rot)
 {
     const Geometry& g = c->g;
-    launch_rotate(g, d_images, m, c->d_cs, c->d_sn, base_fits_smem(g) ? nullptr : c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream);
+    LAUNCH_TRY(launch_rotate(g, d_images, m, c->d_cs, c->d_sn, base_fits_smem(g) ? nullptr : c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream));
     DistanceArgs da{};
     da.a0 = c->d_a0; da.a1 = c->d_a1; da.anorm = c->d_anorm; da.n = c->count;
     da.b0 = c->d_b0; da.b1 = c->d_b1; da.bnorm = c->d_bnorm; da.n_img = m;
@@ -527,7 +542,7 @@ static int map_chunk(pink_b200_ctx* c, const float* d_images, uint32_t m, float*
     const char* why = "";
     cudaError_t e = launch_distance(g, da, c->stream, &why);
     if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
-    launch_map_finalize(g, c->d_keys, m, c->count, d_dist, d_rot, c->stream);
+    LAUNCH_TRY(launch_map_finalize(g, c->d_keys, m, c->count, d_dist, d_rot, c->stream));
     return PINK_B200_OK;
 }
 
@@ -603,7 +618,7 @@ void* pink_b200_stream(pink_b200_ctx* c) { return c ? c->stream : nullptr; }
 
 static int* g_op_status = nullptr;   // device status word shared by the single-stage entries
 
-static int stage_tables(const Geometry& g, float** d_cs, float** d_sn)
+static int stage_tables(const Geometry& g, float** d_cs, float** d_sn, cudaStream_t st)
 {
     const uint32_t nq = g.q ? g.q : 1;
     std::vector<float> cs(nq), sn(nq);
@@ -611,8 +626,9 @@ static int stage_tables(const Geometry& g, float** d_cs, float** d_sn)
     for (uint32_t t = 0; t < nq; ++t) { const float a = t * step; cs[t] = std::cos(a); sn[t] = std::sin(a); }
     CU_TRY(cudaMalloc(d_cs, nq * sizeof(float)));
     CU_TRY(cudaMalloc(d_sn, nq * sizeof(float)));
-    CU_TRY(cudaMemcpy(*d_cs, cs.data(), nq * sizeof(float), cudaMemcpyHostToDevice));
-    CU_TRY(cudaMemcpy(*d_sn, sn.data(), nq * sizeof(float), cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemcpyAsync(*d_cs, cs.data(), nq * sizeof(float), cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(*d_sn, sn.data(), nq * sizeof(float), cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaStreamSynchronize(st));
     return PINK_B200_OK;
 }
 
@@ -626,11 +642,10 @@ int pink_b200_op_rotate(const pink_b200_config* cfg, const float* dev_images, ui
     if (!dev_base && (size_t)g.P * sizeof(float) > 200 * 1024)
         return fail(PINK_B200_EINVAL, "dev_base is required when a base rotation does not fit shared memory");
     float *d_cs = nullptr, *d_sn = nullptr;
-    rc = stage_tables(g, &d_cs, &d_sn);
-    if (rc) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    launch_rotate(g, dev_images, n_img, d_cs, d_sn, dev_base, dev_b0, dev_b1, dev_bnorm, st);
-    cudaError_t e = cudaGetLastError();
+    rc = stage_tables(g, &d_cs, &d_sn, st);
+    if (rc) return rc;
+    cudaError_t e = launch_rotate(g, dev_images, n_img, d_cs, d_sn, dev_base, dev_b0, dev_b1, dev_bnorm, st);
     cudaStreamSynchronize(st);
     cudaFree(d_cs); cudaFree(d_sn);
     if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string("rotate_kernel launch: ") + cudaGetErrorString(e));
@@ -645,8 +660,7 @@ int pink_b200_op_quantize_som(const pink_b200_config* cfg, const float* dev_som,
     int rc = make_geometry(*cfg, &g);
     if (rc) return rc;
     if (g.P != g.Pp) return fail(PINK_B200_EINVAL, "this entry needs a neuron size that is a multiple of 4 floats");
-    launch_quantize_som(g, dev_som, n_neurons, dev_a0, dev_a1, dev_anorm, static_cast<cudaStream_t>(stream));
-    CU_TRY(cudaGetLastError());
+    LAUNCH_TRY(launch_quantize_som(g, dev_som, n_neurons, dev_a0, dev_a1, dev_anorm, static_cast<cudaStream_t>(stream)));
     return PINK_B200_OK;
 }
 

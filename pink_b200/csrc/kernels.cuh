@@ -45,12 +45,12 @@ struct BmuPair { unsigned long long code; unsigned long long neuron; };
 // b0/b1: operand planes [n_img*T][Kp] (u8: b0; u16: b0 = high byte, b1 = low
 // byte; f32: b0 as float).  bnorm: [n_img*T] sum of squares (u32 for u8,
 // u64 for u16, unused for f32).
-void launch_rotate(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
+cudaError_t launch_rotate(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
                    float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st);
 
 // ---- SOM operand ------------------------------------------------------------
 // som: [n][Pp] float.  a0/a1/anorm: as b0/b1/bnorm with one row per neuron.
-void launch_quantize_som(const Geometry& g, const float* som, uint32_t n, void* a0, void* a1, void* anorm,
+cudaError_t launch_quantize_som(const Geometry& g, const float* som, uint32_t n, void* a0, void* a1, void* anorm,
                          cudaStream_t st);
 
 // ---- distances + minimum over transforms ------------------------------------
@@ -67,7 +67,7 @@ cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream
 
 // ---- best matching unit -----------------------------------------------------
 // Reduces keys[0..n) to the local (code, first_neuron + argmin) record.
-void launch_bmu(const Geometry& g, const unsigned long long* keys, uint32_t n, uint32_t first_neuron,
+cudaError_t launch_bmu(const Geometry& g, const unsigned long long* keys, uint32_t n, uint32_t first_neuron,
                 BmuPair* out, cudaStream_t st);
 
 // ---- neighbourhood update ---------------------------------------------------
@@ -83,13 +83,13 @@ struct UpdateArgs
     uint32_t* counts;                 // [N_global] BMU hit counters (incremented by the owner)
     uint32_t* bmu_log;                // nullable: receives the global BMU index of this step
 };
-void launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st);
+cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st);
 
 // ---- mapping epilogue -------------------------------------------------------
 // dist[i][n] = sqrt(reported distance), rot[i][n] = transform; re-arms the keys.
-void launch_map_finalize(const Geometry& g, unsigned long long* keys, uint32_t n_img, uint32_t n,
+cudaError_t launch_map_finalize(const Geometry& g, unsigned long long* keys, uint32_t n_img, uint32_t n,
                          float* dist, uint32_t* rot, cudaStream_t st);
 
-void launch_fill_keys(unsigned long long* keys, size_t count, cudaStream_t st);
+cudaError_t launch_fill_keys(unsigned long long* keys, size_t count, cudaStream_t st);
 
 } // namespace pinkb

@@ -243,48 +243,56 @@ __global__ void fill_keys_kernel(unsigned long long* keys, size_t count)
 constexpr size_t kRotateSmemLimit = 200 * 1024;
 
 template <int MODE>
-void rotate_dispatch(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
+cudaError_t rotate_dispatch(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
                      float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st)
 {
     size_t smem = (size_t)g.P * sizeof(float);
     uint32_t use_smem = smem <= kRotateSmemLimit;
     if (!use_smem) smem = 0;
-    static int attr_dev = -1;   // the opt-in shared-memory size is a per-device function attribute
+    // Dynamic shared memory above 48 KB is an opt-in, per-device function attribute.
+    static int attr_dev = -1;
+    static size_t attr_bytes = 0;
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev != attr_dev) {
-        cudaFuncSetAttribute(rotate_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRotateSmemLimit);
+    if (smem > 48 * 1024 && (dev != attr_dev || smem > attr_bytes)) {
+        cudaError_t e = cudaFuncSetAttribute(rotate_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
         attr_dev = dev;
+        attr_bytes = smem;
     }
     dim3 grid(g.q ? g.q : 1, n_img);
     rotate_kernel<MODE><<<grid, 256, smem, st>>>(g, images, use_smem, cs, sn, base_out, b0, b1, bnorm);
+    return cudaGetLastError();
 }
 
 } // namespace
 
-void launch_rotate(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
-                   float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st)
+cudaError_t launch_rotate(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
+                          float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st)
 {
-    if (g.mode == kModeU8) rotate_dispatch<kModeU8>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
-    else if (g.mode == kModeU16) rotate_dispatch<kModeU16>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
-    else rotate_dispatch<kModeF32>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
+    if (n_img == 0) return cudaSuccess;
+    if (g.mode == kModeU8) return rotate_dispatch<kModeU8>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
+    if (g.mode == kModeU16) return rotate_dispatch<kModeU16>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
+    return rotate_dispatch<kModeF32>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
 }
 
-void launch_quantize_som(const Geometry& g, const float* som, uint32_t n, void* a0, void* a1, void* anorm,
-                         cudaStream_t st)
+cudaError_t launch_quantize_som(const Geometry& g, const float* som, uint32_t n, void* a0, void* a1, void* anorm,
+                                cudaStream_t st)
 {
-    if (n == 0) return;
+    if (n == 0) return cudaSuccess;
     if (g.mode == kModeU8) quantize_som_kernel<kModeU8><<<n, 256, 0, st>>>(g, som, a0, a1, anorm);
     else if (g.mode == kModeU16) quantize_som_kernel<kModeU16><<<n, 256, 0, st>>>(g, som, a0, a1, anorm);
     else quantize_som_kernel<kModeF32><<<n, 256, 0, st>>>(g, som, a0, a1, anorm);
+    return cudaGetLastError();
 }
 
-void launch_fill_keys(unsigned long long* keys, size_t count, cudaStream_t st)
+cudaError_t launch_fill_keys(unsigned long long* keys, size_t count, cudaStream_t st)
 {
-    if (count == 0) return;
+    if (count == 0) return cudaSuccess;
     unsigned blocks = (unsigned)((count + 255) / 256);
     if (blocks > 1184) blocks = 1184;
     fill_keys_kernel<<<blocks, 256, 0, st>>>(keys, count);
+    return cudaGetLastError();
 }
 
 } // namespace pinkb

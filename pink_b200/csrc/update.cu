@@ -68,11 +68,11 @@ bmu_kernel(const unsigned long long* __restrict__ keys, uint32_t n, uint32_t fir
 
 template <int MODE>
 __global__ void __launch_bounds__(256)
-update_kernel(Geometry g, UpdateArgs a)
+update_kernel(Geometry g, UpdateArgs a, uint32_t stage_base)
 {
     extern __shared__ __align__(16) uint8_t dyn[];
     float* base_s = reinterpret_cast<float*>(dyn);                       // [P] base rotation (all channels)
-    uint8_t* crop_s = dyn + (((size_t)g.P * 4 + 15) & ~size_t(15));      // operand row(s) being rebuilt
+    uint8_t* crop_s = dyn + (stage_base ? (((size_t)g.P * 4 + 15) & ~size_t(15)) : 0);   // operand row(s) being rebuilt
     __shared__ unsigned long long red[8];
     __shared__ unsigned long long key_s;
     __shared__ uint32_t bmu_s;
@@ -102,13 +102,19 @@ update_kernel(Geometry g, UpdateArgs a)
     const uint32_t j = g.q ? r / g.q : 0, tq = g.q ? r - j * g.q : 0;
     const float* base = a.base + (size_t)tq * g.P;
 
-    if ((g.P & 3) == 0) {
-        for (uint32_t i = threadIdx.x; i < g.P / 4; i += blockDim.x)
-            reinterpret_cast<float4*>(base_s)[i] = __ldg(reinterpret_cast<const float4*>(base) + i);
-    } else {
-        for (uint32_t i = threadIdx.x; i < g.P; i += blockDim.x) base_s[i] = __ldg(base + i);
+    // Stage the base rotation in shared memory when it fits; otherwise read it
+    // through the read-only cache (it is shared by all neurons and L2 resident).
+    const float* bsrc = base;
+    if (stage_base) {
+        if ((g.P & 3) == 0) {
+            for (uint32_t i = threadIdx.x; i < g.P / 4; i += blockDim.x)
+                reinterpret_cast<float4*>(base_s)[i] = __ldg(reinterpret_cast<const float4*>(base) + i);
+        } else {
+            for (uint32_t i = threadIdx.x; i < g.P; i += blockDim.x) base_s[i] = __ldg(base + i);
+        }
+        __syncthreads();
+        bsrc = base_s;
     }
-    __syncthreads();
 
     float* w = a.som + (size_t)n * g.Pp;
     const uint32_t P1 = g.nd * g.nd, K1 = g.ed * g.ed;
@@ -130,7 +136,7 @@ update_kernel(Geometry g, UpdateArgs a)
                     case 2: bx = nd1 - sx; by = nd1 - y; break;
                     default: bx = y; by = nd1 - sx; break;
                 }
-                const float rv = base_s[c * P1 + bx * g.nd + by];
+                const float rv = bsrc[c * P1 + bx * g.nd + by];
                 const float nv = __fsub_rn(e[k], __fmul_rn(__fsub_rn(e[k], rv), f));
                 e[k] = nv;
                 const uint32_t ci = x - g.off, cj = y - g.off;    // unsigned wrap rejects x < off
@@ -203,46 +209,55 @@ __global__ void map_finalize_kernel(unsigned long long* __restrict__ keys, size_
 }
 
 template <int MODE>
-void update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t st)
+cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t st)
 {
     const size_t crop = MODE == kModeF32 ? (size_t)g.Kp * 4 : (MODE == kModeU16 ? (size_t)g.Kp * 2 : g.Kp);
-    const size_t smem = (((size_t)g.P * 4 + 15) & ~size_t(15)) + crop;
-    static int attr_dev = -1;   // the opt-in shared-memory size is a per-device function attribute
+    const size_t staged = (((size_t)g.P * 4 + 15) & ~size_t(15)) + crop;
+    const uint32_t stage_base = staged <= 200 * 1024;
+    const size_t smem = stage_base ? staged : crop;
+    // Dynamic shared memory above 48 KB is an opt-in, per-device function attribute.
+    static int attr_dev = -1;
+    static size_t attr_bytes = 0;
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev != attr_dev) {
-        cudaFuncSetAttribute(update_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (smem > 48 * 1024 && (dev != attr_dev || smem > attr_bytes)) {
+        cudaError_t e = cudaFuncSetAttribute(update_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
         attr_dev = dev;
+        attr_bytes = smem;
     }
-    update_kernel<MODE><<<a.n, 256, smem, st>>>(g, a);
+    update_kernel<MODE><<<a.n, 256, smem, st>>>(g, a, stage_base);
+    return cudaGetLastError();
 }
 
 } // namespace
 
-void launch_bmu(const Geometry& g, const unsigned long long* keys, uint32_t n, uint32_t first_neuron,
-                BmuPair* out, cudaStream_t st)
+cudaError_t launch_bmu(const Geometry& g, const unsigned long long* keys, uint32_t n, uint32_t first_neuron,
+                       BmuPair* out, cudaStream_t st)
 {
     bmu_kernel<<<1, 1024, 0, st>>>(keys, n, first_neuron, key_shift(g.mode), out);
+    return cudaGetLastError();
 }
 
-void launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st)
+cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st)
 {
-    if (a.n == 0) return;
-    if (g.mode == kModeU8) update_dispatch<kModeU8>(g, a, st);
-    else if (g.mode == kModeU16) update_dispatch<kModeU16>(g, a, st);
-    else update_dispatch<kModeF32>(g, a, st);
+    if (a.n == 0) return cudaSuccess;
+    if (g.mode == kModeU8) return update_dispatch<kModeU8>(g, a, st);
+    if (g.mode == kModeU16) return update_dispatch<kModeU16>(g, a, st);
+    return update_dispatch<kModeF32>(g, a, st);
 }
 
-void launch_map_finalize(const Geometry& g, unsigned long long* keys, uint32_t n_img, uint32_t n,
-                         float* dist, uint32_t* rot, cudaStream_t st)
+cudaError_t launch_map_finalize(const Geometry& g, unsigned long long* keys, uint32_t n_img, uint32_t n,
+                                float* dist, uint32_t* rot, cudaStream_t st)
 {
     const size_t count = (size_t)n_img * n;
-    if (count == 0) return;
+    if (count == 0) return cudaSuccess;
     unsigned blocks = (unsigned)((count + 255) / 256);
     if (blocks > 1184) blocks = 1184;
     if (g.mode == kModeU8) map_finalize_kernel<kModeU8><<<blocks, 256, 0, st>>>(keys, count, dist, rot);
     else if (g.mode == kModeU16) map_finalize_kernel<kModeU16><<<blocks, 256, 0, st>>>(keys, count, dist, rot);
     else map_finalize_kernel<kModeF32><<<blocks, 256, 0, st>>>(keys, count, dist, rot);
+    return cudaGetLastError();
 }
 
 } // namespace pinkb

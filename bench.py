@@ -1,0 +1,329 @@
+#!/usr/bin/env python
+"""Benchmark of the rotation/flip-invariant SOM hot path on B200.
+
+Workload (the large hexagonal SOM the scaling target is quoted on): hexagonal
+SOM of radius 30 (2,791 neurons), 128x128 single-channel images, 90x90
+neurons, 64x64 distance region, 720 rotations + flip (1,440 transforms), uint8
+distance, Gaussian neighbourhood sigma 3.0 / damping 0.05, random-uniform SOM,
+synthetic Gaussian-blob images.  One step = sequential training on one batch
+of images (image i+1 sees the SOM updated by image i).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B]
+  python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+  python bench.py --impl reference ...     # the reference's CPU path on the host cores
+
+Prints ONE JSON line (rank 0).  `value` is images/s with the image batches
+resident in HBM; `e2e` is the same metric through the host-buffer entry point
+(pinned host images copied in, BMU hit counters copied out, every step).
+With N > 1 the neurons are sharded over the ranks (strong scaling): every rank
+sees every image, computes distances for its shard, the shards' best matching
+units are exchanged, and each rank updates its own neurons.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(name="hex-r30 SOM (2791 neurons) train, 128x128 images, 90x90 neurons, 64x64 ED, 720 rot + flip, uint8",
+                som_layout=1, som_dim=61, channels=1, image_dim=128, neuron_dim=90, ed_dim=64,
+                rotations=720, flip=True, sigma=3.0, damping=0.05)
+POOL_IMAGES = 2048          # distinct synthetic images; steps take consecutive, wrapping slices of the pool
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.proc = index, [], None
+
+    def run(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            for line in self.proc.stdout:
+                self.samples.append([x.strip() for x in line.split(",")])
+        except Exception:
+            pass
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+        self.join(timeout=2)
+        sm = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples if len(s) >= 6 for i in range(4) if s[2 + i] == "Active"})
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=reasons, samples=len(sm))
+
+
+def make_inputs(w):
+    from pink_b200.synthetic import blob_images, mt19937_uniform
+    from pink_b200 import engine
+    N = engine.som_size(w["som_layout"], w["som_dim"], w["som_dim"])
+    P = w["channels"] * w["neuron_dim"] ** 2
+    som = mt19937_uniform(N * P, 1234).reshape(N, P)
+    pool = blob_images(POOL_IMAGES, w["image_dim"], w["channels"], seed=1004).reshape(POOL_IMAGES, -1)
+    return N, som, pool
+
+
+def cpu_baseline(w, N, som, pool, budget_s=12.0, max_images=4):
+    """Times the reference's CPU training step (float32, its only CPU mode) on the first images of the workload."""
+    import oracle as O
+    threads = os.cpu_count() or 1
+    if O.have_ref():
+        kind = "reference"
+        sess = O.RefSession(som.reshape(N, w["channels"], w["neuron_dim"], w["neuron_dim"]), w["som_layout"],
+                            w["som_dim"], w["som_dim"], 0 if w["channels"] == 1 else w["channels"], w["image_dim"],
+                            w["neuron_dim"], w["ed_dim"], w["rotations"], w["flip"], O.FUNC_GAUSSIAN, w["sigma"],
+                            w["damping"])
+        step = lambda i: sess.train(pool[i:i + 1])
+        cores = int(O.ref().ref_num_threads())
+    else:
+        kind = "port"
+        F = O.update_factors(w["som_layout"], w["som_dim"], w["som_dim"], O.FUNC_GAUSSIAN, w["sigma"], w["damping"])
+        s = som.reshape(N, w["channels"], w["neuron_dim"], w["neuron_dim"]).copy()
+        img_shape = (w["channels"], w["image_dim"], w["image_dim"])
+        step = lambda i: O.train_step(s, pool[i].reshape(img_shape), F, w["ed_dim"], w["rotations"], w["flip"], 0)
+        cores = 1
+    t0 = time.perf_counter()
+    n = 0
+    while n < max_images and (n == 0 or time.perf_counter() - t0 < budget_s):
+        step(n)
+        n += 1
+    dt = time.perf_counter() - t0
+    return dict(value=n / dt, unit="images/s", cores=cores, kind=kind, host_cpus=threads,
+                sample="first %d images of the workload, float32 distance (the reference has no integer CPU mode), "
+                       "%.1f s wall" % (n, dt))
+
+
+def run_reference(args, w):
+    """The reference's own CPU implementation on the host cores; one step = one image."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle as O
+    N, som, pool = make_inputs(w)
+    if O.have_ref():
+        kind = "reference"
+        sess = O.RefSession(som.reshape(N, w["channels"], w["neuron_dim"], w["neuron_dim"]), w["som_layout"],
+                            w["som_dim"], w["som_dim"], 0 if w["channels"] == 1 else w["channels"], w["image_dim"],
+                            w["neuron_dim"], w["ed_dim"], w["rotations"], w["flip"], O.FUNC_GAUSSIAN, w["sigma"],
+                            w["damping"])
+        step = lambda i: sess.train(pool[i % POOL_IMAGES:i % POOL_IMAGES + 1])
+        cores = int(O.ref().ref_num_threads())
+    else:
+        kind = "port"
+        F = O.update_factors(w["som_layout"], w["som_dim"], w["som_dim"], O.FUNC_GAUSSIAN, w["sigma"], w["damping"])
+        s = som.reshape(N, w["channels"], w["neuron_dim"], w["neuron_dim"]).copy()
+        shape = (w["channels"], w["image_dim"], w["image_dim"])
+        step = lambda i: O.train_step(s, pool[i % POOL_IMAGES].reshape(shape), F, w["ed_dim"], w["rotations"],
+                                      w["flip"], 0)
+        cores = 1
+    for i in range(args.warmup):
+        step(i)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    dt = time.perf_counter() - t0
+    v = args.steps / dt
+    sample = "1 image per step, float32 distance (the reference's CPU path has no integer mode)"
+    print(json.dumps({
+        "impl": "reference", "metric": "train_images_per_sec", "value": v, "unit": "images/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["name"], "images_per_step": 1},
+        "cpu_baseline": {"value": v, "unit": "images/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": v, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=512, help="images per step")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOAD
+    if args.impl == "reference":
+        return run_reference(args, w)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    from pink_b200 import capi, engine
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            sys.exit("bench.py --gpus %d must be launched with torch.distributed.run (one rank per GPU)" % args.gpus)
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    N, som, pool = make_inputs(w)
+    F = engine.update_factors(w["som_layout"], w["som_dim"], w["som_dim"], capi.FUNC_GAUSSIAN, w["sigma"], w["damping"])
+    B = args.batch
+    isz = pool.shape[1]
+    eng = engine.Engine(N, w["channels"], w["image_dim"], w["neuron_dim"], w["ed_dim"], w["rotations"], w["flip"],
+                        capi.UINT8, device=local, rank=rank, world_size=world, max_batch=B)
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            uid.copy_(torch.frombuffer(bytearray(engine.Engine.unique_id()), dtype=torch.uint8))
+        dist.broadcast(uid, 0)
+        eng.comm_init(bytes(uid.cpu().numpy()))
+    eng.set_som(som)
+    eng.set_update_factors(F)
+
+    d_pool = torch.from_numpy(pool).cuda()
+    h_pool = torch.from_numpy(pool).pin_memory()
+    stream = torch.cuda.ExternalStream(eng.stream)
+    n_slices = POOL_IMAGES // B
+
+    def slice_ptr(t, step):
+        return t.data_ptr() + (step % n_slices) * B * isz * 4
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for s in range(steps):
+            fn(s)
+        e1.record(stream)
+        eng.synchronize()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- device-resident throughput -----------------------------------------
+    step_dev = lambda s: eng.train_device(slice_ptr(d_pool, s), B)
+    for s in range(args.warmup):
+        step_dev(s)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms = timed(lambda s: step_dev(args.warmup + s), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    value = args.steps * B / (ms * 1e-3)
+
+    # ---- end to end: pinned host images in, BMU hit counters out, every step --
+    counts = np.empty(N, np.uint32)
+
+    def step_e2e(s):
+        capi.check(capi.lib.pink_b200_train(eng._h, slice_ptr(h_pool, s), B))
+        capi.check(capi.lib.pink_b200_get_update_counts(eng._h, counts.ctypes.data))
+    for s in range(3):
+        step_e2e(s)
+    ms_e2e = timed(step_e2e, args.steps)
+    e2e = args.steps * B / (ms_e2e * 1e-3)
+
+    # ---- per-kernel device time (separate profiled pass of the same workload) --
+    prof_steps = min(B, 256)
+    eng.profile_begin(prof_steps)
+    eng.train_device(slice_ptr(d_pool, 1), prof_steps)
+    phase_ms, covered = eng.profile_end()
+    bmus = eng.bmu_log(prof_steps)
+
+    peaks = measured_peaks()
+    T = w["rotations"] * (2 if w["flip"] else 1)
+    K = w["channels"] * w["ed_dim"] ** 2
+    P = w["channels"] * w["neuron_dim"] ** 2
+    nl = eng.count
+    # neurons this rank actually rewrites per image: non-zero factor for that image's BMU
+    owned = bmus[bmus != 0xFFFFFFFF]
+    nz_rows = (F[:, eng.first:eng.first + nl] != 0).sum(1)
+    if world == 1:
+        n_upd = float(nz_rows[owned].mean()) if len(owned) else float(nl)
+    else:
+        n_upd = float(nz_rows.mean())          # BMUs of other shards are not logged locally
+    t_dist = phase_ms["distance"] / covered * 1e-3
+    t_upd = phase_ms["update"] / covered * 1e-3
+    dist_ops = 2.0 * nl * T * K
+    upd_bytes = 8.0 * n_upd * P
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    kernels = {
+        "update_kernel": {"bound": "hbm", "achieved": upd_bytes / t_upd / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                          "frac": upd_bytes / t_upd / 1e9 / peaks["hbm_gbs"], "us_per_launch": t_upd * 1e6,
+                          "algorithmic_bytes": upd_bytes},
+        "distance_tc_kernel": {"bound": "tensor", "achieved": dist_ops / t_dist / 1e12, "peak": int8_peak,
+                               "unit": "TOP/s", "frac": dist_ops / t_dist / 1e12 / int8_peak,
+                               "us_per_launch": t_dist * 1e6, "algorithmic_ops": dist_ops,
+                               "peak_note": "int8 peak taken as 2 x the %s bf16 cuBLAS figure" % peaks["source"]},
+        "rotate_kernel": {"us_per_launch": phase_ms["rotate"] / covered * 1e3},
+        "bmu_kernel+exchange": {"us_per_launch": phase_ms["bmu"] / covered * 1e3},
+    }
+    dominant = "update_kernel" if t_upd >= t_dist else "distance_tc_kernel"
+    roof = dict(kernels[dominant])
+    roof["kernel"] = dominant
+    roof["traffic"] = None
+    roof["peak_source"] = peaks["source"]
+    roof["timing"] = "CUDA events around every launch in a separate profiled pass of %d steps" % covered
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            cpu = cpu_baseline(w, N, som, pool)
+        except Exception as ex:          # the checker is optional equipment of the benchmark
+            cpu = {"unavailable": repr(ex)}
+
+    if rank == 0:
+        line = {
+            "metric": "train_images_per_sec", "value": value, "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": w["name"], "images_per_step": B, "parallelism": "neuron-shard x%d" % world,
+                       "l2": "every step trains on a different slice of a 134 MB image pool; SOM (90 MB) + operand "
+                             "(11 MB) + batch (34 MB) exceed the 126 MB L2"},
+            "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": B * isz * 4, "d2h_bytes_per_step": N * 4,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": args.steps * B * 4,
+            "clocks": clocks,
+            "roofline": roof,
+            "kernels": kernels,
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -55,6 +55,16 @@ extern "C" {
 #define PINK_B200_NEAREST_NEIGHBOR 0
 #define PINK_B200_BILINEAR         1
 
+/* SOM grid layouts (src/UtilitiesLib/Layout.h:15-19). */
+#define PINK_B200_LAYOUT_CARTESIAN 0
+#define PINK_B200_LAYOUT_HEXAGONAL 1
+
+/* Neighbourhood functions (src/UtilitiesLib/DistributionFunctor.h:32-104). */
+#define PINK_B200_FUNC_GAUSSIAN        0   /* p0 = sigma, p1 = damping */
+#define PINK_B200_FUNC_UNITY_GAUSSIAN  1   /* p0 = sigma, p1 = damping */
+#define PINK_B200_FUNC_MEXICAN_HAT     2   /* p0 = sigma, p1 = damping */
+#define PINK_B200_FUNC_STEP            3   /* p0 = value               */
+
 typedef struct pink_b200_ctx pink_b200_ctx;
 
 /* Everything the Trainer / Mapper constructors take that shapes device state
@@ -120,6 +130,20 @@ int pink_b200_get_som(pink_b200_ctx* ctx, float* host_som);
  * (Trainer.h:69-76, uploaded at :243).  Each rank keeps its columns. */
 int pink_b200_set_update_factors(pink_b200_ctx* ctx, const float* host_factors);
 
+/* Host helpers (no GPU involved) for the tables the reference computes on the
+ * host.  Number of neurons of a SOM grid: dim0 * dim1 (cartesian) or the
+ * row-packed hexagon of side dim0 (HexagonalLayout.h:61-64). */
+uint32_t pink_b200_som_size(uint32_t som_layout, uint32_t dim0, uint32_t dim1);
+/* out[i * N + j] = layout.get_distance(i, j) (CartesianLayout.h:47-60,108-114;
+ * HexagonalLayout.h:90-118). */
+int pink_b200_som_distances(uint32_t som_layout, uint32_t dim0, uint32_t dim1, float* out);
+/* out[i * N + j] = func(distance) if max_update_distance <= 0 or distance <
+ * max_update_distance, else 0 -- the TrainerCommon loop (Trainer.h:69-76) for
+ * the built-in functors (DistributionFunctor.cpp:18-59).  Callers with their
+ * own distribution function fill the table themselves. */
+int pink_b200_update_factors(uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t func, float p0, float p1,
+                             float max_update_distance, float* out);
+
 /* ---- training --------------------------------------------------------------
  * n sequential training steps; image i+1 sees the SOM updated by image i.
  * Stands for n calls of Trainer<...,true>::operator() (Trainer.h:263-304).
@@ -150,6 +174,16 @@ int pink_b200_synchronize(pink_b200_ctx* ctx);
 /* The CUDA stream (cudaStream_t) the context launches on, for callers that
  * time or order work against it. */
 void* pink_b200_stream(pink_b200_ctx* ctx);
+
+/* Opt-in phase timing (the reference only has a wall clock around the whole
+ * run, src/Pink/main.cpp:37-62).  After profile_begin, CUDA events on the
+ * context's stream bracket the four kernels of each of the next max_steps
+ * training steps; profile_end waits for them and returns the summed device
+ * time in milliseconds of {rotation set, distance, BMU + exchange, update} and
+ * the number of steps covered.  Event records perturb the pipeline slightly:
+ * use it to apportion time between kernels, not to measure throughput. */
+int pink_b200_profile_begin(pink_b200_ctx* ctx, uint32_t max_steps);
+int pink_b200_profile_end(pink_b200_ctx* ctx, double ms_sum[4], uint64_t* steps);
 
 /* ---- single stages on device buffers (what the context calls internally) ---
  * Exposed for kernel-level parity tests and benchmarks.  `stream` is a

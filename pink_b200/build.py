@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpink_b200.so")
-SOURCES = ["capi.cu", "operands.cu", "distance_tc.cu", "distance_f32.cu", "update.cu"]
+SOURCES = ["capi.cu", "operands.cu", "distance_tc.cu", "distance_f32.cu", "update.cu", "host_tables.cpp"]
 HEADERS = ["kernels.cuh", "ptx.cuh", os.path.join("..", "..", "include", "pink_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
@@ -31,10 +31,11 @@ def build(force=False, verbose=False):
     objs, procs = [], []
     for src in SOURCES:
         path = os.path.join(CSRC, src)
-        obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        obj = os.path.join(objdir, os.path.splitext(src)[0] + ".o")
         objs.append(obj)
         if force or _stale(obj, [path] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj]
+            cmd = [nvcc] + NVCC_FLAGS + ["-Xcompiler", "-ffp-contract=off"] \
+                + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj]
             procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for cmd, p in procs:
         out, _ = p.communicate()

@@ -15,6 +15,8 @@ OK, EINVAL, ECUDA, ENCCL, ETIMEOUT, ESTATE = 0, -1, -2, -3, -4, -5
 FLOAT, UINT16, UINT8 = 0, 1, 2
 QUADRATIC, CIRCULAR = 0, 1
 NEAREST_NEIGHBOR, BILINEAR = 0, 1
+LAYOUT_CARTESIAN, LAYOUT_HEXAGONAL = 0, 1
+FUNC_GAUSSIAN, FUNC_UNITY_GAUSSIAN, FUNC_MEXICAN_HAT, FUNC_STEP = 0, 1, 2, 3
 
 
 class Config(C.Structure):
@@ -46,6 +48,12 @@ SYMBOLS = {
     "pink_b200_map_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),
     "pink_b200_synchronize": (C.c_int, [C.c_void_p]),
     "pink_b200_stream": (C.c_void_p, [C.c_void_p]),
+    "pink_b200_profile_begin": (C.c_int, [C.c_void_p, C.c_uint32]),
+    "pink_b200_profile_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
+    "pink_b200_som_size": (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32]),
+    "pink_b200_som_distances": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
+    "pink_b200_update_factors": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
+                                           C.c_float, C.c_void_p]),
     "pink_b200_operand_stride": (C.c_uint32, [C.c_uint32, C.c_uint32]),
     "pink_b200_op_rotate": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p]),

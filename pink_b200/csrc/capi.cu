@@ -155,6 +155,9 @@ struct pink_b200_ctx
     float* d_dist = nullptr; uint32_t* d_rot = nullptr; size_t out_imgs = 0;
     bool have_som = false, have_factors = false;
     ncclComm_t comm = nullptr;
+    // opt-in phase timing: five events per profiled training step
+    std::vector<cudaEvent_t> prof_events;
+    size_t prof_cap = 0, prof_used = 0;
 
     size_t image_size() const { return (size_t)g.C * g.id * g.id; }
 };
@@ -221,14 +224,19 @@ int check_status(pink_b200_ctx* c)
 int train_one(pink_b200_ctx* c, const float* d_image, uint32_t* bmu_slot)
 {
     const Geometry& g = c->g;
+    cudaEvent_t* ev = nullptr;
+    if (c->prof_used < c->prof_cap) ev = &c->prof_events[5 * c->prof_used++];
+    if (ev) CU_TRY(cudaEventRecord(ev[0], c->stream));
     LAUNCH_TRY(launch_rotate(g, d_image, 1, c->d_cs, c->d_sn, c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream));
     DistanceArgs da{};
     da.a0 = c->d_a0; da.a1 = c->d_a1; da.anorm = c->d_anorm; da.n = c->count;
     da.b0 = c->d_b0; da.b1 = c->d_b1; da.bnorm = c->d_bnorm; da.n_img = 1;
     da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status;
     const char* why = "";
+    if (ev) CU_TRY(cudaEventRecord(ev[1], c->stream));
     cudaError_t e = launch_distance(g, da, c->stream, &why);
     if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
+    if (ev) CU_TRY(cudaEventRecord(ev[2], c->stream));
     LAUNCH_TRY(launch_bmu(g, c->d_keys, c->count, c->first, c->d_pairs + c->cfg.rank, c->stream));
     if (c->cfg.world_size > 1)
         NCCL_TRY(nccl().AllGather(c->d_pairs + c->cfg.rank, c->d_pairs, 2, ncclUint64, c->comm, c->stream));
@@ -238,7 +246,9 @@ int train_one(pink_b200_ctx* c, const float* d_image, uint32_t* bmu_slot)
     ua.factors = c->d_factors; ua.n = c->count; ua.first_neuron = c->first;
     ua.a0 = c->d_a0; ua.a1 = c->d_a1; ua.anorm = c->d_anorm;
     ua.counts = c->d_counts; ua.bmu_log = bmu_slot;
+    if (ev) CU_TRY(cudaEventRecord(ev[3], c->stream));
     LAUNCH_TRY(launch_update(g, ua, c->stream));
+    if (ev) CU_TRY(cudaEventRecord(ev[4], c->stream));
     return PINK_B200_OK;
 }
 
@@ -377,6 +387,7 @@ int pink_b200_destroy(pink_b200_ctx* c)
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
     free_dev(c->d_pairs); free_dev(c->d_counts); free_dev(c->d_bmu_log); free_dev(c->d_status);
     free_dev(c->d_images[0]); free_dev(c->d_images[1]); free_dev(c->d_dist); free_dev(c->d_rot);
+    for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
     for (int i = 0; i < 2; ++i) {
         if (c->copied[i]) cudaEventDestroy(c->copied[i]);
         if (c->consumed[i]) cudaEventDestroy(c->consumed[i]);
@@ -613,6 +624,37 @@ int pink_b200_synchronize(pink_b200_ctx* c)
 }
 
 void* pink_b200_stream(pink_b200_ctx* c) { return c ? c->stream : nullptr; }
+
+int pink_b200_profile_begin(pink_b200_ctx* c, uint32_t max_steps)
+{
+    if (!c) return fail(PINK_B200_EINVAL, "null context");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    while (c->prof_events.size() < (size_t)5 * max_steps) {
+        cudaEvent_t e;
+        CU_TRY(cudaEventCreate(&e));
+        c->prof_events.push_back(e);
+    }
+    c->prof_cap = max_steps;
+    c->prof_used = 0;
+    return PINK_B200_OK;
+}
+
+int pink_b200_profile_end(pink_b200_ctx* c, double ms_sum[4], uint64_t* steps)
+{
+    if (!c || !ms_sum || !steps) return fail(PINK_B200_EINVAL, "null argument");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    for (int k = 0; k < 4; ++k) ms_sum[k] = 0.0;
+    for (size_t s = 0; s < c->prof_used; ++s)
+        for (int k = 0; k < 4; ++k) {
+            float ms = 0.f;
+            CU_TRY(cudaEventElapsedTime(&ms, c->prof_events[5 * s + k], c->prof_events[5 * s + k + 1]));
+            ms_sum[k] += ms;
+        }
+    *steps = c->prof_used;
+    c->prof_cap = c->prof_used = 0;
+    return PINK_B200_OK;
+}
 
 // ---- single stages ---------------------------------------------------------------
 

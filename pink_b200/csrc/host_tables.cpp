@@ -1,0 +1,105 @@
+// Host-side tables that feed the device path: SOM grid distances and the
+// N x N update-factor table.  The reference builds the same table in the
+// TrainerCommon constructor (src/SelfOrganizingMapLib/Trainer.h:69-76) from
+// layout.get_distance (CartesianLayout.h:47-60,108-114; HexagonalLayout.h:90-118)
+// and a distribution functor (src/UtilitiesLib/DistributionFunctor.cpp:18-59).
+// All arithmetic is float32 with the reference's expression shapes so that the
+// factors, and therefore the trained weights, agree bit for bit.
+#include "../../include/pink_b200.h"
+
+#include <cmath>
+#include <cstdint>
+#include <cstdlib>
+#include <vector>
+
+namespace {
+
+struct Cell { int32_t q, r; };
+
+// Axial position of array index i in the row-packed hexagon of side `dim`.
+Cell hex_cell(uint32_t i, const std::vector<uint32_t>& row_offset, uint32_t radius)
+{
+    uint32_t r = 0;
+    while (i >= row_offset[r + 1]) ++r;
+    uint32_t q = i - row_offset[r];
+    if (radius > r) q += radius - r;
+    return { (int32_t)q, (int32_t)r };
+}
+
+float neighbourhood(uint32_t func, float d, float p0, float p1)
+{
+    switch (func) {
+        case PINK_B200_FUNC_GAUSSIAN:
+            return p1 / (p0 * std::sqrt(2.0f * static_cast<float>(M_PI))) * std::exp(-0.5f * std::pow(d / p0, 2.0f));
+        case PINK_B200_FUNC_UNITY_GAUSSIAN:
+            return p1 * std::exp(-0.5f * std::pow(d / p0, 2.0f));
+        case PINK_B200_FUNC_MEXICAN_HAT: {
+            const float d2 = d * d, s2 = p0 * p0;
+            return 2.0f * p1 / (std::sqrt(3.0f * p0) * std::pow(static_cast<float>(M_PI), 0.25f))
+                   * (1.0f - d2 / s2) * std::exp(-d2 / (2.0f * s2));
+        }
+        default:
+            return d <= p0 ? 1.0f : 0.0f;
+    }
+}
+
+} // namespace
+
+extern "C" {
+
+uint32_t pink_b200_som_size(uint32_t som_layout, uint32_t dim0, uint32_t dim1)
+{
+    if (som_layout == PINK_B200_LAYOUT_CARTESIAN) return dim0 * dim1;
+    const uint32_t radius = (dim0 - 1) / 2;
+    return dim0 * dim0 - radius * (radius + 1);
+}
+
+int pink_b200_som_distances(uint32_t som_layout, uint32_t dim0, uint32_t dim1, float* out)
+{
+    if (!out || dim0 == 0 || dim1 == 0) return PINK_B200_EINVAL;
+    const uint32_t N = pink_b200_som_size(som_layout, dim0, dim1);
+    if (som_layout == PINK_B200_LAYOUT_CARTESIAN) {
+        for (uint32_t i = 0; i < N; ++i)
+            for (uint32_t j = 0; j < N; ++j) {
+                const uint32_t a[2] = { i % dim1, i / dim1 }, b[2] = { j % dim1, j / dim1 };
+                float d = 0.0f;
+                for (int k = 0; k < 2; ++k) {
+                    const float diff = static_cast<float>(a[k]) - static_cast<float>(b[k]);
+                    d += static_cast<float>(static_cast<double>(diff) * static_cast<double>(diff));
+                }
+                out[(size_t)i * N + j] = std::sqrt(d);
+            }
+        return PINK_B200_OK;
+    }
+    if (som_layout != PINK_B200_LAYOUT_HEXAGONAL || dim0 % 2 == 0 || dim0 != dim1) return PINK_B200_EINVAL;
+    const uint32_t radius = (dim0 - 1) / 2;
+    std::vector<uint32_t> row_offset(dim0 + 1, 0);
+    for (uint32_t r = 0; r < dim0; ++r)
+        row_offset[r + 1] = row_offset[r] + dim0 - (r > radius ? r - radius : radius - r);
+    std::vector<Cell> cells(N);
+    for (uint32_t i = 0; i < N; ++i) cells[i] = hex_cell(i, row_offset, radius);
+    for (uint32_t i = 0; i < N; ++i)
+        for (uint32_t j = 0; j < N; ++j) {
+            const int32_t dx = cells[i].q - cells[j].q, dy = cells[i].r - cells[j].r;
+            const int32_t hops = ((dx >= 0) == (dy >= 0)) ? std::abs(dx + dy) : std::max(std::abs(dx), std::abs(dy));
+            out[(size_t)i * N + j] = static_cast<float>(hops);
+        }
+    return PINK_B200_OK;
+}
+
+int pink_b200_update_factors(uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t func, float p0, float p1,
+                             float max_update_distance, float* out)
+{
+    if (func > PINK_B200_FUNC_STEP) return PINK_B200_EINVAL;
+    if (func == PINK_B200_FUNC_MEXICAN_HAT && p0 <= 0.0f) return PINK_B200_EINVAL;
+    int rc = pink_b200_som_distances(som_layout, dim0, dim1, out);
+    if (rc) return rc;
+    const size_t N = pink_b200_som_size(som_layout, dim0, dim1);
+    for (size_t i = 0; i < N * N; ++i) {
+        const float d = out[i];
+        out[i] = (max_update_distance <= 0.0f || d < max_update_distance) ? neighbourhood(func, d, p0, p1) : 0.0f;
+    }
+    return PINK_B200_OK;
+}
+
+} // extern "C"

@@ -4,7 +4,8 @@ import numpy as np
 import pytest
 
 import oracle as O
-from util import Context, blob_images, make_config
+from pink_b200.synthetic import blob_images
+from util import Context, make_config
 
 pytestmark = pytest.mark.gpu
 

@@ -313,7 +313,7 @@ def main():
                              "(11 MB) + batch (34 MB) exceed the 126 MB L2"},
             "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": B * isz * 4, "d2h_bytes_per_step": N * 4,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": args.steps * B * 4,
+            "gpu_launches": args.steps * (B * 3 + (B + 15) // 16),
             "clocks": clocks,
             "roofline": roof,
             "kernels": kernels,

@@ -177,10 +177,10 @@ void* pink_b200_stream(pink_b200_ctx* ctx);
 
 /* Opt-in phase timing (the reference only has a wall clock around the whole
  * run, src/Pink/main.cpp:37-62).  After profile_begin, CUDA events on the
- * context's stream bracket the four kernels of each of the next max_steps
+ * context's streams bracket the kernels of each of the next max_steps
  * training steps; profile_end waits for them and returns the summed device
- * time in milliseconds of {rotation set, distance, BMU + exchange, update} and
- * the number of steps covered.  Event records perturb the pipeline slightly:
+ * time in milliseconds of {rotation sets (batched, overlapped with the steps),
+ * distance, BMU + exchange, update} and the number of steps covered.  Event records perturb the pipeline slightly:
  * use it to apportion time between kernels, not to measure throughput. */
 int pink_b200_profile_begin(pink_b200_ctx* ctx, uint32_t max_steps);
 int pink_b200_profile_end(pink_b200_ctx* ctx, double ms_sum[4], uint64_t* steps);

@@ -8,6 +8,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <dlfcn.h>
 #include <nccl.h>
@@ -137,8 +138,13 @@ struct pink_b200_ctx
     Geometry g{};
     uint32_t first = 0, count = 0;
     uint32_t train_batch = 0, map_batch = 0;
-    cudaStream_t stream = nullptr, copy_stream = nullptr;
+    cudaStream_t stream = nullptr, copy_stream = nullptr, rot_stream = nullptr;
     cudaEvent_t copied[2] = { nullptr, nullptr }, consumed[2] = { nullptr, nullptr };
+    // Training pipelines the rotation sets of the next kRotBatch images (they do
+    // not depend on the SOM) on rot_stream while the sequential steps of the
+    // current batch run on stream; two slots of transform buffers alternate.
+    cudaEvent_t rotated[2] = { nullptr, nullptr }, rot_free[2] = { nullptr, nullptr };
+    uint64_t rot_seq = 0;
 
     float* d_som = nullptr;
     void *d_a0 = nullptr, *d_a1 = nullptr, *d_anorm = nullptr;
@@ -148,6 +154,8 @@ struct pink_b200_ctx
     void *d_b0 = nullptr, *d_b1 = nullptr, *d_bnorm = nullptr; size_t b_imgs = 0;
     unsigned long long* d_keys = nullptr; size_t key_imgs = 0;
     BmuPair* d_pairs = nullptr;
+    uint32_t *d_active = nullptr, *d_tactive = nullptr, *d_nactive = nullptr;
+    float* d_factive = nullptr;
     uint32_t* d_counts = nullptr;
     uint32_t* d_bmu_log = nullptr; size_t bmu_log_cap = 0, bmu_log_n = 0;
     int* d_status = nullptr;
@@ -155,9 +163,9 @@ struct pink_b200_ctx
     float* d_dist = nullptr; uint32_t* d_rot = nullptr; size_t out_imgs = 0;
     bool have_som = false, have_factors = false;
     ncclComm_t comm = nullptr;
-    // opt-in phase timing: five events per profiled training step
-    std::vector<cudaEvent_t> prof_events;
-    size_t prof_cap = 0, prof_used = 0;
+    // opt-in phase timing: four events per profiled training step, two per rotation batch
+    std::vector<cudaEvent_t> prof_events, prof_rot_events;
+    size_t prof_cap = 0, prof_used = 0, prof_rot_used = 0;
 
     size_t image_size() const { return (size_t)g.C * g.id * g.id; }
 };
@@ -188,12 +196,14 @@ int ensure_transform_buffers(pink_b200_ctx* c, size_t imgs, size_t base_needed)
         CU_TRY(cudaMalloc(&c->d_base, base_needed * (g.q ? g.q : 1) * (size_t)g.P * sizeof(float)));
         c->base_imgs = base_needed;
     }
-    if (c->key_imgs < imgs) {
+    const size_t key_imgs_needed = imgs;
+    if (c->key_imgs < key_imgs_needed) {
         free_dev(c->d_keys);
         CU_TRY(cudaMalloc(&c->d_keys, imgs * c->count * sizeof(unsigned long long)));
         LAUNCH_TRY(launch_fill_keys(c->d_keys, imgs * c->count, c->stream));
         c->key_imgs = imgs;
     }
+    CU_TRY(cudaStreamSynchronize(c->stream));   // initialisation complete before other streams touch the buffers
     return PINK_B200_OK;
 }
 
@@ -220,35 +230,86 @@ int check_status(pink_b200_ctx* c)
     return PINK_B200_OK;
 }
 
-// One training step on an image that is already on the device.
-int train_one(pink_b200_ctx* c, const float* d_image, uint32_t* bmu_slot)
+constexpr uint32_t kRotBatch = 16;
+
+// One training step on image `slot_img` of the transform buffers (its rotation
+// set is already there): distance + minimum over transforms, best matching
+// unit (+ exchange between ranks), neighbourhood update.
+int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
 {
     const Geometry& g = c->g;
+    const size_t esz = g.mode == kModeF32 ? 4 : 1;
+    const size_t row0 = slot_img * g.T;
     cudaEvent_t* ev = nullptr;
-    if (c->prof_used < c->prof_cap) ev = &c->prof_events[5 * c->prof_used++];
-    if (ev) CU_TRY(cudaEventRecord(ev[0], c->stream));
-    LAUNCH_TRY(launch_rotate(g, d_image, 1, c->d_cs, c->d_sn, c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream));
+    if (c->prof_used < c->prof_cap) ev = &c->prof_events[4 * c->prof_used++];
     DistanceArgs da{};
     da.a0 = c->d_a0; da.a1 = c->d_a1; da.anorm = c->d_anorm; da.n = c->count;
-    da.b0 = c->d_b0; da.b1 = c->d_b1; da.bnorm = c->d_bnorm; da.n_img = 1;
+    da.b0 = static_cast<uint8_t*>(c->d_b0) + row0 * g.Kp * esz;
+    da.b1 = c->d_b1 ? static_cast<uint8_t*>(c->d_b1) + row0 * g.Kp * esz : nullptr;
+    da.bnorm = static_cast<uint8_t*>(c->d_bnorm) + row0 * (g.mode == kModeU16 ? 8 : 4);
+    da.n_img = 1;
     da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status;
     const char* why = "";
-    if (ev) CU_TRY(cudaEventRecord(ev[1], c->stream));
+    if (ev) CU_TRY(cudaEventRecord(ev[0], c->stream));
     cudaError_t e = launch_distance(g, da, c->stream, &why);
     if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
-    if (ev) CU_TRY(cudaEventRecord(ev[2], c->stream));
-    LAUNCH_TRY(launch_bmu(g, c->d_keys, c->count, c->first, c->d_pairs + c->cfg.rank, c->stream));
-    if (c->cfg.world_size > 1)
+    if (ev) CU_TRY(cudaEventRecord(ev[1], c->stream));
+    BmuArgs ba{};
+    ba.keys = c->d_keys; ba.n = c->count; ba.first_neuron = c->first; ba.shift = key_shift(g.mode);
+    ba.pairs = c->d_pairs; ba.rank = c->cfg.rank; ba.world = c->cfg.world_size;
+    ba.factors = c->d_factors;
+    ba.active = c->d_active; ba.f_active = c->d_factive; ba.t_active = c->d_tactive; ba.n_active = c->d_nactive;
+    ba.counts = c->d_counts; ba.bmu_log = bmu_slot;
+    if (c->cfg.world_size == 1) {
+        LAUNCH_TRY(launch_bmu(ba, 3, c->stream));
+    } else {
+        LAUNCH_TRY(launch_bmu(ba, 1, c->stream));
         NCCL_TRY(nccl().AllGather(c->d_pairs + c->cfg.rank, c->d_pairs, 2, ncclUint64, c->comm, c->stream));
+        LAUNCH_TRY(launch_bmu(ba, 2, c->stream));
+    }
     UpdateArgs ua{};
-    ua.som = c->d_som; ua.base = c->d_base; ua.keys = c->d_keys;
-    ua.pairs = c->d_pairs; ua.world = c->cfg.world_size;
-    ua.factors = c->d_factors; ua.n = c->count; ua.first_neuron = c->first;
+    ua.som = c->d_som;
+    ua.base = c->d_base + slot_img * (g.q ? g.q : 1) * (size_t)g.P;
+    ua.active = c->d_active; ua.f_active = c->d_factive; ua.t_active = c->d_tactive; ua.n_active = c->d_nactive;
+    ua.n = c->count;
     ua.a0 = c->d_a0; ua.a1 = c->d_a1; ua.anorm = c->d_anorm;
-    ua.counts = c->d_counts; ua.bmu_log = bmu_slot;
-    if (ev) CU_TRY(cudaEventRecord(ev[3], c->stream));
+    if (ev) CU_TRY(cudaEventRecord(ev[2], c->stream));
     LAUNCH_TRY(launch_update(g, ua, c->stream));
-    if (ev) CU_TRY(cudaEventRecord(ev[4], c->stream));
+    if (ev) CU_TRY(cudaEventRecord(ev[3], c->stream));
+    return PINK_B200_OK;
+}
+
+// m sequential steps over images resident on the device.  `ready` (nullable) is
+// an event the rotation stream must wait for before reading the images.
+int train_chunk(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* log, cudaEvent_t ready)
+{
+    const Geometry& g = c->g;
+    const size_t esz = g.mode == kModeF32 ? 4 : 1, isz = c->image_size();
+    for (uint64_t s0 = 0; s0 < m; s0 += kRotBatch) {
+        const uint32_t cnt = (uint32_t)(m - s0 < kRotBatch ? m - s0 : kRotBatch);
+        const size_t slot = (size_t)(c->rot_seq++ & 1) * kRotBatch;
+        const size_t row0 = slot * g.T;
+        CU_TRY(cudaStreamWaitEvent(c->rot_stream, c->rot_free[slot ? 1 : 0], 0));
+        if (ready && s0 == 0) CU_TRY(cudaStreamWaitEvent(c->rot_stream, ready, 0));
+        cudaEvent_t* ev = nullptr;
+        if (c->prof_used < c->prof_cap && 2 * (c->prof_rot_used + 1) <= c->prof_rot_events.size())
+            ev = &c->prof_rot_events[2 * c->prof_rot_used++];
+        if (ev) CU_TRY(cudaEventRecord(ev[0], c->rot_stream));
+        LAUNCH_TRY(launch_rotate(g, d_images + s0 * isz, cnt, c->d_cs, c->d_sn,
+                                 c->d_base + slot * (g.q ? g.q : 1) * (size_t)g.P,
+                                 static_cast<uint8_t*>(c->d_b0) + row0 * g.Kp * esz,
+                                 c->d_b1 ? static_cast<uint8_t*>(c->d_b1) + row0 * g.Kp * esz : nullptr,
+                                 static_cast<uint8_t*>(c->d_bnorm) + row0 * (g.mode == kModeU16 ? 8 : 4),
+                                 c->rot_stream));
+        if (ev) CU_TRY(cudaEventRecord(ev[1], c->rot_stream));
+        CU_TRY(cudaEventRecord(c->rotated[slot ? 1 : 0], c->rot_stream));
+        CU_TRY(cudaStreamWaitEvent(c->stream, c->rotated[slot ? 1 : 0], 0));
+        for (uint32_t i = 0; i < cnt; ++i) {
+            int rc = train_step(c, slot + i, log + s0 + i);
+            if (rc) return rc;
+        }
+        CU_TRY(cudaEventRecord(c->rot_free[slot ? 1 : 0], c->stream));
+    }
     return PINK_B200_OK;
 }
 
@@ -258,7 +319,7 @@ int train_prepare(pink_b200_ctx* c, uint64_t n)
     if (!c->have_factors) return fail(PINK_B200_ESTATE, "pink_b200_set_update_factors must be called before training");
     if (c->cfg.world_size > 1 && !c->comm)
         return fail(PINK_B200_ESTATE, "pink_b200_comm_init must be called before training with world_size > 1");
-    int rc = ensure_transform_buffers(c, 1, 1);
+    int rc = ensure_transform_buffers(c, 2 * kRotBatch, 2 * kRotBatch);
     if (rc) return rc;
     if (c->bmu_log_cap < n) {
         free_dev(c->d_bmu_log);
@@ -330,11 +391,21 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
         }                                                                                         \
     } while (0)
 
-    CTX_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
-    CTX_TRY(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+    {
+        // The sequential steps run at the highest priority so that their blocks are
+        // placed before pending blocks of the look-ahead rotation kernel.
+        int lo = 0, hi = 0;
+        CTX_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        CTX_TRY(cudaStreamCreateWithPriority(&c->stream, cudaStreamNonBlocking, hi));
+        CTX_TRY(cudaStreamCreateWithPriority(&c->copy_stream, cudaStreamNonBlocking, hi));
+        if (getenv("PINK_B200_ROT_SERIAL")) c->rot_stream = c->stream;
+        else CTX_TRY(cudaStreamCreateWithPriority(&c->rot_stream, cudaStreamNonBlocking, lo));
+    }
     for (int i = 0; i < 2; ++i) {
         CTX_TRY(cudaEventCreateWithFlags(&c->copied[i], cudaEventDisableTiming));
         CTX_TRY(cudaEventCreateWithFlags(&c->consumed[i], cudaEventDisableTiming));
+        CTX_TRY(cudaEventCreateWithFlags(&c->rotated[i], cudaEventDisableTiming));
+        CTX_TRY(cudaEventCreateWithFlags(&c->rot_free[i], cudaEventDisableTiming));
     }
     CTX_TRY(cudaMalloc(&c->d_som, (size_t)c->count * g.Pp * sizeof(float)));
     CTX_TRY(cudaMemsetAsync(c->d_som, 0, (size_t)c->count * g.Pp * sizeof(float), c->stream));
@@ -347,6 +418,12 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     CTX_TRY(cudaMalloc(&c->d_anorm, norm_bytes(g, c->count)));
     CTX_TRY(cudaMalloc(&c->d_pairs, W * sizeof(BmuPair)));
     CTX_TRY(cudaMemsetAsync(c->d_pairs, 0xFF, W * sizeof(BmuPair), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_active, c->count * sizeof(uint32_t)));
+    CTX_TRY(cudaMemsetAsync(c->d_active, 0, c->count * sizeof(uint32_t), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_tactive, c->count * sizeof(uint32_t)));
+    CTX_TRY(cudaMemsetAsync(c->d_tactive, 0, c->count * sizeof(uint32_t), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_factive, c->count * sizeof(float)));
+    CTX_TRY(cudaMalloc(&c->d_nactive, sizeof(uint32_t)));
     CTX_TRY(cudaMalloc(&c->d_counts, N * sizeof(uint32_t)));
     CTX_TRY(cudaMemsetAsync(c->d_counts, 0, N * sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_status, sizeof(int)));
@@ -381,19 +458,25 @@ int pink_b200_destroy(pink_b200_ctx* c)
     cudaSetDevice(c->cfg.device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->copy_stream) cudaStreamSynchronize(c->copy_stream);
+    if (c->rot_stream) cudaStreamSynchronize(c->rot_stream);
     if (c->comm && nccl().ok) nccl().CommDestroy(c->comm);
     free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
     free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_base);
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
+    free_dev(c->d_active); free_dev(c->d_tactive); free_dev(c->d_factive); free_dev(c->d_nactive);
     free_dev(c->d_pairs); free_dev(c->d_counts); free_dev(c->d_bmu_log); free_dev(c->d_status);
     free_dev(c->d_images[0]); free_dev(c->d_images[1]); free_dev(c->d_dist); free_dev(c->d_rot);
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
+    for (cudaEvent_t e : c->prof_rot_events) cudaEventDestroy(e);
     for (int i = 0; i < 2; ++i) {
         if (c->copied[i]) cudaEventDestroy(c->copied[i]);
         if (c->consumed[i]) cudaEventDestroy(c->consumed[i]);
+        if (c->rotated[i]) cudaEventDestroy(c->rotated[i]);
+        if (c->rot_free[i]) cudaEventDestroy(c->rot_free[i]);
     }
     if (c->stream) cudaStreamDestroy(c->stream);
     if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
+    if (c->rot_stream && c->rot_stream != c->stream) cudaStreamDestroy(c->rot_stream);
     delete c;
     return PINK_B200_OK;
 }
@@ -482,10 +565,8 @@ int pink_b200_train_device(pink_b200_ctx* c, const float* dev_images, uint64_t n
     CU_TRY(cudaSetDevice(c->cfg.device));
     int rc = train_prepare(c, n);
     if (rc) return rc;
-    for (uint64_t i = 0; i < n; ++i) {
-        rc = train_one(c, dev_images + i * c->image_size(), c->d_bmu_log + i);
-        if (rc) return rc;
-    }
+    rc = train_chunk(c, dev_images, n, c->d_bmu_log, nullptr);
+    if (rc) return rc;
     CU_TRY(cudaGetLastError());
     return PINK_B200_OK;
 }
@@ -508,11 +589,8 @@ int pink_b200_train(pink_b200_ctx* c, const float* host_images, uint64_t n)
         CU_TRY(cudaMemcpyAsync(c->d_images[buf], host_images + done * isz, m * isz * sizeof(float),
                                cudaMemcpyHostToDevice, c->copy_stream));
         CU_TRY(cudaEventRecord(c->copied[buf], c->copy_stream));
-        CU_TRY(cudaStreamWaitEvent(c->stream, c->copied[buf], 0));
-        for (uint64_t i = 0; i < m; ++i) {
-            rc = train_one(c, c->d_images[buf] + i * isz, c->d_bmu_log + done + i);
-            if (rc) return rc;
-        }
+        rc = train_chunk(c, c->d_images[buf], m, c->d_bmu_log + done, c->copied[buf]);
+        if (rc) return rc;
         CU_TRY(cudaEventRecord(c->consumed[buf], c->stream));
         done += m;
     }
@@ -620,6 +698,7 @@ int pink_b200_synchronize(pink_b200_ctx* c)
     if (!c) return fail(PINK_B200_EINVAL, "null context");
     CU_TRY(cudaSetDevice(c->cfg.device));
     CU_TRY(cudaStreamSynchronize(c->copy_stream));
+    CU_TRY(cudaStreamSynchronize(c->rot_stream));
     return check_status(c);
 }
 
@@ -629,13 +708,18 @@ int pink_b200_profile_begin(pink_b200_ctx* c, uint32_t max_steps)
 {
     if (!c) return fail(PINK_B200_EINVAL, "null context");
     CU_TRY(cudaSetDevice(c->cfg.device));
-    while (c->prof_events.size() < (size_t)5 * max_steps) {
+    while (c->prof_events.size() < (size_t)4 * max_steps) {
         cudaEvent_t e;
         CU_TRY(cudaEventCreate(&e));
         c->prof_events.push_back(e);
     }
+    while (c->prof_rot_events.size() < (size_t)2 * (max_steps / kRotBatch + 2)) {
+        cudaEvent_t e;
+        CU_TRY(cudaEventCreate(&e));
+        c->prof_rot_events.push_back(e);
+    }
     c->prof_cap = max_steps;
-    c->prof_used = 0;
+    c->prof_used = c->prof_rot_used = 0;
     return PINK_B200_OK;
 }
 
@@ -644,15 +728,21 @@ int pink_b200_profile_end(pink_b200_ctx* c, double ms_sum[4], uint64_t* steps)
     if (!c || !ms_sum || !steps) return fail(PINK_B200_EINVAL, "null argument");
     CU_TRY(cudaSetDevice(c->cfg.device));
     CU_TRY(cudaStreamSynchronize(c->stream));
+    CU_TRY(cudaStreamSynchronize(c->rot_stream));
     for (int k = 0; k < 4; ++k) ms_sum[k] = 0.0;
+    for (size_t s = 0; s < c->prof_rot_used; ++s) {
+        float ms = 0.f;
+        CU_TRY(cudaEventElapsedTime(&ms, c->prof_rot_events[2 * s], c->prof_rot_events[2 * s + 1]));
+        ms_sum[0] += ms;
+    }
     for (size_t s = 0; s < c->prof_used; ++s)
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < 3; ++k) {
             float ms = 0.f;
-            CU_TRY(cudaEventElapsedTime(&ms, c->prof_events[5 * s + k], c->prof_events[5 * s + k + 1]));
-            ms_sum[k] += ms;
+            CU_TRY(cudaEventElapsedTime(&ms, c->prof_events[4 * s + k], c->prof_events[4 * s + k + 1]));
+            ms_sum[k + 1] += ms;
         }
     *steps = c->prof_used;
-    c->prof_cap = c->prof_used = 0;
+    c->prof_cap = c->prof_used = c->prof_rot_used = 0;
     return PINK_B200_OK;
 }
 

@@ -83,30 +83,23 @@ __device__ __forceinline__ Acc block_sum(Acc v, Acc* scratch)
     return r;   // valid in thread 0
 }
 
-// Source coordinate inside the base rotation of pixel (x, y) of transform
-// (flip f, quadrant j):  flip is a row reversal applied last
+// Transform (flip f, quadrant j) reads pixel (x, y) from the base rotation at
+// an affine position: flip is a row reversal applied last
 // (src/CudaLib/flip_kernel.h:28); one quarter turn maps (x, y) <- (nd-1-y, x)
 // (src/CudaLib/rotate_90_degrees_list.h:28).
-__device__ __forceinline__ void base_coord(uint32_t nd, uint32_t f, uint32_t j, uint32_t x, uint32_t y,
-                                           uint32_t& bx, uint32_t& by)
-{
-    if (f) x = nd - 1 - x;
-    switch (j) {
-        case 0: bx = x; by = y; break;
-        case 1: bx = nd - 1 - y; by = x; break;
-        case 2: bx = nd - 1 - x; by = nd - 1 - y; break;
-        default: bx = y; by = nd - 1 - x; break;
-    }
-}
+constexpr int kRotThreads = 512;
+
+// v / d for v * d < 2^32 with magic = floor(2^32 / d) + 1 (checked on the host).
+__device__ __forceinline__ uint32_t fast_div(uint32_t v, uint32_t magic) { return __umulhi(v, magic); }
 
 template <int MODE>
-__global__ void __launch_bounds__(256)
-rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem,
+__global__ void __launch_bounds__(kRotThreads)
+rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, uint32_t magic_nd, uint32_t magic_ed,
               const float* __restrict__ cs, const float* __restrict__ sn, float* __restrict__ base_out,
               void* __restrict__ b0, void* __restrict__ b1, void* __restrict__ bnorm)
 {
     extern __shared__ __align__(16) float base_s[];
-    __shared__ unsigned long long red[8];
+    __shared__ unsigned long long norm_s[8];
 
     const uint32_t tq = blockIdx.x, img_i = blockIdx.y;
     const uint32_t nbase = g.q ? g.q : 1;
@@ -114,14 +107,15 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem,
     const float* img = images + (size_t)img_i * g.C * g.id * g.id;
     float* gbase = base_out + ((size_t)img_i * nbase + tq) * g.P;
     const float* stage = use_smem ? base_s : gbase;
+    if (threadIdx.x < 8) norm_s[threadIdx.x] = 0;
 
     // Phase 1: the base rotation (quadrant 0, no flip) of all channels.
     {
         const float sc = (g.id - 1) * 0.5f, dc = (g.nd - 1) * 0.5f, lim = (float)(g.id - 1);
         const float ca = tq ? cs[tq] : 1.0f, sa = tq ? sn[tq] : 0.0f;
-        for (uint32_t idx = threadIdx.x; idx < g.P; idx += blockDim.x) {
-            uint32_t c = idx / P1, r = idx - c * P1;
-            uint32_t x = r / g.nd, y = r - x * g.nd;
+        for (uint32_t idx = threadIdx.x; idx < g.P; idx += kRotThreads) {
+            const uint32_t row = fast_div(idx, magic_nd), y = idx - row * g.nd;     // row = c * nd + x
+            const uint32_t c = fast_div(row, magic_nd), x = row - c * g.nd;
             const float* plane = img + (size_t)c * g.id * g.id;
             float v = tq == 0 ? resize_pixel(plane, g.id, g.nd, x, y)
                               : bilinear_pixel(plane, g.id, sc, dc, lim, ca, sa, x, y);
@@ -131,27 +125,39 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem,
     }
     __syncthreads();   // also orders this block's global writes before its own reads below
 
-    // Phase 2: operand rows of every transform derived from this base.
+    // Phase 2: operand rows of every transform derived from this base.  A
+    // thread packs four consecutive operand elements; their source positions
+    // follow the affine map src = c*nd*nd + ax*x + ay*y + a0 of the transform.
     const uint32_t nq = g.q ? 4 : 1, nv = nq * (g.flip ? 2 : 1);
-    const uint32_t K1 = g.ed * g.ed;
     const uint32_t groups = (g.K + 3) / 4;
+    const int32_t nd = (int32_t)g.nd, nd1 = nd - 1;
     for (uint32_t v = 0; v < nv; ++v) {
         const uint32_t f = v / nq, j = v - f * nq;
         const uint32_t t = f * g.R + j * g.q + tq;
         const size_t row = (size_t)img_i * g.T + t;
+        int32_t ax, ay, a0;
+        switch (j) {
+            case 0:  ax = f ? -nd : nd; ay = 1;   a0 = f ? nd1 * nd : 0; break;
+            case 1:  ax = f ? -1 : 1;   ay = -nd; a0 = nd1 * nd + (f ? nd1 : 0); break;
+            case 2:  ax = f ? nd : -nd; ay = -1;  a0 = f ? nd1 : nd1 * nd + nd1; break;
+            default: ax = f ? 1 : -1;   ay = nd;  a0 = f ? 0 : nd1; break;
+        }
+        a0 += (ax + ay) * (int32_t)g.off;            // x = off + i, y = off + jj
         unsigned long long acc = 0;
-        for (uint32_t k4 = threadIdx.x; k4 < groups; k4 += blockDim.x) {
+        for (uint32_t k4 = threadIdx.x; k4 < groups; k4 += kRotThreads) {
+            const uint32_t k = k4 * 4;
+            uint32_t r = fast_div(k, magic_ed), jj = k - r * g.ed;                  // r = c * ed + i
+            uint32_t c = fast_div(r, magic_ed), i = r - c * g.ed;
+            int32_t s = (int32_t)(c * P1) + ax * (int32_t)i + ay * (int32_t)jj + a0;
             float val[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                uint32_t k = k4 * 4 + e;
-                val[e] = 0.0f;
-                if (k < g.K) {
-                    uint32_t c = k / K1, r = k - c * K1;
-                    uint32_t i = r / g.ed, jj = r - i * g.ed;
-                    uint32_t bx, by;
-                    base_coord(g.nd, f, j, g.off + i, g.off + jj, bx, by);
-                    val[e] = stage[c * P1 + bx * g.nd + by];
+                val[e] = k + e < g.K ? stage[s] : 0.0f;
+                ++jj; s += ay;
+                if (jj == g.ed) {
+                    jj = 0; ++i;
+                    if (i == g.ed) { i = 0; ++c; }
+                    s = (int32_t)(c * P1) + ax * (int32_t)i + a0;
                 }
             }
             if (MODE == kModeU8) {
@@ -173,11 +179,17 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem,
             }
         }
         if (MODE != kModeF32) {
-            unsigned long long s = block_sum<unsigned long long>(acc, red);
-            if (threadIdx.x == 0) {
-                if (MODE == kModeU8) static_cast<uint32_t*>(bnorm)[row] = (uint32_t)s;
-                else static_cast<unsigned long long*>(bnorm)[row] = s;
-            }
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+            if ((threadIdx.x & 31) == 0) atomicAdd(&norm_s[v], acc);
+        }
+    }
+    if (MODE != kModeF32) {
+        __syncthreads();
+        if (threadIdx.x < nv) {
+            const uint32_t v = threadIdx.x, f = v / nq, j = v - f * nq;
+            const size_t row = (size_t)img_i * g.T + f * g.R + j * g.q + tq;
+            if (MODE == kModeU8) static_cast<uint32_t*>(bnorm)[row] = (uint32_t)norm_s[v];
+            else static_cast<unsigned long long*>(bnorm)[row] = norm_s[v];
         }
     }
 }
@@ -260,8 +272,11 @@ cudaError_t rotate_dispatch(const Geometry& g, const float* images, uint32_t n_i
         attr_dev = dev;
         attr_bytes = smem;
     }
+    if ((uint64_t)g.P * g.nd >= (1ull << 32) || (uint64_t)g.K * g.ed >= (1ull << 32)) return cudaErrorInvalidValue;
+    const uint32_t magic_nd = (uint32_t)((1ull << 32) / g.nd) + 1, magic_ed = (uint32_t)((1ull << 32) / g.ed) + 1;
     dim3 grid(g.q ? g.q : 1, n_img);
-    rotate_kernel<MODE><<<grid, 256, smem, st>>>(g, images, use_smem, cs, sn, base_out, b0, b1, bnorm);
+    rotate_kernel<MODE><<<grid, kRotThreads, smem, st>>>(g, images, use_smem, magic_nd, magic_ed, cs, sn, base_out,
+                                                         b0, b1, bnorm);
     return cudaGetLastError();
 }
 

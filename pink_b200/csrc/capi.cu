@@ -154,8 +154,6 @@ struct pink_b200_ctx
     void *d_b0 = nullptr, *d_b1 = nullptr, *d_bnorm = nullptr; size_t b_imgs = 0;
     unsigned long long* d_keys = nullptr; size_t key_imgs = 0;
     BmuPair* d_pairs = nullptr;
-    uint32_t *d_active = nullptr, *d_tactive = nullptr, *d_nactive = nullptr;
-    float* d_factive = nullptr;
     uint32_t* d_counts = nullptr;
     uint32_t* d_bmu_log = nullptr; size_t bmu_log_cap = 0, bmu_log_n = 0;
     int* d_status = nullptr;
@@ -256,23 +254,17 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     if (ev) CU_TRY(cudaEventRecord(ev[1], c->stream));
     BmuArgs ba{};
     ba.keys = c->d_keys; ba.n = c->count; ba.first_neuron = c->first; ba.shift = key_shift(g.mode);
-    ba.pairs = c->d_pairs; ba.rank = c->cfg.rank; ba.world = c->cfg.world_size;
-    ba.factors = c->d_factors;
-    ba.active = c->d_active; ba.f_active = c->d_factive; ba.t_active = c->d_tactive; ba.n_active = c->d_nactive;
-    ba.counts = c->d_counts; ba.bmu_log = bmu_slot;
-    if (c->cfg.world_size == 1) {
-        LAUNCH_TRY(launch_bmu(ba, 3, c->stream));
-    } else {
-        LAUNCH_TRY(launch_bmu(ba, 1, c->stream));
+    ba.out = c->d_pairs + c->cfg.rank;
+    LAUNCH_TRY(launch_bmu(ba, c->stream));
+    if (c->cfg.world_size > 1)
         NCCL_TRY(nccl().AllGather(c->d_pairs + c->cfg.rank, c->d_pairs, 2, ncclUint64, c->comm, c->stream));
-        LAUNCH_TRY(launch_bmu(ba, 2, c->stream));
-    }
     UpdateArgs ua{};
     ua.som = c->d_som;
     ua.base = c->d_base + slot_img * (g.q ? g.q : 1) * (size_t)g.P;
-    ua.active = c->d_active; ua.f_active = c->d_factive; ua.t_active = c->d_tactive; ua.n_active = c->d_nactive;
-    ua.n = c->count;
+    ua.keys = c->d_keys; ua.pairs = c->d_pairs; ua.world = c->cfg.world_size;
+    ua.factors = c->d_factors; ua.n = c->count; ua.first_neuron = c->first;
     ua.a0 = c->d_a0; ua.a1 = c->d_a1; ua.anorm = c->d_anorm;
+    ua.counts = c->d_counts; ua.bmu_log = bmu_slot;
     if (ev) CU_TRY(cudaEventRecord(ev[2], c->stream));
     LAUNCH_TRY(launch_update(g, ua, c->stream));
     if (ev) CU_TRY(cudaEventRecord(ev[3], c->stream));
@@ -418,12 +410,6 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     CTX_TRY(cudaMalloc(&c->d_anorm, norm_bytes(g, c->count)));
     CTX_TRY(cudaMalloc(&c->d_pairs, W * sizeof(BmuPair)));
     CTX_TRY(cudaMemsetAsync(c->d_pairs, 0xFF, W * sizeof(BmuPair), c->stream));
-    CTX_TRY(cudaMalloc(&c->d_active, c->count * sizeof(uint32_t)));
-    CTX_TRY(cudaMemsetAsync(c->d_active, 0, c->count * sizeof(uint32_t), c->stream));
-    CTX_TRY(cudaMalloc(&c->d_tactive, c->count * sizeof(uint32_t)));
-    CTX_TRY(cudaMemsetAsync(c->d_tactive, 0, c->count * sizeof(uint32_t), c->stream));
-    CTX_TRY(cudaMalloc(&c->d_factive, c->count * sizeof(float)));
-    CTX_TRY(cudaMalloc(&c->d_nactive, sizeof(uint32_t)));
     CTX_TRY(cudaMalloc(&c->d_counts, N * sizeof(uint32_t)));
     CTX_TRY(cudaMemsetAsync(c->d_counts, 0, N * sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_status, sizeof(int)));
@@ -463,7 +449,6 @@ int pink_b200_destroy(pink_b200_ctx* c)
     free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
     free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_base);
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
-    free_dev(c->d_active); free_dev(c->d_tactive); free_dev(c->d_factive); free_dev(c->d_nactive);
     free_dev(c->d_pairs); free_dev(c->d_counts); free_dev(c->d_bmu_log); free_dev(c->d_status);
     free_dev(c->d_images[0]); free_dev(c->d_images[1]); free_dev(c->d_dist); free_dev(c->d_rot);
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);

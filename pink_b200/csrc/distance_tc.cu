@@ -39,8 +39,8 @@ constexpr uint32_t kUmmaK = 32;            // K per kind::i8 instruction
 constexpr uint32_t kThreads = 192;
 
 template <int MODE> struct TcCfg;
-template <> struct TcCfg<kModeU8>  { static constexpr uint32_t planes = 1, max_n = 256, stages = 4, accs = 1, cols = 256; };
-template <> struct TcCfg<kModeU16> { static constexpr uint32_t planes = 2, max_n = 128, stages = 3, accs = 3, cols = 512; };
+template <> struct TcCfg<kModeU8>  { static constexpr uint32_t planes = 1, max_n = 256, stages = 4, cols = 256; };
+template <> struct TcCfg<kModeU16> { static constexpr uint32_t planes = 2, max_n = 128, stages = 3, cols = 512; };
 
 template <int MODE>
 struct SmemLayout

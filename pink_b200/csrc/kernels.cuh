@@ -68,25 +68,24 @@ cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream
 // ---- best matching unit -----------------------------------------------------
 struct BmuArgs
 {
-    unsigned long long* keys; uint32_t n, first_neuron, shift;   // this shard's per-neuron minima (re-armed in phase 2)
-    BmuPair* pairs; uint32_t rank, world;                              // per-rank records (world entries)
-    const float* factors;             // [N_global][n] update factors, column = local neuron
-    uint32_t* active; float* f_active; uint32_t* t_active; uint32_t* n_active;   // compacted neurons to update:
-                                      // local index, update factor, best transform; and their number
-    uint32_t* counts;                 // [N_global] BMU hit counters (incremented by the owner)
-    uint32_t* bmu_log;                // nullable: receives the global BMU index of this step
+    const unsigned long long* keys; uint32_t n, first_neuron, shift;   // this shard's per-neuron minima
+    BmuPair* out;                                                       // this rank's record
 };
-// phase 1: local reduction -> pairs[rank]; phase 2: global selection + active list; 3: both.
-cudaError_t launch_bmu(const BmuArgs& a, uint32_t phase, cudaStream_t st);
+// Reduces keys[0..n) to the shard's (code, first_neuron + argmin) record.
+cudaError_t launch_bmu(const BmuArgs& a, cudaStream_t st);
 
 // ---- neighbourhood update ---------------------------------------------------
 struct UpdateArgs
 {
     float* som;                       // [n][Pp]
     const float* base;                // [max(q,1)][C][nd][nd] base rotations of the current image
-    const uint32_t* active; const float* f_active; const uint32_t* t_active; const uint32_t* n_active;
-    uint32_t n;                       // blocks to launch = local neurons
+    unsigned long long* keys;         // [n]; read, then re-armed to kKeyEmpty
+    const BmuPair* pairs; uint32_t world;   // per-rank BMU records (world entries)
+    const float* factors;             // [N_global][n] update factors, column = local neuron
+    uint32_t n, first_neuron;
     void* a0; void* a1; void* anorm;  // SOM operand rows to refresh
+    uint32_t* counts;                 // [N_global] BMU hit counters (incremented by the owner)
+    uint32_t* bmu_log;                // nullable: receives the global BMU index of this step
 };
 cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st);
 

@@ -46,27 +46,6 @@ __device__ __forceinline__ float resize_pixel(const float* __restrict__ img, uin
     return __ldg(img + (size_t)(x - m) * id + (y - m));
 }
 
-// Bilinear sample of the inverse-rotated position (CPU rounding order).
-__device__ __forceinline__ float bilinear_pixel(const float* __restrict__ img, uint32_t id, float sc, float dc,
-                                                float lim, float ca, float sa, uint32_t x, uint32_t y)
-{
-    float px = __fsub_rn((float)x, dc);
-    float py = __fsub_rn((float)y, dc);
-    float sx = __fadd_rn(__fsub_rn(__fmul_rn(px, ca), __fmul_rn(py, sa)), sc);
-    float sy = __fadd_rn(__fadd_rn(__fmul_rn(px, sa), __fmul_rn(py, ca)), sc);
-    if (sx < 0.0f || sx > lim || sy < 0.0f || sy > lim) return 0.0f;
-    uint32_t ix = (uint32_t)sx, iy = (uint32_t)sy;
-    // The +1 taps carry weight 0 when they would fall outside; clamp the index.
-    uint32_t ix1 = min(ix + 1, id - 1), iy1 = min(iy + 1, id - 1);
-    float rx = __fsub_rn(sx, (float)ix), ry = __fsub_rn(sy, (float)iy);
-    float cx = __fsub_rn(1.0f, rx), cy = __fsub_rn(1.0f, ry);
-    float a = __fmul_rn(__fmul_rn(cx, cy), __ldg(img + (size_t)ix * id + iy));
-    float b = __fmul_rn(__fmul_rn(cx, ry), __ldg(img + (size_t)ix * id + iy1));
-    float c = __fmul_rn(__fmul_rn(rx, cy), __ldg(img + (size_t)ix1 * id + iy));
-    float d = __fmul_rn(__fmul_rn(rx, ry), __ldg(img + (size_t)ix1 * id + iy1));
-    return __fadd_rn(__fadd_rn(__fadd_rn(a, b), c), d);
-}
-
 template <typename Acc>
 __device__ __forceinline__ Acc block_sum(Acc v, Acc* scratch)
 {
@@ -87,18 +66,45 @@ __device__ __forceinline__ Acc block_sum(Acc v, Acc* scratch)
 // an affine position: flip is a row reversal applied last
 // (src/CudaLib/flip_kernel.h:28); one quarter turn maps (x, y) <- (nd-1-y, x)
 // (src/CudaLib/rotate_90_degrees_list.h:28).
-constexpr int kRotThreads = 512;
+constexpr int kRotThreads = 256;
 
 // v / d for v * d < 2^32 with magic = floor(2^32 / d) + 1 (checked on the host).
-__device__ __forceinline__ uint32_t fast_div(uint32_t v, uint32_t magic) { return __umulhi(v, magic); }
+// magic == 0 encodes the divisor 1.
+__device__ __forceinline__ uint32_t fast_div(uint32_t v, uint32_t magic) { return magic ? __umulhi(v, magic) : v; }
+inline uint32_t div_magic(uint32_t d) { return d == 1 ? 0u : (uint32_t)((1ull << 32) / d) + 1; }
 
+template <int MODE> struct StageType;
+template <> struct StageType<kModeU8>  { using type = uint8_t; };
+template <> struct StageType<kModeU16> { using type = uint16_t; };
+template <> struct StageType<kModeF32> { using type = float; };
+
+template <int MODE>
+__device__ __forceinline__ typename StageType<MODE>::type to_stage(float v)
+{
+    if (MODE == kModeU8) return (typename StageType<MODE>::type)quant_u8(v);
+    if (MODE == kModeU16) return (typename StageType<MODE>::type)quant_u16(v);
+    return (typename StageType<MODE>::type)v;
+}
+
+// One block = one base rotation of one image.
+// Phase 1 walks the neuron-sized output row by row (a warp per row, lanes along
+// the row) so that the row terms of the inverse rotation are computed once per
+// row; the float pixel goes to global memory (the update step reads it) and its
+// converted value (uint8 / uint16 / float) is staged in shared memory.
+// Phase 2 emits, for each of the up to eight transforms that are index
+// permutations of this base, the K-contiguous operand row: a thread gathers 16
+// consecutive operand elements from the staged plane along the transform's
+// affine source map, packs them and stores 16 bytes per plane; sums of squares
+// use dp4a on the packed bytes.
 template <int MODE>
 __global__ void __launch_bounds__(kRotThreads)
 rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, uint32_t magic_nd, uint32_t magic_ed,
               const float* __restrict__ cs, const float* __restrict__ sn, float* __restrict__ base_out,
               void* __restrict__ b0, void* __restrict__ b1, void* __restrict__ bnorm)
 {
-    extern __shared__ __align__(16) float base_s[];
+    using stage_t = typename StageType<MODE>::type;
+    extern __shared__ __align__(16) uint8_t rot_dyn[];
+    stage_t* stage = reinterpret_cast<stage_t*>(rot_dyn);
     __shared__ unsigned long long norm_s[8];
 
     const uint32_t tq = blockIdx.x, img_i = blockIdx.y;
@@ -106,35 +112,62 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
     const uint32_t P1 = g.nd * g.nd;
     const float* img = images + (size_t)img_i * g.C * g.id * g.id;
     float* gbase = base_out + ((size_t)img_i * nbase + tq) * g.P;
-    const float* stage = use_smem ? base_s : gbase;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x < 8) norm_s[threadIdx.x] = 0;
 
     // Phase 1: the base rotation (quadrant 0, no flip) of all channels.
     {
         const float sc = (g.id - 1) * 0.5f, dc = (g.nd - 1) * 0.5f, lim = (float)(g.id - 1);
         const float ca = tq ? cs[tq] : 1.0f, sa = tq ? sn[tq] : 0.0f;
-        for (uint32_t idx = threadIdx.x; idx < g.P; idx += kRotThreads) {
-            const uint32_t row = fast_div(idx, magic_nd), y = idx - row * g.nd;     // row = c * nd + x
+        const uint32_t rows = g.C * g.nd;
+        for (uint32_t row = warp; row < rows; row += kRotThreads / 32) {
             const uint32_t c = fast_div(row, magic_nd), x = row - c * g.nd;
             const float* plane = img + (size_t)c * g.id * g.id;
-            float v = tq == 0 ? resize_pixel(plane, g.id, g.nd, x, y)
-                              : bilinear_pixel(plane, g.id, sc, dc, lim, ca, sa, x, y);
-            if (use_smem) base_s[idx] = v;
-            if (base_out) gbase[idx] = v;
+            const float px = __fsub_rn((float)x, dc);
+            const float xc = __fmul_rn(px, ca), xs = __fmul_rn(px, sa);
+            for (uint32_t y = lane; y < g.nd; y += 32) {
+                float v;
+                if (tq == 0) {
+                    v = resize_pixel(plane, g.id, g.nd, x, y);
+                } else {
+                    // inverse rotation and bilinear taps; every product and sum rounded
+                    // separately, in the order of src/ImageProcessingLib/rotate.h:37-63
+                    const float py = __fsub_rn((float)y, dc);
+                    const float sx = __fadd_rn(__fsub_rn(xc, __fmul_rn(py, sa)), sc);
+                    const float sy = __fadd_rn(__fadd_rn(xs, __fmul_rn(py, ca)), sc);
+                    v = 0.0f;
+                    if (!(sx < 0.0f || sx > lim || sy < 0.0f || sy > lim)) {
+                        const uint32_t ix = (uint32_t)sx, iy = (uint32_t)sy;
+                        // the +1 taps carry weight 0 when they would fall outside; clamp the index
+                        const uint32_t ix1 = min(ix + 1, g.id - 1), iy1 = min(iy + 1, g.id - 1);
+                        const float rx = __fsub_rn(sx, (float)ix), ry = __fsub_rn(sy, (float)iy);
+                        const float cx = __fsub_rn(1.0f, rx), cy = __fsub_rn(1.0f, ry);
+                        const float* r0 = plane + (size_t)ix * g.id;
+                        const float* r1 = plane + (size_t)ix1 * g.id;
+                        const float t00 = __fmul_rn(__fmul_rn(cx, cy), __ldg(r0 + iy));
+                        const float t01 = __fmul_rn(__fmul_rn(cx, ry), __ldg(r0 + iy1));
+                        const float t10 = __fmul_rn(__fmul_rn(rx, cy), __ldg(r1 + iy));
+                        const float t11 = __fmul_rn(__fmul_rn(rx, ry), __ldg(r1 + iy1));
+                        v = __fadd_rn(__fadd_rn(__fadd_rn(t00, t01), t10), t11);
+                    }
+                }
+                const uint32_t idx = row * g.nd + y;
+                if (use_smem) stage[idx] = to_stage<MODE>(v);
+                if (base_out) gbase[idx] = v;
+            }
         }
     }
     __syncthreads();   // also orders this block's global writes before its own reads below
 
-    // Phase 2: operand rows of every transform derived from this base.  A
-    // thread packs four consecutive operand elements; their source positions
-    // follow the affine map src = c*nd*nd + ax*x + ay*y + a0 of the transform.
+    // Phase 2: operand rows of every transform derived from this base.
     const uint32_t nq = g.q ? 4 : 1, nv = nq * (g.flip ? 2 : 1);
-    const uint32_t groups = (g.K + 3) / 4;
+    constexpr uint32_t kGroup = MODE == kModeF32 ? 4 : 16;         // operand elements per thread and store
+    const uint32_t groups = (g.K + kGroup - 1) / kGroup;
     const int32_t nd = (int32_t)g.nd, nd1 = nd - 1;
     for (uint32_t v = 0; v < nv; ++v) {
         const uint32_t f = v / nq, j = v - f * nq;
         const uint32_t t = f * g.R + j * g.q + tq;
-        const size_t row = (size_t)img_i * g.T + t;
+        const size_t orow = (size_t)img_i * g.T + t;
         int32_t ax, ay, a0;
         switch (j) {
             case 0:  ax = f ? -nd : nd; ay = 1;   a0 = f ? nd1 * nd : 0; break;
@@ -144,15 +177,16 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
         }
         a0 += (ax + ay) * (int32_t)g.off;            // x = off + i, y = off + jj
         unsigned long long acc = 0;
-        for (uint32_t k4 = threadIdx.x; k4 < groups; k4 += kRotThreads) {
-            const uint32_t k = k4 * 4;
+        for (uint32_t gi = threadIdx.x; gi < groups; gi += kRotThreads) {
+            const uint32_t k = gi * kGroup;
             uint32_t r = fast_div(k, magic_ed), jj = k - r * g.ed;                  // r = c * ed + i
             uint32_t c = fast_div(r, magic_ed), i = r - c * g.ed;
             int32_t s = (int32_t)(c * P1) + ax * (int32_t)i + ay * (int32_t)jj + a0;
-            float val[4];
+            stage_t val[kGroup];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                val[e] = k + e < g.K ? stage[s] : 0.0f;
+            for (uint32_t e = 0; e < kGroup; ++e) {
+                val[e] = 0;
+                if (k + e < g.K) val[e] = use_smem ? stage[s] : to_stage<MODE>(gbase[s]);
                 ++jj; s += ay;
                 if (jj == g.ed) {
                     jj = 0; ++i;
@@ -161,35 +195,46 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
                 }
             }
             if (MODE == kModeU8) {
-                uint32_t q0 = quant_u8(val[0]), q1 = quant_u8(val[1]), q2 = quant_u8(val[2]), q3 = quant_u8(val[3]);
-                acc += q0 * q0 + q1 * q1 + q2 * q2 + q3 * q3;
-                reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(b0) + row * g.Kp)[k4] =
-                    q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+                uint32_t wv[4];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    wv[q4] = (uint32_t)val[4 * q4] | ((uint32_t)val[4 * q4 + 1] << 8)
+                           | ((uint32_t)val[4 * q4 + 2] << 16) | ((uint32_t)val[4 * q4 + 3] << 24);
+                    acc += __dp4a(wv[q4], wv[q4], 0u);
+                }
+                reinterpret_cast<uint4*>(static_cast<uint8_t*>(b0) + orow * g.Kp)[gi] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
             } else if (MODE == kModeU16) {
-                uint32_t q0 = quant_u16(val[0]), q1 = quant_u16(val[1]), q2 = quant_u16(val[2]), q3 = quant_u16(val[3]);
-                acc += (unsigned long long)q0 * q0 + (unsigned long long)q1 * q1
-                     + (unsigned long long)q2 * q2 + (unsigned long long)q3 * q3;
-                reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(b0) + row * g.Kp)[k4] =
-                    (q0 >> 8) | ((q1 >> 8) << 8) | ((q2 >> 8) << 16) | ((q3 >> 8) << 24);
-                reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(b1) + row * g.Kp)[k4] =
-                    (q0 & 255) | ((q1 & 255) << 8) | ((q2 & 255) << 16) | ((q3 & 255) << 24);
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    hi[q4] = lo[q4] = 0;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t qv = (uint32_t)val[4 * q4 + e];
+                        hi[q4] |= (qv >> 8) << (8 * e);
+                        lo[q4] |= (qv & 255u) << (8 * e);
+                        acc += (unsigned long long)qv * qv;
+                    }
+                }
+                reinterpret_cast<uint4*>(static_cast<uint8_t*>(b0) + orow * g.Kp)[gi] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                reinterpret_cast<uint4*>(static_cast<uint8_t*>(b1) + orow * g.Kp)[gi] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             } else {
-                reinterpret_cast<float4*>(static_cast<float*>(b0) + row * g.Kp)[k4] =
-                    make_float4(val[0], val[1], val[2], val[3]);
+                reinterpret_cast<float4*>(static_cast<float*>(b0) + orow * g.Kp)[gi] =
+                    make_float4((float)val[0], (float)val[1], (float)val[2], (float)val[3]);
             }
         }
         if (MODE != kModeF32) {
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
-            if ((threadIdx.x & 31) == 0) atomicAdd(&norm_s[v], acc);
+            if (lane == 0) atomicAdd(&norm_s[v], acc);
         }
     }
     if (MODE != kModeF32) {
         __syncthreads();
         if (threadIdx.x < nv) {
             const uint32_t v = threadIdx.x, f = v / nq, j = v - f * nq;
-            const size_t row = (size_t)img_i * g.T + f * g.R + j * g.q + tq;
-            if (MODE == kModeU8) static_cast<uint32_t*>(bnorm)[row] = (uint32_t)norm_s[v];
-            else static_cast<unsigned long long*>(bnorm)[row] = norm_s[v];
+            const size_t orow = (size_t)img_i * g.T + f * g.R + j * g.q + tq;
+            if (MODE == kModeU8) static_cast<uint32_t*>(bnorm)[orow] = (uint32_t)norm_s[v];
+            else static_cast<unsigned long long*>(bnorm)[orow] = norm_s[v];
         }
     }
 }
@@ -258,7 +303,7 @@ template <int MODE>
 cudaError_t rotate_dispatch(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
                      float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st)
 {
-    size_t smem = (size_t)g.P * sizeof(float);
+    size_t smem = (size_t)g.P * sizeof(typename StageType<MODE>::type);
     uint32_t use_smem = smem <= kRotateSmemLimit;
     if (!use_smem) smem = 0;
     // Dynamic shared memory above 48 KB is an opt-in, per-device function attribute.
@@ -273,7 +318,7 @@ cudaError_t rotate_dispatch(const Geometry& g, const float* images, uint32_t n_i
         attr_bytes = smem;
     }
     if ((uint64_t)g.P * g.nd >= (1ull << 32) || (uint64_t)g.K * g.ed >= (1ull << 32)) return cudaErrorInvalidValue;
-    const uint32_t magic_nd = (uint32_t)((1ull << 32) / g.nd) + 1, magic_ed = (uint32_t)((1ull << 32) / g.ed) + 1;
+    const uint32_t magic_nd = div_magic(g.nd), magic_ed = div_magic(g.ed);
     dim3 grid(g.q ? g.q : 1, n_img);
     rotate_kernel<MODE><<<grid, kRotThreads, smem, st>>>(g, images, use_smem, magic_nd, magic_ed, cs, sn, base_out,
                                                          b0, b1, bnorm);

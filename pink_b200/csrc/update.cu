@@ -18,6 +18,7 @@
 #include "kernels.cuh"
 #include "ptx.cuh"
 
+
 namespace pinkb {
 
 namespace {
@@ -60,207 +61,171 @@ __device__ __forceinline__ void block_min_pair(unsigned long long& bc, unsigned 
     }
 }
 
-// One block.  phase bit 0: reduce this shard's keys to its (code, neuron)
-// record; phase bit 1: pick the global best matching unit from the per-rank
-// records, count the hit, and compact the shard's neurons whose update factor
-// for that unit is non-zero into (active, f_active, n_active), in ascending
-// neuron order.  A single-GPU step runs both phases in one launch; with
-// several ranks the exchange of the records sits between them.
-__global__ void __launch_bounds__(1024)
-bmu_kernel(BmuArgs a, uint32_t phase)
+constexpr int kBmuThreads = 512;
+constexpr int kBmuPer = 8;            // keys a thread loads per pass, all in flight at once
+
+// One block: first minimum of (code, neuron) over this shard's keys.
+__global__ void __launch_bounds__(kBmuThreads)
+bmu_kernel(BmuArgs a)
 {
     __shared__ unsigned long long sc[32], sn[32];
-    __shared__ uint32_t warp_tot[32];
-    __shared__ uint32_t bmu_s, base_s;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    if (phase & 1u) {
-        unsigned long long bc = ~0ull, bn = ~0ull;
-        for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) {
-            unsigned long long c = a.keys[i] >> a.shift;
-            if (pair_less(c, i, bc, bn)) { bc = c; bn = i; }
+    unsigned long long bc = ~0ull, bn = ~0ull;
+    for (uint32_t p0 = 0; p0 < a.n; p0 += kBmuThreads * kBmuPer) {
+        unsigned long long k[kBmuPer];
+#pragma unroll
+        for (int e = 0; e < kBmuPer; ++e) {
+            const uint32_t i = p0 + e * kBmuThreads + threadIdx.x;
+            k[e] = i < a.n ? a.keys[i] : ~0ull;
         }
-        block_min_pair(bc, bn, sc, sn);
-        if (threadIdx.x == 0) {
-            a.pairs[a.rank].code = bc;
-            a.pairs[a.rank].neuron = bn == ~0ull ? ~0ull : bn + a.first_neuron;
+#pragma unroll
+        for (int e = 0; e < kBmuPer; ++e) {
+            const uint32_t i = p0 + e * kBmuThreads + threadIdx.x;
+            if (i < a.n && pair_less(k[e] >> a.shift, i, bc, bn)) { bc = k[e] >> a.shift; bn = i; }
         }
-        if (!(phase & 2u)) return;
-        __syncthreads();
     }
-
+    block_min_pair(bc, bn, sc, sn);
     if (threadIdx.x == 0) {
+        a.out->code = bc;
+        a.out->neuron = bn == ~0ull ? ~0ull : bn + a.first_neuron;
+    }
+}
+
+constexpr int kUpdThreads = 256;
+constexpr int kUpdWarps = kUpdThreads / 32;
+constexpr int kRowBatch = 12;         // neuron rows a thread keeps in flight (one float each)
+
+// v / d for v * d < 2^32 with magic = floor(2^32 / d) + 1 (ranges checked on the host).
+// magic == 0 encodes the divisor 1.
+__device__ __forceinline__ uint32_t fast_div(uint32_t v, uint32_t magic) { return magic ? __umulhi(v, magic) : v; }
+inline uint32_t div_magic(uint32_t d) { return d == 1 ? 0u : (uint32_t)((1ull << 32) / d) + 1; }
+
+// Per neuron row (over all channels): where the row starts in the base
+// rotation under the neuron's best transform, and where it lands in the
+// distance operand (negative when the row lies outside the distance region).
+struct RowInfo { int32_t src; int32_t kk; };
+
+// One block per neuron of the shard.  The block looks up the best matching
+// unit and its own update factor, leaves at once when the factor is zero, and
+// otherwise walks the neuron in tasks of kRowBatch rows x 32 columns: a thread
+// owns one column of the task, so its global address, its source position in
+// the base rotation and its operand position advance by per-row constants
+// taken from a small shared table, and kRowBatch loads are in flight per
+// thread before anything depends on them.
+template <int MODE>
+__global__ void __launch_bounds__(kUpdThreads, 4)
+update_kernel(Geometry g, UpdateArgs a, uint32_t stage_base, uint32_t magic_nd, uint32_t magic_blocks)
+{
+    extern __shared__ __align__(16) uint8_t dyn[];
+    const uint32_t rows = g.C * g.nd;
+    RowInfo* rowinfo = reinterpret_cast<RowInfo*>(dyn);                                  // [rows]
+    uint8_t* crop_s = dyn + (((size_t)rows * sizeof(RowInfo) + 15) & ~size_t(15));       // operand row(s) being rebuilt
+    const size_t crop_bytes = MODE == kModeF32 ? (size_t)g.Kp * 4 : (MODE == kModeU16 ? (size_t)g.Kp * 2 : g.Kp);
+    float* base_s = reinterpret_cast<float*>(crop_s + ((crop_bytes + 15) & ~size_t(15))); // [P] base rotation
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ unsigned long long red[kUpdWarps];
+    __shared__ uint32_t t_s;
+    __shared__ float f_s;
+
+    const uint32_t n = blockIdx.x;
+    if (threadIdx.x == 0) {
+        // Global best matching unit: lexicographic minimum over the per-rank records.
         unsigned long long bc = a.pairs[0].code, bn = a.pairs[0].neuron;
+        const unsigned long long key = a.keys[n];
         for (uint32_t r = 1; r < a.world; ++r)
             if (pair_less(a.pairs[r].code, a.pairs[r].neuron, bc, bn)) { bc = a.pairs[r].code; bn = a.pairs[r].neuron; }
         const uint32_t bmu = (uint32_t)bn;
-        bmu_s = bmu;
-        base_s = 0;
-        if (bmu >= a.first_neuron && bmu - a.first_neuron < a.n) {      // this rank owns the unit
+        f_s = a.factors[(size_t)bmu * a.n + n];
+        t_s = (uint32_t)(key & ((1ull << key_shift(MODE)) - 1));
+        a.keys[n] = kKeyEmpty;            // re-arm for the next image's distance kernel
+        if (a.first_neuron + n == bmu) {  // the owner counts the hit
             a.counts[bmu] += 1;
             if (a.bmu_log) *a.bmu_log = bmu;
         }
-    }
-    __syncthreads();
-    const float* frow = a.factors + (size_t)bmu_s * a.n;
-    for (uint32_t i0 = 0; i0 < a.n; i0 += blockDim.x) {
-        const uint32_t i = i0 + threadIdx.x;
-        const float f = i < a.n ? frow[i] : 0.0f;
-        const bool on = f != 0.0f;
-        const uint32_t ballot = __ballot_sync(0xffffffffu, on);
-        if (lane == 0) warp_tot[warp] = __popc(ballot);
-        __syncthreads();
-        uint32_t before = base_s;
-        for (int w = 0; w < warp; ++w) before += warp_tot[w];
-        if (i < a.n) {
-            const unsigned long long key = a.keys[i];
-            a.keys[i] = kKeyEmpty;        // re-arm every key for the next image's distance kernel
-            if (on) {
-                const uint32_t slot = before + __popc(ballot & ((1u << lane) - 1));
-                a.active[slot] = i;
-                a.f_active[slot] = f;
-                a.t_active[slot] = (uint32_t)(key & ((1ull << a.shift) - 1));
-            }
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            uint32_t tot = 0;
-            for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) tot += warp_tot[w];
-            base_s += tot;
-        }
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) *a.n_active = base_s;
-}
-
-constexpr int kUpdVec = 8;            // float4 loads a thread keeps in flight
-constexpr int kUpdThreads = 256;
-
-// Flat element index -> (row over all channels, column) with a multiply-high;
-// exact while idx * nd < 2^32 (checked on the host).
-__device__ __forceinline__ uint32_t fast_div(uint32_t v, uint32_t magic) { return __umulhi(v, magic); }
-
-template <int MODE>
-__global__ void __launch_bounds__(kUpdThreads, 3)
-update_kernel(Geometry g, UpdateArgs a, uint32_t stage_base, uint32_t magic_nd)
-{
-    extern __shared__ __align__(16) uint8_t dyn[];
-    float* base_s = reinterpret_cast<float*>(dyn);                       // [P] base rotation (all channels)
-    uint8_t* crop_s = dyn + (stage_base ? (((size_t)g.P * 4 + 15) & ~size_t(15)) : 0);   // operand row(s) being rebuilt
-    __shared__ __align__(8) uint64_t bar;
-    __shared__ unsigned long long red[8];
-    __shared__ uint32_t n_s, t_s, coef_s[4];
-    __shared__ float f_s;
-
-    if (threadIdx.x == 0) {
-        // independent loads; entries beyond n_active are stale but in bounds
-        const uint32_t cnt = *a.n_active, n = a.active[blockIdx.x], t = a.t_active[blockIdx.x];
-        f_s = a.f_active[blockIdx.x];
-        t_s = t;
-        n_s = blockIdx.x < cnt ? n : ~0u;
         mbar_init(&bar, 1);
         mbar_fence_init();
     }
     __syncthreads();
-    const uint32_t n = n_s;
-    if (n == ~0u) return;                 // fewer active neurons than blocks
     const float f = f_s;
-
-    // Everything this block will read from the SOM goes in flight before any
-    // dependent work: kUpdVec 128-bit loads per thread.
-    float* w = a.som + (size_t)n * g.Pp;
-    const uint32_t nvec = g.Pp / 4;
-    float4 v[kUpdVec];
-#pragma unroll
-    for (int u = 0; u < kUpdVec; ++u) {
-        const uint32_t i4 = threadIdx.x + u * kUpdThreads;
-        if (i4 < nvec) v[u] = __ldcs(reinterpret_cast<const float4*>(w) + i4);
-    }
+    if (f == 0.0f) return;                // uniform for the block
 
     // Best transform -> (flip, quadrant, base rotation) and the affine map
     // src = c*nd*nd + ax*x + ay*y + a0 from a neuron pixel (x, y) to the base
     // rotation: flip reverses rows last (src/CudaLib/flip_kernel.h:28), a
     // quarter turn maps (x, y) <- (nd-1-y, x) (src/CudaLib/rotate_90_degrees_list.h:28).
-    if (threadIdx.x == 0) {
-        const uint32_t t = t_s;
-        const uint32_t fl = t / g.R, r = t - fl * g.R;
-        const uint32_t j = g.q ? r / g.q : 0, tq = g.q ? r - j * g.q : 0;
-        const int32_t nd = (int32_t)g.nd, nd1 = nd - 1;
-        int32_t ax, ay, a0;
-        switch (j) {
-            case 0:  ax = fl ? -nd : nd; ay = 1;   a0 = fl ? nd1 * nd : 0; break;
-            case 1:  ax = fl ? -1 : 1;   ay = -nd; a0 = nd1 * nd + (fl ? nd1 : 0); break;
-            case 2:  ax = fl ? nd : -nd; ay = -1;  a0 = fl ? nd1 : nd1 * nd + nd1; break;
-            default: ax = fl ? 1 : -1;   ay = nd;  a0 = fl ? 0 : nd1; break;
-        }
-        coef_s[0] = (uint32_t)ax; coef_s[1] = (uint32_t)ay; coef_s[2] = (uint32_t)a0; coef_s[3] = tq;
-        if (stage_base) {
-            // one bulk asynchronous copy (TMA) of the whole base rotation into shared memory
-            mbar_expect_tx(&bar, g.P * 4);
-            bulk_load(base_s, a.base + (size_t)tq * g.P, g.P * 4, &bar);
-        }
+    const uint32_t t = t_s;
+    const uint32_t fl = t / g.R, r = t - fl * g.R;
+    const uint32_t j = g.q ? r / g.q : 0, tq = g.q ? r - j * g.q : 0;
+    const int32_t nd = (int32_t)g.nd, nd1 = nd - 1;
+    int32_t ax, ay, a0;
+    switch (j) {
+        case 0:  ax = fl ? -nd : nd; ay = 1;   a0 = fl ? nd1 * nd : 0; break;
+        case 1:  ax = fl ? -1 : 1;   ay = -nd; a0 = nd1 * nd + (fl ? nd1 : 0); break;
+        case 2:  ax = fl ? nd : -nd; ay = -1;  a0 = fl ? nd1 : nd1 * nd + nd1; break;
+        default: ax = fl ? 1 : -1;   ay = nd;  a0 = fl ? 0 : nd1; break;
+    }
+    const float* bsrc = a.base + (size_t)tq * g.P;
+    if (stage_base && threadIdx.x == 0) {
+        // one bulk asynchronous copy (TMA) of the whole base rotation into shared memory
+        mbar_expect_tx(&bar, g.P * 4);
+        bulk_load(base_s, bsrc, g.P * 4, &bar);
+    }
+    const uint32_t P1 = g.nd * g.nd, K1 = g.ed * g.ed;
+    for (uint32_t rr = threadIdx.x; rr < rows; rr += kUpdThreads) {
+        const uint32_t c = fast_div(rr, magic_nd), x = rr - c * g.nd;
+        const uint32_t ci = x - g.off;                                   // unsigned wrap rejects x < off
+        rowinfo[rr].src = (int32_t)(c * P1) + ax * (int32_t)x + a0;
+        rowinfo[rr].kk = ci < g.ed ? (int32_t)(c * K1 + ci * g.ed) : -1;
     }
     __syncthreads();
-    const int32_t ax = (int32_t)coef_s[0], ay = (int32_t)coef_s[1], a0 = (int32_t)coef_s[2];
-    const float* bsrc = a.base + (size_t)coef_s[3] * g.P;
-    if (stage_base) {
-        if (!mbar_wait(&bar, 0)) return;  // bounded; cannot expire unless the copy faulted
-        bsrc = base_s;
-    }
 
-    const uint32_t P1 = g.nd * g.nd, K1 = g.ed * g.ed;
+    float* w = a.som + (size_t)n * g.Pp;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t blocks_per_col = (rows + kRowBatch - 1) / kRowBatch;
+    const uint32_t ntask = ((g.nd + 31) / 32) * blocks_per_col;
     unsigned long long acc = 0;
-    for (uint32_t chunk = 0; chunk < nvec; chunk += kUpdVec * kUpdThreads) {
-        if (chunk) {
+    bool staged = false;
+    for (uint32_t task = warp; task < ntask; task += kUpdWarps) {
+        const uint32_t col = fast_div(task, magic_blocks), row0 = (task - col * blocks_per_col) * kRowBatch;
+        const uint32_t y = col * 32 + lane;
+        const bool valid = y < g.nd;
+        const uint32_t cj = y - g.off;                                   // unsigned wrap rejects y < off
+        const bool in_col = cj < g.ed;
+        const int32_t ayy = ay * (int32_t)y;
+        float* p0 = w + (size_t)row0 * g.nd + y;
+        float v[kRowBatch];
 #pragma unroll
-            for (int u = 0; u < kUpdVec; ++u) {
-                const uint32_t i4 = chunk + threadIdx.x + u * kUpdThreads;
-                if (i4 < nvec) v[u] = __ldcs(reinterpret_cast<const float4*>(w) + i4);
-            }
+        for (int u = 0; u < kRowBatch; ++u) {
+            v[u] = 0.0f;
+            if (valid && row0 + u < rows) v[u] = __ldcs(p0 + (size_t)u * g.nd);
+        }
+        if (stage_base && !staged) {
+            if (!mbar_wait(&bar, 0)) return;      // bounded; cannot expire unless the copy faulted
+            bsrc = base_s;
+            staged = true;
         }
 #pragma unroll
-        for (int u = 0; u < kUpdVec; ++u) {
-            const uint32_t i4 = chunk + threadIdx.x + u * kUpdThreads;
-            if (i4 >= nvec) break;
-            float e[4] = { v[u].x, v[u].y, v[u].z, v[u].w };
-            const uint32_t idx = i4 * 4;
-            uint32_t row = fast_div(idx, magic_nd);            // c * nd + x
-            uint32_t y = idx - row * g.nd;
-            uint32_t c = fast_div(row, magic_nd), x = row - c * g.nd;
-            int32_t s = (int32_t)(c * P1) + ax * (int32_t)x + ay * (int32_t)y + a0;
-            uint32_t ci = x - g.off;                             // unsigned wrap rejects x < off
-            uint32_t kk = c * K1 + ci * g.ed - g.off;            // + y gives the operand position
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                if (idx + k < g.P) {
-                    const float rv = bsrc[s];
-                    const float nv = __fsub_rn(e[k], __fmul_rn(__fsub_rn(e[k], rv), f));
-                    e[k] = nv;
-                    if (ci < g.ed && y - g.off < g.ed) {
-                        if (MODE == kModeU8) {
-                            const uint32_t qv = quant_u8(nv);
-                            crop_s[kk + y] = (uint8_t)qv;
-                            acc += qv * qv;
-                        } else if (MODE == kModeU16) {
-                            const uint32_t qv = quant_u16(nv);
-                            crop_s[kk + y] = (uint8_t)(qv >> 8);
-                            crop_s[g.Kp + kk + y] = (uint8_t)(qv & 255);
-                            acc += (unsigned long long)qv * qv;
-                        } else {
-                            reinterpret_cast<float*>(crop_s)[kk + y] = nv;
-                        }
+        for (int u = 0; u < kRowBatch; ++u) {
+            if (valid && row0 + u < rows) {
+                const RowInfo ri = rowinfo[row0 + u];
+                const float rv = bsrc[ri.src + ayy];
+                const float nv = __fsub_rn(v[u], __fmul_rn(__fsub_rn(v[u], rv), f));
+                __stcs(p0 + (size_t)u * g.nd, nv);
+                if (in_col && ri.kk >= 0) {
+                    const uint32_t kk = (uint32_t)ri.kk + cj;
+                    if (MODE == kModeU8) {
+                        const uint32_t qv = quant_u8(nv);
+                        crop_s[kk] = (uint8_t)qv;
+                        acc += qv * qv;
+                    } else if (MODE == kModeU16) {
+                        const uint32_t qv = quant_u16(nv);
+                        crop_s[kk] = (uint8_t)(qv >> 8);
+                        crop_s[g.Kp + kk] = (uint8_t)(qv & 255);
+                        acc += (unsigned long long)qv * qv;
+                    } else {
+                        reinterpret_cast<float*>(crop_s)[kk] = nv;
                     }
                 }
-                ++y; s += ay;
-                if (y == g.nd) {                                 // next row (and possibly next channel)
-                    y = 0; ++x;
-                    if (x == g.nd) { x = 0; ++c; }
-                    s = (int32_t)(c * P1) + ax * (int32_t)x + a0;
-                    ci = x - g.off;
-                    kk = c * K1 + ci * g.ed - g.off;
-                }
             }
-            __stcs(reinterpret_cast<float4*>(w) + i4, make_float4(e[0], e[1], e[2], e[3]));
         }
     }
     __syncthreads();
@@ -316,11 +281,13 @@ cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t
 {
     if ((uint64_t)g.P * g.nd >= (1ull << 32)) return cudaErrorInvalidValue;   // multiply-high division range
     const size_t crop = MODE == kModeF32 ? (size_t)g.Kp * 4 : (MODE == kModeU16 ? (size_t)g.Kp * 2 : g.Kp);
-    const size_t staged = (((size_t)g.P * 4 + 15) & ~size_t(15)) + crop;
+    const size_t rows = (size_t)g.C * g.nd;
+    const size_t fixed = ((rows * 8 + 15) & ~size_t(15)) + ((crop + 15) & ~size_t(15));
+    const size_t staged = fixed + (size_t)g.P * 4;
     // The bulk copy needs a size that is a multiple of 16 bytes; otherwise (and
     // when a base rotation does not fit) the base is read through the cache.
     const uint32_t stage_base = staged <= 200 * 1024 && (g.P & 3) == 0;
-    const size_t smem = stage_base ? staged : crop;
+    const size_t smem = stage_base ? staged : fixed;
     // Dynamic shared memory above 48 KB is an opt-in, per-device function attribute.
     static int attr_dev = -1;
     static size_t attr_bytes = 0;
@@ -332,16 +299,16 @@ cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t
         attr_dev = dev;
         attr_bytes = smem;
     }
-    const uint32_t magic = (uint32_t)((1ull << 32) / g.nd) + 1;
-    update_kernel<MODE><<<a.n, kUpdThreads, smem, st>>>(g, a, stage_base, magic);
+    const uint32_t blocks_per_col = (uint32_t)((rows + kRowBatch - 1) / kRowBatch);
+    update_kernel<MODE><<<a.n, kUpdThreads, smem, st>>>(g, a, stage_base, div_magic(g.nd), div_magic(blocks_per_col));
     return cudaGetLastError();
 }
 
 } // namespace
 
-cudaError_t launch_bmu(const BmuArgs& a, uint32_t phase, cudaStream_t st)
+cudaError_t launch_bmu(const BmuArgs& a, cudaStream_t st)
 {
-    bmu_kernel<<<1, 512, 0, st>>>(a, phase);
+    bmu_kernel<<<1, kBmuThreads, 0, st>>>(a);
     return cudaGetLastError();
 }
 

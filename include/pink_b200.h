@@ -106,6 +106,8 @@ int pink_b200_destroy(pink_b200_ctx* ctx);
  * N/world (+1 for the first N % world ranks), contiguous, as the reference's
  * multi-GPU split (src/CudaLib/generate_euclidean_distance_matrix_first_step_multi_gpu.h:65-77). */
 int pink_b200_shard(const pink_b200_ctx* ctx, uint32_t* first, uint32_t* count);
+/* The same split as a pure host function (no context, no GPU). */
+int pink_b200_shard_range(uint32_t n_neurons, uint32_t world_size, uint32_t rank, uint32_t* first, uint32_t* count);
 
 /* ---- multi-GPU: one process per GPU, neuron shards, NCCL for the BMU exchange
  * (replaces the per-image cudaMemcpyPeer traffic of

@@ -35,6 +35,8 @@ SYMBOLS = {
     "pink_b200_create": (C.c_int, [C.POINTER(Config), C.POINTER(C.c_void_p)]),
     "pink_b200_destroy": (C.c_int, [C.c_void_p]),
     "pink_b200_shard": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
+    "pink_b200_shard_range": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32),
+                                        C.POINTER(C.c_uint32)]),
     "pink_b200_comm_unique_id": (C.c_int, [C.c_void_p]),
     "pink_b200_comm_init": (C.c_int, [C.c_void_p, C.c_void_p]),
     "pink_b200_set_som": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -16,6 +16,7 @@
 #include <string>
 #include <vector>
 
+namespace pinkb { void fetch_tl(long long*); }
 using namespace pinkb;
 
 namespace {
@@ -223,7 +224,7 @@ int check_status(pink_b200_ctx* c)
     CU_TRY(cudaStreamSynchronize(c->stream));
     if (st != kDevOk) {
         cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream);
-        return fail(PINK_B200_ETIMEOUT, "device-side wait expired in the distance kernel (code " + std::to_string(st) + ")");
+        return fail(PINK_B200_ETIMEOUT, "a bounded device-side wait expired (code " + std::to_string(st) + ")");
     }
     return PINK_B200_OK;
 }
@@ -266,7 +267,7 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     ua.a0 = c->d_a0; ua.a1 = c->d_a1; ua.anorm = c->d_anorm;
     ua.counts = c->d_counts; ua.bmu_log = bmu_slot;
     if (ev) CU_TRY(cudaEventRecord(ev[2], c->stream));
-    LAUNCH_TRY(launch_update(g, ua, c->stream));
+    LAUNCH_TRY(launch_update(g, ua, c->stream, c->d_status));
     if (ev) CU_TRY(cudaEventRecord(ev[3], c->stream));
     return PINK_B200_OK;
 }
@@ -359,9 +360,7 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     c->cfg = *cfg;
     c->g = g;
     const uint32_t W = cfg->world_size, N = cfg->n_neurons;
-    const uint32_t base = N / W, extra = N % W;
-    c->count = base + (cfg->rank < extra ? 1 : 0);
-    c->first = cfg->rank * base + (cfg->rank < extra ? cfg->rank : extra);
+    pink_b200_shard_range(N, W, cfg->rank, &c->first, &c->count);
     c->train_batch = cfg->max_batch ? cfg->max_batch : 256;
     {
         // Mapping batch: bound the transform operand of one batch to about 1 GiB.
@@ -678,6 +677,8 @@ int pink_b200_map(pink_b200_ctx* c, const float* host_images, uint64_t n, float*
     return check_status(c);
 }
 
+int pink_b200_dbg_dump(long long* host) { pinkb::fetch_tl(host); return 0; }
+
 int pink_b200_synchronize(pink_b200_ctx* c)
 {
     if (!c) return fail(PINK_B200_EINVAL, "null context");
@@ -815,7 +816,7 @@ int pink_b200_op_status(void)
     CU_TRY(cudaMemcpy(&st, g_op_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != kDevOk) {
         cudaMemset(g_op_status, 0, sizeof(int));
-        return fail(PINK_B200_ETIMEOUT, "device-side wait expired in the distance kernel (code " + std::to_string(st) + ")");
+        return fail(PINK_B200_ETIMEOUT, "a bounded device-side wait expired (code " + std::to_string(st) + ")");
     }
     return PINK_B200_OK;
 }

@@ -47,6 +47,15 @@ float neighbourhood(uint32_t func, float d, float p0, float p1)
 
 extern "C" {
 
+int pink_b200_shard_range(uint32_t n_neurons, uint32_t world_size, uint32_t rank, uint32_t* first, uint32_t* count)
+{
+    if (world_size == 0 || rank >= world_size || world_size > n_neurons || !first || !count) return PINK_B200_EINVAL;
+    const uint32_t base = n_neurons / world_size, extra = n_neurons % world_size;
+    *count = base + (rank < extra ? 1 : 0);
+    *first = rank * base + (rank < extra ? rank : extra);
+    return PINK_B200_OK;
+}
+
 uint32_t pink_b200_som_size(uint32_t som_layout, uint32_t dim0, uint32_t dim1)
 {
     if (som_layout == PINK_B200_LAYOUT_CARTESIAN) return dim0 * dim1;

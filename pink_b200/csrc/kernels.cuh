@@ -13,7 +13,8 @@ namespace pinkb {
 enum : int { kModeF32 = 0, kModeU16 = 1, kModeU8 = 2 };
 
 // Status codes a kernel may leave in the device status word.
-enum : int { kDevOk = 0, kDevTimeoutProducer = 1, kDevTimeoutMma = 2, kDevTimeoutEpilogue = 3 };
+enum : int { kDevOk = 0, kDevTimeoutProducer = 1, kDevTimeoutMma = 2, kDevTimeoutEpilogue = 3,
+             kDevTimeoutUpdateProducer = 11, kDevTimeoutUpdateConsumer = 12 };
 
 struct Geometry
 {
@@ -87,7 +88,8 @@ struct UpdateArgs
     uint32_t* counts;                 // [N_global] BMU hit counters (incremented by the owner)
     uint32_t* bmu_log;                // nullable: receives the global BMU index of this step
 };
-cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st);
+// status: device status word that receives a code if a bounded wait expires.
+cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st, int* status);
 
 // ---- mapping epilogue -------------------------------------------------------
 // dist[i][n] = sqrt(reported distance), rot[i][n] = transform; re-arms the keys.

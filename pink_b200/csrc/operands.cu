@@ -23,14 +23,20 @@ namespace pinkb {
 
 namespace {
 
+// Truncating conversion of v * 255 (v * 65535); float-to-integer cvt clamps to
+// the destination range, so one instruction both converts and saturates.
 __device__ __forceinline__ uint32_t quant_u8(float v)
 {
-    return min(__float2uint_rz(__fmul_rn(v, 255.0f)), 255u);
+    uint32_t q;
+    asm("cvt.rzi.u8.f32 %0, %1;" : "=r"(q) : "f"(__fmul_rn(v, 255.0f)));
+    return q;
 }
 
 __device__ __forceinline__ uint32_t quant_u16(float v)
 {
-    return min(__float2uint_rz(__fmul_rn(v, 65535.0f)), 65535u);
+    uint32_t q;
+    asm("cvt.rzi.u16.f32 %0, %1;" : "=r"(q) : "f"(__fmul_rn(v, 65535.0f)));
+    return q;
 }
 
 // Centre crop / zero pad (src/CudaLib/resize_kernel.h:15-32, integer margins).

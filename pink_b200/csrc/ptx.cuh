@@ -101,6 +101,37 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
         : "memory");
 }
 
+// 1-D bulk copy this CTA's shared memory -> global, tracked by bulk groups.
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 :: "l"(reinterpret_cast<uint64_t>(gdst)), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// Wait until the bulk stores of all committed groups have finished READING shared memory.
+__device__ __forceinline__ void bulk_wait_read_all()
+{
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// Wait until all committed bulk stores are complete.
+__device__ __forceinline__ void bulk_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// Order this thread's generic-proxy writes to shared memory before later
+// asynchronous-proxy (TMA) reads of them.
+__device__ __forceinline__ void fence_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // ------------------------------------------------------------------- TMEM --
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols)
 {

@@ -18,19 +18,27 @@
 #include "kernels.cuh"
 #include "ptx.cuh"
 
+#include <algorithm>
+
 
 namespace pinkb {
 
 namespace {
 
+// Truncating conversion of v * 255 (v * 65535); float-to-integer cvt clamps to
+// the destination range, so one instruction both converts and saturates.
 __device__ __forceinline__ uint32_t quant_u8(float v)
 {
-    return min(__float2uint_rz(__fmul_rn(v, 255.0f)), 255u);
+    uint32_t q;
+    asm("cvt.rzi.u8.f32 %0, %1;" : "=r"(q) : "f"(__fmul_rn(v, 255.0f)));
+    return q;
 }
 
 __device__ __forceinline__ uint32_t quant_u16(float v)
 {
-    return min(__float2uint_rz(__fmul_rn(v, 65535.0f)), 65535u);
+    uint32_t q;
+    asm("cvt.rzi.u16.f32 %0, %1;" : "=r"(q) : "f"(__fmul_rn(v, 65535.0f)));
+    return q;
 }
 
 __device__ __forceinline__ bool pair_less(unsigned long long c0, unsigned long long n0,
@@ -257,6 +265,307 @@ update_kernel(Geometry g, UpdateArgs a, uint32_t stage_base, uint32_t magic_nd, 
     }
 }
 
+// ---------------------------------------------------------------------------
+// Persistent, TMA-pipelined update: one block per SM walks its share of the
+// shard's neurons (round robin).  Warp 0 is the producer: for every neuron
+// with a non-zero factor it streams the neuron (P floats) and the base
+// rotation of its best transform into a shared-memory stage with two bulk
+// asynchronous copies, and, once the consumer warps are done with a stage,
+// writes the updated neuron and its rebuilt operand row(s) back with bulk
+// stores.  Several stages are in flight, so the memory system always has
+// tens of kilobytes outstanding per SM while the consumers compute from
+// shared memory.  The consumers first update the whole neuron (a thread owns
+// one column of a block of rows; everything that does not depend on the
+// neuron is computed once per kernel), then rebuild the operand row from the
+// updated values, four elements per thread.  All waits are bounded.
+constexpr int kPipeThreads = 1024;
+constexpr int kPipeConsumerWarps = kPipeThreads / 32 - 1;
+constexpr int kPipeConsumers = kPipeConsumerWarps * 32;
+constexpr int kPipeMaxStages = 4;
+constexpr int kPipeMaxItems = 256;    // neurons one block may own
+constexpr int kPipeUnroll = 3;        // neuron rows a consumer thread processes together
+constexpr int kPipeMaxTasks = 2;      // (row block, column) tasks per thread and neuron
+constexpr int kPipeScan = 4;          // factors a thread ranks per pass of the header scan
+constexpr int kPipeMaxUnits = 2;      // operand groups of four elements per thread and neuron
+
+struct PipeParams
+{
+    uint32_t stages, stage_bytes, off_base, off_crop, crop_bytes;   // shared-memory layout of a stage
+    uint32_t col_chunks, row_blocks, rows_per_block;                // consumer task grid per channel
+    int* status;
+};
+
+struct PipeItem { uint32_t n, tq; int32_t ax, ay, a0; float f; };
+
+__device__ long long g_tl[148 * 64 * 3];
+
+template <int MODE>
+__global__ void __launch_bounds__(kPipeThreads, 1)
+update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp)
+{
+    extern __shared__ __align__(128) uint8_t pipe_dyn[];
+    __shared__ __align__(8) uint64_t full_bar[kPipeMaxStages], done_bar[kPipeMaxStages];
+    __shared__ unsigned long long norm_s[kPipeMaxStages][kPipeConsumerWarps];   // per-warp partial sums of squares
+    __shared__ PipeItem items[kPipeMaxItems];
+    __shared__ uint32_t bmu_s, m_s, scan_s[kPipeThreads / 32];
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        // Global best matching unit: lexicographic minimum over the per-rank records.
+        unsigned long long bc = a.pairs[0].code, bn = a.pairs[0].neuron;
+        for (uint32_t r = 1; r < a.world; ++r)
+            if (pair_less(a.pairs[r].code, a.pairs[r].neuron, bc, bn)) { bc = a.pairs[r].code; bn = a.pairs[r].neuron; }
+        bmu_s = (uint32_t)bn;
+        for (uint32_t s = 0; s < pp.stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&done_bar[s], kPipeConsumerWarps);
+        }
+        mbar_fence_init();
+    }
+    // operand staging starts as zeros: the padding beyond K is never written again
+    for (uint32_t s = 0; s < pp.stages; ++s)
+        for (uint32_t i = threadIdx.x; i < pp.crop_bytes / 4; i += kPipeThreads)
+            reinterpret_cast<uint32_t*>(pipe_dyn + (size_t)s * pp.stage_bytes + pp.off_crop)[i] = 0;
+    __syncthreads();
+
+    // Every block scans the whole factor row of the best matching unit and ranks
+    // the neurons whose factor is non-zero; block b takes the neurons of rank
+    // b, b + gridDim.x, ...  so that all blocks get the same number of neurons
+    // (+-1) however the zero factors are distributed.  For its neurons the block
+    // reads the best transform and decodes it into the affine map
+    // src = c*nd*nd + ax*x + ay*y + a0 from a neuron pixel to the base rotation
+    // (flip reverses rows last, src/CudaLib/flip_kernel.h:28; a quarter turn maps
+    // (x, y) <- (nd-1-y, x), src/CudaLib/rotate_90_degrees_list.h:28).  Keys are
+    // re-armed for the next image: those of ranked neurons by the block that
+    // takes them, the others by block (index mod gridDim.x).
+    const uint32_t bmu = bmu_s;
+    const float* frow = a.factors + (size_t)bmu * a.n;
+    uint32_t rank_base = 0;
+    for (uint32_t p0 = 0; p0 < a.n; p0 += kPipeThreads * kPipeScan) {
+        float fv[kPipeScan];
+        const uint32_t i0 = p0 + threadIdx.x * kPipeScan;
+        uint32_t cnt = 0;
+#pragma unroll
+        for (int e = 0; e < kPipeScan; ++e) {
+            fv[e] = i0 + e < a.n ? frow[i0 + e] : 0.0f;
+            cnt += fv[e] != 0.0f;
+        }
+        uint32_t incl = cnt;
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((int)lane >= o) incl += up;
+        }
+        if (lane == 31) scan_s[warp] = incl;
+        __syncthreads();
+        uint32_t before = rank_base, total = 0;
+        for (uint32_t wv = 0; wv < kPipeThreads / 32; ++wv) {
+            const uint32_t tcount = scan_s[wv];
+            if (wv < warp) before += tcount;
+            total += tcount;
+        }
+        uint32_t rank = before + incl - cnt;
+#pragma unroll
+        for (int e = 0; e < kPipeScan; ++e) {
+            const uint32_t n = i0 + e;
+            if (n >= a.n) break;
+            if (fv[e] != 0.0f) {
+                if (rank % gridDim.x == blockIdx.x) {
+                    const unsigned long long key = a.keys[n];
+                    a.keys[n] = kKeyEmpty;
+                    const uint32_t t = (uint32_t)(key & ((1ull << key_shift(MODE)) - 1));
+                    const uint32_t fl = t / g.R, r = t - fl * g.R;
+                    const uint32_t jq = g.q ? r / g.q : 0;
+                    const int32_t nd = (int32_t)g.nd, nd1 = nd - 1;
+                    PipeItem it;
+                    it.n = n;
+                    it.tq = g.q ? r - jq * g.q : 0;
+                    it.f = fv[e];
+                    switch (jq) {
+                        case 0:  it.ax = fl ? -nd : nd; it.ay = 1;   it.a0 = fl ? nd1 * nd : 0; break;
+                        case 1:  it.ax = fl ? -1 : 1;   it.ay = -nd; it.a0 = nd1 * nd + (fl ? nd1 : 0); break;
+                        case 2:  it.ax = fl ? nd : -nd; it.ay = -1;  it.a0 = fl ? nd1 : nd1 * nd + nd1; break;
+                        default: it.ax = fl ? 1 : -1;   it.ay = nd;  it.a0 = fl ? 0 : nd1; break;
+                    }
+                    items[rank / gridDim.x] = it;
+                }
+                ++rank;
+            } else if (n % gridDim.x == blockIdx.x) {
+                a.keys[n] = kKeyEmpty;
+            }
+        }
+        rank_base += total;
+        __syncthreads();                  // scan_s is reused by the next pass
+    }
+    if (threadIdx.x == 0) {
+        m_s = rank_base > blockIdx.x ? (rank_base - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        if (blockIdx.x == 0 && bmu >= a.first_neuron && bmu - a.first_neuron < a.n) {   // the owner counts the hit
+            a.counts[bmu] += 1;
+            if (a.bmu_log) *a.bmu_log = bmu;
+        }
+    }
+    fence_async_smem();                   // zeroed operand staging visible to later bulk stores
+    __syncthreads();
+    const uint32_t M = m_s;
+    const uint32_t plane_bytes = g.P * 4;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer --
+        // (the whole warp stays converged; lane 0 issues the asynchronous copies)
+        auto issue = [&](uint32_t jx) {
+            const uint32_t s = jx % pp.stages;
+            uint8_t* st = pipe_dyn + (size_t)s * pp.stage_bytes;
+            mbar_expect_tx(&full_bar[s], 2 * plane_bytes);
+            bulk_load(st, a.som + (size_t)items[jx].n * g.Pp, plane_bytes, &full_bar[s]);
+            bulk_load(st + pp.off_base, a.base + (size_t)items[jx].tq * g.P, plane_bytes, &full_bar[s]);
+        };
+        if (lane == 0)
+            for (uint32_t jx = 0; jx < M && jx < pp.stages; ++jx) issue(jx);
+        for (uint32_t jx = 0; jx < M; ++jx) {
+            const uint32_t s = jx % pp.stages, ph = (jx / pp.stages) & 1;
+            if (!mbar_wait(&done_bar[s], ph)) { if (pp.status) atomicCAS(pp.status, kDevOk, kDevTimeoutUpdateProducer); break; }
+            const uint32_t n = items[jx].n;
+            uint8_t* st = pipe_dyn + (size_t)s * pp.stage_bytes;
+            if (MODE != kModeF32) {
+                unsigned long long tot = lane < kPipeConsumerWarps ? norm_s[s][lane] : 0ull;
+                for (int o = 16; o > 0; o >>= 1) tot += __shfl_down_sync(0xffffffffu, tot, o);
+                if (lane == 0) {
+                    if (MODE == kModeU8) static_cast<uint32_t*>(a.anorm)[n] = (uint32_t)tot;
+                    else static_cast<unsigned long long*>(a.anorm)[n] = tot;
+                }
+            }
+            if (lane == 0) {
+                bulk_store(a.som + (size_t)n * g.Pp, st, plane_bytes);
+                if (MODE == kModeF32) {
+                    bulk_store(static_cast<float*>(a.a0) + (size_t)n * g.Kp, st + pp.off_crop, g.Kp * 4);
+                } else {
+                    bulk_store(static_cast<uint8_t*>(a.a0) + (size_t)n * g.Kp, st + pp.off_crop, g.Kp);
+                    if (MODE == kModeU16)
+                        bulk_store(static_cast<uint8_t*>(a.a1) + (size_t)n * g.Kp, st + pp.off_crop + g.Kp, g.Kp);
+                }
+                bulk_commit();
+                if (jx + pp.stages < M) {
+                    bulk_wait_read_all();             // the stage's stores no longer read it
+                    issue(jx + pp.stages);
+                }
+            }
+            __syncwarp();
+        }
+        if (lane == 0) bulk_wait_all();
+    } else {
+        // ----------------------------------------------------------- consumers --
+        const uint32_t cwarp = warp - 1, ctid = threadIdx.x - 32;
+        const uint32_t P1 = g.nd * g.nd, K1 = g.ed * g.ed;
+        // Update tasks of this thread (the same for every neuron): channel c, column y, rows
+        // [x0, x0 + 3 * full + tail).  Idle lanes and tasks get an empty range.
+        const uint32_t tasks_per_channel = pp.col_chunks * pp.row_blocks, ntask = g.C * tasks_per_channel;
+        uint32_t tk_si[kPipeMaxTasks], tk_x0[kPipeMaxTasks], tk_full[kPipeMaxTasks], tk_tail[kPipeMaxTasks];
+        uint32_t tk_c[kPipeMaxTasks], tk_y[kPipeMaxTasks];
+#pragma unroll
+        for (int k = 0; k < kPipeMaxTasks; ++k) {
+            const uint32_t task = cwarp + k * kPipeConsumerWarps;
+            const uint32_t c = task / tasks_per_channel, tc = task - c * tasks_per_channel;
+            const uint32_t chunk = tc / pp.row_blocks, blk = tc - chunk * pp.row_blocks;
+            const uint32_t y = chunk * 32 + lane, x0 = blk * pp.rows_per_block;
+            const bool live = task < ntask && y < g.nd && x0 < g.nd;
+            const uint32_t nrows = live ? min(pp.rows_per_block, g.nd - x0) : 0;
+            tk_c[k] = c; tk_y[k] = y; tk_x0[k] = x0;
+            tk_full[k] = nrows / kPipeUnroll; tk_tail[k] = nrows - tk_full[k] * kPipeUnroll;
+            tk_si[k] = c * P1 + x0 * g.nd + y;
+        }
+        // Operand units of this thread: within a segment of 128 consecutive operand elements, lane l
+        // of a warp converts elements l, l + 32, l + 64, l + 96, so that every shared-memory read of a
+        // warp touches 32 consecutive floats (no bank conflicts).  Elements beyond K read position 0
+        // and are never stored.
+        const uint32_t nunit = ((g.K + 127) / 128) * 32;
+        uint32_t un_src[kPipeMaxUnits][4], un_dst[kPipeMaxUnits][4];
+#pragma unroll
+        for (int k = 0; k < kPipeMaxUnits; ++k) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t unit = ctid + k * kPipeConsumers;
+                const uint32_t kk = (unit / 32) * 128 + (unit % 32) + 32 * e;
+                const uint32_t c = kk / K1, rem = kk - c * K1, ci = rem / g.ed, cj = rem - ci * g.ed;
+                const bool ok = unit < nunit && kk < g.K;
+                un_src[k][e] = ok ? c * P1 + (g.off + ci) * g.nd + g.off + cj : 0u;
+                un_dst[k][e] = ok ? kk : ~0u;
+            }
+        }
+        const uint32_t nd = g.nd;
+        for (uint32_t jx = 0; jx < M; ++jx) {
+            const uint32_t s = jx % pp.stages, ph = (jx / pp.stages) & 1;
+            long long c0 = clock64();
+            if (!mbar_wait(&full_bar[s], ph)) { if (pp.status) atomicCAS(pp.status, kDevOk, kDevTimeoutUpdateConsumer); break; }
+            uint8_t* st = pipe_dyn + (size_t)s * pp.stage_bytes;
+            float* som_s = reinterpret_cast<float*>(st);
+            const float* base_s = reinterpret_cast<const float*>(st + pp.off_base);
+            uint8_t* crop_s = st + pp.off_crop;
+            long long c1 = clock64();
+            const PipeItem it = items[jx];
+            const float f = it.f;
+            const int32_t ax = it.ax;
+            // -- w <- w - (w - r) * f over the whole neuron, kPipeUnroll rows per step:
+            //    all loads, then the arithmetic, then the stores; no predicates in the steady loop
+#pragma unroll
+            for (int k = 0; k < kPipeMaxTasks; ++k) {
+                float* ps = som_s + tk_si[k];
+                const float* pb = base_s + ((int32_t)(tk_c[k] * P1) + ax * (int32_t)tk_x0[k] + it.a0 + it.ay * (int32_t)tk_y[k]);
+                for (uint32_t i = 0; i < tk_full[k]; ++i) {
+                    float e[kPipeUnroll], rv[kPipeUnroll];
+#pragma unroll
+                    for (int u = 0; u < kPipeUnroll; ++u) { e[u] = ps[u * nd]; rv[u] = pb[u * ax]; }
+#pragma unroll
+                    for (int u = 0; u < kPipeUnroll; ++u) e[u] = __fsub_rn(e[u], __fmul_rn(__fsub_rn(e[u], rv[u]), f));
+#pragma unroll
+                    for (int u = 0; u < kPipeUnroll; ++u) ps[u * nd] = e[u];
+                    ps += kPipeUnroll * nd; pb += kPipeUnroll * ax;
+                }
+                for (uint32_t i = 0; i < tk_tail[k]; ++i) {
+                    const float e = *ps;
+                    *ps = __fsub_rn(e, __fmul_rn(__fsub_rn(e, *pb), f));
+                    ps += nd; pb += ax;
+                }
+            }
+            asm volatile("bar.sync 1, %0;" :: "n"(kPipeConsumers) : "memory");   // whole neuron updated
+            // -- operand row(s) from the updated values
+            unsigned long long acc = 0;
+#pragma unroll
+            for (int k = 0; k < kPipeMaxUnits; ++k) {
+                if (ctid + k * kPipeConsumers < nunit) {
+                    float v[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[e] = som_s[un_src[k][e]];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t kk = un_dst[k][e];
+                        if (kk != ~0u) {
+                            if (MODE == kModeU8) {
+                                const uint32_t qv = quant_u8(v[e]);
+                                crop_s[kk] = (uint8_t)qv;
+                                acc += qv * qv;
+                            } else if (MODE == kModeU16) {
+                                const uint32_t qv = quant_u16(v[e]);
+                                crop_s[kk] = (uint8_t)(qv >> 8);
+                                crop_s[g.Kp + kk] = (uint8_t)(qv & 255u);
+                                acc += (unsigned long long)qv * qv;
+                            } else {
+                                reinterpret_cast<float*>(crop_s)[kk] = v[e];
+                            }
+                        }
+                    }
+                }
+            }
+            if (MODE != kModeF32) {
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+                if (lane == 0) norm_s[s][cwarp] = acc;
+            }
+            fence_async_smem();           // this thread's stage writes before the producer's bulk stores
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&done_bar[s]);
+            if (ctid == 0 && jx < 64) { long long* d = g_tl + (blockIdx.x * 64 + jx) * 3; d[0] = c0; d[1] = c1; d[2] = clock64(); }
+        }
+    }
+}
+
 // Reported distance (src/SelfOrganizingMapLib/Mapper.h:201-207: device float,
 // then host sqrt): integer modes S / scale^2 rounded once to float.
 template <int MODE>
@@ -277,7 +586,7 @@ __global__ void map_finalize_kernel(unsigned long long* __restrict__ keys, size_
 }
 
 template <int MODE>
-cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t st)
+cudaError_t update_classic(const Geometry& g, const UpdateArgs& a, cudaStream_t st)
 {
     if ((uint64_t)g.P * g.nd >= (1ull << 32)) return cudaErrorInvalidValue;   // multiply-high division range
     const size_t crop = MODE == kModeF32 ? (size_t)g.Kp * 4 : (MODE == kModeU16 ? (size_t)g.Kp * 2 : g.Kp);
@@ -304,6 +613,64 @@ cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t
     return cudaGetLastError();
 }
 
+int device_sm_count()
+{
+    static int dev_cached = -1, sms = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev != dev_cached) {
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        dev_cached = dev;
+    }
+    return sms;
+}
+
+template <int MODE>
+cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t st, int* status)
+{
+    // The pipelined kernel needs bulk-copyable planes (16-byte multiples) and at
+    // least two stages of {neuron, base rotation, operand rows} in shared memory.
+    const size_t crop = MODE == kModeF32 ? (size_t)g.Kp * 4 : (MODE == kModeU16 ? (size_t)g.Kp * 2 : g.Kp);
+    const size_t plane = ((size_t)g.P * 4 + 127) & ~size_t(127);
+    const size_t stage = 2 * plane + ((crop + 127) & ~size_t(127));
+    const size_t budget = 216 * 1024;      // of the 227 KB a block may use; the kernel has ~7 KB of static arrays
+    const int sms = device_sm_count();
+    if ((g.P & 3) != 0 || g.P != g.Pp || stage * 2 > budget || sms <= 0) return update_classic<MODE>(g, a, st);
+    const uint32_t chunks = (g.nd + 31) / 32;
+    const uint32_t units = ((g.K + 127) / 128) * 32;
+    // every consumer thread keeps its tasks and operand units in registers
+    if (g.C * chunks > (uint32_t)(kPipeMaxTasks * kPipeConsumerWarps) || units > (uint32_t)(kPipeMaxUnits * kPipeConsumers))
+        return update_classic<MODE>(g, a, st);
+    PipeParams pp{};
+    pp.stages = (uint32_t)std::min<size_t>(kPipeMaxStages, budget / stage);
+    pp.stage_bytes = (uint32_t)stage;
+    pp.off_base = (uint32_t)plane;
+    pp.off_crop = (uint32_t)(2 * plane);
+    pp.crop_bytes = (uint32_t)((crop + 127) & ~size_t(127));
+    pp.col_chunks = (g.nd + 31) / 32;
+    // as many row blocks as keep all consumer warps busy without exceeding the per-thread task cap
+    pp.row_blocks = std::max<uint32_t>(1, kPipeConsumerWarps / (pp.col_chunks * g.C));
+    pp.rows_per_block = (g.nd + pp.row_blocks - 1) / pp.row_blocks;
+    pp.rows_per_block = (pp.rows_per_block + kPipeUnroll - 1) / kPipeUnroll * kPipeUnroll;   // whole unrolled steps
+    pp.row_blocks = (g.nd + pp.rows_per_block - 1) / pp.rows_per_block;
+    pp.status = status;
+    uint32_t grid = std::min<uint32_t>(a.n, (uint32_t)sms);
+    if ((a.n + grid - 1) / grid > (uint32_t)kPipeMaxItems) grid = (a.n + kPipeMaxItems - 1) / kPipeMaxItems;
+    const size_t smem = (size_t)pp.stages * stage;
+    static int attr_dev = -1;
+    static size_t attr_bytes = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev != attr_dev || smem > attr_bytes) {
+        cudaError_t e = cudaFuncSetAttribute(update_pipe_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_dev = dev;
+        attr_bytes = smem;
+    }
+    update_pipe_kernel<MODE><<<grid, kPipeThreads, smem, st>>>(g, a, pp);
+    return cudaGetLastError();
+}
+
 } // namespace
 
 cudaError_t launch_bmu(const BmuArgs& a, cudaStream_t st)
@@ -312,12 +679,14 @@ cudaError_t launch_bmu(const BmuArgs& a, cudaStream_t st)
     return cudaGetLastError();
 }
 
-cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st)
+void fetch_tl(long long* host) { cudaDeviceSynchronize(); cudaMemcpyFromSymbol(host, g_tl, sizeof(long long) * 148 * 64 * 3); }
+
+cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st, int* status)
 {
     if (a.n == 0) return cudaSuccess;
-    if (g.mode == kModeU8) return update_dispatch<kModeU8>(g, a, st);
-    if (g.mode == kModeU16) return update_dispatch<kModeU16>(g, a, st);
-    return update_dispatch<kModeF32>(g, a, st);
+    if (g.mode == kModeU8) return update_dispatch<kModeU8>(g, a, st, status);
+    if (g.mode == kModeU16) return update_dispatch<kModeU16>(g, a, st, status);
+    return update_dispatch<kModeF32>(g, a, st, status);
 }
 
 cudaError_t launch_map_finalize(const Geometry& g, unsigned long long* keys, uint32_t n_img, uint32_t n,

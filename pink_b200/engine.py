@@ -18,6 +18,15 @@ def som_size(layout, dim0, dim1):
     return int(capi.lib.pink_b200_som_size(layout, dim0, dim1))
 
 
+def shard_range(n_neurons, world_size, rank):
+    """(first, count) of the contiguous neuron shard of `rank` (host computation)."""
+    first, count = C.c_uint32(), C.c_uint32()
+    rc = capi.lib.pink_b200_shard_range(n_neurons, world_size, rank, C.byref(first), C.byref(count))
+    if rc != capi.OK:
+        raise capi.PinkError(rc, "invalid shard request")
+    return first.value, count.value
+
+
 def update_factors(layout, dim0, dim1, func=capi.FUNC_GAUSSIAN, p0=1.1, p1=0.2, max_update_distance=-1.0):
     """N x N table F[bmu, n] of the built-in neighbourhood functions (host computation)."""
     N = som_size(layout, dim0, dim1)

@@ -16,7 +16,6 @@
 #include <string>
 #include <vector>
 
-namespace pinkb { void fetch_tl(long long*); }
 using namespace pinkb;
 
 namespace {
@@ -111,6 +110,7 @@ int make_geometry(const pink_b200_config& c, Geometry* g)
     if (g->mode == kModeU8 && g->K > 33025) return fail(PINK_B200_EINVAL, "uint8 distance supports at most 33025 elements");
     if (g->mode == kModeU16 && g->K > 16512) return fail(PINK_B200_EINVAL, "uint16 distance supports at most 16512 elements");
     if (g->mode == kModeU16 && g->T > 65536) return fail(PINK_B200_EINVAL, "uint16 distance supports at most 65536 transforms");
+    if ((uint64_t)g->T * g->R >= (1ull << 32)) return fail(PINK_B200_EINVAL, "too many rotations");
     return PINK_B200_OK;
 }
 
@@ -155,6 +155,7 @@ struct pink_b200_ctx
     void *d_b0 = nullptr, *d_b1 = nullptr, *d_bnorm = nullptr; size_t b_imgs = 0;
     unsigned long long* d_keys = nullptr; size_t key_imgs = 0;
     BmuPair* d_pairs = nullptr;
+    UpdateItem* d_items = nullptr; uint32_t* d_nitems = nullptr;   // per-step work list of the update
     uint32_t* d_counts = nullptr;
     uint32_t* d_bmu_log = nullptr; size_t bmu_log_cap = 0, bmu_log_n = 0;
     int* d_status = nullptr;
@@ -255,17 +256,24 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     if (ev) CU_TRY(cudaEventRecord(ev[1], c->stream));
     BmuArgs ba{};
     ba.keys = c->d_keys; ba.n = c->count; ba.first_neuron = c->first; ba.shift = key_shift(g.mode);
-    ba.out = c->d_pairs + c->cfg.rank;
-    LAUNCH_TRY(launch_bmu(ba, c->stream));
-    if (c->cfg.world_size > 1)
+    ba.pairs = c->d_pairs; ba.rank = c->cfg.rank; ba.world = c->cfg.world_size;
+    ba.factors = c->d_factors; ba.items = c->d_items; ba.n_items = c->d_nitems;
+    ba.counts = c->d_counts; ba.bmu_log = bmu_slot;
+    ba.R = g.R; ba.q = g.q; ba.nd = g.nd;
+    ba.magic_R = g.R == 1 ? 0u : (uint32_t)((1ull << 32) / g.R) + 1;
+    ba.magic_q = g.q <= 1 ? 0u : (uint32_t)((1ull << 32) / g.q) + 1;
+    if (c->cfg.world_size == 1) {
+        LAUNCH_TRY(launch_bmu(ba, 3, c->stream));
+    } else {
+        LAUNCH_TRY(launch_bmu(ba, 1, c->stream));
         NCCL_TRY(nccl().AllGather(c->d_pairs + c->cfg.rank, c->d_pairs, 2, ncclUint64, c->comm, c->stream));
+        LAUNCH_TRY(launch_bmu(ba, 2, c->stream));
+    }
     UpdateArgs ua{};
     ua.som = c->d_som;
     ua.base = c->d_base + slot_img * (g.q ? g.q : 1) * (size_t)g.P;
-    ua.keys = c->d_keys; ua.pairs = c->d_pairs; ua.world = c->cfg.world_size;
-    ua.factors = c->d_factors; ua.n = c->count; ua.first_neuron = c->first;
+    ua.items = c->d_items; ua.n_items = c->d_nitems; ua.n = c->count;
     ua.a0 = c->d_a0; ua.a1 = c->d_a1; ua.anorm = c->d_anorm;
-    ua.counts = c->d_counts; ua.bmu_log = bmu_slot;
     if (ev) CU_TRY(cudaEventRecord(ev[2], c->stream));
     LAUNCH_TRY(launch_update(g, ua, c->stream, c->d_status));
     if (ev) CU_TRY(cudaEventRecord(ev[3], c->stream));
@@ -360,7 +368,9 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     c->cfg = *cfg;
     c->g = g;
     const uint32_t W = cfg->world_size, N = cfg->n_neurons;
-    pink_b200_shard_range(N, W, cfg->rank, &c->first, &c->count);
+    const uint32_t base = N / W, extra = N % W;
+    c->count = base + (cfg->rank < extra ? 1 : 0);
+    c->first = cfg->rank * base + (cfg->rank < extra ? cfg->rank : extra);
     c->train_batch = cfg->max_batch ? cfg->max_batch : 256;
     {
         // Mapping batch: bound the transform operand of one batch to about 1 GiB.
@@ -409,6 +419,10 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     CTX_TRY(cudaMalloc(&c->d_anorm, norm_bytes(g, c->count)));
     CTX_TRY(cudaMalloc(&c->d_pairs, W * sizeof(BmuPair)));
     CTX_TRY(cudaMemsetAsync(c->d_pairs, 0xFF, W * sizeof(BmuPair), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_items, c->count * sizeof(UpdateItem)));
+    CTX_TRY(cudaMemsetAsync(c->d_items, 0, c->count * sizeof(UpdateItem), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_nitems, sizeof(uint32_t)));
+    CTX_TRY(cudaMemsetAsync(c->d_nitems, 0, sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_counts, N * sizeof(uint32_t)));
     CTX_TRY(cudaMemsetAsync(c->d_counts, 0, N * sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_status, sizeof(int)));
@@ -448,6 +462,7 @@ int pink_b200_destroy(pink_b200_ctx* c)
     free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
     free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_base);
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
+    free_dev(c->d_items); free_dev(c->d_nitems);
     free_dev(c->d_pairs); free_dev(c->d_counts); free_dev(c->d_bmu_log); free_dev(c->d_status);
     free_dev(c->d_images[0]); free_dev(c->d_images[1]); free_dev(c->d_dist); free_dev(c->d_rot);
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
@@ -676,8 +691,6 @@ int pink_b200_map(pink_b200_ctx* c, const float* host_images, uint64_t n, float*
     }
     return check_status(c);
 }
-
-int pink_b200_dbg_dump(long long* host) { pinkb::fetch_tl(host); return 0; }
 
 int pink_b200_synchronize(pink_b200_ctx* c)
 {

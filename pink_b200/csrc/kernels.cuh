@@ -66,27 +66,39 @@ struct DistanceArgs
 // Returns cudaSuccess or the launch / tensor-map error; *why receives a static message.
 cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why);
 
-// ---- best matching unit -----------------------------------------------------
+// ---- best matching unit and work list of the update ----------------------------
+// One neuron the update must rewrite: local index, update factor, and its best
+// transform decoded into the base rotation tq and the affine map
+// src = c*nd*nd + ax*x + ay*y + a0 from a neuron pixel (x, y) to that base
+// rotation (flip reverses rows last, src/CudaLib/flip_kernel.h:28; a quarter
+// turn maps (x, y) <- (nd-1-y, x), src/CudaLib/rotate_90_degrees_list.h:28).
+struct UpdateItem { uint32_t n, tq; int32_t ax, ay, a0; float f; };
+
 struct BmuArgs
 {
-    const unsigned long long* keys; uint32_t n, first_neuron, shift;   // this shard's per-neuron minima
-    BmuPair* out;                                                       // this rank's record
+    unsigned long long* keys; uint32_t n, first_neuron, shift;   // this shard's per-neuron minima (re-armed in phase 2)
+    BmuPair* pairs; uint32_t rank, world;                        // per-rank records (world entries)
+    const float* factors;             // [N_global][n] update factors, column = local neuron
+    UpdateItem* items; uint32_t* n_items;   // out: neurons with a non-zero factor, ascending, and their number
+    uint32_t* counts;                 // [N_global] BMU hit counters (incremented by the owner)
+    uint32_t* bmu_log;                // nullable: receives the global BMU index of this step
+    uint32_t R, q, nd;                // geometry needed to decode a transform index
+    uint32_t magic_R, magic_q;        // multiply-high reciprocals of R and q (0 = divisor 1); need T * R < 2^32
 };
-// Reduces keys[0..n) to the shard's (code, first_neuron + argmin) record.
-cudaError_t launch_bmu(const BmuArgs& a, cudaStream_t st);
+// phase bit 0: reduce keys[0..n) to this shard's (code, first_neuron + argmin) record in pairs[rank];
+// phase bit 1: pick the global best matching unit from pairs, count the hit, re-arm the keys and emit
+// the work list.  A single-GPU step runs both in one launch; with several ranks the exchange of the
+// records sits between them.
+cudaError_t launch_bmu(const BmuArgs& a, uint32_t phase, cudaStream_t st);
 
 // ---- neighbourhood update ---------------------------------------------------
 struct UpdateArgs
 {
     float* som;                       // [n][Pp]
     const float* base;                // [max(q,1)][C][nd][nd] base rotations of the current image
-    unsigned long long* keys;         // [n]; read, then re-armed to kKeyEmpty
-    const BmuPair* pairs; uint32_t world;   // per-rank BMU records (world entries)
-    const float* factors;             // [N_global][n] update factors, column = local neuron
-    uint32_t n, first_neuron;
+    const UpdateItem* items; const uint32_t* n_items;   // work list from launch_bmu
+    uint32_t n;                       // local neurons (upper bound of the work list)
     void* a0; void* a1; void* anorm;  // SOM operand rows to refresh
-    uint32_t* counts;                 // [N_global] BMU hit counters (incremented by the owner)
-    uint32_t* bmu_log;                // nullable: receives the global BMU index of this step
 };
 // status: device status word that receives a code if a bounded wait expires.
 cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st, int* status);

@@ -69,10 +69,13 @@ __device__ __forceinline__ void block_min_pair(unsigned long long& bc, unsigned 
     }
 }
 
+// v / d for v * d < 2^32 with magic = floor(2^32 / d) + 1; magic == 0 encodes the divisor 1.
+__device__ __forceinline__ uint32_t bmu_div(uint32_t v, uint32_t magic) { return magic ? __umulhi(v, magic) : v; }
+
 constexpr int kBmuThreads = 512;
 constexpr int kBmuPer = 8;            // keys a thread loads per pass, all in flight at once
 
-// One block: first minimum of (code, neuron) over this shard's keys.
+// Phase 1, one block: first minimum of (code, neuron) over this shard's keys -> pairs[rank].
 __global__ void __launch_bounds__(kBmuThreads)
 bmu_kernel(BmuArgs a)
 {
@@ -93,9 +96,72 @@ bmu_kernel(BmuArgs a)
     }
     block_min_pair(bc, bn, sc, sn);
     if (threadIdx.x == 0) {
-        a.out->code = bc;
-        a.out->neuron = bn == ~0ull ? ~0ull : bn + a.first_neuron;
+        a.pairs[a.rank].code = bc;
+        a.pairs[a.rank].neuron = bn == ~0ull ? ~0ull : bn + a.first_neuron;
     }
+}
+
+constexpr int kListThreads = 256;
+
+// Phase 2, one block per kListThreads neurons: pick the global best matching unit
+// from the per-rank records, count the hit, re-arm the keys and emit the work list
+// of the update (neurons with a non-zero factor, ascending).  A block finds the
+// list position of its first entry by counting the non-zero factors before its
+// range, so the list order does not depend on scheduling and no atomics are needed.
+__global__ void __launch_bounds__(kListThreads)
+worklist_kernel(BmuArgs a)
+{
+    __shared__ uint32_t warp_cnt[kListThreads / 32], warp_pre[kListThreads / 32];
+    __shared__ uint32_t bmu_s;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        // lexicographic minimum over the per-rank records: lowest distance, then lowest neuron index
+        unsigned long long bc = a.pairs[0].code, bn = a.pairs[0].neuron;
+        for (uint32_t r = 1; r < a.world; ++r)
+            if (pair_less(a.pairs[r].code, a.pairs[r].neuron, bc, bn)) { bc = a.pairs[r].code; bn = a.pairs[r].neuron; }
+        const uint32_t bmu = (uint32_t)bn;
+        bmu_s = bmu;
+        if (blockIdx.x == 0 && bmu >= a.first_neuron && bmu - a.first_neuron < a.n) {   // this rank owns the unit
+            atomicAdd(&a.counts[bmu], 1u);
+            if (a.bmu_log) *a.bmu_log = bmu;
+        }
+    }
+    __syncthreads();
+    const float* frow = a.factors + (size_t)bmu_s * a.n;
+    const uint32_t start = blockIdx.x * kListThreads, i = start + threadIdx.x;
+    const float f = i < a.n ? frow[i] : 0.0f;
+    const unsigned long long key = i < a.n ? a.keys[i] : 0ull;
+    uint32_t pre = 0;                                   // non-zero factors before this block, counted per warp
+    for (uint32_t j = threadIdx.x; j < start; j += kListThreads) pre += __popc(__ballot_sync(0xffffffffu, frow[j] != 0.0f));
+    const uint32_t ballot = __ballot_sync(0xffffffffu, f != 0.0f);
+    if (lane == 0) { warp_cnt[warp] = __popc(ballot); warp_pre[warp] = pre; }
+    __syncthreads();
+    uint32_t slot = __popc(ballot & ((1u << lane) - 1)), total = 0;
+    for (uint32_t wv = 0; wv < kListThreads / 32; ++wv) {
+        slot += warp_pre[wv] + (wv < warp ? warp_cnt[wv] : 0);
+        total += warp_pre[wv] + warp_cnt[wv];
+    }
+    if (i < a.n) {
+        a.keys[i] = kKeyEmpty;                          // re-arm every key for the next image's distance kernel
+        if (f != 0.0f) {
+            const uint32_t t = (uint32_t)(key & ((1ull << a.shift) - 1));
+            const uint32_t fl = bmu_div(t, a.magic_R), r = t - fl * a.R;
+            const uint32_t jq = a.q ? bmu_div(r, a.magic_q) : 0;
+            const int32_t nd = (int32_t)a.nd, nd1 = nd - 1, sgn = fl ? -1 : 1;
+            UpdateItem it;
+            it.n = i;
+            it.tq = a.q ? r - jq * a.q : 0;
+            it.f = f;
+            switch (jq) {
+                case 0:  it.ax = sgn * nd;  it.ay = 1;   it.a0 = fl ? nd1 * nd : 0; break;
+                case 1:  it.ax = sgn;       it.ay = -nd; it.a0 = nd1 * nd + (fl ? nd1 : 0); break;
+                case 2:  it.ax = -sgn * nd; it.ay = -1;  it.a0 = fl ? nd1 : nd1 * nd + nd1; break;
+                default: it.ax = -sgn;      it.ay = nd;  it.a0 = fl ? 0 : nd1; break;
+            }
+            a.items[slot] = it;
+        }
+    }
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *a.n_items = total;
 }
 
 constexpr int kUpdThreads = 256;
@@ -131,46 +197,21 @@ update_kernel(Geometry g, UpdateArgs a, uint32_t stage_base, uint32_t magic_nd, 
     float* base_s = reinterpret_cast<float*>(crop_s + ((crop_bytes + 15) & ~size_t(15))); // [P] base rotation
     __shared__ __align__(8) uint64_t bar;
     __shared__ unsigned long long red[kUpdWarps];
-    __shared__ uint32_t t_s;
-    __shared__ float f_s;
 
-    const uint32_t n = blockIdx.x;
+    __shared__ UpdateItem item_s;
+    __shared__ uint32_t live_s;
     if (threadIdx.x == 0) {
-        // Global best matching unit: lexicographic minimum over the per-rank records.
-        unsigned long long bc = a.pairs[0].code, bn = a.pairs[0].neuron;
-        const unsigned long long key = a.keys[n];
-        for (uint32_t r = 1; r < a.world; ++r)
-            if (pair_less(a.pairs[r].code, a.pairs[r].neuron, bc, bn)) { bc = a.pairs[r].code; bn = a.pairs[r].neuron; }
-        const uint32_t bmu = (uint32_t)bn;
-        f_s = a.factors[(size_t)bmu * a.n + n];
-        t_s = (uint32_t)(key & ((1ull << key_shift(MODE)) - 1));
-        a.keys[n] = kKeyEmpty;            // re-arm for the next image's distance kernel
-        if (a.first_neuron + n == bmu) {  // the owner counts the hit
-            a.counts[bmu] += 1;
-            if (a.bmu_log) *a.bmu_log = bmu;
-        }
+        live_s = blockIdx.x < *a.n_items;
+        item_s = a.items[blockIdx.x];     // entries beyond n_items are stale but in bounds
         mbar_init(&bar, 1);
         mbar_fence_init();
     }
     __syncthreads();
-    const float f = f_s;
-    if (f == 0.0f) return;                // uniform for the block
-
-    // Best transform -> (flip, quadrant, base rotation) and the affine map
-    // src = c*nd*nd + ax*x + ay*y + a0 from a neuron pixel (x, y) to the base
-    // rotation: flip reverses rows last (src/CudaLib/flip_kernel.h:28), a
-    // quarter turn maps (x, y) <- (nd-1-y, x) (src/CudaLib/rotate_90_degrees_list.h:28).
-    const uint32_t t = t_s;
-    const uint32_t fl = t / g.R, r = t - fl * g.R;
-    const uint32_t j = g.q ? r / g.q : 0, tq = g.q ? r - j * g.q : 0;
-    const int32_t nd = (int32_t)g.nd, nd1 = nd - 1;
-    int32_t ax, ay, a0;
-    switch (j) {
-        case 0:  ax = fl ? -nd : nd; ay = 1;   a0 = fl ? nd1 * nd : 0; break;
-        case 1:  ax = fl ? -1 : 1;   ay = -nd; a0 = nd1 * nd + (fl ? nd1 : 0); break;
-        case 2:  ax = fl ? nd : -nd; ay = -1;  a0 = fl ? nd1 : nd1 * nd + nd1; break;
-        default: ax = fl ? 1 : -1;   ay = nd;  a0 = fl ? 0 : nd1; break;
-    }
+    if (!live_s) return;                  // fewer neurons to update than blocks
+    const UpdateItem it = item_s;
+    const uint32_t n = it.n, tq = it.tq;
+    const float f = it.f;
+    const int32_t ax = it.ax, ay = it.ay, a0 = it.a0;
     const float* bsrc = a.base + (size_t)tq * g.P;
     if (stage_base && threadIdx.x == 0) {
         // one bulk asynchronous copy (TMA) of the whole base rotation into shared memory
@@ -285,7 +326,6 @@ constexpr int kPipeMaxStages = 4;
 constexpr int kPipeMaxItems = 256;    // neurons one block may own
 constexpr int kPipeUnroll = 3;        // neuron rows a consumer thread processes together
 constexpr int kPipeMaxTasks = 2;      // (row block, column) tasks per thread and neuron
-constexpr int kPipeScan = 4;          // factors a thread ranks per pass of the header scan
 constexpr int kPipeMaxUnits = 2;      // operand groups of four elements per thread and neuron
 
 struct PipeParams
@@ -295,10 +335,6 @@ struct PipeParams
     int* status;
 };
 
-struct PipeItem { uint32_t n, tq; int32_t ax, ay, a0; float f; };
-
-__device__ long long g_tl[148 * 64 * 3];
-
 template <int MODE>
 __global__ void __launch_bounds__(kPipeThreads, 1)
 update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp)
@@ -306,106 +342,29 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp)
     extern __shared__ __align__(128) uint8_t pipe_dyn[];
     __shared__ __align__(8) uint64_t full_bar[kPipeMaxStages], done_bar[kPipeMaxStages];
     __shared__ unsigned long long norm_s[kPipeMaxStages][kPipeConsumerWarps];   // per-warp partial sums of squares
-    __shared__ PipeItem items[kPipeMaxItems];
-    __shared__ uint32_t bmu_s, m_s, scan_s[kPipeThreads / 32];
+    __shared__ UpdateItem items[kPipeMaxItems];
+    __shared__ uint32_t m_s;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // This block takes entries b, b + gridDim.x, ... of the work list, so all blocks
+    // get the same number of neurons (+-1).
+    const uint32_t total = *a.n_items;
+    const uint32_t M = total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    for (uint32_t i = threadIdx.x; i < M; i += kPipeThreads) items[i] = a.items[blockIdx.x + i * gridDim.x];
     if (threadIdx.x == 0) {
-        // Global best matching unit: lexicographic minimum over the per-rank records.
-        unsigned long long bc = a.pairs[0].code, bn = a.pairs[0].neuron;
-        for (uint32_t r = 1; r < a.world; ++r)
-            if (pair_less(a.pairs[r].code, a.pairs[r].neuron, bc, bn)) { bc = a.pairs[r].code; bn = a.pairs[r].neuron; }
-        bmu_s = (uint32_t)bn;
         for (uint32_t s = 0; s < pp.stages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&done_bar[s], kPipeConsumerWarps);
         }
         mbar_fence_init();
+        m_s = M;
     }
     // operand staging starts as zeros: the padding beyond K is never written again
     for (uint32_t s = 0; s < pp.stages; ++s)
         for (uint32_t i = threadIdx.x; i < pp.crop_bytes / 4; i += kPipeThreads)
             reinterpret_cast<uint32_t*>(pipe_dyn + (size_t)s * pp.stage_bytes + pp.off_crop)[i] = 0;
-    __syncthreads();
-
-    // Every block scans the whole factor row of the best matching unit and ranks
-    // the neurons whose factor is non-zero; block b takes the neurons of rank
-    // b, b + gridDim.x, ...  so that all blocks get the same number of neurons
-    // (+-1) however the zero factors are distributed.  For its neurons the block
-    // reads the best transform and decodes it into the affine map
-    // src = c*nd*nd + ax*x + ay*y + a0 from a neuron pixel to the base rotation
-    // (flip reverses rows last, src/CudaLib/flip_kernel.h:28; a quarter turn maps
-    // (x, y) <- (nd-1-y, x), src/CudaLib/rotate_90_degrees_list.h:28).  Keys are
-    // re-armed for the next image: those of ranked neurons by the block that
-    // takes them, the others by block (index mod gridDim.x).
-    const uint32_t bmu = bmu_s;
-    const float* frow = a.factors + (size_t)bmu * a.n;
-    uint32_t rank_base = 0;
-    for (uint32_t p0 = 0; p0 < a.n; p0 += kPipeThreads * kPipeScan) {
-        float fv[kPipeScan];
-        const uint32_t i0 = p0 + threadIdx.x * kPipeScan;
-        uint32_t cnt = 0;
-#pragma unroll
-        for (int e = 0; e < kPipeScan; ++e) {
-            fv[e] = i0 + e < a.n ? frow[i0 + e] : 0.0f;
-            cnt += fv[e] != 0.0f;
-        }
-        uint32_t incl = cnt;
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
-            if ((int)lane >= o) incl += up;
-        }
-        if (lane == 31) scan_s[warp] = incl;
-        __syncthreads();
-        uint32_t before = rank_base, total = 0;
-        for (uint32_t wv = 0; wv < kPipeThreads / 32; ++wv) {
-            const uint32_t tcount = scan_s[wv];
-            if (wv < warp) before += tcount;
-            total += tcount;
-        }
-        uint32_t rank = before + incl - cnt;
-#pragma unroll
-        for (int e = 0; e < kPipeScan; ++e) {
-            const uint32_t n = i0 + e;
-            if (n >= a.n) break;
-            if (fv[e] != 0.0f) {
-                if (rank % gridDim.x == blockIdx.x) {
-                    const unsigned long long key = a.keys[n];
-                    a.keys[n] = kKeyEmpty;
-                    const uint32_t t = (uint32_t)(key & ((1ull << key_shift(MODE)) - 1));
-                    const uint32_t fl = t / g.R, r = t - fl * g.R;
-                    const uint32_t jq = g.q ? r / g.q : 0;
-                    const int32_t nd = (int32_t)g.nd, nd1 = nd - 1;
-                    PipeItem it;
-                    it.n = n;
-                    it.tq = g.q ? r - jq * g.q : 0;
-                    it.f = fv[e];
-                    switch (jq) {
-                        case 0:  it.ax = fl ? -nd : nd; it.ay = 1;   it.a0 = fl ? nd1 * nd : 0; break;
-                        case 1:  it.ax = fl ? -1 : 1;   it.ay = -nd; it.a0 = nd1 * nd + (fl ? nd1 : 0); break;
-                        case 2:  it.ax = fl ? nd : -nd; it.ay = -1;  it.a0 = fl ? nd1 : nd1 * nd + nd1; break;
-                        default: it.ax = fl ? 1 : -1;   it.ay = nd;  it.a0 = fl ? 0 : nd1; break;
-                    }
-                    items[rank / gridDim.x] = it;
-                }
-                ++rank;
-            } else if (n % gridDim.x == blockIdx.x) {
-                a.keys[n] = kKeyEmpty;
-            }
-        }
-        rank_base += total;
-        __syncthreads();                  // scan_s is reused by the next pass
-    }
-    if (threadIdx.x == 0) {
-        m_s = rank_base > blockIdx.x ? (rank_base - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-        if (blockIdx.x == 0 && bmu >= a.first_neuron && bmu - a.first_neuron < a.n) {   // the owner counts the hit
-            a.counts[bmu] += 1;
-            if (a.bmu_log) *a.bmu_log = bmu;
-        }
-    }
     fence_async_smem();                   // zeroed operand staging visible to later bulk stores
     __syncthreads();
-    const uint32_t M = m_s;
     const uint32_t plane_bytes = g.P * 4;
 
     if (warp == 0) {
@@ -493,14 +452,12 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp)
         const uint32_t nd = g.nd;
         for (uint32_t jx = 0; jx < M; ++jx) {
             const uint32_t s = jx % pp.stages, ph = (jx / pp.stages) & 1;
-            long long c0 = clock64();
             if (!mbar_wait(&full_bar[s], ph)) { if (pp.status) atomicCAS(pp.status, kDevOk, kDevTimeoutUpdateConsumer); break; }
             uint8_t* st = pipe_dyn + (size_t)s * pp.stage_bytes;
             float* som_s = reinterpret_cast<float*>(st);
             const float* base_s = reinterpret_cast<const float*>(st + pp.off_base);
             uint8_t* crop_s = st + pp.off_crop;
-            long long c1 = clock64();
-            const PipeItem it = items[jx];
+            const UpdateItem it = items[jx];
             const float f = it.f;
             const int32_t ax = it.ax;
             // -- w <- w - (w - r) * f over the whole neuron, kPipeUnroll rows per step:
@@ -561,7 +518,6 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp)
             fence_async_smem();           // this thread's stage writes before the producer's bulk stores
             __syncwarp();
             if (lane == 0) mbar_arrive(&done_bar[s]);
-            if (ctid == 0 && jx < 64) { long long* d = g_tl + (blockIdx.x * 64 + jx) * 3; d[0] = c0; d[1] = c1; d[2] = clock64(); }
         }
     }
 }
@@ -673,13 +629,12 @@ cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t
 
 } // namespace
 
-cudaError_t launch_bmu(const BmuArgs& a, cudaStream_t st)
+cudaError_t launch_bmu(const BmuArgs& a, uint32_t phase, cudaStream_t st)
 {
-    bmu_kernel<<<1, kBmuThreads, 0, st>>>(a);
+    if (phase & 1u) bmu_kernel<<<1, kBmuThreads, 0, st>>>(a);
+    if (phase & 2u) worklist_kernel<<<(a.n + kListThreads - 1) / kListThreads, kListThreads, 0, st>>>(a);
     return cudaGetLastError();
 }
-
-void fetch_tl(long long* host) { cudaDeviceSynchronize(); cudaMemcpyFromSymbol(host, g_tl, sizeof(long long) * 148 * 64 * 3); }
 
 cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st, int* status)
 {

@@ -206,6 +206,25 @@ uint32_t pink_b200_operand_stride(uint32_t K, uint32_t dist_type);
 int pink_b200_op_rotate(const pink_b200_config* cfg, const float* dev_images, uint32_t n_img,
                         float* dev_base, void* dev_b0, void* dev_b1, void* dev_bnorm, void* stream);
 
+/* Same computation and arguments as pink_b200_op_rotate, for callers that cannot
+ * allocate device memory: it calls neither cudaMalloc nor cudaFree nor any other
+ * allocating routine.  (This entry has no counterpart in the reference.)
+ * Who needs it: code that runs while the CUDA allocator must not be entered --
+ * inside the callbacks of a caching allocator or memory pool, in a process that
+ * has handed all device memory to its own arena, or in a loop that cannot afford
+ * the implicit device synchronisation of cudaMalloc / cudaFree.
+ * The table of rotation angles (the scratch pink_b200_op_rotate allocates per
+ * call) lives in a fixed 32 KB device array inside the library, held by every GPU
+ * that loads it until the process exits.  Limits and rules:
+ *   - at most 16384 rotations (4096 per quadrant); more returns PINK_B200_EINVAL;
+ *   - the first call on a device looks up the array's device address; make that
+ *     first call before any stream capture begins;
+ *   - all calls share the one array (each overwrites the part it uses), so two
+ *     calls whose GPU work may overlap -- different streams or host threads --
+ *     race; serialise them.  The call returns after its work on `stream` is done. */
+int pink_b200_op_rotate_static(const pink_b200_config* cfg, const float* dev_images, uint32_t n_img,
+                               float* dev_base, void* dev_b0, void* dev_b1, void* dev_bnorm, void* stream);
+
 /* SOM half of the crop/convert (generate_euclidean_distance_matrix.h:64-84). */
 int pink_b200_op_quantize_som(const pink_b200_config* cfg, const float* dev_som, uint32_t n_neurons,
                               void* dev_a0, void* dev_a1, void* dev_anorm, void* stream);

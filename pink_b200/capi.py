@@ -59,6 +59,8 @@ SYMBOLS = {
     "pink_b200_operand_stride": (C.c_uint32, [C.c_uint32, C.c_uint32]),
     "pink_b200_op_rotate": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p]),
+    "pink_b200_op_rotate_static": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p,
+                                             C.c_void_p, C.c_void_p, C.c_void_p]),
     "pink_b200_op_quantize_som": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p,
                                             C.c_void_p, C.c_void_p]),
     "pink_b200_op_distance": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p,

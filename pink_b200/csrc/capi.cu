@@ -133,6 +133,11 @@ void free_dev(T*& p)
 
 } // namespace
 
+namespace pinkb {
+int geometry_from_config(const pink_b200_config* cfg, Geometry* g) { return cfg && g ? make_geometry(*cfg, g) : fail(PINK_B200_EINVAL, "null argument"); }
+int report_error(int code, const char* msg) { return fail(code, msg); }
+} // namespace pinkb
+
 struct pink_b200_ctx
 {
     pink_b200_config cfg{};

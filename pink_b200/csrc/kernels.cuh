@@ -7,6 +7,8 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+struct pink_b200_config;
+
 namespace pinkb {
 
 // Distance modes; numbering follows pink::DataType (UtilitiesLib/DataType.h).
@@ -109,5 +111,11 @@ cudaError_t launch_map_finalize(const Geometry& g, unsigned long long* keys, uin
                          float* dist, uint32_t* rot, cudaStream_t st);
 
 cudaError_t launch_fill_keys(unsigned long long* keys, size_t count, cudaStream_t st);
+
+// Helpers of the C-ABI layer that entry points defined beside their kernels use:
+// validate a configuration into a Geometry (returns a PINK_B200_* status and sets
+// the calling thread's error message), and record an error message.
+int geometry_from_config(const pink_b200_config* cfg, Geometry* g);
+int report_error(int code, const char* msg);
 
 } // namespace pinkb

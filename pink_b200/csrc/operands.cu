@@ -17,7 +17,10 @@
 // separately (__fmul_rn/__fadd_rn are never contracted to FMA), in the order
 // of the reference's CPU code (src/ImageProcessingLib/rotate.h:31-63), so the
 // float pixels are bit-identical to the CPU reference built without FMA.
+#include "../../include/pink_b200.h"
 #include "kernels.cuh"
+
+#include <cmath>
 
 namespace pinkb {
 
@@ -362,3 +365,80 @@ cudaError_t launch_fill_keys(unsigned long long* keys, size_t count, cudaStream_
 }
 
 } // namespace pinkb
+
+// ---------------------------------------------------------------------------
+// Rotation-set entry point that never allocates.
+//
+// pink_b200_op_rotate stages the cos/sin table of the rotation angles in device
+// memory it obtains with cudaMalloc on every call.  Some callers must not do
+// that: code running while the CUDA allocator is locked or forbidden (inside a
+// memory-pool or caching-allocator callback, in a process whose device memory
+// is fully pre-reserved by its own arena, or in a latency-critical loop where an
+// implicit device synchronisation of cudaMalloc/cudaFree is unacceptable).
+// For them the table lives in the fixed device array below, which every GPU
+// that loads this library holds until the process exits.
+namespace pinkb {
+namespace {
+
+constexpr uint32_t kStaticMaxQuadrant = 4096;     // rotations per quadrant, i.e. number_of_rotations <= 16384
+static __device__ __align__(256) float g_rotate_scratch[2 * kStaticMaxQuadrant];   // [cos | sin], 32 KB
+
+// Device address of the scratch array on the current device (looked up once per device).
+cudaError_t rotate_scratch_address(float** out)
+{
+    constexpr int kMaxDevices = 64;
+    static float* addr[kMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!addr[dev]) {
+        // In host code the array's name is only a handle; the kernels need its device address.
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_rotate_scratch);
+        if (e != cudaSuccess) return e;
+        addr[dev] = static_cast<float*>(p);
+    }
+    *out = addr[dev];
+    return cudaSuccess;
+}
+
+} // namespace
+} // namespace pinkb
+
+extern "C" int pink_b200_op_rotate_static(const pink_b200_config* cfg, const float* dev_images, uint32_t n_img,
+                                          float* dev_base, void* dev_b0, void* dev_b1, void* dev_bnorm, void* stream)
+{
+    using namespace pinkb;
+    if (!cfg || !dev_images || !dev_b0) return report_error(PINK_B200_EINVAL, "null argument");
+    Geometry g{};
+    int rc = geometry_from_config(cfg, &g);
+    if (rc) return rc;
+    const uint32_t nq = g.q ? g.q : 1;
+    if (nq > kStaticMaxQuadrant)
+        return report_error(PINK_B200_EINVAL,
+                            "pink_b200_op_rotate_static supports at most 16384 rotations (4096 per quadrant); "
+                            "use pink_b200_op_rotate for more");
+    if (!dev_base && (size_t)g.P * sizeof(float) > kRotateSmemLimit)
+        return report_error(PINK_B200_EINVAL, "dev_base is required when a base rotation does not fit shared memory");
+    float* scratch = nullptr;
+    cudaError_t e = rotate_scratch_address(&scratch);
+    if (e != cudaSuccess) return report_error(PINK_B200_ECUDA, cudaGetErrorString(e));
+
+    // cos/sin of t * (float(2*pi)/R), t < R/4, with the reference's expressions
+    // (src/SelfOrganizingMapLib/generate_rotated_images.h:70, src/ImageProcessingLib/rotate.h:20-21).
+    static thread_local float table[2 * kStaticMaxQuadrant];
+    const float step = static_cast<float>(2 * M_PI) / g.R;
+    for (uint32_t t = 0; t < nq; ++t) {
+        const float angle = t * step;
+        table[t] = std::cos(angle);
+        table[nq + t] = std::sin(angle);
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The shared array still holds the previous call's table; the part this call uses is overwritten in full.
+    e = cudaMemcpyAsync(scratch, table, 2 * nq * sizeof(float), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = launch_rotate(g, dev_images, n_img, scratch, scratch + nq, dev_base, dev_b0, dev_b1, dev_bnorm, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);      // `table` is reused by this thread's next call
+    if (e != cudaSuccess) return report_error(PINK_B200_ECUDA, cudaGetErrorString(e));
+    return PINK_B200_OK;
+}

@@ -1,0 +1,69 @@
+"""Neuron-sharded training on several GPUs (one process per GPU, NCCL exchange of the per-shard BMU records)
+against the single-process CPU oracle.  Needs at least two GPUs; skipped otherwise."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, mode, q):
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch
+    import torch.distributed as dist
+    from pink_b200 import capi, engine
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    lay, s0, s1, idim, nd, ed, R, flip, n_img = 0, 5, 4, 32, 22, 15, 40, True, 6
+    N = s0 * s1
+    rng = np.random.default_rng(77)
+    som = rng.random((N, 1, nd, nd), dtype=np.float32)
+    som[13] = som[4]                                   # identical neurons in different shards: BMU ties
+    imgs = rng.random((n_img, 1, idim, idim), dtype=np.float32)
+    F = engine.update_factors(lay, s0, s1, capi.FUNC_GAUSSIAN, 1.1, 0.2)
+    eng = engine.Engine(N, 1, idim, nd, ed, R, flip, mode, device=rank, rank=rank, world_size=world)
+    uid = [engine.Engine.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(uid, 0)
+    eng.comm_init(uid[0])
+    eng.set_som(som)
+    eng.set_update_factors(F)
+    eng.train(imgs)
+    eng.synchronize()
+    part = eng.get_som(np.zeros_like(som))
+    counts = eng.update_counts()
+    out = [None] * world
+    dist.all_gather_object(out, (eng.first, eng.count, part[eng.first:eng.first + eng.count], counts))
+    if rank == 0:
+        whole = np.concatenate([p[2] for p in sorted(out, key=lambda p: p[0])])
+        q.put((whole, sum(p[3] for p in out), som, imgs, F))
+    eng.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", [2, 1])
+def test_two_gpu_sharded_training_bit_exact(cuda, mode):
+    torch = cuda
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    import oracle as O
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29700 + mode + (os.getpid() % 100)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, mode, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    whole, counts, som, imgs, F = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    want = som.copy()
+    bmus = [O.train_step(want, im, F, 15, 40, True, mode)[2] for im in imgs]
+    assert np.array_equal(whole.view(np.uint32), want.view(np.uint32))
+    assert counts.sum() == len(imgs) and all(counts[b] > 0 for b in bmus)

@@ -98,13 +98,19 @@ __device__ __forceinline__ typename StageType<MODE>::type to_stage(float v)
 // One block = one base rotation of one image.
 // Phase 1 walks the neuron-sized output row by row (a warp per row, lanes along
 // the row) so that the row terms of the inverse rotation are computed once per
-// row; the float pixel goes to global memory (the update step reads it) and its
-// converted value (uint8 / uint16 / float) is staged in shared memory.
+// row and the column terms once per thread; the float pixel goes to global
+// memory (the update step reads it) and its converted value (uint8 / uint16 /
+// float) is staged in shared memory -- for uint8 also transposed.
 // Phase 2 emits, for each of the up to eight transforms that are index
-// permutations of this base, the K-contiguous operand row: a thread gathers 16
-// consecutive operand elements from the staged plane along the transform's
-// affine source map, packs them and stores 16 bytes per plane; sums of squares
+// permutations of this base, the K-contiguous operand row, 16 elements per
+// thread and store.  In uint8 mode a run of 16 operand bytes inside one row of
+// the distance region is a contiguous (ascending or descending) run of bytes of
+// the staged plane or of its transpose, so it is fetched with five aligned
+// 32-bit loads and funnel shifts instead of sixteen byte gathers; sums of squares
 // use dp4a on the packed bytes.
+constexpr uint32_t kRotMaxSlots = 8;          // column slots (of 32) per thread with hoisted column terms
+constexpr uint32_t kStagePad = 16;            // slack around the staged byte planes for aligned over-reads
+
 template <int MODE>
 __global__ void __launch_bounds__(kRotThreads)
 rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, uint32_t magic_nd, uint32_t magic_ed,
@@ -113,7 +119,9 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
 {
     using stage_t = typename StageType<MODE>::type;
     extern __shared__ __align__(16) uint8_t rot_dyn[];
-    stage_t* stage = reinterpret_cast<stage_t*>(rot_dyn);
+    // uint8: [pad | plane | pad | transposed plane | pad]; other modes: the plane only
+    stage_t* stage = reinterpret_cast<stage_t*>(rot_dyn + (MODE == kModeU8 ? kStagePad : 0));
+    uint8_t* stage_tr = rot_dyn + 2 * kStagePad + ((g.P + 15) & ~15u);
     __shared__ unsigned long long norm_s[8];
 
     const uint32_t tq = blockIdx.x, img_i = blockIdx.y;
@@ -129,40 +137,68 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
         const float sc = (g.id - 1) * 0.5f, dc = (g.nd - 1) * 0.5f, lim = (float)(g.id - 1);
         const float ca = tq ? cs[tq] : 1.0f, sa = tq ? sn[tq] : 0.0f;
         const uint32_t rows = g.C * g.nd;
+        const uint32_t slots = (g.nd + 31) / 32;
+        const bool hoisted = slots <= kRotMaxSlots;
+        float pys[kRotMaxSlots], pyc[kRotMaxSlots];               // column terms py*sin, py*cos of this thread's columns
+#pragma unroll
+        for (uint32_t i = 0; i < kRotMaxSlots; ++i) {
+            const float py = __fsub_rn((float)(lane + 32 * i), dc);
+            pys[i] = __fmul_rn(py, sa);
+            pyc[i] = __fmul_rn(py, ca);
+        }
         for (uint32_t row = warp; row < rows; row += kRotThreads / 32) {
             const uint32_t c = fast_div(row, magic_nd), x = row - c * g.nd;
             const float* plane = img + (size_t)c * g.id * g.id;
             const float px = __fsub_rn((float)x, dc);
             const float xc = __fmul_rn(px, ca), xs = __fmul_rn(px, sa);
-            for (uint32_t y = lane; y < g.nd; y += 32) {
+            // one output pixel; ys, yc are the column terms py*sin, py*cos
+            auto pixel = [&](uint32_t y, float ys, float yc) {
                 float v;
                 if (tq == 0) {
                     v = resize_pixel(plane, g.id, g.nd, x, y);
                 } else {
                     // inverse rotation and bilinear taps; every product and sum rounded
                     // separately, in the order of src/ImageProcessingLib/rotate.h:37-63
-                    const float py = __fsub_rn((float)y, dc);
-                    const float sx = __fadd_rn(__fsub_rn(xc, __fmul_rn(py, sa)), sc);
-                    const float sy = __fadd_rn(__fadd_rn(xs, __fmul_rn(py, ca)), sc);
+                    const float sx = __fadd_rn(__fsub_rn(xc, ys), sc);
+                    const float sy = __fadd_rn(__fadd_rn(xs, yc), sc);
                     v = 0.0f;
                     if (!(sx < 0.0f || sx > lim || sy < 0.0f || sy > lim)) {
-                        const uint32_t ix = (uint32_t)sx, iy = (uint32_t)sy;
+                        // floor by adding 2^23 with truncation: exact for 0 <= s < 2^23, and it keeps
+                        // the conversions off the (slow) conversion pipe
+                        const float tx = __fadd_rz(sx, 8388608.0f), ty = __fadd_rz(sy, 8388608.0f);
+                        const uint32_t ix = __float_as_uint(tx) & 0x7FFFFFu, iy = __float_as_uint(ty) & 0x7FFFFFu;
+                        const float rx = __fsub_rn(sx, __fsub_rn(tx, 8388608.0f));
+                        const float ry = __fsub_rn(sy, __fsub_rn(ty, 8388608.0f));
                         // the +1 taps carry weight 0 when they would fall outside; clamp the index
-                        const uint32_t ix1 = min(ix + 1, g.id - 1), iy1 = min(iy + 1, g.id - 1);
-                        const float rx = __fsub_rn(sx, (float)ix), ry = __fsub_rn(sy, (float)iy);
+                        const uint32_t dx = ix + 1 < g.id ? g.id : 0u, dy = iy + 1 < g.id ? 1u : 0u;
                         const float cx = __fsub_rn(1.0f, rx), cy = __fsub_rn(1.0f, ry);
-                        const float* r0 = plane + (size_t)ix * g.id;
-                        const float* r1 = plane + (size_t)ix1 * g.id;
-                        const float t00 = __fmul_rn(__fmul_rn(cx, cy), __ldg(r0 + iy));
-                        const float t01 = __fmul_rn(__fmul_rn(cx, ry), __ldg(r0 + iy1));
-                        const float t10 = __fmul_rn(__fmul_rn(rx, cy), __ldg(r1 + iy));
-                        const float t11 = __fmul_rn(__fmul_rn(rx, ry), __ldg(r1 + iy1));
+                        const float* r0 = plane + (ix * g.id + iy);
+                        const float t00 = __fmul_rn(__fmul_rn(cx, cy), __ldg(r0));
+                        const float t01 = __fmul_rn(__fmul_rn(cx, ry), __ldg(r0 + dy));
+                        const float t10 = __fmul_rn(__fmul_rn(rx, cy), __ldg(r0 + dx));
+                        const float t11 = __fmul_rn(__fmul_rn(rx, ry), __ldg(r0 + dx + dy));
                         v = __fadd_rn(__fadd_rn(__fadd_rn(t00, t01), t10), t11);
                     }
                 }
                 const uint32_t idx = row * g.nd + y;
-                if (use_smem) stage[idx] = to_stage<MODE>(v);
+                if (use_smem) {
+                    const stage_t sv = to_stage<MODE>(v);
+                    stage[idx] = sv;
+                    if (MODE == kModeU8) stage_tr[c * P1 + y * g.nd + x] = (uint8_t)sv;
+                }
                 if (base_out) gbase[idx] = v;
+            };
+            if (hoisted) {
+#pragma unroll
+                for (uint32_t i = 0; i < kRotMaxSlots; ++i) {
+                    const uint32_t y = lane + 32 * i;
+                    if (y < g.nd) pixel(y, pys[i], pyc[i]);
+                }
+            } else {
+                for (uint32_t y = lane; y < g.nd; y += 32) {
+                    const float py = __fsub_rn((float)y, dc);
+                    pixel(y, __fmul_rn(py, sa), __fmul_rn(py, ca));
+                }
             }
         }
     }
@@ -185,11 +221,36 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
             default: ax = f ? 1 : -1;   ay = nd;  a0 = f ? 0 : nd1; break;
         }
         a0 += (ax + ay) * (int32_t)g.off;            // x = off + i, y = off + jj
+        const bool asc = j == 0 || j == 3;           // source bytes ascend with the operand index
+        const uint8_t* run_plane = (j & 1) ? stage_tr : reinterpret_cast<const uint8_t*>(stage);
         unsigned long long acc = 0;
         for (uint32_t gi = threadIdx.x; gi < groups; gi += kRotThreads) {
             const uint32_t k = gi * kGroup;
             uint32_t r = fast_div(k, magic_ed), jj = k - r * g.ed;                  // r = c * ed + i
             uint32_t c = fast_div(r, magic_ed), i = r - c * g.ed;
+            if (MODE == kModeU8 && use_smem && jj + 16 <= g.ed) {
+                // whole group inside one row of the region: one contiguous run of 16 staged bytes
+                const uint32_t x = g.off + i, sx = f ? (uint32_t)nd1 - x : x, y0 = g.off + jj;
+                const uint32_t rowsel = j < 2 ? sx : (uint32_t)nd1 - sx;
+                const uint32_t first = c * P1 + rowsel * g.nd + (asc ? y0 : (uint32_t)nd1 - y0 - 15u);
+                const uint8_t* pa = run_plane + first;
+                const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(pa) & 3u);
+                const uint32_t* pw = reinterpret_cast<const uint32_t*>(pa - mis);
+                uint32_t w[5], o[4];
+#pragma unroll
+                for (int m = 0; m < 5; ++m) w[m] = pw[m];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) o[m] = __funnelshift_r(w[m], w[m + 1], mis * 8);
+                if (!asc) {
+                    const uint32_t r0 = __byte_perm(o[3], 0, 0x0123), r1 = __byte_perm(o[2], 0, 0x0123);
+                    const uint32_t r2 = __byte_perm(o[1], 0, 0x0123), r3 = __byte_perm(o[0], 0, 0x0123);
+                    o[0] = r0; o[1] = r1; o[2] = r2; o[3] = r3;
+                }
+#pragma unroll
+                for (int m = 0; m < 4; ++m) acc += __dp4a(o[m], o[m], 0u);
+                reinterpret_cast<uint4*>(static_cast<uint8_t*>(b0) + orow * g.Kp)[gi] = make_uint4(o[0], o[1], o[2], o[3]);
+                continue;
+            }
             int32_t s = (int32_t)(c * P1) + ax * (int32_t)i + ay * (int32_t)jj + a0;
             stage_t val[kGroup];
 #pragma unroll
@@ -312,7 +373,8 @@ template <int MODE>
 cudaError_t rotate_dispatch(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
                      float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st)
 {
-    size_t smem = (size_t)g.P * sizeof(typename StageType<MODE>::type);
+    size_t smem = MODE == kModeU8 ? 2 * (((size_t)g.P + 15) & ~size_t(15)) + 3 * kStagePad
+                                  : (size_t)g.P * sizeof(typename StageType<MODE>::type);
     uint32_t use_smem = smem <= kRotateSmemLimit;
     if (!use_smem) smem = 0;
     // Dynamic shared memory above 48 KB is an opt-in, per-device function attribute.

@@ -239,7 +239,9 @@ def main():
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    launches0 = eng.launch_count()
     ms = timed(lambda s: step_dev(args.warmup + s), args.steps)
+    launches = eng.launch_count() - launches0          # kernels of this library launched inside the timed region
     clocks = sampler.stop() if rank == 0 else None
     value = args.steps * B / (ms * 1e-3)
 
@@ -313,7 +315,7 @@ def main():
                              "(11 MB) + batch (34 MB) exceed the 126 MB L2"},
             "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": B * isz * 4, "d2h_bytes_per_step": N * 4,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": args.steps * (B * 3 + (B + 15) // 16),
+            "gpu_launches": launches,
             "clocks": clocks,
             "roofline": roof,
             "kernels": kernels,

@@ -177,6 +177,10 @@ int pink_b200_synchronize(pink_b200_ctx* ctx);
  * time or order work against it. */
 void* pink_b200_stream(pink_b200_ctx* ctx);
 
+/* Number of CUDA kernels the context has launched since it was created (the
+ * reference has no counterpart; benchmarks report it). */
+uint64_t pink_b200_launch_count(pink_b200_ctx* ctx);
+
 /* Opt-in phase timing (the reference only has a wall clock around the whole
  * run, src/Pink/main.cpp:37-62).  After profile_begin, CUDA events on the
  * context's streams bracket the kernels of each of the next max_steps

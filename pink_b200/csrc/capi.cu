@@ -161,6 +161,8 @@ struct pink_b200_ctx
     unsigned long long* d_keys = nullptr; size_t key_imgs = 0;
     BmuPair* d_pairs = nullptr;
     UpdateItem* d_items = nullptr; uint32_t* d_nitems = nullptr;   // per-step work list of the update
+    uint64_t launches = 0;            // kernels launched by this context so far
+    bool fuse_update = false;         // the update kernel finds the best matching unit and its work list itself
     uint32_t* d_counts = nullptr;
     uint32_t* d_bmu_log = nullptr; size_t bmu_log_cap = 0, bmu_log_n = 0;
     int* d_status = nullptr;
@@ -206,6 +208,7 @@ int ensure_transform_buffers(pink_b200_ctx* c, size_t imgs, size_t base_needed)
         free_dev(c->d_keys);
         CU_TRY(cudaMalloc(&c->d_keys, imgs * c->count * sizeof(unsigned long long)));
         LAUNCH_TRY(launch_fill_keys(c->d_keys, imgs * c->count, c->stream));
+        c->launches += 1;
         c->key_imgs = imgs;
     }
     CU_TRY(cudaStreamSynchronize(c->stream));   // initialisation complete before other streams touch the buffers
@@ -267,12 +270,17 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     ba.R = g.R; ba.q = g.q; ba.nd = g.nd;
     ba.magic_R = g.R == 1 ? 0u : (uint32_t)((1ull << 32) / g.R) + 1;
     ba.magic_q = g.q <= 1 ? 0u : (uint32_t)((1ull << 32) / g.q) + 1;
+    ba.arrive = c->d_nitems + 1;
+    // Fused form: the update kernel reduces the keys (or the exchanged records) and derives its
+    // work list itself; otherwise a reduction and a compaction kernel run in between.
+    const bool fused = c->fuse_update;
     if (c->cfg.world_size == 1) {
-        LAUNCH_TRY(launch_bmu(ba, 3, c->stream));
+        if (!fused) { LAUNCH_TRY(launch_bmu(ba, 3, c->stream)); c->launches += 2; }
     } else {
         LAUNCH_TRY(launch_bmu(ba, 1, c->stream));
+        c->launches += 1;
         NCCL_TRY(nccl().AllGather(c->d_pairs + c->cfg.rank, c->d_pairs, 2, ncclUint64, c->comm, c->stream));
-        LAUNCH_TRY(launch_bmu(ba, 2, c->stream));
+        if (!fused) { LAUNCH_TRY(launch_bmu(ba, 2, c->stream)); c->launches += 1; }
     }
     UpdateArgs ua{};
     ua.som = c->d_som;
@@ -280,7 +288,9 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     ua.items = c->d_items; ua.n_items = c->d_nitems; ua.n = c->count;
     ua.a0 = c->d_a0; ua.a1 = c->d_a1; ua.anorm = c->d_anorm;
     if (ev) CU_TRY(cudaEventRecord(ev[2], c->stream));
-    LAUNCH_TRY(launch_update(g, ua, c->stream, c->d_status));
+    if (fused) LAUNCH_TRY(launch_update_fused(g, ua, ba, c->stream, c->d_status));
+    else LAUNCH_TRY(launch_update(g, ua, c->stream, c->d_status));
+    c->launches += 2;                 // distance + update
     if (ev) CU_TRY(cudaEventRecord(ev[3], c->stream));
     return PINK_B200_OK;
 }
@@ -307,6 +317,7 @@ int train_chunk(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* l
                                  c->d_b1 ? static_cast<uint8_t*>(c->d_b1) + row0 * g.Kp * esz : nullptr,
                                  static_cast<uint8_t*>(c->d_bnorm) + row0 * (g.mode == kModeU16 ? 8 : 4),
                                  c->rot_stream));
+        c->launches += 1;
         if (ev) CU_TRY(cudaEventRecord(ev[1], c->rot_stream));
         CU_TRY(cudaEventRecord(c->rotated[slot ? 1 : 0], c->rot_stream));
         CU_TRY(cudaStreamWaitEvent(c->stream, c->rotated[slot ? 1 : 0], 0));
@@ -404,6 +415,10 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
         CTX_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
         CTX_TRY(cudaStreamCreateWithPriority(&c->stream, cudaStreamNonBlocking, hi));
         CTX_TRY(cudaStreamCreateWithPriority(&c->copy_stream, cudaStreamNonBlocking, hi));
+        // Diagnostic switches (timing the kernels in isolation, exercising the unfused path):
+        // PINK_B200_ROT_SERIAL puts the rotation kernels on the training stream,
+        // PINK_B200_SPLIT_UPDATE keeps best-matching-unit reduction and work list in kernels of their own.
+        c->fuse_update = update_can_fuse(c->g) && !getenv("PINK_B200_SPLIT_UPDATE");
         if (getenv("PINK_B200_ROT_SERIAL")) c->rot_stream = c->stream;
         else CTX_TRY(cudaStreamCreateWithPriority(&c->rot_stream, cudaStreamNonBlocking, lo));
     }
@@ -426,8 +441,8 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     CTX_TRY(cudaMemsetAsync(c->d_pairs, 0xFF, W * sizeof(BmuPair), c->stream));
     CTX_TRY(cudaMalloc(&c->d_items, c->count * sizeof(UpdateItem)));
     CTX_TRY(cudaMemsetAsync(c->d_items, 0, c->count * sizeof(UpdateItem), c->stream));
-    CTX_TRY(cudaMalloc(&c->d_nitems, sizeof(uint32_t)));
-    CTX_TRY(cudaMemsetAsync(c->d_nitems, 0, sizeof(uint32_t), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_nitems, 2 * sizeof(uint32_t)));       // [0] work-list length, [1] block arrival counter
+    CTX_TRY(cudaMemsetAsync(c->d_nitems, 0, 2 * sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_counts, N * sizeof(uint32_t)));
     CTX_TRY(cudaMemsetAsync(c->d_counts, 0, N * sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_status, sizeof(int)));
@@ -530,6 +545,7 @@ int pink_b200_set_som(pink_b200_ctx* c, const float* host_som)
                              (size_t)g.P * sizeof(float), (size_t)g.P * sizeof(float), c->count,
                              cudaMemcpyHostToDevice, c->stream));
     LAUNCH_TRY(launch_quantize_som(g, c->d_som, c->count, c->d_a0, c->d_a1, c->d_anorm, c->stream));
+    c->launches += 1;
     CU_TRY(cudaStreamSynchronize(c->stream));
     c->have_som = true;
     return PINK_B200_OK;
@@ -636,6 +652,7 @@ static int map_chunk(pink_b200_ctx* c, const float* d_images, uint32_t m, float*
     cudaError_t e = launch_distance(g, da, c->stream, &why);
     if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
     LAUNCH_TRY(launch_map_finalize(g, c->d_keys, m, c->count, d_dist, d_rot, c->stream));
+    c->launches += 3;                 // rotation set, distance, epilogue
     return PINK_B200_OK;
 }
 
@@ -707,6 +724,8 @@ int pink_b200_synchronize(pink_b200_ctx* c)
 }
 
 void* pink_b200_stream(pink_b200_ctx* c) { return c ? c->stream : nullptr; }
+
+uint64_t pink_b200_launch_count(pink_b200_ctx* c) { return c ? c->launches : 0; }
 
 int pink_b200_profile_begin(pink_b200_ctx* c, uint32_t max_steps)
 {

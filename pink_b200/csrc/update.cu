@@ -101,6 +101,26 @@ bmu_kernel(BmuArgs a)
     }
 }
 
+// Transform index -> base rotation and affine source map of a work-list entry.
+__device__ __forceinline__ UpdateItem make_item(const BmuArgs& a, uint32_t i, unsigned long long key, float f)
+{
+    const uint32_t t = (uint32_t)(key & ((1ull << a.shift) - 1));
+    const uint32_t fl = bmu_div(t, a.magic_R), r = t - fl * a.R;
+    const uint32_t jq = a.q ? bmu_div(r, a.magic_q) : 0;
+    const int32_t nd = (int32_t)a.nd, nd1 = nd - 1, sgn = fl ? -1 : 1;
+    UpdateItem it;
+    it.n = i;
+    it.tq = a.q ? r - jq * a.q : 0;
+    it.f = f;
+    switch (jq) {
+        case 0:  it.ax = sgn * nd;  it.ay = 1;   it.a0 = fl ? nd1 * nd : 0; break;
+        case 1:  it.ax = sgn;       it.ay = -nd; it.a0 = nd1 * nd + (fl ? nd1 : 0); break;
+        case 2:  it.ax = -sgn * nd; it.ay = -1;  it.a0 = fl ? nd1 : nd1 * nd + nd1; break;
+        default: it.ax = -sgn;      it.ay = nd;  it.a0 = fl ? 0 : nd1; break;
+    }
+    return it;
+}
+
 constexpr int kListThreads = 256;
 
 // Phase 2, one block per kListThreads neurons: pick the global best matching unit
@@ -144,21 +164,7 @@ worklist_kernel(BmuArgs a)
     if (i < a.n) {
         a.keys[i] = kKeyEmpty;                          // re-arm every key for the next image's distance kernel
         if (f != 0.0f) {
-            const uint32_t t = (uint32_t)(key & ((1ull << a.shift) - 1));
-            const uint32_t fl = bmu_div(t, a.magic_R), r = t - fl * a.R;
-            const uint32_t jq = a.q ? bmu_div(r, a.magic_q) : 0;
-            const int32_t nd = (int32_t)a.nd, nd1 = nd - 1, sgn = fl ? -1 : 1;
-            UpdateItem it;
-            it.n = i;
-            it.tq = a.q ? r - jq * a.q : 0;
-            it.f = f;
-            switch (jq) {
-                case 0:  it.ax = sgn * nd;  it.ay = 1;   it.a0 = fl ? nd1 * nd : 0; break;
-                case 1:  it.ax = sgn;       it.ay = -nd; it.a0 = nd1 * nd + (fl ? nd1 : 0); break;
-                case 2:  it.ax = -sgn * nd; it.ay = -1;  it.a0 = fl ? nd1 : nd1 * nd + nd1; break;
-                default: it.ax = -sgn;      it.ay = nd;  it.a0 = fl ? 0 : nd1; break;
-            }
-            a.items[slot] = it;
+            a.items[slot] = make_item(a, i, key, f);
         }
     }
     if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *a.n_items = total;
@@ -332,33 +338,124 @@ struct PipeParams
 {
     uint32_t stages, stage_bytes, off_base, off_crop, crop_bytes;   // shared-memory layout of a stage
     uint32_t col_chunks, row_blocks, rows_per_block;                // consumer task grid per channel
+    uint32_t fused;                                                 // 1: the kernel derives its work list itself
+    uint32_t magic_grid;                                            // multiply-high reciprocal of the grid size
     int* status;
 };
 
+
 template <int MODE>
 __global__ void __launch_bounds__(kPipeThreads, 1)
-update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp)
+update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
 {
     extern __shared__ __align__(128) uint8_t pipe_dyn[];
     __shared__ __align__(8) uint64_t full_bar[kPipeMaxStages], done_bar[kPipeMaxStages];
     __shared__ unsigned long long norm_s[kPipeMaxStages][kPipeConsumerWarps];   // per-warp partial sums of squares
     __shared__ UpdateItem items[kPipeMaxItems];
-    __shared__ uint32_t m_s;
+    __shared__ unsigned long long red_c[32], red_n[32];
+    __shared__ uint32_t scan_s[32], bmu_s, last_s;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // This block takes entries b, b + gridDim.x, ... of the work list, so all blocks
-    // get the same number of neurons (+-1).
-    const uint32_t total = *a.n_items;
-    const uint32_t M = total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    for (uint32_t i = threadIdx.x; i < M; i += kPipeThreads) items[i] = a.items[blockIdx.x + i * gridDim.x];
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < pp.stages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&done_bar[s], kPipeConsumerWarps);
         }
         mbar_fence_init();
-        m_s = M;
     }
+    // This block takes entries b, b + gridDim.x, ... of the work list (the neurons with a
+    // non-zero factor, ascending), so all blocks get the same number of neurons (+-1).
+    uint32_t total = 0;
+    if (pp.fused) {
+        // Every block derives the best matching unit and its own part of the work list from the
+        // distance kernel's per-neuron minima: two kernel boundaries less per image than reducing
+        // and compacting in kernels of their own, at the price of each block reading the keys
+        // (8 bytes per neuron) and one row of the factor table.
+        // A thread owns four consecutive neurons of every chunk of 4 * kPipeThreads; with a single
+        // chunk (the usual case) their keys stay in registers between the two passes.
+        constexpr uint32_t kChunk = 4 * kPipeThreads;
+        const bool one_chunk = b.n <= kChunk;
+        unsigned long long kreg[4] = {~0ull, ~0ull, ~0ull, ~0ull};
+        auto load_keys = [&](uint32_t i0) {
+            if (i0 + 3 < b.n) {
+                const ulonglong2 k01 = *reinterpret_cast<const ulonglong2*>(b.keys + i0);
+                const ulonglong2 k23 = *reinterpret_cast<const ulonglong2*>(b.keys + i0 + 2);
+                kreg[0] = k01.x; kreg[1] = k01.y; kreg[2] = k23.x; kreg[3] = k23.y;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) kreg[e] = i0 + e < b.n ? b.keys[i0 + e] : ~0ull;
+            }
+        };
+        unsigned long long bc = ~0ull, bn = ~0ull;
+        if (b.world == 1) {
+            for (uint32_t c0 = 0; c0 < b.n; c0 += kChunk) {
+                const uint32_t i0 = c0 + 4 * threadIdx.x;
+                load_keys(i0);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const unsigned long long code = kreg[e] >> b.shift;
+                    if (i0 + e < b.n && pair_less(code, i0 + e, bc, bn)) { bc = code; bn = i0 + e; }
+                }
+            }
+            block_min_pair(bc, bn, red_c, red_n);
+        }
+        if (threadIdx.x == 0) {
+            if (b.world > 1) {
+                // lexicographic minimum over the per-rank records: lowest distance, then lowest neuron index
+                bc = b.pairs[0].code; bn = b.pairs[0].neuron;
+                for (uint32_t r = 1; r < b.world; ++r)
+                    if (pair_less(b.pairs[r].code, b.pairs[r].neuron, bc, bn)) { bc = b.pairs[r].code; bn = b.pairs[r].neuron; }
+            } else {
+                bn += b.first_neuron;
+            }
+            const uint32_t bmu = (uint32_t)bn;
+            bmu_s = bmu;
+            if (blockIdx.x == 0 && bmu >= b.first_neuron && bmu - b.first_neuron < b.n) {   // this rank owns the unit
+                atomicAdd(&b.counts[bmu], 1u);
+                if (b.bmu_log) *b.bmu_log = bmu;
+            }
+        }
+        __syncthreads();
+        const float* frow = b.factors + (size_t)bmu_s * b.n;
+        for (uint32_t c0 = 0; c0 < b.n; c0 += kChunk) {
+            const uint32_t i0 = c0 + 4 * threadIdx.x;
+            float f[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) f[e] = i0 + e < b.n ? frow[i0 + e] : 0.0f;
+            if (!one_chunk || b.world > 1) load_keys(i0);
+            const uint32_t cnt = (f[0] != 0.0f) + (f[1] != 0.0f) + (f[2] != 0.0f) + (f[3] != 0.0f);
+            uint32_t incl = cnt;                                   // inclusive scan over the warp's threads
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+                if ((int)lane >= o) incl += up;
+            }
+            if (lane == 31) scan_s[warp] = incl;
+            __syncthreads();
+            const uint32_t own = scan_s[lane];                     // kPipeThreads / 32 == 32 warps
+            uint32_t wincl = own;                                  // inclusive scan over the warps' totals
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, wincl, o);
+                if ((int)lane >= o) wincl += up;
+            }
+            uint32_t slot = total + __shfl_sync(0xffffffffu, wincl - own, warp) + incl - cnt;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (f[e] != 0.0f) {
+                    const uint32_t local = bmu_div(slot, pp.magic_grid);
+                    if (slot - local * gridDim.x == blockIdx.x && local < (uint32_t)kPipeMaxItems)
+                        items[local] = make_item(b, i0 + e, kreg[e], f[e]);
+                    ++slot;
+                }
+            }
+            total += __shfl_sync(0xffffffffu, wincl, 31);
+            __syncthreads();
+        }
+    } else {
+        total = *a.n_items;
+    }
+    const uint32_t M = total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    if (!pp.fused)
+        for (uint32_t i = threadIdx.x; i < M; i += kPipeThreads) items[i] = a.items[blockIdx.x + i * gridDim.x];
     // operand staging starts as zeros: the padding beyond K is never written again
     for (uint32_t s = 0; s < pp.stages; ++s)
         for (uint32_t i = threadIdx.x; i < pp.crop_bytes / 4; i += kPipeThreads)
@@ -450,6 +547,20 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp)
             }
         }
         const uint32_t nd = g.nd;
+        if (pp.fused) {
+            // The block that is last to have read the keys re-arms them for the next image's
+            // distance kernel; its consumers do so while the first neuron is still in flight.
+            if (ctid == 0) {
+                __threadfence();
+                const uint32_t old = atomicAdd(b.arrive, 1u);
+                last_s = old == gridDim.x - 1;
+                if (old == gridDim.x - 1) *b.arrive = 0;
+                __threadfence();
+            }
+            asm volatile("bar.sync 1, %0;" :: "n"(kPipeConsumers) : "memory");
+            if (last_s)
+                for (uint32_t i = ctid; i < b.n; i += kPipeConsumers) b.keys[i] = kKeyEmpty;
+        }
         for (uint32_t jx = 0; jx < M; ++jx) {
             const uint32_t s = jx % pp.stages, ph = (jx / pp.stages) & 1;
             if (!mbar_wait(&full_bar[s], ph)) { if (pp.status) atomicCAS(pp.status, kDevOk, kDevTimeoutUpdateConsumer); break; }
@@ -581,22 +692,34 @@ int device_sm_count()
     return sms;
 }
 
-template <int MODE>
-cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t st, int* status)
+constexpr size_t kPipeBudget = 216 * 1024;   // of the 227 KB a block may use; the kernel has ~8 KB of static arrays
+
+size_t pipe_stage_bytes(const Geometry& g)
 {
-    // The pipelined kernel needs bulk-copyable planes (16-byte multiples) and at
-    // least two stages of {neuron, base rotation, operand rows} in shared memory.
-    const size_t crop = MODE == kModeF32 ? (size_t)g.Kp * 4 : (MODE == kModeU16 ? (size_t)g.Kp * 2 : g.Kp);
+    const size_t crop = g.mode == kModeF32 ? (size_t)g.Kp * 4 : (g.mode == kModeU16 ? (size_t)g.Kp * 2 : g.Kp);
     const size_t plane = ((size_t)g.P * 4 + 127) & ~size_t(127);
-    const size_t stage = 2 * plane + ((crop + 127) & ~size_t(127));
-    const size_t budget = 216 * 1024;      // of the 227 KB a block may use; the kernel has ~7 KB of static arrays
-    const int sms = device_sm_count();
-    if ((g.P & 3) != 0 || g.P != g.Pp || stage * 2 > budget || sms <= 0) return update_classic<MODE>(g, a, st);
+    return 2 * plane + ((crop + 127) & ~size_t(127));
+}
+
+// The pipelined kernel needs bulk-copyable planes (16-byte multiples), at least two
+// stages of {neuron, base rotation, operand rows} in shared memory, and every
+// consumer thread keeps its tasks and operand units in registers.
+bool pipe_eligible(const Geometry& g)
+{
+    if ((g.P & 3) != 0 || g.P != g.Pp || pipe_stage_bytes(g) * 2 > kPipeBudget || device_sm_count() <= 0) return false;
     const uint32_t chunks = (g.nd + 31) / 32;
     const uint32_t units = ((g.K + 127) / 128) * 32;
-    // every consumer thread keeps its tasks and operand units in registers
-    if (g.C * chunks > (uint32_t)(kPipeMaxTasks * kPipeConsumerWarps) || units > (uint32_t)(kPipeMaxUnits * kPipeConsumers))
-        return update_classic<MODE>(g, a, st);
+    return g.C * chunks <= (uint32_t)(kPipeMaxTasks * kPipeConsumerWarps) && units <= (uint32_t)(kPipeMaxUnits * kPipeConsumers);
+}
+
+template <int MODE>
+cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, const BmuArgs* fused, cudaStream_t st, int* status)
+{
+    if (!pipe_eligible(g)) return fused ? cudaErrorInvalidValue : update_classic<MODE>(g, a, st);
+    const size_t crop = MODE == kModeF32 ? (size_t)g.Kp * 4 : (MODE == kModeU16 ? (size_t)g.Kp * 2 : g.Kp);
+    const size_t plane = ((size_t)g.P * 4 + 127) & ~size_t(127);
+    const size_t stage = pipe_stage_bytes(g), budget = kPipeBudget;
+    const int sms = device_sm_count();
     PipeParams pp{};
     pp.stages = (uint32_t)std::min<size_t>(kPipeMaxStages, budget / stage);
     pp.stage_bytes = (uint32_t)stage;
@@ -610,8 +733,11 @@ cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t
     pp.rows_per_block = (pp.rows_per_block + kPipeUnroll - 1) / kPipeUnroll * kPipeUnroll;   // whole unrolled steps
     pp.row_blocks = (g.nd + pp.rows_per_block - 1) / pp.rows_per_block;
     pp.status = status;
+    pp.fused = fused ? 1u : 0u;
     uint32_t grid = std::min<uint32_t>(a.n, (uint32_t)sms);
     if ((a.n + grid - 1) / grid > (uint32_t)kPipeMaxItems) grid = (a.n + kPipeMaxItems - 1) / kPipeMaxItems;
+    if (fused && (uint64_t)a.n * grid >= (1ull << 32)) return cudaErrorInvalidValue;   // multiply-high division range
+    pp.magic_grid = div_magic(grid);
     const size_t smem = (size_t)pp.stages * stage;
     static int attr_dev = -1;
     static size_t attr_bytes = 0;
@@ -623,7 +749,7 @@ cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, cudaStream_t
         attr_dev = dev;
         attr_bytes = smem;
     }
-    update_pipe_kernel<MODE><<<grid, kPipeThreads, smem, st>>>(g, a, pp);
+    update_pipe_kernel<MODE><<<grid, kPipeThreads, smem, st>>>(g, a, pp, fused ? *fused : BmuArgs{});
     return cudaGetLastError();
 }
 
@@ -639,9 +765,19 @@ cudaError_t launch_bmu(const BmuArgs& a, uint32_t phase, cudaStream_t st)
 cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st, int* status)
 {
     if (a.n == 0) return cudaSuccess;
-    if (g.mode == kModeU8) return update_dispatch<kModeU8>(g, a, st, status);
-    if (g.mode == kModeU16) return update_dispatch<kModeU16>(g, a, st, status);
-    return update_dispatch<kModeF32>(g, a, st, status);
+    if (g.mode == kModeU8) return update_dispatch<kModeU8>(g, a, nullptr, st, status);
+    if (g.mode == kModeU16) return update_dispatch<kModeU16>(g, a, nullptr, st, status);
+    return update_dispatch<kModeF32>(g, a, nullptr, st, status);
+}
+
+bool update_can_fuse(const Geometry& g) { return pipe_eligible(g); }
+
+cudaError_t launch_update_fused(const Geometry& g, const UpdateArgs& a, const BmuArgs& b, cudaStream_t st, int* status)
+{
+    if (a.n == 0 || !b.arrive) return cudaErrorInvalidValue;
+    if (g.mode == kModeU8) return update_dispatch<kModeU8>(g, a, &b, st, status);
+    if (g.mode == kModeU16) return update_dispatch<kModeU16>(g, a, &b, st, status);
+    return update_dispatch<kModeF32>(g, a, &b, st, status);
 }
 
 cudaError_t launch_map_finalize(const Geometry& g, unsigned long long* keys, uint32_t n_img, uint32_t n,

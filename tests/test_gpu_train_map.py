@@ -53,6 +53,35 @@ def test_train_integer_modes_bit_exact(cuda, case, mode):
     assert counts.sum() == n and all(counts[b] > 0 for b in want_bmu)
 
 
+@pytest.mark.parametrize("case", [TRAIN_CASES[0], TRAIN_CASES[4]])
+@pytest.mark.parametrize("mode", [2, 1, 0])
+def test_train_fused_and_split_update_agree(cuda, case, mode, monkeypatch):
+    """The update kernel that finds the best matching unit and its work list itself and the path with
+    separate reduction and compaction kernels give the same SOM, BMU sequence and counters bit for bit."""
+    import pink_b200.capi as capi
+    layout, s0, s1, C_, idim, nd, ed, R, flip, n = case
+    N = _som_size(layout, s0, s1)
+    rng = np.random.default_rng(77)
+    som0 = rng.random((N, C_, nd, nd), dtype=np.float32)
+    imgs = blob_images(n, idim, C_, seed=5).reshape(n, C_, idim, idim)
+    F = O.update_factors(layout, s0, s1, O.FUNC_GAUSSIAN, 1.1, 0.2)
+    out = []
+    for split in (False, True):
+        if split:
+            monkeypatch.setenv("PINK_B200_SPLIT_UPDATE", "1")
+        with Context(capi, make_config(capi, N, C_, idim, nd, ed, R, flip, mode)) as ctx:
+            ctx.set_som(som0)
+            ctx.set_factors(F)
+            log = ctx.train(imgs)
+            log2 = ctx.train(imgs[::-1].copy())
+            out.append((list(log) + list(log2), ctx.get_som(som0).copy(), ctx.counts().copy(),
+                        ctx.e.launch_count()))
+    assert out[0][0] == out[1][0]
+    assert np.array_equal(out[0][1].view(np.uint32), out[1][1].view(np.uint32))
+    assert np.array_equal(out[0][2], out[1][2])
+    assert out[0][3] < out[1][3]          # the fused path really ran: two kernels less per image
+
+
 @pytest.mark.parametrize("case", TRAIN_CASES[:5])
 def test_train_float_mode(cuda, case):
     """float32: one teacher-forced step at a time; the SOM must match the oracle bit for bit whenever

@@ -258,32 +258,30 @@ def main():
 
     # ---- per-kernel device time (separate profiled pass of the same workload) --
     prof_steps = min(B, 256)
+    stats0 = eng.update_stats()
     eng.profile_begin(prof_steps)
     eng.train_device(slice_ptr(d_pool, 1), prof_steps)
     phase_ms, covered = eng.profile_end()
-    bmus = eng.bmu_log(prof_steps)
+    stats1 = eng.update_stats()
 
     peaks = measured_peaks()
     T = w["rotations"] * (2 if w["flip"] else 1)
     K = w["channels"] * w["ed_dim"] ** 2
     P = w["channels"] * w["neuron_dim"] ** 2
     nl = eng.count
-    # neurons this rank actually rewrites per image: non-zero factor for that image's BMU
-    owned = bmus[bmus != 0xFFFFFFFF]
-    nz_rows = (F[:, eng.first:eng.first + nl] != 0).sum(1)
-    if world == 1:
-        n_upd = float(nz_rows[owned].mean()) if len(owned) else float(nl)
-    else:
-        n_upd = float(nz_rows.mean())          # BMUs of other shards are not logged locally
+    # Per image, the update reads every neuron of this shard whose factor is not zero and writes back
+    # those in which at least one value changed (counted on the device), plus their operand rows.
+    n_read = (stats1[0] - stats0[0]) / prof_steps
+    n_written = (stats1[1] - stats0[1]) / prof_steps
     t_dist = phase_ms["distance"] / covered * 1e-3
     t_upd = phase_ms["update"] / covered * 1e-3
     dist_ops = 2.0 * nl * T * K
-    upd_bytes = 8.0 * n_upd * P
+    upd_bytes = 4.0 * P * n_read + (4.0 * P + K) * n_written
     int8_peak = 2.0 * peaks["bf16_tflops"]
     kernels = {
         "update_kernel": {"bound": "hbm", "achieved": upd_bytes / t_upd / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                           "frac": upd_bytes / t_upd / 1e9 / peaks["hbm_gbs"], "us_per_launch": t_upd * 1e6,
-                          "algorithmic_bytes": upd_bytes},
+                          "algorithmic_bytes": upd_bytes, "neurons_read": n_read, "neurons_written": n_written},
         "distance_tc_kernel": {"bound": "tensor", "achieved": dist_ops / t_dist / 1e12, "peak": int8_peak,
                                "unit": "TOP/s", "frac": dist_ops / t_dist / 1e12 / int8_peak,
                                "us_per_launch": t_dist * 1e6, "algorithmic_ops": dist_ops,

@@ -181,6 +181,12 @@ void* pink_b200_stream(pink_b200_ctx* ctx);
  * reference has no counterpart; benchmarks report it). */
 uint64_t pink_b200_launch_count(pink_b200_ctx* ctx);
 
+/* Totals over all training steps of this context (this rank's shard): out[0] =
+ * neurons that had a non-zero update factor, out[1] = neurons written back.
+ * The reference rewrites every neuron (update_neurons.h:34-49); here a neuron
+ * whose new values all equal the old ones bit for bit is read but not written. */
+int pink_b200_get_update_stats(pink_b200_ctx* ctx, uint64_t* out);
+
 /* Opt-in phase timing (the reference only has a wall clock around the whole
  * run, src/Pink/main.cpp:37-62).  After profile_begin, CUDA events on the
  * context's streams bracket the kernels of each of the next max_steps

@@ -161,6 +161,7 @@ struct pink_b200_ctx
     unsigned long long* d_keys = nullptr; size_t key_imgs = 0;
     BmuPair* d_pairs = nullptr;
     UpdateItem* d_items = nullptr; uint32_t* d_nitems = nullptr;   // per-step work list of the update
+    unsigned long long* d_stats = nullptr;   // [0] neurons with a non-zero factor, [1] neurons written back, summed over steps
     uint64_t launches = 0;            // kernels launched by this context so far
     bool fuse_update = false;         // the update kernel finds the best matching unit and its work list itself
     uint32_t* d_counts = nullptr;
@@ -271,6 +272,7 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     ba.magic_R = g.R == 1 ? 0u : (uint32_t)((1ull << 32) / g.R) + 1;
     ba.magic_q = g.q <= 1 ? 0u : (uint32_t)((1ull << 32) / g.q) + 1;
     ba.arrive = c->d_nitems + 1;
+    ba.stats = c->d_stats;
     // Fused form: the update kernel reduces the keys (or the exchanged records) and derives its
     // work list itself; otherwise a reduction and a compaction kernel run in between.
     const bool fused = c->fuse_update;
@@ -441,6 +443,8 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     CTX_TRY(cudaMemsetAsync(c->d_pairs, 0xFF, W * sizeof(BmuPair), c->stream));
     CTX_TRY(cudaMalloc(&c->d_items, c->count * sizeof(UpdateItem)));
     CTX_TRY(cudaMemsetAsync(c->d_items, 0, c->count * sizeof(UpdateItem), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_stats, 2 * sizeof(unsigned long long)));
+    CTX_TRY(cudaMemsetAsync(c->d_stats, 0, 2 * sizeof(unsigned long long), c->stream));
     CTX_TRY(cudaMalloc(&c->d_nitems, 2 * sizeof(uint32_t)));       // [0] work-list length, [1] block arrival counter
     CTX_TRY(cudaMemsetAsync(c->d_nitems, 0, 2 * sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_counts, N * sizeof(uint32_t)));
@@ -482,7 +486,7 @@ int pink_b200_destroy(pink_b200_ctx* c)
     free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
     free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_base);
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
-    free_dev(c->d_items); free_dev(c->d_nitems);
+    free_dev(c->d_items); free_dev(c->d_nitems); free_dev(c->d_stats);
     free_dev(c->d_pairs); free_dev(c->d_counts); free_dev(c->d_bmu_log); free_dev(c->d_status);
     free_dev(c->d_images[0]); free_dev(c->d_images[1]); free_dev(c->d_dist); free_dev(c->d_rot);
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
@@ -726,6 +730,17 @@ int pink_b200_synchronize(pink_b200_ctx* c)
 void* pink_b200_stream(pink_b200_ctx* c) { return c ? c->stream : nullptr; }
 
 uint64_t pink_b200_launch_count(pink_b200_ctx* c) { return c ? c->launches : 0; }
+
+int pink_b200_get_update_stats(pink_b200_ctx* c, uint64_t* out)
+{
+    if (!c || !out) return fail(PINK_B200_EINVAL, "null argument");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    unsigned long long v[2] = {0, 0};
+    CU_TRY(cudaMemcpyAsync(v, c->d_stats, sizeof(v), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    out[0] = v[0]; out[1] = v[1];
+    return PINK_B200_OK;
+}
 
 int pink_b200_profile_begin(pink_b200_ctx* c, uint32_t max_steps)
 {

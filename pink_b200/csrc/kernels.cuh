@@ -87,6 +87,7 @@ struct BmuArgs
     uint32_t R, q, nd;                // geometry needed to decode a transform index
     uint32_t magic_R, magic_q;        // multiply-high reciprocals of R and q (0 = divisor 1); need T * R < 2^32
     uint32_t* arrive;                 // fused update only: block arrival counter, zero between launches
+    unsigned long long* stats;        // nullable: [0] += neurons with a non-zero factor, [1] += neurons written back
 };
 // phase bit 0: reduce keys[0..n) to this shard's (code, first_neuron + argmin) record in pairs[rank];
 // phase bit 1: pick the global best matching unit from pairs, count the hit, re-arm the keys and emit
@@ -103,12 +104,13 @@ struct UpdateArgs
     uint32_t n;                       // local neurons (upper bound of the work list)
     void* a0; void* a1; void* anorm;  // SOM operand rows to refresh
 };
-// status: device status word that receives a code if a bounded wait expires.
+// Unfused form: one block per neuron works through the list launch_bmu (phase 2) wrote.
 cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st, int* status);
-// Fused form: the update kernel itself reduces the keys (world == 1) or the exchanged per-rank
-// records (world > 1, after launch_bmu phase 1 and the exchange) to the best matching unit, counts
-// the hit, derives its work list and re-arms the keys; a.items / a.n_items and launch_bmu phase 2 are
-// not used.  Available when update_can_fuse(g); b.arrive must point to a zeroed counter.
+// Fused form, a persistent pipelined kernel: it reduces the keys (world == 1) or the exchanged
+// per-rank records (world > 1, after launch_bmu phase 1 and the exchange) to the best matching unit,
+// counts the hit, derives its work list and re-arms the keys itself; a.items / a.n_items and
+// launch_bmu phase 2 are not used.  Available when update_can_fuse(g); b.arrive must point to a
+// zeroed counter.  status: device status word that receives a code if a bounded wait expires.
 bool update_can_fuse(const Geometry& g);
 cudaError_t launch_update_fused(const Geometry& g, const UpdateArgs& a, const BmuArgs& b, cudaStream_t st, int* status);
 

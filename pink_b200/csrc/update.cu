@@ -167,7 +167,10 @@ worklist_kernel(BmuArgs a)
             a.items[slot] = make_item(a, i, key, f);
         }
     }
-    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *a.n_items = total;
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+        *a.n_items = total;
+        if (a.stats) { atomicAdd(a.stats, (unsigned long long)total); atomicAdd(a.stats + 1, (unsigned long long)total); }
+    }
 }
 
 constexpr int kUpdThreads = 256;
@@ -313,18 +316,30 @@ update_kernel(Geometry g, UpdateArgs a, uint32_t stage_base, uint32_t magic_nd, 
 }
 
 // ---------------------------------------------------------------------------
-// Persistent, TMA-pipelined update: one block per SM walks its share of the
-// shard's neurons (round robin).  Warp 0 is the producer: for every neuron
-// with a non-zero factor it streams the neuron (P floats) and the base
-// rotation of its best transform into a shared-memory stage with two bulk
-// asynchronous copies, and, once the consumer warps are done with a stage,
-// writes the updated neuron and its rebuilt operand row(s) back with bulk
-// stores.  Several stages are in flight, so the memory system always has
-// tens of kilobytes outstanding per SM while the consumers compute from
-// shared memory.  The consumers first update the whole neuron (a thread owns
-// one column of a block of rows; everything that does not depend on the
-// neuron is computed once per kernel), then rebuild the operand row from the
-// updated values, four elements per thread.  All waits are bounded.
+// Persistent, TMA-pipelined update that also finds the best matching unit and
+// its own work list: one block per SM.  Warp 0 is the producer: it streams a
+// neuron (P floats) and the base rotation of its best transform into a
+// shared-memory stage with two bulk asynchronous copies, and, once the consumer
+// warps are done with a stage, writes the updated neuron and its rebuilt operand
+// row(s) back with bulk stores.  Several stages are in flight, so the memory
+// system always has tens of kilobytes outstanding per SM while the consumers
+// compute from shared memory.
+//
+// Which neurons a block rewrites: the first `stages` entries are fixed (neurons
+// blockIdx + i * gridDim), so the producer can start their copies at once --
+// which base rotation a neuron needs follows from the neuron's own key, only
+// the update factor depends on the best matching unit.  Meanwhile the consumer
+// warps reduce the keys to the best matching unit (or pick it from the
+// exchanged per-rank records), fetch its row of the factor table and compact
+// the remaining neurons with a non-zero factor; compacted entry s goes to block
+// s % gridDim, so every block gets the same number (+-1).  A fixed entry whose
+// factor turns out to be zero is loaded in vain and skipped.  The block that is
+// last to have read the keys re-arms them for the next image's distance kernel.
+//
+// The consumers first update the whole neuron (a thread owns one column of a
+// block of rows; everything that does not depend on the neuron is computed once
+// per kernel), then rebuild the operand row from the updated values, four
+// elements per thread.  All waits are bounded.
 constexpr int kPipeThreads = 1024;
 constexpr int kPipeConsumerWarps = kPipeThreads / 32 - 1;
 constexpr int kPipeConsumers = kPipeConsumerWarps * 32;
@@ -338,22 +353,26 @@ struct PipeParams
 {
     uint32_t stages, stage_bytes, off_base, off_crop, crop_bytes;   // shared-memory layout of a stage
     uint32_t col_chunks, row_blocks, rows_per_block;                // consumer task grid per channel
-    uint32_t fused;                                                 // 1: the kernel derives its work list itself
     uint32_t magic_grid;                                            // multiply-high reciprocal of the grid size
     int* status;
 };
 
+__device__ __forceinline__ void consumer_sync()
+{
+    asm volatile("bar.sync 1, %0;" :: "n"(kPipeConsumers) : "memory");
+}
 
 template <int MODE>
 __global__ void __launch_bounds__(kPipeThreads, 1)
 update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
 {
     extern __shared__ __align__(128) uint8_t pipe_dyn[];
-    __shared__ __align__(8) uint64_t full_bar[kPipeMaxStages], done_bar[kPipeMaxStages];
+    __shared__ __align__(8) uint64_t full_bar[kPipeMaxStages], done_bar[kPipeMaxStages], list_bar;
     __shared__ unsigned long long norm_s[kPipeMaxStages][kPipeConsumerWarps];   // per-warp partial sums of squares
     __shared__ UpdateItem items[kPipeMaxItems];
     __shared__ unsigned long long red_c[32], red_n[32];
-    __shared__ uint32_t scan_s[32], bmu_s, last_s;
+    __shared__ uint32_t scan_s[32], bmu_s, last_s, m_s;
+    __shared__ uint32_t chg_s[kPipeMaxStages][32];                            // per warp: did any value of the neuron change?
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -361,101 +380,16 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             mbar_init(&full_bar[s], 1);
             mbar_init(&done_bar[s], kPipeConsumerWarps);
         }
+        mbar_init(&list_bar, 1);
         mbar_fence_init();
     }
-    // This block takes entries b, b + gridDim.x, ... of the work list (the neurons with a
-    // non-zero factor, ascending), so all blocks get the same number of neurons (+-1).
-    uint32_t total = 0;
-    if (pp.fused) {
-        // Every block derives the best matching unit and its own part of the work list from the
-        // distance kernel's per-neuron minima: two kernel boundaries less per image than reducing
-        // and compacting in kernels of their own, at the price of each block reading the keys
-        // (8 bytes per neuron) and one row of the factor table.
-        // A thread owns four consecutive neurons of every chunk of 4 * kPipeThreads; with a single
-        // chunk (the usual case) their keys stay in registers between the two passes.
-        constexpr uint32_t kChunk = 4 * kPipeThreads;
-        const bool one_chunk = b.n <= kChunk;
-        unsigned long long kreg[4] = {~0ull, ~0ull, ~0ull, ~0ull};
-        auto load_keys = [&](uint32_t i0) {
-            if (i0 + 3 < b.n) {
-                const ulonglong2 k01 = *reinterpret_cast<const ulonglong2*>(b.keys + i0);
-                const ulonglong2 k23 = *reinterpret_cast<const ulonglong2*>(b.keys + i0 + 2);
-                kreg[0] = k01.x; kreg[1] = k01.y; kreg[2] = k23.x; kreg[3] = k23.y;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) kreg[e] = i0 + e < b.n ? b.keys[i0 + e] : ~0ull;
-            }
-        };
-        unsigned long long bc = ~0ull, bn = ~0ull;
-        if (b.world == 1) {
-            for (uint32_t c0 = 0; c0 < b.n; c0 += kChunk) {
-                const uint32_t i0 = c0 + 4 * threadIdx.x;
-                load_keys(i0);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const unsigned long long code = kreg[e] >> b.shift;
-                    if (i0 + e < b.n && pair_less(code, i0 + e, bc, bn)) { bc = code; bn = i0 + e; }
-                }
-            }
-            block_min_pair(bc, bn, red_c, red_n);
-        }
-        if (threadIdx.x == 0) {
-            if (b.world > 1) {
-                // lexicographic minimum over the per-rank records: lowest distance, then lowest neuron index
-                bc = b.pairs[0].code; bn = b.pairs[0].neuron;
-                for (uint32_t r = 1; r < b.world; ++r)
-                    if (pair_less(b.pairs[r].code, b.pairs[r].neuron, bc, bn)) { bc = b.pairs[r].code; bn = b.pairs[r].neuron; }
-            } else {
-                bn += b.first_neuron;
-            }
-            const uint32_t bmu = (uint32_t)bn;
-            bmu_s = bmu;
-            if (blockIdx.x == 0 && bmu >= b.first_neuron && bmu - b.first_neuron < b.n) {   // this rank owns the unit
-                atomicAdd(&b.counts[bmu], 1u);
-                if (b.bmu_log) *b.bmu_log = bmu;
-            }
-        }
-        __syncthreads();
-        const float* frow = b.factors + (size_t)bmu_s * b.n;
-        for (uint32_t c0 = 0; c0 < b.n; c0 += kChunk) {
-            const uint32_t i0 = c0 + 4 * threadIdx.x;
-            float f[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) f[e] = i0 + e < b.n ? frow[i0 + e] : 0.0f;
-            if (!one_chunk || b.world > 1) load_keys(i0);
-            const uint32_t cnt = (f[0] != 0.0f) + (f[1] != 0.0f) + (f[2] != 0.0f) + (f[3] != 0.0f);
-            uint32_t incl = cnt;                                   // inclusive scan over the warp's threads
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
-                if ((int)lane >= o) incl += up;
-            }
-            if (lane == 31) scan_s[warp] = incl;
-            __syncthreads();
-            const uint32_t own = scan_s[lane];                     // kPipeThreads / 32 == 32 warps
-            uint32_t wincl = own;                                  // inclusive scan over the warps' totals
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t up = __shfl_up_sync(0xffffffffu, wincl, o);
-                if ((int)lane >= o) wincl += up;
-            }
-            uint32_t slot = total + __shfl_sync(0xffffffffu, wincl - own, warp) + incl - cnt;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (f[e] != 0.0f) {
-                    const uint32_t local = bmu_div(slot, pp.magic_grid);
-                    if (slot - local * gridDim.x == blockIdx.x && local < (uint32_t)kPipeMaxItems)
-                        items[local] = make_item(b, i0 + e, kreg[e], f[e]);
-                    ++slot;
-                }
-            }
-            total += __shfl_sync(0xffffffffu, wincl, 31);
-            __syncthreads();
-        }
-    } else {
-        total = *a.n_items;
+    // fixed entries of this block; their factor is filled in once the best matching unit is known
+    const uint32_t n_fixed = min(pp.stages * gridDim.x, b.n);               // neurons below this index are fixed entries
+    const uint32_t m_fixed = b.n > blockIdx.x ? min(pp.stages, (b.n - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0u;
+    if (threadIdx.x < m_fixed) {
+        const uint32_t n = blockIdx.x + threadIdx.x * gridDim.x;
+        items[threadIdx.x] = make_item(b, n, b.keys[n], 0.0f);
     }
-    const uint32_t M = total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    if (!pp.fused)
-        for (uint32_t i = threadIdx.x; i < M; i += kPipeThreads) items[i] = a.items[blockIdx.x + i * gridDim.x];
     // operand staging starts as zeros: the padding beyond K is never written again
     for (uint32_t s = 0; s < pp.stages; ++s)
         for (uint32_t i = threadIdx.x; i < pp.crop_bytes / 4; i += kPipeThreads)
@@ -475,13 +409,24 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             bulk_load(st + pp.off_base, a.base + (size_t)items[jx].tq * g.P, plane_bytes, &full_bar[s]);
         };
         if (lane == 0)
-            for (uint32_t jx = 0; jx < M && jx < pp.stages; ++jx) issue(jx);
+            for (uint32_t jx = 0; jx < m_fixed; ++jx) issue(jx);
+        // the consumers publish the rest of the list and the factors
+        uint32_t M = 0;
+        if (mbar_wait(&list_bar, 0)) M = m_s;
+        else if (pp.status) atomicCAS(pp.status, kDevOk, kDevTimeoutUpdateProducer);
+        uint32_t n_live = 0, n_rewritten = 0;
         for (uint32_t jx = 0; jx < M; ++jx) {
             const uint32_t s = jx % pp.stages, ph = (jx / pp.stages) & 1;
             if (!mbar_wait(&done_bar[s], ph)) { if (pp.status) atomicCAS(pp.status, kDevOk, kDevTimeoutUpdateProducer); break; }
             const uint32_t n = items[jx].n;
+            // A neuron none of whose values changed (the factor is so small that every product
+            // vanished against the value it is subtracted from) is not written back: neuron and
+            // operand row in memory already hold exactly what the stage holds.
+            const bool nonzero = items[jx].f != 0.0f;
+            const bool live = nonzero && __any_sync(0xffffffffu, lane < kPipeConsumerWarps && chg_s[s][lane] != 0);
+            n_live += nonzero; n_rewritten += live;
             uint8_t* st = pipe_dyn + (size_t)s * pp.stage_bytes;
-            if (MODE != kModeF32) {
+            if (MODE != kModeF32 && live) {
                 unsigned long long tot = lane < kPipeConsumerWarps ? norm_s[s][lane] : 0ull;
                 for (int o = 16; o > 0; o >>= 1) tot += __shfl_down_sync(0xffffffffu, tot, o);
                 if (lane == 0) {
@@ -490,15 +435,17 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                 }
             }
             if (lane == 0) {
-                bulk_store(a.som + (size_t)n * g.Pp, st, plane_bytes);
-                if (MODE == kModeF32) {
-                    bulk_store(static_cast<float*>(a.a0) + (size_t)n * g.Kp, st + pp.off_crop, g.Kp * 4);
-                } else {
-                    bulk_store(static_cast<uint8_t*>(a.a0) + (size_t)n * g.Kp, st + pp.off_crop, g.Kp);
-                    if (MODE == kModeU16)
-                        bulk_store(static_cast<uint8_t*>(a.a1) + (size_t)n * g.Kp, st + pp.off_crop + g.Kp, g.Kp);
+                if (live) {
+                    bulk_store(a.som + (size_t)n * g.Pp, st, plane_bytes);
+                    if (MODE == kModeF32) {
+                        bulk_store(static_cast<float*>(a.a0) + (size_t)n * g.Kp, st + pp.off_crop, g.Kp * 4);
+                    } else {
+                        bulk_store(static_cast<uint8_t*>(a.a0) + (size_t)n * g.Kp, st + pp.off_crop, g.Kp);
+                        if (MODE == kModeU16)
+                            bulk_store(static_cast<uint8_t*>(a.a1) + (size_t)n * g.Kp, st + pp.off_crop + g.Kp, g.Kp);
+                    }
+                    bulk_commit();
                 }
-                bulk_commit();
                 if (jx + pp.stages < M) {
                     bulk_wait_read_all();             // the stage's stores no longer read it
                     issue(jx + pp.stages);
@@ -506,7 +453,10 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             }
             __syncwarp();
         }
-        if (lane == 0) bulk_wait_all();
+        if (lane == 0) {
+            if (b.stats) { atomicAdd(b.stats, (unsigned long long)n_live); atomicAdd(b.stats + 1, (unsigned long long)n_rewritten); }
+            bulk_wait_all();
+        }
     } else {
         // ----------------------------------------------------------- consumers --
         const uint32_t cwarp = warp - 1, ctid = threadIdx.x - 32;
@@ -547,20 +497,119 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             }
         }
         const uint32_t nd = g.nd;
-        if (pp.fused) {
-            // The block that is last to have read the keys re-arms them for the next image's
-            // distance kernel; its consumers do so while the first neuron is still in flight.
-            if (ctid == 0) {
-                __threadfence();
-                const uint32_t old = atomicAdd(b.arrive, 1u);
-                last_s = old == gridDim.x - 1;
-                if (old == gridDim.x - 1) *b.arrive = 0;
-                __threadfence();
+
+        // ---- best matching unit: first minimum of (code, neuron) over the keys.  A thread owns four
+        //      consecutive neurons of every chunk of 4 * kPipeConsumers; with a single chunk (the
+        //      usual case) their keys stay in registers for the compaction below.
+        constexpr uint32_t kChunk = 4 * kPipeConsumers;
+        const bool one_chunk = b.n <= kChunk;
+        unsigned long long kreg[4] = {~0ull, ~0ull, ~0ull, ~0ull};
+        auto load_keys = [&](uint32_t i0) {
+            if (i0 + 3 < b.n) {
+                const ulonglong2 k01 = *reinterpret_cast<const ulonglong2*>(b.keys + i0);
+                const ulonglong2 k23 = *reinterpret_cast<const ulonglong2*>(b.keys + i0 + 2);
+                kreg[0] = k01.x; kreg[1] = k01.y; kreg[2] = k23.x; kreg[3] = k23.y;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) kreg[e] = i0 + e < b.n ? b.keys[i0 + e] : ~0ull;
             }
-            asm volatile("bar.sync 1, %0;" :: "n"(kPipeConsumers) : "memory");
-            if (last_s)
-                for (uint32_t i = ctid; i < b.n; i += kPipeConsumers) b.keys[i] = kKeyEmpty;
+        };
+        unsigned long long bc = ~0ull, bn = ~0ull;
+        if (b.world == 1) {
+            for (uint32_t c0 = 0; c0 < b.n; c0 += kChunk) {
+                const uint32_t i0 = c0 + 4 * ctid;
+                load_keys(i0);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const unsigned long long code = kreg[e] >> b.shift;
+                    if (i0 + e < b.n && pair_less(code, i0 + e, bc, bn)) { bc = code; bn = i0 + e; }
+                }
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long oc = __shfl_down_sync(0xffffffffu, bc, o), on = __shfl_down_sync(0xffffffffu, bn, o);
+                if (pair_less(oc, on, bc, bn)) { bc = oc; bn = on; }
+            }
+            if (lane == 0) { red_c[cwarp] = bc; red_n[cwarp] = bn; }
+            consumer_sync();
         }
+        if (cwarp == 0) {
+            if (b.world == 1) {
+                bc = lane < kPipeConsumerWarps ? red_c[lane] : ~0ull;
+                bn = lane < kPipeConsumerWarps ? red_n[lane] : ~0ull;
+                for (int o = 16; o > 0; o >>= 1) {
+                    const unsigned long long oc = __shfl_down_sync(0xffffffffu, bc, o), on = __shfl_down_sync(0xffffffffu, bn, o);
+                    if (pair_less(oc, on, bc, bn)) { bc = oc; bn = on; }
+                }
+                bn += b.first_neuron;
+            } else {
+                // lexicographic minimum over the per-rank records: lowest distance, then lowest neuron index
+                bc = b.pairs[0].code; bn = b.pairs[0].neuron;
+                for (uint32_t r = 1; r < b.world; ++r)
+                    if (pair_less(b.pairs[r].code, b.pairs[r].neuron, bc, bn)) { bc = b.pairs[r].code; bn = b.pairs[r].neuron; }
+            }
+            if (lane == 0) {
+                const uint32_t bmu = (uint32_t)bn;
+                bmu_s = bmu;
+                if (blockIdx.x == 0 && bmu >= b.first_neuron && bmu - b.first_neuron < b.n) {   // this rank owns the unit
+                    atomicAdd(&b.counts[bmu], 1u);
+                    if (b.bmu_log) *b.bmu_log = bmu;
+                }
+            }
+        }
+        consumer_sync();
+
+        // ---- factors of the fixed entries; ordered compaction of the other neurons with a non-zero factor
+        const float* frow = b.factors + (size_t)bmu_s * b.n;
+        if (ctid < m_fixed) items[ctid].f = frow[items[ctid].n];
+        uint32_t total = 0;
+        for (uint32_t c0 = 0; c0 < b.n; c0 += kChunk) {
+            const uint32_t i0 = c0 + 4 * ctid;
+            float f[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) f[e] = (i0 + e < b.n && i0 + e >= n_fixed) ? frow[i0 + e] : 0.0f;
+            if (!one_chunk || b.world > 1) load_keys(i0);
+            const uint32_t cnt = (f[0] != 0.0f) + (f[1] != 0.0f) + (f[2] != 0.0f) + (f[3] != 0.0f);
+            uint32_t incl = cnt;                                   // inclusive scan over the warp's threads
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+                if ((int)lane >= o) incl += up;
+            }
+            if (lane == 31) scan_s[cwarp] = incl;
+            consumer_sync();
+            const uint32_t own = lane < kPipeConsumerWarps ? scan_s[lane] : 0u;
+            uint32_t wincl = own;                                  // inclusive scan over the warps' totals
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, wincl, o);
+                if ((int)lane >= o) wincl += up;
+            }
+            uint32_t slot = total + __shfl_sync(0xffffffffu, wincl - own, cwarp) + incl - cnt;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (f[e] != 0.0f) {
+                    const uint32_t round = bmu_div(slot, pp.magic_grid);
+                    if (slot - round * gridDim.x == blockIdx.x && pp.stages + round < (uint32_t)kPipeMaxItems)
+                        items[pp.stages + round] = make_item(b, i0 + e, kreg[e], f[e]);
+                    ++slot;
+                }
+            }
+            total += __shfl_sync(0xffffffffu, wincl, 31);
+            consumer_sync();
+        }
+        const uint32_t M = m_fixed + (total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u);
+        if (ctid == 0) {
+            m_s = M;
+            mbar_arrive(&list_bar);           // the list is complete (ordered after all entries by the barrier above)
+            // The block that is last to have read the keys re-arms them for the next image's
+            // distance kernel; its consumers do so while the first neurons are still in flight.
+            __threadfence();
+            const uint32_t old = atomicAdd(b.arrive, 1u);
+            last_s = old == gridDim.x - 1;
+            if (old == gridDim.x - 1) *b.arrive = 0;
+            __threadfence();
+        }
+        consumer_sync();
+        if (last_s)
+            for (uint32_t i = ctid; i < b.n; i += kPipeConsumers) b.keys[i] = kKeyEmpty;
         for (uint32_t jx = 0; jx < M; ++jx) {
             const uint32_t s = jx % pp.stages, ph = (jx / pp.stages) & 1;
             if (!mbar_wait(&full_bar[s], ph)) { if (pp.status) atomicCAS(pp.status, kDevOk, kDevTimeoutUpdateConsumer); break; }
@@ -571,8 +620,14 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             const UpdateItem it = items[jx];
             const float f = it.f;
             const int32_t ax = it.ax;
+            if (f == 0.0f) {                  // a fixed entry outside the neighbourhood: nothing to do
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&done_bar[s]);
+                continue;
+            }
             // -- w <- w - (w - r) * f over the whole neuron, kPipeUnroll rows per step:
             //    all loads, then the arithmetic, then the stores; no predicates in the steady loop
+            bool changed = false;
 #pragma unroll
             for (int k = 0; k < kPipeMaxTasks; ++k) {
                 float* ps = som_s + tk_si[k];
@@ -582,18 +637,32 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
 #pragma unroll
                     for (int u = 0; u < kPipeUnroll; ++u) { e[u] = ps[u * nd]; rv[u] = pb[u * ax]; }
 #pragma unroll
-                    for (int u = 0; u < kPipeUnroll; ++u) e[u] = __fsub_rn(e[u], __fmul_rn(__fsub_rn(e[u], rv[u]), f));
+                    for (int u = 0; u < kPipeUnroll; ++u) {
+                        const float w = e[u];
+                        e[u] = __fsub_rn(w, __fmul_rn(__fsub_rn(w, rv[u]), f));
+                        changed |= __float_as_uint(e[u]) != __float_as_uint(w);
+                    }
 #pragma unroll
                     for (int u = 0; u < kPipeUnroll; ++u) ps[u * nd] = e[u];
                     ps += kPipeUnroll * nd; pb += kPipeUnroll * ax;
                 }
                 for (uint32_t i = 0; i < tk_tail[k]; ++i) {
-                    const float e = *ps;
-                    *ps = __fsub_rn(e, __fmul_rn(__fsub_rn(e, *pb), f));
+                    const float w = *ps;
+                    const float e = __fsub_rn(w, __fmul_rn(__fsub_rn(w, *pb), f));
+                    changed |= __float_as_uint(e) != __float_as_uint(w);
+                    *ps = e;
                     ps += nd; pb += ax;
                 }
             }
-            asm volatile("bar.sync 1, %0;" :: "n"(kPipeConsumers) : "memory");   // whole neuron updated
+            {
+                const bool warp_changed = __any_sync(0xffffffffu, changed);
+                if (lane == 0) chg_s[s][cwarp] = warp_changed;
+            }
+            consumer_sync();                  // whole neuron updated
+            if (!__any_sync(0xffffffffu, lane < kPipeConsumerWarps && chg_s[s][lane] != 0)) {
+                if (lane == 0) mbar_arrive(&done_bar[s]);    // nothing changed: operand row and sum stay as they are
+                continue;
+            }
             // -- operand row(s) from the updated values
             unsigned long long acc = 0;
 #pragma unroll
@@ -715,7 +784,8 @@ bool pipe_eligible(const Geometry& g)
 template <int MODE>
 cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, const BmuArgs* fused, cudaStream_t st, int* status)
 {
-    if (!pipe_eligible(g)) return fused ? cudaErrorInvalidValue : update_classic<MODE>(g, a, st);
+    if (!fused) return update_classic<MODE>(g, a, st);
+    if (!pipe_eligible(g)) return cudaErrorInvalidValue;
     const size_t crop = MODE == kModeF32 ? (size_t)g.Kp * 4 : (MODE == kModeU16 ? (size_t)g.Kp * 2 : g.Kp);
     const size_t plane = ((size_t)g.P * 4 + 127) & ~size_t(127);
     const size_t stage = pipe_stage_bytes(g), budget = kPipeBudget;
@@ -733,10 +803,9 @@ cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, const BmuArg
     pp.rows_per_block = (pp.rows_per_block + kPipeUnroll - 1) / kPipeUnroll * kPipeUnroll;   // whole unrolled steps
     pp.row_blocks = (g.nd + pp.rows_per_block - 1) / pp.rows_per_block;
     pp.status = status;
-    pp.fused = fused ? 1u : 0u;
     uint32_t grid = std::min<uint32_t>(a.n, (uint32_t)sms);
     if ((a.n + grid - 1) / grid > (uint32_t)kPipeMaxItems) grid = (a.n + kPipeMaxItems - 1) / kPipeMaxItems;
-    if (fused && (uint64_t)a.n * grid >= (1ull << 32)) return cudaErrorInvalidValue;   // multiply-high division range
+    if ((uint64_t)a.n * grid >= (1ull << 32)) return cudaErrorInvalidValue;   // multiply-high division range
     pp.magic_grid = div_magic(grid);
     const size_t smem = (size_t)pp.stages * stage;
     static int attr_dev = -1;
@@ -749,7 +818,7 @@ cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, const BmuArg
         attr_dev = dev;
         attr_bytes = smem;
     }
-    update_pipe_kernel<MODE><<<grid, kPipeThreads, smem, st>>>(g, a, pp, fused ? *fused : BmuArgs{});
+    update_pipe_kernel<MODE><<<grid, kPipeThreads, smem, st>>>(g, a, pp, *fused);
     return cudaGetLastError();
 }
 

@@ -116,6 +116,12 @@ class Engine:
         """Kernels launched by this context so far."""
         return int(capi.lib.pink_b200_launch_count(self._h))
 
+    def update_stats(self):
+        """(neurons with a non-zero factor, neurons written back), summed over all training steps so far."""
+        out = np.zeros(2, np.uint64)
+        capi.check(capi.lib.pink_b200_get_update_stats(self._h, _vp(out)))
+        return int(out[0]), int(out[1])
+
     def synchronize(self):
         capi.check(capi.lib.pink_b200_synchronize(self._h))
 

@@ -51,6 +51,7 @@ SYMBOLS = {
     "pink_b200_synchronize": (C.c_int, [C.c_void_p]),
     "pink_b200_stream": (C.c_void_p, [C.c_void_p]),
     "pink_b200_launch_count": (C.c_uint64, [C.c_void_p]),
+    "pink_b200_exchange_kind": (C.c_int, [C.c_void_p]),
     "pink_b200_get_update_stats": (C.c_int, [C.c_void_p, C.c_void_p]),
     "pink_b200_profile_begin": (C.c_int, [C.c_void_p, C.c_uint32]),
     "pink_b200_profile_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),

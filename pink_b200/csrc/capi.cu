@@ -161,6 +161,8 @@ struct pink_b200_ctx
     unsigned long long* d_keys = nullptr; size_t key_imgs = 0;
     BmuPair* d_pairs = nullptr;
     UpdateItem* d_items = nullptr; uint32_t* d_nitems = nullptr;   // per-step work list of the update
+    // records of the ranks' best matching units exchanged by peer stores (world_size > 1, all ranks on one node)
+    XchgRecord* d_xchg = nullptr; XchgRecord* xchg_peer[kXchgMaxRanks] = {}; bool xchg_on = false; unsigned long long xchg_seq = 0;
     unsigned long long* d_stats = nullptr;   // [0] neurons with a non-zero factor, [1] neurons written back, summed over steps
     uint64_t launches = 0;            // kernels launched by this context so far
     bool fuse_update = false;         // the update kernel finds the best matching unit and its work list itself
@@ -258,11 +260,6 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     da.bnorm = static_cast<uint8_t*>(c->d_bnorm) + row0 * (g.mode == kModeU16 ? 8 : 4);
     da.n_img = 1;
     da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status;
-    const char* why = "";
-    if (ev) CU_TRY(cudaEventRecord(ev[0], c->stream));
-    cudaError_t e = launch_distance(g, da, c->stream, &why);
-    if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
-    if (ev) CU_TRY(cudaEventRecord(ev[1], c->stream));
     BmuArgs ba{};
     ba.keys = c->d_keys; ba.n = c->count; ba.first_neuron = c->first; ba.shift = key_shift(g.mode);
     ba.pairs = c->d_pairs; ba.rank = c->cfg.rank; ba.world = c->cfg.world_size;
@@ -273,15 +270,31 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     ba.magic_q = g.q <= 1 ? 0u : (uint32_t)((1ull << 32) / g.q) + 1;
     ba.arrive = c->d_nitems + 1;
     ba.stats = c->d_stats;
+    ba.status = c->d_status;
     // Fused form: the update kernel reduces the keys (or the exchanged records) and derives its
     // work list itself; otherwise a reduction and a compaction kernel run in between.
     const bool fused = c->fuse_update;
-    if (c->cfg.world_size == 1) {
+    const bool multi = c->cfg.world_size > 1;
+    const bool peer = multi && fused && c->xchg_on;
+    if (peer) {
+        // this rank's record goes into every rank's array by peer stores; the update kernel waits for all
+        ba.xchg_seq = ++c->xchg_seq;
+        ba.xchg_local = c->d_xchg;
+        for (uint32_t r = 0; r < c->cfg.world_size; ++r) ba.xchg_peer[r] = c->xchg_peer[r];
+    }
+    // with several ranks the distance kernel's last block reduces the shard's keys to its record
+    const bool tail = multi && distance_has_tail(g);
+    if (tail) { da.tail = &ba; da.tail_counter = c->d_nitems + 2; }
+    const char* why = "";
+    if (ev) CU_TRY(cudaEventRecord(ev[0], c->stream));
+    cudaError_t e = launch_distance(g, da, c->stream, &why);
+    if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
+    if (ev) CU_TRY(cudaEventRecord(ev[1], c->stream));
+    if (!multi) {
         if (!fused) { LAUNCH_TRY(launch_bmu(ba, 3, c->stream)); c->launches += 2; }
     } else {
-        LAUNCH_TRY(launch_bmu(ba, 1, c->stream));
-        c->launches += 1;
-        NCCL_TRY(nccl().AllGather(c->d_pairs + c->cfg.rank, c->d_pairs, 2, ncclUint64, c->comm, c->stream));
+        if (!tail) { LAUNCH_TRY(launch_bmu(ba, 1, c->stream)); c->launches += 1; }
+        if (!peer) NCCL_TRY(nccl().AllGather(c->d_pairs + c->cfg.rank, c->d_pairs, 2, ncclUint64, c->comm, c->stream));
         if (!fused) { LAUNCH_TRY(launch_bmu(ba, 2, c->stream)); c->launches += 1; }
     }
     UpdateArgs ua{};
@@ -329,6 +342,77 @@ int train_chunk(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* l
         }
         CU_TRY(cudaEventRecord(c->rot_free[slot ? 1 : 0], c->stream));
     }
+    return PINK_B200_OK;
+}
+
+void release_peer_exchange(pink_b200_ctx* c)
+{
+    for (uint32_t r = 0; r < kXchgMaxRanks; ++r) {
+        if (c->xchg_peer[r] && c->xchg_peer[r] != c->d_xchg) cudaIpcCloseMemHandle(c->xchg_peer[r]);
+        c->xchg_peer[r] = nullptr;
+    }
+    if (c->d_xchg) cudaFree(c->d_xchg);
+    c->d_xchg = nullptr;
+    c->xchg_on = false;
+}
+
+// Sets up the exchange of best-matching-unit records through peer memory: every rank
+// allocates its record array, the CUDA IPC handles travel once through an NCCL all-gather,
+// and each rank maps the other ranks' arrays.  The exchange is switched on only if every
+// rank could map every array and no two ranks share a GPU (a kernel that waits for a peer's
+// record must never share its GPU with the kernel that writes it); otherwise the per-step
+// NCCL all-gather stays in use.  PINK_B200_NCCL_EXCHANGE (diagnostic switch) keeps NCCL too.
+int setup_peer_exchange(pink_b200_ctx* c)
+{
+    const uint32_t W = c->cfg.world_size, rank = c->cfg.rank;
+    struct Hello { cudaIpcMemHandle_t handle; char bus[32]; uint32_t want; uint32_t ok; };
+    Hello mine{};
+    std::vector<Hello> all(W);
+    Hello* d_all = nullptr;
+    // (distance codes must leave room for the 8-bit tag of a record word: 65535^2 * K < 2^56)
+    mine.want = W <= kXchgMaxRanks && c->fuse_update && c->g.K < (1u << 24) && !getenv("PINK_B200_NCCL_EXCHANGE");
+    if (mine.want) {
+        const size_t bytes = (size_t)kXchgSlots * W * sizeof(XchgRecord);
+        CU_TRY(cudaMalloc(&c->d_xchg, bytes));
+        CU_TRY(cudaMemsetAsync(c->d_xchg, 0, bytes, c->stream));
+        CU_TRY(cudaStreamSynchronize(c->stream));          // zeroed before any rank can learn the handle
+        if (cudaIpcGetMemHandle(&mine.handle, c->d_xchg) != cudaSuccess) { cudaGetLastError(); mine.want = 0; }
+        if (cudaDeviceGetPCIBusId(mine.bus, sizeof(mine.bus), c->cfg.device) != cudaSuccess) { cudaGetLastError(); mine.want = 0; }
+    }
+    CU_TRY(cudaMalloc(&d_all, W * sizeof(Hello)));
+    auto gather = [&]() -> int {
+        CU_TRY(cudaMemcpyAsync(d_all + rank, &mine, sizeof(Hello), cudaMemcpyHostToDevice, c->stream));
+        NCCL_TRY(nccl().AllGather(d_all + rank, d_all, sizeof(Hello), ncclUint8, c->comm, c->stream));
+        CU_TRY(cudaMemcpyAsync(all.data(), d_all, W * sizeof(Hello), cudaMemcpyDeviceToHost, c->stream));
+        CU_TRY(cudaStreamSynchronize(c->stream));
+        return PINK_B200_OK;
+    };
+    int rc = gather();
+    if (rc) { cudaFree(d_all); return rc; }
+    bool ok = true;
+    for (uint32_t r = 0; r < W; ++r) {
+        ok = ok && all[r].want;
+        for (uint32_t q = 0; q < r; ++q) ok = ok && std::strncmp(all[r].bus, all[q].bus, sizeof(mine.bus)) != 0;
+    }
+    if (ok) {
+        for (uint32_t r = 0; r < W && ok; ++r) {
+            if (r == rank) { c->xchg_peer[r] = c->d_xchg; continue; }
+            void* ptr = nullptr;
+            if (cudaIpcOpenMemHandle(&ptr, all[r].handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                cudaGetLastError();
+                ok = false;
+            } else {
+                c->xchg_peer[r] = static_cast<XchgRecord*>(ptr);
+            }
+        }
+    }
+    mine.ok = ok;
+    rc = gather();                                          // all ranks must agree on the way they exchange
+    cudaFree(d_all);
+    if (rc) return rc;
+    for (uint32_t r = 0; r < W; ++r) ok = ok && all[r].ok;
+    c->xchg_on = ok;
+    if (!ok) release_peer_exchange(c);
     return PINK_B200_OK;
 }
 
@@ -445,8 +529,9 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     CTX_TRY(cudaMemsetAsync(c->d_items, 0, c->count * sizeof(UpdateItem), c->stream));
     CTX_TRY(cudaMalloc(&c->d_stats, 2 * sizeof(unsigned long long)));
     CTX_TRY(cudaMemsetAsync(c->d_stats, 0, 2 * sizeof(unsigned long long), c->stream));
-    CTX_TRY(cudaMalloc(&c->d_nitems, 2 * sizeof(uint32_t)));       // [0] work-list length, [1] block arrival counter
-    CTX_TRY(cudaMemsetAsync(c->d_nitems, 0, 2 * sizeof(uint32_t), c->stream));
+    // [0] work-list length, [1] block arrival counter of the update kernel, [2] of the distance kernel
+    CTX_TRY(cudaMalloc(&c->d_nitems, 3 * sizeof(uint32_t)));
+    CTX_TRY(cudaMemsetAsync(c->d_nitems, 0, 3 * sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_counts, N * sizeof(uint32_t)));
     CTX_TRY(cudaMemsetAsync(c->d_counts, 0, N * sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_status, sizeof(int)));
@@ -482,6 +567,7 @@ int pink_b200_destroy(pink_b200_ctx* c)
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->copy_stream) cudaStreamSynchronize(c->copy_stream);
     if (c->rot_stream) cudaStreamSynchronize(c->rot_stream);
+    release_peer_exchange(c);
     if (c->comm && nccl().ok) nccl().CommDestroy(c->comm);
     free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
     free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_base);
@@ -533,7 +619,7 @@ int pink_b200_comm_init(pink_b200_ctx* c, const void* id128)
     ncclUniqueId id;
     std::memcpy(&id, id128, 128);
     NCCL_TRY(nccl().CommInitRank(&c->comm, (int)c->cfg.world_size, id, (int)c->cfg.rank));
-    return PINK_B200_OK;
+    return setup_peer_exchange(c);
 }
 
 int pink_b200_set_som(pink_b200_ctx* c, const float* host_som)
@@ -730,6 +816,12 @@ int pink_b200_synchronize(pink_b200_ctx* c)
 void* pink_b200_stream(pink_b200_ctx* c) { return c ? c->stream : nullptr; }
 
 uint64_t pink_b200_launch_count(pink_b200_ctx* c) { return c ? c->launches : 0; }
+
+int pink_b200_exchange_kind(pink_b200_ctx* c)
+{
+    if (!c || c->cfg.world_size == 1 || !c->comm) return PINK_B200_EXCHANGE_NONE;
+    return c->xchg_on ? PINK_B200_EXCHANGE_PEER : PINK_B200_EXCHANGE_NCCL;
+}
 
 int pink_b200_get_update_stats(pink_b200_ctx* c, uint64_t* out)
 {

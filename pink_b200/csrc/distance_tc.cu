@@ -26,6 +26,9 @@
 // and unwinds through the common exit that frees its tensor memory.
 #include "kernels.cuh"
 #include "ptx.cuh"
+#include "record.cuh"
+
+#include <algorithm>
 
 #include <cudaTypedefs.h>
 
@@ -64,6 +67,8 @@ struct TcParams
     void* s_out;
     int* status;
     uint32_t n, T, num_kb, n_tile;
+    uint32_t* tail_counter;     // nullable: block arrival counter (zero between launches) that enables the tail below
+    BmuArgs tail;               // the last block to finish reduces the shard's keys to its record and publishes it
 };
 
 __device__ __forceinline__ void report(int* status, int code)
@@ -224,6 +229,31 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::cols);
+
+    // Tail (training with several ranks): the block that finishes last has all per-neuron minima in
+    // front of it; it reduces them to this shard's best-matching-unit record and hands the record to the
+    // other ranks, which saves a kernel of its own between this one and the update.
+    if (p.tail_counter) {
+        __shared__ uint32_t last_s;
+        __shared__ unsigned long long tc_s[kThreads / 32], tn_s[kThreads / 32];
+        if (threadIdx.x == 0) {
+            __threadfence();                                   // this block's key updates before its arrival
+            const uint32_t blocks = gridDim.x * gridDim.y * gridDim.z;
+            const uint32_t old = atomicAdd(p.tail_counter, 1u);
+            last_s = old == blocks - 1;
+            if (old == blocks - 1) *p.tail_counter = 0;
+            __threadfence();
+        }
+        __syncthreads();
+        if (last_s) {
+            unsigned long long bc, bn;
+            block_argmin_keys(p.tail.keys, p.tail.n, p.tail.shift, kThreads, tc_s, tn_s, bc, bn);
+            __syncthreads();
+            if (threadIdx.x == 0) { tc_s[0] = bc; tn_s[0] = bn == ~0ull ? ~0ull : bn + p.tail.first_neuron; }
+            __syncthreads();
+            publish_record(p.tail, tc_s[0], tn_s[0]);
+        }
+    }
 }
 
 // ------------------------------------------------------------------ host side --
@@ -261,8 +291,21 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
 {
     using Cfg = TcCfg<MODE>;
     using L = SmemLayout<MODE>;
-    // Balanced transform tiles: the fewest tiles of at most max_n columns, each a multiple of 16.
-    const uint32_t tiles = (g.T + Cfg::max_n - 1) / Cfg::max_n;
+    // Balanced transform tiles, each a multiple of 16 columns: the fewest tiles of at most max_n
+    // columns -- unless that leaves SMs without a block (a small neuron shard, few images): a block's
+    // run time is set by the bytes it pulls through its SM, (128 + n_tile) * K, so narrower tiles
+    // spread over all SMs finish sooner.  Below 32 columns the neuron tile dominates and nothing is gained.
+    uint32_t tiles = (g.T + Cfg::max_n - 1) / Cfg::max_n;
+    {
+        static int sm_dev = -1, sms = 0;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev != sm_dev) { cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); sm_dev = dev; }
+        const uint64_t rows = (uint64_t)((a.n + kBlockM - 1) / kBlockM) * a.n_img;
+        const uint32_t most = std::max<uint32_t>(tiles, g.T / 32);
+        if (sms > 0 && rows * tiles < (uint64_t)sms)
+            tiles = (uint32_t)std::max<uint64_t>(tiles, std::min<uint64_t>(most, (uint64_t)sms / rows));   // one wave
+    }
     uint32_t n_tile = ((g.T + tiles - 1) / tiles + 15) & ~15u;
     if (n_tile > Cfg::max_n) n_tile = Cfg::max_n;
     const uint32_t n_tiles = (g.T + n_tile - 1) / n_tile;
@@ -286,6 +329,8 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     TcParams p;
     p.anorm = a.anorm; p.bnorm = a.bnorm; p.keys = a.keys; p.s_out = a.s_out; p.status = a.status;
     p.n = a.n; p.T = g.T; p.num_kb = g.Kp / kBlockK; p.n_tile = n_tile;
+    p.tail_counter = a.tail ? a.tail_counter : nullptr;
+    if (a.tail) p.tail = *a.tail;
     dim3 grid((a.n + kBlockM - 1) / kBlockM, n_tiles, a.n_img);
     distance_tc_kernel<MODE><<<grid, kThreads, L::total, st>>>(ma0, ma1, mb0, mb1, p);
     *why = "distance_tc_kernel launch";
@@ -295,6 +340,8 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
 } // namespace
 
 cudaError_t launch_distance_f32(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why);
+
+bool distance_has_tail(const Geometry& g) { return g.mode == kModeU8 || g.mode == kModeU16; }
 
 cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why)
 {

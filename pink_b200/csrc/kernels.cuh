@@ -16,7 +16,7 @@ enum : int { kModeF32 = 0, kModeU16 = 1, kModeU8 = 2 };
 
 // Status codes a kernel may leave in the device status word.
 enum : int { kDevOk = 0, kDevTimeoutProducer = 1, kDevTimeoutMma = 2, kDevTimeoutEpilogue = 3,
-             kDevTimeoutUpdateProducer = 11, kDevTimeoutUpdateConsumer = 12 };
+             kDevTimeoutUpdateProducer = 11, kDevTimeoutUpdateConsumer = 12, kDevTimeoutExchange = 13 };
 
 struct Geometry
 {
@@ -64,7 +64,12 @@ struct DistanceArgs
     unsigned long long* keys;   // [n_img][n], must hold kKeyEmpty on entry
     void* s_out;                // optional full matrix [n_img][n][T]: u32 (u8), u64 (u16), f32 (f32)
     int* status;                // device status word
+    // Optional tail (one image, integer modes): the last block to finish reduces keys[0..n) to this
+    // shard's record and publishes it as launch_bmu phase 1 would.  tail_counter: zeroed uint32.
+    const struct BmuArgs* tail; uint32_t* tail_counter;
 };
+// True when launch_distance honours DistanceArgs::tail for this geometry.
+bool distance_has_tail(const Geometry& g);
 // Returns cudaSuccess or the launch / tensor-map error; *why receives a static message.
 cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why);
 
@@ -75,6 +80,18 @@ cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream
 // rotation (flip reverses rows last, src/CudaLib/flip_kernel.h:28; a quarter
 // turn maps (x, y) <- (nd-1-y, x), src/CudaLib/rotate_90_degrees_list.h:28).
 struct UpdateItem { uint32_t n, tq; int32_t ax, ay, a0; float f; };
+
+// Exchange of the per-rank best-matching-unit records through peer memory: every rank owns
+// kXchgSlots x world records; rank r writes its record of step `seq` into entry
+// [seq % kXchgSlots][r] of EVERY rank's array with two plain 8-byte stores over NVLink, and the
+// update kernel polls its own array.  Each word carries the low 8 bits of `seq` as a tag
+// (w0 = code << 8 | tag, w1 = neuron << 8 | tag), so a word is valid as soon as its tag matches
+// and no fence or flag has to follow the data; a slot is reused every kXchgSlots steps, whose
+// tags differ.  A rank can be at most one step ahead of another (it needs the other's record to
+// finish a step), so the ring is never overrun.  Codes stay below 2^56 (checked on the host).
+struct XchgRecord { unsigned long long w0, w1; };
+constexpr uint32_t kXchgSlots = 4;
+constexpr uint32_t kXchgMaxRanks = 16;
 
 struct BmuArgs
 {
@@ -88,6 +105,9 @@ struct BmuArgs
     uint32_t magic_R, magic_q;        // multiply-high reciprocals of R and q (0 = divisor 1); need T * R < 2^32
     uint32_t* arrive;                 // fused update only: block arrival counter, zero between launches
     unsigned long long* stats;        // nullable: [0] += neurons with a non-zero factor, [1] += neurons written back
+    // peer-memory exchange (world > 1, xchg_seq != 0): this rank's record array and every rank's (own included)
+    XchgRecord* xchg_local; XchgRecord* xchg_peer[kXchgMaxRanks]; unsigned long long xchg_seq;
+    int* status;                      // device status word (receives a code if the wait for the records expires)
 };
 // phase bit 0: reduce keys[0..n) to this shard's (code, first_neuron + argmin) record in pairs[rank];
 // phase bit 1: pick the global best matching unit from pairs, count the hit, re-arm the keys and emit

@@ -17,6 +17,7 @@
 // the reference's CPU loop (src/SelfOrganizingMapLib/Trainer.h:167-179).
 #include "kernels.cuh"
 #include "ptx.cuh"
+#include "record.cuh"
 
 #include <algorithm>
 
@@ -41,64 +42,24 @@ __device__ __forceinline__ uint32_t quant_u16(float v)
     return q;
 }
 
-__device__ __forceinline__ bool pair_less(unsigned long long c0, unsigned long long n0,
-                                          unsigned long long c1, unsigned long long n1)
-{
-    return c0 < c1 || (c0 == c1 && n0 < n1);
-}
-
-// Block-wide first minimum of (code, index) pairs held one per thread.
-__device__ __forceinline__ void block_min_pair(unsigned long long& bc, unsigned long long& bn,
-                                               unsigned long long* sc, unsigned long long* sn)
-{
-    for (int o = 16; o > 0; o >>= 1) {
-        unsigned long long oc = __shfl_down_sync(0xffffffffu, bc, o), on = __shfl_down_sync(0xffffffffu, bn, o);
-        if (pair_less(oc, on, bc, bn)) { bc = oc; bn = on; }
-    }
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (lane == 0) { sc[warp] = bc; sn[warp] = bn; }
-    __syncthreads();
-    if (warp == 0) {
-        const int nw = blockDim.x >> 5;
-        bc = lane < nw ? sc[lane] : ~0ull;
-        bn = lane < nw ? sn[lane] : ~0ull;
-        for (int o = 16; o > 0; o >>= 1) {
-            unsigned long long oc = __shfl_down_sync(0xffffffffu, bc, o), on = __shfl_down_sync(0xffffffffu, bn, o);
-            if (pair_less(oc, on, bc, bn)) { bc = oc; bn = on; }
-        }
-    }
-}
+constexpr uint32_t kXchgSpinLimit = 1u << 22;     // polls of >= 128 ns each: gives up after roughly a second
 
 // v / d for v * d < 2^32 with magic = floor(2^32 / d) + 1; magic == 0 encodes the divisor 1.
 __device__ __forceinline__ uint32_t bmu_div(uint32_t v, uint32_t magic) { return magic ? __umulhi(v, magic) : v; }
 
 constexpr int kBmuThreads = 512;
-constexpr int kBmuPer = 8;            // keys a thread loads per pass, all in flight at once
 
-// Phase 1, one block: first minimum of (code, neuron) over this shard's keys -> pairs[rank].
+// Phase 1, one block: first minimum of (code, neuron) over this shard's keys -> this rank's record.
 __global__ void __launch_bounds__(kBmuThreads)
 bmu_kernel(BmuArgs a)
 {
     __shared__ unsigned long long sc[32], sn[32];
-    unsigned long long bc = ~0ull, bn = ~0ull;
-    for (uint32_t p0 = 0; p0 < a.n; p0 += kBmuThreads * kBmuPer) {
-        unsigned long long k[kBmuPer];
-#pragma unroll
-        for (int e = 0; e < kBmuPer; ++e) {
-            const uint32_t i = p0 + e * kBmuThreads + threadIdx.x;
-            k[e] = i < a.n ? a.keys[i] : ~0ull;
-        }
-#pragma unroll
-        for (int e = 0; e < kBmuPer; ++e) {
-            const uint32_t i = p0 + e * kBmuThreads + threadIdx.x;
-            if (i < a.n && pair_less(k[e] >> a.shift, i, bc, bn)) { bc = k[e] >> a.shift; bn = i; }
-        }
-    }
-    block_min_pair(bc, bn, sc, sn);
-    if (threadIdx.x == 0) {
-        a.pairs[a.rank].code = bc;
-        a.pairs[a.rank].neuron = bn == ~0ull ? ~0ull : bn + a.first_neuron;
-    }
+    unsigned long long bc, bn;
+    block_argmin_keys(a.keys, a.n, a.shift, kBmuThreads, sc, sn, bc, bn);
+    __syncthreads();
+    if (threadIdx.x == 0) { sc[0] = bc; sn[0] = bn == ~0ull ? ~0ull : bn + a.first_neuron; }
+    __syncthreads();
+    publish_record(a, sc[0], sn[0]);
 }
 
 // Transform index -> base rotation and affine source map of a work-list entry.
@@ -541,14 +502,42 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                     if (pair_less(oc, on, bc, bn)) { bc = oc; bn = on; }
                 }
                 bn += b.first_neuron;
-            } else {
+            } else if (b.xchg_seq == 0) {
                 // lexicographic minimum over the per-rank records: lowest distance, then lowest neuron index
                 bc = b.pairs[0].code; bn = b.pairs[0].neuron;
                 for (uint32_t r = 1; r < b.world; ++r)
                     if (pair_less(b.pairs[r].code, b.pairs[r].neuron, bc, bn)) { bc = b.pairs[r].code; bn = b.pairs[r].neuron; }
+            } else {
+                // the records arrive through peer stores: lane r waits (bounded) for rank r's record of this step
+                const XchgRecord* slot = b.xchg_local + (b.xchg_seq % kXchgSlots) * b.world;
+                const unsigned long long tag = b.xchg_seq & 0xFFull;
+                bool arrived = true;
+                for (uint32_t r = lane; r < b.world; r += 32) {
+                    unsigned long long w0 = 0, w1 = 0;
+                    bool seen = false;
+                    for (uint32_t spin = 0; spin < kXchgSpinLimit; ++spin) {
+                        w0 = ld_relaxed_sys(&slot[r].w0);
+                        w1 = ld_relaxed_sys(&slot[r].w1);
+                        if ((w0 & 0xFFull) == tag && (w1 & 0xFFull) == tag) { seen = true; break; }
+                        __nanosleep(128);
+                    }
+                    // an absent neuron index (~0) lost its upper bits to the tag; restore it so it never wins
+                    const unsigned long long oc = w0 >> 8, on = (w1 >> 8) == (~0ull >> 8) ? ~0ull : w1 >> 8;
+                    if (seen && pair_less(oc, on, bc, bn)) { bc = oc; bn = on; }
+                    arrived = arrived && seen;
+                }
+                arrived = __all_sync(0xffffffffu, arrived);
+                for (int o = 16; o > 0; o >>= 1) {
+                    const unsigned long long oc = __shfl_down_sync(0xffffffffu, bc, o), on = __shfl_down_sync(0xffffffffu, bn, o);
+                    if (pair_less(oc, on, bc, bn)) { bc = oc; bn = on; }
+                }
+                if (!arrived) {               // a rank never delivered: report, and leave the map untouched
+                    bn = ~0ull;
+                    if (lane == 0 && b.status) atomicCAS(b.status, kDevOk, kDevTimeoutExchange);
+                }
             }
             if (lane == 0) {
-                const uint32_t bmu = (uint32_t)bn;
+                const uint32_t bmu = (uint32_t)bn;          // ~0u: no best matching unit (exchange failed)
                 bmu_s = bmu;
                 if (blockIdx.x == 0 && bmu >= b.first_neuron && bmu - b.first_neuron < b.n) {   // this rank owns the unit
                     atomicAdd(&b.counts[bmu], 1u);
@@ -559,14 +548,15 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
         consumer_sync();
 
         // ---- factors of the fixed entries; ordered compaction of the other neurons with a non-zero factor
-        const float* frow = b.factors + (size_t)bmu_s * b.n;
-        if (ctid < m_fixed) items[ctid].f = frow[items[ctid].n];
+        const bool have_bmu = bmu_s != ~0u;
+        const float* frow = b.factors + (have_bmu ? (size_t)bmu_s * b.n : 0);
+        if (ctid < m_fixed) items[ctid].f = have_bmu ? frow[items[ctid].n] : 0.0f;
         uint32_t total = 0;
         for (uint32_t c0 = 0; c0 < b.n; c0 += kChunk) {
             const uint32_t i0 = c0 + 4 * ctid;
             float f[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) f[e] = (i0 + e < b.n && i0 + e >= n_fixed) ? frow[i0 + e] : 0.0f;
+            for (int e = 0; e < 4; ++e) f[e] = (have_bmu && i0 + e < b.n && i0 + e >= n_fixed) ? frow[i0 + e] : 0.0f;
             if (!one_chunk || b.world > 1) load_keys(i0);
             const uint32_t cnt = (f[0] != 0.0f) + (f[1] != 0.0f) + (f[2] != 0.0f) + (f[3] != 0.0f);
             uint32_t incl = cnt;                                   // inclusive scan over the warp's threads

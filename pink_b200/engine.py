@@ -112,6 +112,10 @@ class Engine:
     def train_device(self, dev_ptr, n):
         capi.check(capi.lib.pink_b200_train_device(self._h, C.c_void_p(dev_ptr), n))
 
+    def exchange_kind(self):
+        """0 none, 1 NCCL all-gather per step, 2 peer-memory stores."""
+        return int(capi.lib.pink_b200_exchange_kind(self._h))
+
     def launch_count(self):
         """Kernels launched by this context so far."""
         return int(capi.lib.pink_b200_launch_count(self._h))

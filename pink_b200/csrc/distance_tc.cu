@@ -19,7 +19,10 @@
 //   hh = ah.bh,  ll = al.bl,  cross = ah.bl + al.bh,
 //   a.b = 65536*hh + 256*cross + ll        (combined in 64-bit integers).
 //
-// One CTA computes a 128-neuron x n_tile-transform tile: warp 0 streams
+// A CTA computes a 128-neuron x n_tile-transform tile.  The kernel is bound by the operand bytes an
+// SM pulls from L2, so two CTAs of a cluster work as a pair where possible (tcgen05 cta_group::2:
+// one M=256 MMA over both CTAs' neuron rows; each CTA stages only half of the transform rows; the
+// even CTA issues, its commits signal both CTAs).  No TMA multicast is used.  Warp 0 streams
 // 128-byte-swizzled K slices of both operands with TMA into a multi-stage
 // shared-memory ring, warp 1 issues the MMAs, warps 2-5 run the epilogue.
 // Every mbarrier wait is bounded; on a time-out the CTA records a status code
@@ -29,6 +32,8 @@
 #include "record.cuh"
 
 #include <algorithm>
+#include <type_traits>
+#include <cstdlib>
 
 #include <cudaTypedefs.h>
 
@@ -41,16 +46,20 @@ constexpr uint32_t kBlockK = 128;          // bytes of K per pipeline stage = on
 constexpr uint32_t kUmmaK = 32;            // K per kind::i8 instruction
 constexpr uint32_t kThreads = 192;
 
-template <int MODE> struct TcCfg;
-template <> struct TcCfg<kModeU8>  { static constexpr uint32_t planes = 1, max_n = 256, stages = 4, cols = 256; };
-template <> struct TcCfg<kModeU16> { static constexpr uint32_t planes = 2, max_n = 128, stages = 3, cols = 512; };
+// PAIR: two CTAs of a cluster share one M=256 MMA (cta_group::2); each stages its own 128 neuron
+// rows and only half of the transform rows, which frees shared memory for deeper rings.
+template <int MODE, bool PAIR> struct TcCfg;
+template <> struct TcCfg<kModeU8, false>  { static constexpr uint32_t planes = 1, max_n = 256, stages = 4, cols = 256; };
+template <> struct TcCfg<kModeU16, false> { static constexpr uint32_t planes = 2, max_n = 128, stages = 3, cols = 512; };
+template <> struct TcCfg<kModeU8, true>   { static constexpr uint32_t planes = 1, max_n = 256, stages = 6, cols = 256; };
+template <> struct TcCfg<kModeU16, true>  { static constexpr uint32_t planes = 2, max_n = 128, stages = 4, cols = 512; };
 
-template <int MODE>
+template <int MODE, bool PAIR>
 struct SmemLayout
 {
-    using Cfg = TcCfg<MODE>;
+    using Cfg = TcCfg<MODE, PAIR>;
     static constexpr uint32_t a_bytes = kBlockM * kBlockK;            // per plane
-    static constexpr uint32_t b_bytes = Cfg::max_n * kBlockK;         // per plane (capacity)
+    static constexpr uint32_t b_bytes = Cfg::max_n / (PAIR ? 2 : 1) * kBlockK;   // per plane (capacity)
     static constexpr uint32_t stage_bytes = Cfg::planes * (a_bytes + b_bytes);
     static constexpr uint32_t ring_bytes = Cfg::stages * stage_bytes;
     static constexpr uint32_t bar_off = ring_bytes;                   // full[stages], empty[stages], tmem_full
@@ -76,14 +85,14 @@ __device__ __forceinline__ void report(int* status, int code)
     if (status) atomicCAS(status, kDevOk, code);
 }
 
-template <int MODE>
+template <int MODE, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                    const __grid_constant__ CUtensorMap map_b0, const __grid_constant__ CUtensorMap map_b1,
                    const TcParams p)
 {
-    using Cfg = TcCfg<MODE>;
-    using L = SmemLayout<MODE>;
+    using Cfg = TcCfg<MODE, PAIR>;
+    using L = SmemLayout<MODE, PAIR>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -97,44 +106,75 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
     const uint32_t m0 = blockIdx.x * kBlockM;
     const uint32_t t0 = blockIdx.y * p.n_tile;
     const uint32_t img = blockIdx.z;
-    const uint32_t stage_tx = Cfg::planes * (L::a_bytes + p.n_tile * kBlockK);
+    // PAIR: rank of this CTA in its pair (the even CTA issues the MMAs) and the transform rows it stages
+    const uint32_t pair_rank = PAIR ? cluster_ctarank() : 0u;
+    const uint32_t b_rows = PAIR ? p.n_tile / 2 : p.n_tile;
+    const uint32_t stage_tx = Cfg::planes * (L::a_bytes + b_rows * kBlockK);
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < Cfg::stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        // PAIR: both CTAs' producers arrive (with their byte counts) on the issuing CTA's full barriers
+        for (uint32_t s = 0; s < Cfg::stages; ++s) { mbar_init(&full_bar[s], PAIR ? 2 : 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(tmem_full_bar, 1);
         mbar_fence_init();
         tma_prefetch_desc(&map_a0);
         tma_prefetch_desc(&map_b0);
         if (MODE == kModeU16) { tma_prefetch_desc(&map_a1); tma_prefetch_desc(&map_b1); }
     }
-    if (warp == 1) { tmem_alloc(tmem_ptr_s, Cfg::cols); tmem_relinquish(); }
+    if (warp == 1) {
+        if (PAIR) { tmem_alloc_pair(tmem_ptr_s, Cfg::cols); tmem_relinquish_pair(); }
+        else { tmem_alloc(tmem_ptr_s, Cfg::cols); tmem_relinquish(); }
+    }
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync();             // the peer's barriers are initialised before anything arrives on them
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_s;
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer --
         if (elect_one()) {
-            const int32_t brow = (int32_t)(img * p.T + t0);
+            const int32_t brow = (int32_t)(img * p.T + t0 + pair_rank * b_rows);
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                 const uint32_t s = kb % Cfg::stages, ph = (kb / Cfg::stages) & 1;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1)) { report(p.status, kDevTimeoutProducer); break; }
-                mbar_expect_tx(&full_bar[s], stage_tx);
                 uint8_t* st = smem + s * L::stage_bytes;
                 const int32_t kx = (int32_t)(kb * kBlockK);
-                tma_load_2d(st, &map_a0, &full_bar[s], kx, (int32_t)m0);
-                tma_load_2d(st + Cfg::planes * L::a_bytes, &map_b0, &full_bar[s], kx, brow);
-                if (MODE == kModeU16) {
-                    tma_load_2d(st + L::a_bytes, &map_a1, &full_bar[s], kx, (int32_t)m0);
-                    tma_load_2d(st + Cfg::planes * L::a_bytes + L::b_bytes, &map_b1, &full_bar[s], kx, brow);
+                if (PAIR) {
+                    const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);      // the issuing CTA's barrier
+                    mbar_expect_tx_cluster(bar, stage_tx);
+                    tma_load_2d_pair(st, &map_a0, bar, kx, (int32_t)m0);
+                    tma_load_2d_pair(st + Cfg::planes * L::a_bytes, &map_b0, bar, kx, brow);
+                    if (MODE == kModeU16) {
+                        tma_load_2d_pair(st + L::a_bytes, &map_a1, bar, kx, (int32_t)m0);
+                        tma_load_2d_pair(st + Cfg::planes * L::a_bytes + L::b_bytes, &map_b1, bar, kx, brow);
+                    }
+                } else {
+                    mbar_expect_tx(&full_bar[s], stage_tx);
+                    tma_load_2d(st, &map_a0, &full_bar[s], kx, (int32_t)m0);
+                    tma_load_2d(st + Cfg::planes * L::a_bytes, &map_b0, &full_bar[s], kx, brow);
+                    if (MODE == kModeU16) {
+                        tma_load_2d(st + L::a_bytes, &map_a1, &full_bar[s], kx, (int32_t)m0);
+                        tma_load_2d(st + Cfg::planes * L::a_bytes + L::b_bytes, &map_b1, &full_bar[s], kx, brow);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer --
-        if (elect_one()) {
-            const uint32_t idesc = make_idesc_u8(kBlockM, p.n_tile);
+        if (pair_rank == 0 && elect_one()) {
+            const uint32_t idesc = make_idesc_u8(PAIR ? 2 * kBlockM : kBlockM, p.n_tile);
+            // PAIR: one instruction computes both CTAs' tiles; completion is signalled to both
+            auto mma = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t acc) {
+                if (PAIR) umma_i8_pair(d, a, b, idesc, acc); else umma_i8(d, a, b, idesc, acc);
+            };
+            auto commit = [&](uint64_t* bar) {
+                if (PAIR) {
+                    umma_commit_pair(smem_u32(bar));
+                    umma_commit_pair(map_to_cta(smem_u32(bar), 1));
+                } else {
+                    umma_commit(bar);
+                }
+            };
             bool ok = true;
             for (uint32_t kb = 0; kb < p.num_kb && ok; ++kb) {
                 const uint32_t s = kb % Cfg::stages, ph = (kb / Cfg::stages) & 1;
@@ -148,87 +188,118 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     const uint64_t adv = (k * kUmmaK) >> 4;   // 32 bytes along K inside the swizzled row
                     const uint32_t acc = (kb | k) != 0;
                     if (MODE == kModeU8) {
-                        umma_i8(tmem_base, a_hi + adv, b_hi + adv, idesc, acc);
+                        mma(tmem_base, a_hi + adv, b_hi + adv, acc);
                     } else {
                         const uint64_t a_lo = make_sw128_kmajor_desc(st + L::a_bytes);
                         const uint64_t b_lo = make_sw128_kmajor_desc(st + Cfg::planes * L::a_bytes + L::b_bytes);
-                        umma_i8(tmem_base, a_hi + adv, b_hi + adv, idesc, acc);                         // hh
-                        umma_i8(tmem_base + Cfg::max_n, a_lo + adv, b_lo + adv, idesc, acc);            // ll
-                        umma_i8(tmem_base + 2 * Cfg::max_n, a_hi + adv, b_lo + adv, idesc, acc);        // cross
-                        umma_i8(tmem_base + 2 * Cfg::max_n, a_lo + adv, b_hi + adv, idesc, 1u);
+                        mma(tmem_base, a_hi + adv, b_hi + adv, acc);                         // hh
+                        mma(tmem_base + Cfg::max_n, a_lo + adv, b_lo + adv, acc);            // ll
+                        mma(tmem_base + 2 * Cfg::max_n, a_hi + adv, b_lo + adv, acc);        // cross
+                        mma(tmem_base + 2 * Cfg::max_n, a_lo + adv, b_hi + adv, 1u);
                     }
                 }
-                umma_commit(&empty_bar[s]);      // frees the stage once these MMAs have read it
+                commit(&empty_bar[s]);           // frees the stage once these MMAs have read it
             }
-            umma_commit(tmem_full_bar);          // accumulators complete
+            commit(tmem_full_bar);               // accumulators complete
         }
     } else {
         // ----------------------------------------------------------- epilogue --
+        // A thread owns one neuron row (TMEM lane) and walks the tile's columns in chunks of 16: the
+        // next chunk's tcgen05.ld is in flight while the current one is reduced, and four independent
+        // (minimum, column) chains keep the compare/select latency off the critical path.
+        using val_t = typename std::conditional<MODE == kModeU8, uint32_t, unsigned long long>::type;
+        val_t* nbv = reinterpret_cast<val_t*>(nb_s);         // |b|^2 per column of this tile
         const uint32_t et = threadIdx.x - 64;               // 0..127
         const uint32_t quad = warp & 3;                      // TMEM lane quadrant this warp may read
         const uint32_t row = quad * 32 + lane;
         const uint32_t n = m0 + row;
+        const uint32_t ncols = p.T > t0 ? min(p.n_tile, p.T - t0) : 0u;     // columns that are transforms of this image
         for (uint32_t j = et; j < p.n_tile; j += 128) {
-            const uint32_t t = t0 + j;
-            unsigned long long v = 0;
-            if (t < p.T) {
-                v = MODE == kModeU8 ? (unsigned long long)static_cast<const uint32_t*>(p.bnorm)[(size_t)img * p.T + t]
-                                    : static_cast<const unsigned long long*>(p.bnorm)[(size_t)img * p.T + t];
-            }
-            nb_s[j] = v;
+            val_t v = 0;
+            if (j < ncols) v = static_cast<const val_t*>(p.bnorm)[(size_t)img * p.T + t0 + j];
+            nbv[j] = v;
         }
-        unsigned long long na = 0;
-        if (n < p.n) {
-            na = MODE == kModeU8 ? (unsigned long long)static_cast<const uint32_t*>(p.anorm)[n]
-                                 : static_cast<const unsigned long long*>(p.anorm)[n];
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");      // nb_s visible to the four epilogue warps
+        const val_t na = n < p.n ? static_cast<const val_t*>(p.anorm)[n] : val_t(0);
+        asm volatile("bar.sync 1, 128;" ::: "memory");      // nbv visible to the four epilogue warps
 
-        unsigned long long best_s = ~0ull;
-        uint32_t best_t = 0;
+        constexpr int kChains = 4;
+        val_t best[kChains];
+        uint32_t bcol[kChains];
+#pragma unroll
+        for (int c = 0; c < kChains; ++c) { best[c] = ~val_t(0); bcol[c] = 0; }
         if (mbar_wait(tmem_full_bar, 0)) {
             tc_fence_after();
             const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
-            for (uint32_t c0 = 0; c0 < p.n_tile; c0 += 16) {
-                uint32_t v0[16], v1[16], v2[16];
-                tmem_ld_32x16(lane_addr + c0, v0);
+            auto load = [&](uint32_t c0, uint32_t (&x0)[16], uint32_t (&x1)[16], uint32_t (&x2)[16]) {
+                tmem_ld_32x16(lane_addr + c0, x0);
                 if (MODE == kModeU16) {
-                    tmem_ld_32x16(lane_addr + Cfg::max_n + c0, v1);
-                    tmem_ld_32x16(lane_addr + 2 * Cfg::max_n + c0, v2);
+                    tmem_ld_32x16(lane_addr + Cfg::max_n + c0, x1);
+                    tmem_ld_32x16(lane_addr + 2 * Cfg::max_n + c0, x2);
                 }
-                tmem_ld_wait();
+            };
+            auto wait = [&](uint32_t (&x0)[16], uint32_t (&x1)[16], uint32_t (&x2)[16]) {
+                tmem_ld_wait_on(x0);
+                if (MODE == kModeU16) { tmem_ld_wait_on(x1); tmem_ld_wait_on(x2); }
+            };
+            auto reduce = [&](uint32_t c0, const uint32_t (&x0)[16], const uint32_t (&x1)[16], const uint32_t (&x2)[16]) {
+                val_t sv[16];
 #pragma unroll
                 for (uint32_t j = 0; j < 16; ++j) {
-                    const uint32_t t = t0 + c0 + j;
-                    unsigned long long s;
                     if (MODE == kModeU8) {
-                        // exact: 0 <= S < 2^32 although the intermediate wraps modulo 2^32
-                        s = (uint32_t)((uint32_t)na + (uint32_t)nb_s[c0 + j] - 2u * v0[j]);
+                        // exact: 0 <= S < 2^31 although the intermediates wrap modulo 2^32
+                        sv[j] = (uint32_t)(na + nbv[c0 + j]) - 2u * x0[j];
                     } else {
-                        const unsigned long long dot = ((unsigned long long)v0[j] << 16)
-                                                     + ((unsigned long long)v2[j] << 8) + v1[j];
-                        s = na + nb_s[c0 + j] - 2ull * dot;
-                    }
-                    if (t < p.T) {
-                        if (s < best_s) { best_s = s; best_t = t; }
-                        if (p.s_out && n < p.n) {
-                            const size_t o = ((size_t)img * p.n + n) * p.T + t;
-                            if (MODE == kModeU8) static_cast<uint32_t*>(p.s_out)[o] = (uint32_t)s;
-                            else static_cast<unsigned long long*>(p.s_out)[o] = s;
-                        }
+                        const unsigned long long dot = ((unsigned long long)x0[j] << 16)
+                                                     + ((unsigned long long)x2[j] << 8) + x1[j];
+                        sv[j] = na + nbv[c0 + j] - 2ull * dot;
                     }
                 }
+                if (c0 + 16 > ncols) {                        // ragged last chunk: columns beyond T never win
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; ++j) if (c0 + j >= ncols) sv[j] = ~val_t(0);
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < 16; ++j)
+                    if (sv[j] < best[j % kChains]) { best[j % kChains] = sv[j]; bcol[j % kChains] = c0 + j; }
+                if (p.s_out && n < p.n) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; ++j)
+                        if (c0 + j < ncols)
+                            static_cast<val_t*>(p.s_out)[((size_t)img * p.n + n) * p.T + t0 + c0 + j] = sv[j];
+                }
+            };
+            uint32_t a0[16], a1[16], a2[16], b0[16], b1[16], b2[16];
+            if (ncols) load(0, a0, a1, a2);
+            for (uint32_t c0 = 0; c0 < ncols; c0 += 32) {
+                wait(a0, a1, a2);
+                if (c0 + 16 < ncols) load(c0 + 16, b0, b1, b2);
+                reduce(c0, a0, a1, a2);
+                if (c0 + 16 < ncols) {
+                    wait(b0, b1, b2);
+                    if (c0 + 32 < ncols) load(c0 + 32, a0, a1, a2);
+                    reduce(c0 + 16, b0, b1, b2);
+                }
             }
-            if (n < p.n && best_s != ~0ull)
-                atomicMin(&p.keys[(size_t)img * p.n + n], (best_s << key_shift(MODE)) | best_t);
+            // first minimum over the chains: lowest S, then lowest column
+            val_t best_s = best[0];
+            uint32_t best_c = bcol[0];
+#pragma unroll
+            for (int c = 1; c < kChains; ++c)
+                if (best[c] < best_s || (best[c] == best_s && bcol[c] < best_c)) { best_s = best[c]; best_c = bcol[c]; }
+            if (n < p.n && best_s != ~val_t(0))
+                atomicMin(&p.keys[(size_t)img * p.n + n],
+                          ((unsigned long long)best_s << key_shift(MODE)) | (unsigned long long)(t0 + best_c));
         } else {
             report(p.status, kDevTimeoutEpilogue);
         }
     }
 
     tc_fence_before();
-    __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, Cfg::cols);
+    if (PAIR) cluster_sync();             // neither CTA leaves while the other may still signal or read it
+    else __syncthreads();
+    if (warp == 1) {
+        if (PAIR) tmem_dealloc_pair(tmem_base, Cfg::cols); else tmem_dealloc(tmem_base, Cfg::cols);
+    }
 
     // Tail (training with several ranks): the block that finishes last has all per-neuron minima in
     // front of it; it reduces them to this shard's best-matching-unit record and hands the record to the
@@ -286,22 +357,25 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_by
     return r == CUDA_SUCCESS;
 }
 
-template <int MODE>
+template <int MODE, bool PAIR>
 cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why)
 {
-    using Cfg = TcCfg<MODE>;
-    using L = SmemLayout<MODE>;
+    using Cfg = TcCfg<MODE, PAIR>;
+    using L = SmemLayout<MODE, PAIR>;
+    // neuron tiles; CTA pairs take two consecutive ones (an odd count is padded with an empty tile)
+    uint32_t m_tiles = (a.n + kBlockM - 1) / kBlockM;
+    if (PAIR) m_tiles = (m_tiles + 1) & ~1u;
     // Balanced transform tiles, each a multiple of 16 columns: the fewest tiles of at most max_n
     // columns -- unless that leaves SMs without a block (a small neuron shard, few images): a block's
-    // run time is set by the bytes it pulls through its SM, (128 + n_tile) * K, so narrower tiles
-    // spread over all SMs finish sooner.  Below 32 columns the neuron tile dominates and nothing is gained.
+    // run time is set by the bytes it pulls through its SM, (128 + its share of n_tile) * K, so narrower
+    // tiles spread over all SMs finish sooner.  Below 32 columns the neuron tile dominates and nothing is gained.
     uint32_t tiles = (g.T + Cfg::max_n - 1) / Cfg::max_n;
     {
         static int sm_dev = -1, sms = 0;
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev != sm_dev) { cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); sm_dev = dev; }
-        const uint64_t rows = (uint64_t)((a.n + kBlockM - 1) / kBlockM) * a.n_img;
+        const uint64_t rows = (uint64_t)m_tiles * a.n_img;
         const uint32_t most = std::max<uint32_t>(tiles, g.T / 32);
         if (sms > 0 && rows * tiles < (uint64_t)sms)
             tiles = (uint32_t)std::max<uint64_t>(tiles, std::min<uint64_t>(most, (uint64_t)sms / rows));   // one wave
@@ -309,11 +383,12 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     uint32_t n_tile = ((g.T + tiles - 1) / tiles + 15) & ~15u;
     if (n_tile > Cfg::max_n) n_tile = Cfg::max_n;
     const uint32_t n_tiles = (g.T + n_tile - 1) / n_tile;
+    const uint32_t b_box = PAIR ? n_tile / 2 : n_tile;         // transform rows one CTA stages per K slice
 
     CUtensorMap ma0, ma1, mb0, mb1;
-    bool ok = make_map(&ma0, a.a0, a.n, g.Kp, kBlockM) && make_map(&mb0, a.b0, (uint64_t)a.n_img * g.T, g.Kp, n_tile);
+    bool ok = make_map(&ma0, a.a0, a.n, g.Kp, kBlockM) && make_map(&mb0, a.b0, (uint64_t)a.n_img * g.T, g.Kp, b_box);
     if (MODE == kModeU16)
-        ok = ok && make_map(&ma1, a.a1, a.n, g.Kp, kBlockM) && make_map(&mb1, a.b1, (uint64_t)a.n_img * g.T, g.Kp, n_tile);
+        ok = ok && make_map(&ma1, a.a1, a.n, g.Kp, kBlockM) && make_map(&mb1, a.b1, (uint64_t)a.n_img * g.T, g.Kp, b_box);
     else { ma1 = ma0; mb1 = mb0; }
     if (!ok) { *why = "cuTensorMapEncodeTiled failed"; return cudaErrorInvalidValue; }
 
@@ -321,7 +396,7 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev != attr_dev) {
-        cudaError_t e = cudaFuncSetAttribute(distance_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(distance_tc_kernel<MODE, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)L::total);
         if (e != cudaSuccess) { *why = "cudaFuncSetAttribute(distance_tc_kernel)"; return e; }
         attr_dev = dev;
@@ -331,10 +406,30 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     p.n = a.n; p.T = g.T; p.num_kb = g.Kp / kBlockK; p.n_tile = n_tile;
     p.tail_counter = a.tail ? a.tail_counter : nullptr;
     if (a.tail) p.tail = *a.tail;
-    dim3 grid((a.n + kBlockM - 1) / kBlockM, n_tiles, a.n_img);
-    distance_tc_kernel<MODE><<<grid, kThreads, L::total, st>>>(ma0, ma1, mb0, mb1, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(m_tiles, n_tiles, a.n_img);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = L::total;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     *why = "distance_tc_kernel launch";
-    return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, distance_tc_kernel<MODE, PAIR>, ma0, ma1, mb0, mb1, p);
+}
+
+// CTA pairs halve the transform rows every SM pulls through its L2 port (the kernel's bound) as soon
+// as there are two neuron tiles to pair.  PINK_B200_SINGLE_CTA_MMA (diagnostic switch) keeps single CTAs.
+template <int MODE>
+cudaError_t launch_tc_any(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why)
+{
+    static const bool single = getenv("PINK_B200_SINGLE_CTA_MMA") != nullptr;
+    if (a.n > kBlockM && !single) return launch_tc<MODE, true>(g, a, st, why);
+    return launch_tc<MODE, false>(g, a, st, why);
 }
 
 } // namespace
@@ -347,8 +442,8 @@ cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream
 {
     *why = "";
     if (a.n == 0 || a.n_img == 0) return cudaSuccess;
-    if (g.mode == kModeU8) return launch_tc<kModeU8>(g, a, st, why);
-    if (g.mode == kModeU16) return launch_tc<kModeU16>(g, a, st, why);
+    if (g.mode == kModeU8) return launch_tc_any<kModeU8>(g, a, st, why);
+    if (g.mode == kModeU16) return launch_tc_any<kModeU16>(g, a, st, why);
     return launch_distance_f32(g, a, st, why);
 }
 

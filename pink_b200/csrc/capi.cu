@@ -146,9 +146,9 @@ struct pink_b200_ctx
     uint32_t train_batch = 0, map_batch = 0;
     cudaStream_t stream = nullptr, copy_stream = nullptr, rot_stream = nullptr;
     cudaEvent_t copied[2] = { nullptr, nullptr }, consumed[2] = { nullptr, nullptr };
-    // Training pipelines the rotation sets of the next kRotBatch images (they do
-    // not depend on the SOM) on rot_stream while the sequential steps of the
-    // current batch run on stream; two slots of transform buffers alternate.
+    // Training computes the rotation sets of kRotBatch images at once (they do not
+    // depend on the SOM) into one of two alternating slots of transform buffers;
+    // rot_stream is the training stream itself unless PINK_B200_ROT_OVERLAP is set.
     cudaEvent_t rotated[2] = { nullptr, nullptr }, rot_free[2] = { nullptr, nullptr };
     uint64_t rot_seq = 0;
 
@@ -501,11 +501,13 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
         CTX_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
         CTX_TRY(cudaStreamCreateWithPriority(&c->stream, cudaStreamNonBlocking, hi));
         CTX_TRY(cudaStreamCreateWithPriority(&c->copy_stream, cudaStreamNonBlocking, hi));
-        // Diagnostic switches (timing the kernels in isolation, exercising the unfused path):
-        // PINK_B200_ROT_SERIAL puts the rotation kernels on the training stream,
-        // PINK_B200_SPLIT_UPDATE keeps best-matching-unit reduction and work list in kernels of their own.
+        // The rotation kernels (16 images ahead) run on the training stream: on a stream of their own
+        // their blocks keep the other kernels' blocks, which need a whole SM each, from starting, and the
+        // step gets slower (measured).  Diagnostic switches: PINK_B200_ROT_OVERLAP puts them on a second,
+        // low-priority stream anyway; PINK_B200_SPLIT_UPDATE keeps best-matching-unit reduction and work
+        // list in kernels of their own.
         c->fuse_update = update_can_fuse(c->g) && !getenv("PINK_B200_SPLIT_UPDATE");
-        if (getenv("PINK_B200_ROT_SERIAL")) c->rot_stream = c->stream;
+        if (!getenv("PINK_B200_ROT_OVERLAP")) c->rot_stream = c->stream;
         else CTX_TRY(cudaStreamCreateWithPriority(&c->rot_stream, cudaStreamNonBlocking, lo));
     }
     for (int i = 0; i < 2; ++i) {

@@ -129,6 +129,9 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
     else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_s;
+    // Everything above is independent of earlier kernels; the operands, norms and keys are not.
+    griddep_launch();
+    griddep_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer --
@@ -411,13 +414,17 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = L::total;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = PAIR ? 2 : 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // the kernel's set-up may overlap the tail of the kernel before it in the stream (it waits
+    // with griddepcontrol.wait before it touches global memory)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     *why = "distance_tc_kernel launch";
     return cudaLaunchKernelEx(&cfg, distance_tc_kernel<MODE, PAIR>, ma0, ma1, mb0, mb1, p);
 }

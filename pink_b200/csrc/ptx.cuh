@@ -27,6 +27,22 @@ __device__ __forceinline__ bool elect_one()
     return pred != 0;
 }
 
+// ------------------------------------------ programmatic dependent launch --
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still running; it must not touch anything that kernel reads
+// or writes before griddep_wait() returns (which is when that kernel has completed and its
+// writes are visible).  griddep_launch() tells the scheduler that the NEXT kernel may be started
+// as soon as every block of this one has called it (or exited).
+__device__ __forceinline__ void griddep_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void griddep_launch()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier --
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
 {

@@ -344,6 +344,13 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
         mbar_init(&list_bar, 1);
         mbar_fence_init();
     }
+    // operand staging starts as zeros: the padding beyond K is never written again
+    for (uint32_t s = 0; s < pp.stages; ++s)
+        for (uint32_t i = threadIdx.x; i < pp.crop_bytes / 4; i += kPipeThreads)
+            reinterpret_cast<uint32_t*>(pipe_dyn + (size_t)s * pp.stage_bytes + pp.off_crop)[i] = 0;
+    // Everything above is independent of earlier kernels; keys, map and operands are not.
+    griddep_launch();
+    griddep_wait();
     // fixed entries of this block; their factor is filled in once the best matching unit is known
     const uint32_t n_fixed = min(pp.stages * gridDim.x, b.n);               // neurons below this index are fixed entries
     const uint32_t m_fixed = b.n > blockIdx.x ? min(pp.stages, (b.n - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0u;
@@ -351,10 +358,6 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
         const uint32_t n = blockIdx.x + threadIdx.x * gridDim.x;
         items[threadIdx.x] = make_item(b, n, b.keys[n], 0.0f);
     }
-    // operand staging starts as zeros: the padding beyond K is never written again
-    for (uint32_t s = 0; s < pp.stages; ++s)
-        for (uint32_t i = threadIdx.x; i < pp.crop_bytes / 4; i += kPipeThreads)
-            reinterpret_cast<uint32_t*>(pipe_dyn + (size_t)s * pp.stage_bytes + pp.off_crop)[i] = 0;
     fence_async_smem();                   // zeroed operand staging visible to later bulk stores
     __syncthreads();
     const uint32_t plane_bytes = g.P * 4;
@@ -808,8 +811,19 @@ cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, const BmuArg
         attr_dev = dev;
         attr_bytes = smem;
     }
-    update_pipe_kernel<MODE><<<grid, kPipeThreads, smem, st>>>(g, a, pp, *fused);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kPipeThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    // the kernel's set-up may overlap the tail of the kernel before it in the stream (it waits
+    // with griddepcontrol.wait before it touches global memory)
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, update_pipe_kernel<MODE>, g, a, pp, *fused);
 }
 
 } // namespace

@@ -20,6 +20,8 @@
 #include "../../include/pink_b200.h"
 #include "kernels.cuh"
 
+#include <type_traits>
+
 #include <cmath>
 
 namespace pinkb {
@@ -122,7 +124,7 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
     // uint8: [pad | plane | pad | transposed plane | pad]; other modes: the plane only
     stage_t* stage = reinterpret_cast<stage_t*>(rot_dyn + (MODE == kModeU8 ? kStagePad : 0));
     uint8_t* stage_tr = rot_dyn + 2 * kStagePad + ((g.P + 15) & ~15u);
-    __shared__ unsigned long long norm_s[8];
+    __shared__ unsigned long long norm_s[8][kRotThreads / 32];   // per variant and warp: partial sum of squares
 
     const uint32_t tq = blockIdx.x, img_i = blockIdx.y;
     const uint32_t nbase = g.q ? g.q : 1;
@@ -130,7 +132,6 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
     const float* img = images + (size_t)img_i * g.C * g.id * g.id;
     float* gbase = base_out + ((size_t)img_i * nbase + tq) * g.P;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x < 8) norm_s[threadIdx.x] = 0;
 
     // Phase 1: the base rotation (quadrant 0, no flip) of all channels.
     {
@@ -223,7 +224,8 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
         a0 += (ax + ay) * (int32_t)g.off;            // x = off + i, y = off + jj
         const bool asc = j == 0 || j == 3;           // source bytes ascend with the operand index
         const uint8_t* run_plane = (j & 1) ? stage_tr : reinterpret_cast<const uint8_t*>(stage);
-        unsigned long long acc = 0;
+        // a thread's share of a row's sum of squares fits 32 bits in uint8 mode (K * 255^2 < 2^32)
+        typename std::conditional<MODE == kModeU8, uint32_t, unsigned long long>::type acc = 0;
         for (uint32_t gi = threadIdx.x; gi < groups; gi += kRotThreads) {
             const uint32_t k = gi * kGroup;
             uint32_t r = fast_div(k, magic_ed), jj = k - r * g.ed;                  // r = c * ed + i
@@ -247,7 +249,7 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
                     o[0] = r0; o[1] = r1; o[2] = r2; o[3] = r3;
                 }
 #pragma unroll
-                for (int m = 0; m < 4; ++m) acc += __dp4a(o[m], o[m], 0u);
+                for (int m = 0; m < 4; ++m) acc = __dp4a(o[m], o[m], (uint32_t)acc);
                 reinterpret_cast<uint4*>(static_cast<uint8_t*>(b0) + orow * g.Kp)[gi] = make_uint4(o[0], o[1], o[2], o[3]);
                 continue;
             }
@@ -270,7 +272,7 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
                 for (int q4 = 0; q4 < 4; ++q4) {
                     wv[q4] = (uint32_t)val[4 * q4] | ((uint32_t)val[4 * q4 + 1] << 8)
                            | ((uint32_t)val[4 * q4 + 2] << 16) | ((uint32_t)val[4 * q4 + 3] << 24);
-                    acc += __dp4a(wv[q4], wv[q4], 0u);
+                    acc = __dp4a(wv[q4], wv[q4], (uint32_t)acc);
                 }
                 reinterpret_cast<uint4*>(static_cast<uint8_t*>(b0) + orow * g.Kp)[gi] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
             } else if (MODE == kModeU16) {
@@ -295,7 +297,7 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
         }
         if (MODE != kModeF32) {
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
-            if (lane == 0) atomicAdd(&norm_s[v], acc);
+            if (lane == 0) norm_s[v][warp] = acc;
         }
     }
     if (MODE != kModeF32) {
@@ -303,8 +305,10 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
         if (threadIdx.x < nv) {
             const uint32_t v = threadIdx.x, f = v / nq, j = v - f * nq;
             const size_t orow = (size_t)img_i * g.T + f * g.R + j * g.q + tq;
-            if (MODE == kModeU8) static_cast<uint32_t*>(bnorm)[orow] = (uint32_t)norm_s[v];
-            else static_cast<unsigned long long*>(bnorm)[orow] = norm_s[v];
+            unsigned long long tot = 0;
+            for (uint32_t wv = 0; wv < kRotThreads / 32; ++wv) tot += norm_s[v][wv];
+            if (MODE == kModeU8) static_cast<uint32_t*>(bnorm)[orow] = (uint32_t)tot;
+            else static_cast<unsigned long long*>(bnorm)[orow] = tot;
         }
     }
 }

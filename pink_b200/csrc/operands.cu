@@ -147,45 +147,50 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
             pys[i] = __fmul_rn(py, sa);
             pyc[i] = __fmul_rn(py, ca);
         }
+        const uint32_t idm1 = g.id - 1;
         for (uint32_t row = warp; row < rows; row += kRotThreads / 32) {
             const uint32_t c = fast_div(row, magic_nd), x = row - c * g.nd;
             const float* plane = img + (size_t)c * g.id * g.id;
             const float px = __fsub_rn((float)x, dc);
             const float xc = __fmul_rn(px, ca), xs = __fmul_rn(px, sa);
-            // one output pixel; ys, yc are the column terms py*sin, py*cos
+            const uint32_t row_idx = row * g.nd, tr_idx = c * P1 + x;
+            // One output pixel; ys, yc are the column terms py*sin, py*cos.  Branch-free: positions
+            // outside the image are clamped for the (then unused) taps and the result is zeroed.
             auto pixel = [&](uint32_t y, float ys, float yc) {
                 float v;
-                if (tq == 0) {
+                if (tq == 0) {                                     // block-uniform
                     v = resize_pixel(plane, g.id, g.nd, x, y);
                 } else {
                     // inverse rotation and bilinear taps; every product and sum rounded
                     // separately, in the order of src/ImageProcessingLib/rotate.h:37-63
                     const float sx = __fadd_rn(__fsub_rn(xc, ys), sc);
                     const float sy = __fadd_rn(__fadd_rn(xs, yc), sc);
-                    v = 0.0f;
-                    if (!(sx < 0.0f || sx > lim || sy < 0.0f || sy > lim)) {
-                        // floor by adding 2^23 with truncation: exact for 0 <= s < 2^23, and it keeps
-                        // the conversions off the (slow) conversion pipe
-                        const float tx = __fadd_rz(sx, 8388608.0f), ty = __fadd_rz(sy, 8388608.0f);
-                        const uint32_t ix = __float_as_uint(tx) & 0x7FFFFFu, iy = __float_as_uint(ty) & 0x7FFFFFu;
-                        const float rx = __fsub_rn(sx, __fsub_rn(tx, 8388608.0f));
-                        const float ry = __fsub_rn(sy, __fsub_rn(ty, 8388608.0f));
-                        // the +1 taps carry weight 0 when they would fall outside; clamp the index
-                        const uint32_t dx = ix + 1 < g.id ? g.id : 0u, dy = iy + 1 < g.id ? 1u : 0u;
-                        const float cx = __fsub_rn(1.0f, rx), cy = __fsub_rn(1.0f, ry);
-                        const float* r0 = plane + (ix * g.id + iy);
-                        const float t00 = __fmul_rn(__fmul_rn(cx, cy), __ldg(r0));
-                        const float t01 = __fmul_rn(__fmul_rn(cx, ry), __ldg(r0 + dy));
-                        const float t10 = __fmul_rn(__fmul_rn(rx, cy), __ldg(r0 + dx));
-                        const float t11 = __fmul_rn(__fmul_rn(rx, ry), __ldg(r0 + dx + dy));
-                        v = __fadd_rn(__fadd_rn(__fadd_rn(t00, t01), t10), t11);
-                    }
+                    const bool inside = fminf(sx, sy) >= 0.0f && fmaxf(sx, sy) <= lim;
+                    const float qx = fminf(fmaxf(sx, 0.0f), lim), qy = fminf(fmaxf(sy, 0.0f), lim);   // = sx, sy when inside
+                    // floor by adding 2^23 with truncation: exact for 0 <= s < 2^23, and it keeps
+                    // the conversions off the (slow) conversion pipe
+                    const float tx = __fadd_rz(qx, 8388608.0f), ty = __fadd_rz(qy, 8388608.0f);
+                    const uint32_t ix = __float_as_uint(tx) & 0x7FFFFFu, iy = __float_as_uint(ty) & 0x7FFFFFu;
+                    const float rx = __fsub_rn(qx, __fsub_rn(tx, 8388608.0f));
+                    const float ry = __fsub_rn(qy, __fsub_rn(ty, 8388608.0f));
+                    // the +1 taps carry weight 0 when they would fall outside; clamp the index
+                    const uint32_t dx = ix < idm1 ? g.id : 0u, dy = iy < idm1 ? 1u : 0u;
+                    const float cx = __fsub_rn(1.0f, rx), cy = __fsub_rn(1.0f, ry);
+                    const uint32_t o00 = ix * g.id + iy;
+                    const float p00 = __ldg(plane + o00), p01 = __ldg(plane + (o00 + dy));
+                    const float p10 = __ldg(plane + (o00 + dx)), p11 = __ldg(plane + (o00 + dx + dy));
+                    const float t00 = __fmul_rn(__fmul_rn(cx, cy), p00);
+                    const float t01 = __fmul_rn(__fmul_rn(cx, ry), p01);
+                    const float t10 = __fmul_rn(__fmul_rn(rx, cy), p10);
+                    const float t11 = __fmul_rn(__fmul_rn(rx, ry), p11);
+                    v = __fadd_rn(__fadd_rn(__fadd_rn(t00, t01), t10), t11);
+                    v = inside ? v : 0.0f;
                 }
-                const uint32_t idx = row * g.nd + y;
+                const uint32_t idx = row_idx + y;
                 if (use_smem) {
                     const stage_t sv = to_stage<MODE>(v);
                     stage[idx] = sv;
-                    if (MODE == kModeU8) stage_tr[c * P1 + y * g.nd + x] = (uint8_t)sv;
+                    if (MODE == kModeU8) stage_tr[tr_idx + y * g.nd] = (uint8_t)sv;
                 }
                 if (base_out) gbase[idx] = v;
             };

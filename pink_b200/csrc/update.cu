@@ -318,6 +318,25 @@ struct PipeParams
     int* status;
 };
 
+// Shared-memory accesses by 32-bit shared-window address: the consumers' loops step such addresses
+// with one 32-bit add per row instead of carrying 64-bit generic pointers.
+__device__ __forceinline__ float lds_f32(uint32_t addr)
+{
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v)
+{
+    asm volatile("st.shared.f32 [%0], %1;" :: "r"(addr), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ void sts_u8(uint32_t addr, uint32_t v)
+{
+    asm volatile("st.shared.u8 [%0], %1;" :: "r"(addr), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ void consumer_sync()
 {
     asm volatile("bar.sync 1, %0;" :: "n"(kPipeConsumers) : "memory");
@@ -456,7 +475,7 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                 const uint32_t kk = (unit / 32) * 128 + (unit % 32) + 32 * e;
                 const uint32_t c = kk / K1, rem = kk - c * K1, ci = rem / g.ed, cj = rem - ci * g.ed;
                 const bool ok = unit < nunit && kk < g.K;
-                un_src[k][e] = ok ? c * P1 + (g.off + ci) * g.nd + g.off + cj : 0u;
+                un_src[k][e] = ok ? 4 * (c * P1 + (g.off + ci) * g.nd + g.off + cj) : 0u;   // byte offset in the neuron
                 un_dst[k][e] = ok ? kk : ~0u;
             }
         }
@@ -606,13 +625,10 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
         for (uint32_t jx = 0; jx < M; ++jx) {
             const uint32_t s = jx % pp.stages, ph = (jx / pp.stages) & 1;
             if (!mbar_wait(&full_bar[s], ph)) { if (pp.status) atomicCAS(pp.status, kDevOk, kDevTimeoutUpdateConsumer); break; }
-            uint8_t* st = pipe_dyn + (size_t)s * pp.stage_bytes;
-            float* som_s = reinterpret_cast<float*>(st);
-            const float* base_s = reinterpret_cast<const float*>(st + pp.off_base);
-            uint8_t* crop_s = st + pp.off_crop;
+            const uint32_t som_a = smem_u32(pipe_dyn) + s * pp.stage_bytes;       // shared-window byte addresses
+            const uint32_t base_a = som_a + pp.off_base, crop_a = som_a + pp.off_crop;
             const UpdateItem it = items[jx];
             const float f = it.f;
-            const int32_t ax = it.ax;
             if (f == 0.0f) {                  // a fixed entry outside the neighbourhood: nothing to do
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&done_bar[s]);
@@ -621,30 +637,31 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             // -- w <- w - (w - r) * f over the whole neuron, kPipeUnroll rows per step:
             //    all loads, then the arithmetic, then the stores; no predicates in the steady loop
             bool changed = false;
+            const uint32_t sw = nd * 4;                              // byte step of a neuron row
+            const int32_t sb = it.ax * 4;                            // byte step of the base rotation per neuron row
 #pragma unroll
             for (int k = 0; k < kPipeMaxTasks; ++k) {
-                float* ps = som_s + tk_si[k];
-                const float* pb = base_s + ((int32_t)(tk_c[k] * P1) + ax * (int32_t)tk_x0[k] + it.a0 + it.ay * (int32_t)tk_y[k]);
+                uint32_t aw = som_a + tk_si[k] * 4;
+                uint32_t ab = base_a + 4 * (uint32_t)((int32_t)(tk_c[k] * P1) + it.ax * (int32_t)tk_x0[k] + it.a0 + it.ay * (int32_t)tk_y[k]);
                 for (uint32_t i = 0; i < tk_full[k]; ++i) {
-                    float e[kPipeUnroll], rv[kPipeUnroll];
+                    float w[kPipeUnroll], rv[kPipeUnroll], e[kPipeUnroll];
 #pragma unroll
-                    for (int u = 0; u < kPipeUnroll; ++u) { e[u] = ps[u * nd]; rv[u] = pb[u * ax]; }
+                    for (int u = 0; u < kPipeUnroll; ++u) { w[u] = lds_f32(aw + u * sw); rv[u] = lds_f32(ab + u * sb); }
 #pragma unroll
                     for (int u = 0; u < kPipeUnroll; ++u) {
-                        const float w = e[u];
-                        e[u] = __fsub_rn(w, __fmul_rn(__fsub_rn(w, rv[u]), f));
-                        changed |= __float_as_uint(e[u]) != __float_as_uint(w);
+                        e[u] = __fsub_rn(w[u], __fmul_rn(__fsub_rn(w[u], rv[u]), f));
+                        changed |= __float_as_uint(e[u]) != __float_as_uint(w[u]);
                     }
 #pragma unroll
-                    for (int u = 0; u < kPipeUnroll; ++u) ps[u * nd] = e[u];
-                    ps += kPipeUnroll * nd; pb += kPipeUnroll * ax;
+                    for (int u = 0; u < kPipeUnroll; ++u) sts_f32(aw + u * sw, e[u]);
+                    aw += kPipeUnroll * sw; ab += kPipeUnroll * sb;
                 }
                 for (uint32_t i = 0; i < tk_tail[k]; ++i) {
-                    const float w = *ps;
-                    const float e = __fsub_rn(w, __fmul_rn(__fsub_rn(w, *pb), f));
+                    const float w = lds_f32(aw);
+                    const float e = __fsub_rn(w, __fmul_rn(__fsub_rn(w, lds_f32(ab)), f));
                     changed |= __float_as_uint(e) != __float_as_uint(w);
-                    *ps = e;
-                    ps += nd; pb += ax;
+                    sts_f32(aw, e);
+                    aw += sw; ab += sb;
                 }
             }
             {
@@ -663,22 +680,22 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                 if (ctid + k * kPipeConsumers < nunit) {
                     float v[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) v[e] = som_s[un_src[k][e]];
+                    for (int e = 0; e < 4; ++e) v[e] = lds_f32(som_a + un_src[k][e]);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const uint32_t kk = un_dst[k][e];
                         if (kk != ~0u) {
                             if (MODE == kModeU8) {
                                 const uint32_t qv = quant_u8(v[e]);
-                                crop_s[kk] = (uint8_t)qv;
+                                sts_u8(crop_a + kk, qv);
                                 acc += qv * qv;
                             } else if (MODE == kModeU16) {
                                 const uint32_t qv = quant_u16(v[e]);
-                                crop_s[kk] = (uint8_t)(qv >> 8);
-                                crop_s[g.Kp + kk] = (uint8_t)(qv & 255u);
+                                sts_u8(crop_a + kk, qv >> 8);
+                                sts_u8(crop_a + g.Kp + kk, qv & 255u);
                                 acc += (unsigned long long)qv * qv;
                             } else {
-                                reinterpret_cast<float*>(crop_s)[kk] = v[e];
+                                sts_f32(crop_a + 4 * kk, v[e]);
                             }
                         }
                     }

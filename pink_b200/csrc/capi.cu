@@ -163,6 +163,8 @@ struct pink_b200_ctx
     UpdateItem* d_items = nullptr; uint32_t* d_nitems = nullptr;   // per-step work list of the update
     // records of the ranks' best matching units exchanged by peer stores (world_size > 1, all ranks on one node)
     XchgRecord* d_xchg = nullptr; XchgRecord* xchg_peer[kXchgMaxRanks] = {}; bool xchg_on = false; unsigned long long xchg_seq = 0;
+    // value ranges for leaving out neurons that cannot change: per neuron {min |w|, max |w|}, per buffered image max |pixel|
+    uint2* d_wrange = nullptr; uint32_t* d_rmax = nullptr;
     unsigned long long* d_stats = nullptr;   // [0] neurons with a non-zero factor, [1] neurons written back, summed over steps
     uint64_t launches = 0;            // kernels launched by this context so far
     bool fuse_update = false;         // the update kernel finds the best matching unit and its work list itself
@@ -302,6 +304,8 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     ua.base = c->d_base + slot_img * (g.q ? g.q : 1) * (size_t)g.P;
     ua.items = c->d_items; ua.n_items = c->d_nitems; ua.n = c->count;
     ua.a0 = c->d_a0; ua.a1 = c->d_a1; ua.anorm = c->d_anorm;
+    ua.wrange = fused ? c->d_wrange : nullptr;
+    ua.rmax = fused && c->d_wrange ? c->d_rmax + slot_img : nullptr;
     if (ev) CU_TRY(cudaEventRecord(ev[2], c->stream));
     if (fused) LAUNCH_TRY(launch_update_fused(g, ua, ba, c->stream, c->d_status));
     else LAUNCH_TRY(launch_update(g, ua, c->stream, c->d_status));
@@ -326,12 +330,13 @@ int train_chunk(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* l
         if (c->prof_used < c->prof_cap && 2 * (c->prof_rot_used + 1) <= c->prof_rot_events.size())
             ev = &c->prof_rot_events[2 * c->prof_rot_used++];
         if (ev) CU_TRY(cudaEventRecord(ev[0], c->rot_stream));
+        CU_TRY(cudaMemsetAsync(c->d_rmax + slot, 0, cnt * sizeof(uint32_t), c->rot_stream));
         LAUNCH_TRY(launch_rotate(g, d_images + s0 * isz, cnt, c->d_cs, c->d_sn,
                                  c->d_base + slot * (g.q ? g.q : 1) * (size_t)g.P,
                                  static_cast<uint8_t*>(c->d_b0) + row0 * g.Kp * esz,
                                  c->d_b1 ? static_cast<uint8_t*>(c->d_b1) + row0 * g.Kp * esz : nullptr,
                                  static_cast<uint8_t*>(c->d_bnorm) + row0 * (g.mode == kModeU16 ? 8 : 4),
-                                 c->rot_stream));
+                                 c->rot_stream, c->d_rmax + slot));
         c->launches += 1;
         if (ev) CU_TRY(cudaEventRecord(ev[1], c->rot_stream));
         CU_TRY(cudaEventRecord(c->rotated[slot ? 1 : 0], c->rot_stream));
@@ -529,6 +534,8 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     CTX_TRY(cudaMemsetAsync(c->d_pairs, 0xFF, W * sizeof(BmuPair), c->stream));
     CTX_TRY(cudaMalloc(&c->d_items, c->count * sizeof(UpdateItem)));
     CTX_TRY(cudaMemsetAsync(c->d_items, 0, c->count * sizeof(UpdateItem), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_rmax, 2 * kRotBatch * sizeof(uint32_t)));
+    CTX_TRY(cudaMemsetAsync(c->d_rmax, 0, 2 * kRotBatch * sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_stats, 2 * sizeof(unsigned long long)));
     CTX_TRY(cudaMemsetAsync(c->d_stats, 0, 2 * sizeof(unsigned long long), c->stream));
     // [0] work-list length, [1] block arrival counter of the update kernel, [2] of the distance kernel
@@ -574,7 +581,7 @@ int pink_b200_destroy(pink_b200_ctx* c)
     free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
     free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_base);
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
-    free_dev(c->d_items); free_dev(c->d_nitems); free_dev(c->d_stats);
+    free_dev(c->d_items); free_dev(c->d_nitems); free_dev(c->d_stats); free_dev(c->d_wrange); free_dev(c->d_rmax);
     free_dev(c->d_pairs); free_dev(c->d_counts); free_dev(c->d_bmu_log); free_dev(c->d_status);
     free_dev(c->d_images[0]); free_dev(c->d_images[1]); free_dev(c->d_dist); free_dev(c->d_rot);
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
@@ -636,7 +643,8 @@ int pink_b200_set_som(pink_b200_ctx* c, const float* host_som)
     CU_TRY(cudaMemcpy2DAsync(c->d_som, (size_t)g.Pp * sizeof(float), host_som + (size_t)c->first * g.P,
                              (size_t)g.P * sizeof(float), (size_t)g.P * sizeof(float), c->count,
                              cudaMemcpyHostToDevice, c->stream));
-    LAUNCH_TRY(launch_quantize_som(g, c->d_som, c->count, c->d_a0, c->d_a1, c->d_anorm, c->stream));
+    if (c->fuse_update && !c->d_wrange) CU_TRY(cudaMalloc(&c->d_wrange, (size_t)c->count * sizeof(uint2)));
+    LAUNCH_TRY(launch_quantize_som(g, c->d_som, c->count, c->d_a0, c->d_a1, c->d_anorm, c->stream, c->d_wrange));
     c->launches += 1;
     CU_TRY(cudaStreamSynchronize(c->stream));
     c->have_som = true;

@@ -48,13 +48,15 @@ struct BmuPair { unsigned long long code; unsigned long long neuron; };
 // b0/b1: operand planes [n_img*T][Kp] (u8: b0; u16: b0 = high byte, b1 = low
 // byte; f32: b0 as float).  bnorm: [n_img*T] sum of squares (u32 for u8,
 // u64 for u16, unused for f32).
+// rmax (nullable): [n_img] words zeroed by the caller; receives the bit pattern of max |pixel| over each image's base rotations.
 cudaError_t launch_rotate(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
-                   float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st);
+                   float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st, uint32_t* rmax = nullptr);
 
 // ---- SOM operand ------------------------------------------------------------
 // som: [n][Pp] float.  a0/a1/anorm: as b0/b1/bnorm with one row per neuron.
+// wrange (nullable): [n] bit patterns of {min |w|, max |w|} over each whole neuron.
 cudaError_t launch_quantize_som(const Geometry& g, const float* som, uint32_t n, void* a0, void* a1, void* anorm,
-                         cudaStream_t st);
+                         cudaStream_t st, uint2* wrange = nullptr);
 
 // ---- distances + minimum over transforms ------------------------------------
 struct DistanceArgs
@@ -123,7 +125,29 @@ struct UpdateArgs
     const UpdateItem* items; const uint32_t* n_items;   // work list from launch_bmu
     uint32_t n;                       // local neurons (upper bound of the work list)
     void* a0; void* a1; void* anorm;  // SOM operand rows to refresh
+    // Fused form only (both nullable together): per-neuron {min |w|, max |w|} as float bit patterns,
+    // kept up to date by the kernel, and the bit pattern of max |r| over the current image's base
+    // rotations.  With them the kernel leaves out neurons that provably cannot change (see cannot_change).
+    uint2* wrange; const uint32_t* rmax;
 };
+
+// True when  w - (w - r) * f  (each operation rounded to nearest, as the update computes it) returns w
+// itself for EVERY w with wmin <= |w| <= wmax and every |r| <= rmax:  the product is at most
+// up(up(wmax + rmax) * f) in magnitude, and anything below a quarter of the spacing of the floats at
+// wmin rounds away in the final subtraction.  Zero, denormal or NaN inputs give no guarantee (false).
+// Arguments are float bit patterns of non-negative values; f > 0.
+__host__ __device__ inline bool cannot_change(float f, uint32_t wmin_bits, uint32_t wmax_bits, uint32_t rmax_bits)
+{
+#ifdef __CUDA_ARCH__
+    if (wmin_bits < 0x00800000u || wmax_bits >= 0x7F800000u || rmax_bits >= 0x7F800000u) return false;
+    const float quarter_ulp = __uint_as_float(wmin_bits & 0x7F800000u) * 2.98023224e-8f;      // 2^e * 2^-25, exact
+    const float bound = __fmul_ru(__fadd_ru(__uint_as_float(wmax_bits), __uint_as_float(rmax_bits)), fabsf(f));
+    return bound < quarter_ulp;
+#else
+    (void)f; (void)wmin_bits; (void)wmax_bits; (void)rmax_bits;
+    return false;
+#endif
+}
 // Unfused form: one block per neuron works through the list launch_bmu (phase 2) wrote.
 cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t st, int* status);
 // Fused form, a persistent pipelined kernel: it reduces the keys (world == 1) or the exchanged

@@ -117,7 +117,7 @@ template <int MODE>
 __global__ void __launch_bounds__(kRotThreads)
 rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, uint32_t magic_nd, uint32_t magic_ed,
               const float* __restrict__ cs, const float* __restrict__ sn, float* __restrict__ base_out,
-              void* __restrict__ b0, void* __restrict__ b1, void* __restrict__ bnorm)
+              void* __restrict__ b0, void* __restrict__ b1, void* __restrict__ bnorm, uint32_t* __restrict__ rmax)
 {
     using stage_t = typename StageType<MODE>::type;
     extern __shared__ __align__(16) uint8_t rot_dyn[];
@@ -125,6 +125,8 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
     stage_t* stage = reinterpret_cast<stage_t*>(rot_dyn + (MODE == kModeU8 ? kStagePad : 0));
     uint8_t* stage_tr = rot_dyn + 2 * kStagePad + ((g.P + 15) & ~15u);
     __shared__ unsigned long long norm_s[8][kRotThreads / 32];   // per variant and warp: partial sum of squares
+    __shared__ uint32_t vmax_s[kRotThreads / 32];
+    uint32_t vmax = 0;                    // bit pattern of max |pixel| seen by this thread (NaN patterns compare highest)
 
     const uint32_t tq = blockIdx.x, img_i = blockIdx.y;
     const uint32_t nbase = g.q ? g.q : 1;
@@ -186,6 +188,7 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
                     v = __fadd_rn(__fadd_rn(__fadd_rn(t00, t01), t10), t11);
                     v = inside ? v : 0.0f;
                 }
+                vmax = max(vmax, __float_as_uint(v) & 0x7FFFFFFFu);
                 const uint32_t idx = row_idx + y;
                 if (use_smem) {
                     const stage_t sv = to_stage<MODE>(v);
@@ -208,7 +211,16 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
             }
         }
     }
+    if (rmax) {
+        vmax = __reduce_max_sync(0xffffffffu, vmax);
+        if (lane == 0) vmax_s[warp] = vmax;
+    }
     __syncthreads();   // also orders this block's global writes before its own reads below
+    if (rmax && threadIdx.x == 0) {
+        uint32_t m = 0;
+        for (uint32_t wv = 0; wv < kRotThreads / 32; ++wv) m = max(m, vmax_s[wv]);
+        atomicMax(rmax + img_i, m);
+    }
 
     // Phase 2: operand rows of every transform derived from this base.
     const uint32_t nq = g.q ? 4 : 1, nv = nq * (g.flip ? 2 : 1);
@@ -325,9 +337,10 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
 template <int MODE>
 __global__ void __launch_bounds__(256)
 quantize_som_kernel(Geometry g, const float* __restrict__ som, void* __restrict__ a0, void* __restrict__ a1,
-                    void* __restrict__ anorm)
+                    void* __restrict__ anorm, uint2* __restrict__ wrange)
 {
     __shared__ unsigned long long red[8];
+    __shared__ uint32_t lo_s[8], hi_s[8];
     const size_t n = blockIdx.x;
     const float* src = som + n * g.Pp;
     const uint32_t P1 = g.nd * g.nd, K1 = g.ed * g.ed;
@@ -368,6 +381,22 @@ quantize_som_kernel(Geometry g, const float* __restrict__ som, void* __restrict_
             else static_cast<unsigned long long*>(anorm)[n] = s;
         }
     }
+    if (wrange) {
+        // bit patterns of min |w| and max |w| over the whole neuron (integer order = float order for
+        // non-negative values; NaN patterns compare highest)
+        uint32_t lo = 0xFFFFFFFFu, hi = 0;
+        for (uint32_t i = threadIdx.x; i < g.P; i += blockDim.x) {
+            const uint32_t b = __float_as_uint(src[i]) & 0x7FFFFFFFu;
+            lo = min(lo, b); hi = max(hi, b);
+        }
+        lo = __reduce_min_sync(0xffffffffu, lo); hi = __reduce_max_sync(0xffffffffu, hi);
+        if ((threadIdx.x & 31) == 0) { lo_s[threadIdx.x >> 5] = lo; hi_s[threadIdx.x >> 5] = hi; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (uint32_t wv = 1; wv < blockDim.x / 32; ++wv) { lo = min(lo, lo_s[wv]); hi = max(hi, hi_s[wv]); }
+            wrange[n] = make_uint2(lo, hi);
+        }
+    }
 }
 
 __global__ void fill_keys_kernel(unsigned long long* keys, size_t count)
@@ -380,7 +409,7 @@ constexpr size_t kRotateSmemLimit = 200 * 1024;
 
 template <int MODE>
 cudaError_t rotate_dispatch(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
-                     float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st)
+                     float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st, uint32_t* rmax)
 {
     size_t smem = MODE == kModeU8 ? 2 * (((size_t)g.P + 15) & ~size_t(15)) + 3 * kStagePad
                                   : (size_t)g.P * sizeof(typename StageType<MODE>::type);
@@ -401,28 +430,28 @@ cudaError_t rotate_dispatch(const Geometry& g, const float* images, uint32_t n_i
     const uint32_t magic_nd = div_magic(g.nd), magic_ed = div_magic(g.ed);
     dim3 grid(g.q ? g.q : 1, n_img);
     rotate_kernel<MODE><<<grid, kRotThreads, smem, st>>>(g, images, use_smem, magic_nd, magic_ed, cs, sn, base_out,
-                                                         b0, b1, bnorm);
+                                                         b0, b1, bnorm, rmax);
     return cudaGetLastError();
 }
 
 } // namespace
 
 cudaError_t launch_rotate(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
-                          float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st)
+                          float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st, uint32_t* rmax)
 {
     if (n_img == 0) return cudaSuccess;
-    if (g.mode == kModeU8) return rotate_dispatch<kModeU8>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
-    if (g.mode == kModeU16) return rotate_dispatch<kModeU16>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
-    return rotate_dispatch<kModeF32>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st);
+    if (g.mode == kModeU8) return rotate_dispatch<kModeU8>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st, rmax);
+    if (g.mode == kModeU16) return rotate_dispatch<kModeU16>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st, rmax);
+    return rotate_dispatch<kModeF32>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st, rmax);
 }
 
 cudaError_t launch_quantize_som(const Geometry& g, const float* som, uint32_t n, void* a0, void* a1, void* anorm,
-                                cudaStream_t st)
+                                cudaStream_t st, uint2* wrange)
 {
     if (n == 0) return cudaSuccess;
-    if (g.mode == kModeU8) quantize_som_kernel<kModeU8><<<n, 256, 0, st>>>(g, som, a0, a1, anorm);
-    else if (g.mode == kModeU16) quantize_som_kernel<kModeU16><<<n, 256, 0, st>>>(g, som, a0, a1, anorm);
-    else quantize_som_kernel<kModeF32><<<n, 256, 0, st>>>(g, som, a0, a1, anorm);
+    if (g.mode == kModeU8) quantize_som_kernel<kModeU8><<<n, 256, 0, st>>>(g, som, a0, a1, anorm, wrange);
+    else if (g.mode == kModeU16) quantize_som_kernel<kModeU16><<<n, 256, 0, st>>>(g, som, a0, a1, anorm, wrange);
+    else quantize_som_kernel<kModeF32><<<n, 256, 0, st>>>(g, som, a0, a1, anorm, wrange);
     return cudaGetLastError();
 }
 

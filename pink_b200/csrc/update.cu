@@ -353,6 +353,7 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
     __shared__ unsigned long long red_c[32], red_n[32];
     __shared__ uint32_t scan_s[32], bmu_s, last_s, m_s;
     __shared__ uint32_t chg_s[kPipeMaxStages][32];                            // per warp: did any value of the neuron change?
+    __shared__ uint2 rng_s[kPipeMaxStages][32];                               // per warp: bit patterns of min |w|, max |w| of the new values
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -409,6 +410,11 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             const bool live = nonzero && __any_sync(0xffffffffu, lane < kPipeConsumerWarps && chg_s[s][lane] != 0);
             n_live += nonzero; n_rewritten += live;
             uint8_t* st = pipe_dyn + (size_t)s * pp.stage_bytes;
+            if (a.wrange && live) {
+                const uint2 r = lane < kPipeConsumerWarps ? rng_s[s][lane] : make_uint2(0xFFFFFFFFu, 0u);
+                const uint32_t lo = __reduce_min_sync(0xffffffffu, r.x), hi = __reduce_max_sync(0xffffffffu, r.y);
+                if (lane == 0) a.wrange[n] = make_uint2(lo, hi);
+            }
             if (MODE != kModeF32 && live) {
                 unsigned long long tot = lane < kPipeConsumerWarps ? norm_s[s][lane] : 0ull;
                 for (int o = 16; o > 0; o >>= 1) tot += __shfl_down_sync(0xffffffffu, tot, o);
@@ -497,6 +503,23 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                 for (int e = 0; e < 4; ++e) kreg[e] = i0 + e < b.n ? b.keys[i0 + e] : ~0ull;
             }
         };
+        // neurons that provably keep every value (tiny factor against the spacing of their values) will count
+        // as factor 0; their value ranges do not depend on the best matching unit and are fetched up front
+        const bool can_skip = a.wrange != nullptr && a.rmax != nullptr;
+        const uint32_t rmax_bits = can_skip ? *a.rmax : 0u;
+        uint2 wr[4];
+        auto load_ranges = [&](uint32_t i0) {
+            if (i0 + 3 < b.n) {
+                const uint4 r01 = *reinterpret_cast<const uint4*>(a.wrange + i0);
+                const uint4 r23 = *reinterpret_cast<const uint4*>(a.wrange + i0 + 2);
+                wr[0] = make_uint2(r01.x, r01.y); wr[1] = make_uint2(r01.z, r01.w);
+                wr[2] = make_uint2(r23.x, r23.y); wr[3] = make_uint2(r23.z, r23.w);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) wr[e] = i0 + e < b.n ? a.wrange[i0 + e] : make_uint2(0u, 0u);
+            }
+        };
+        if (can_skip && one_chunk) load_ranges(4 * ctid);
         unsigned long long bc = ~0ull, bn = ~0ull;
         if (b.world == 1) {
             for (uint32_t c0 = 0; c0 < b.n; c0 += kChunk) {
@@ -570,15 +593,38 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
         consumer_sync();
 
         // ---- factors of the fixed entries; ordered compaction of the other neurons with a non-zero factor
+        // With a single chunk and a single rank no key is read after this point, so the block can announce
+        // that it is done with the keys now; the answer is needed only after the list has been built.
+        const bool early_arrival = one_chunk && b.world == 1;
+        uint32_t arrival = 0;
+        if (early_arrival && ctid == 0) {
+            __threadfence();
+            arrival = atomicAdd(b.arrive, 1u);
+        }
         const bool have_bmu = bmu_s != ~0u;
         const float* frow = b.factors + (have_bmu ? (size_t)bmu_s * b.n : 0);
-        if (ctid < m_fixed) items[ctid].f = have_bmu ? frow[items[ctid].n] : 0.0f;
+        if (ctid < m_fixed) {
+            float ff = have_bmu ? frow[items[ctid].n] : 0.0f;
+            if (can_skip && ff != 0.0f) {
+                const uint2 r = a.wrange[items[ctid].n];
+                if (cannot_change(ff, r.x, r.y, rmax_bits)) ff = 0.0f;
+            }
+            items[ctid].f = ff;
+        }
         uint32_t total = 0;
         for (uint32_t c0 = 0; c0 < b.n; c0 += kChunk) {
             const uint32_t i0 = c0 + 4 * ctid;
             float f[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) f[e] = (have_bmu && i0 + e < b.n && i0 + e >= n_fixed) ? frow[i0 + e] : 0.0f;
+            for (int e = 0; e < 4; ++e) {
+                f[e] = (have_bmu && i0 + e < b.n && i0 + e >= n_fixed) ? frow[i0 + e] : 0.0f;
+            }
+            if (can_skip) {
+                if (!one_chunk) load_ranges(i0);
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (f[e] != 0.0f && cannot_change(f[e], wr[e].x, wr[e].y, rmax_bits)) f[e] = 0.0f;
+            }
             if (!one_chunk || b.world > 1) load_keys(i0);
             const uint32_t cnt = (f[0] != 0.0f) + (f[1] != 0.0f) + (f[2] != 0.0f) + (f[3] != 0.0f);
             uint32_t incl = cnt;                                   // inclusive scan over the warp's threads
@@ -613,10 +659,12 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             mbar_arrive(&list_bar);           // the list is complete (ordered after all entries by the barrier above)
             // The block that is last to have read the keys re-arms them for the next image's
             // distance kernel; its consumers do so while the first neurons are still in flight.
-            __threadfence();
-            const uint32_t old = atomicAdd(b.arrive, 1u);
-            last_s = old == gridDim.x - 1;
-            if (old == gridDim.x - 1) *b.arrive = 0;
+            if (!early_arrival) {
+                __threadfence();
+                arrival = atomicAdd(b.arrive, 1u);
+            }
+            last_s = arrival == gridDim.x - 1;
+            if (arrival == gridDim.x - 1) *b.arrive = 0;
             __threadfence();
         }
         consumer_sync();
@@ -637,6 +685,7 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             // -- w <- w - (w - r) * f over the whole neuron, kPipeUnroll rows per step:
             //    all loads, then the arithmetic, then the stores; no predicates in the steady loop
             bool changed = false;
+            uint32_t lo_bits = 0xFFFFFFFFu, hi_bits = 0u;            // min |w|, max |w| of the new values, as bit patterns
             const uint32_t sw = nd * 4;                              // byte step of a neuron row
             const int32_t sb = it.ax * 4;                            // byte step of the base rotation per neuron row
 #pragma unroll
@@ -651,6 +700,8 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                     for (int u = 0; u < kPipeUnroll; ++u) {
                         e[u] = __fsub_rn(w[u], __fmul_rn(__fsub_rn(w[u], rv[u]), f));
                         changed |= __float_as_uint(e[u]) != __float_as_uint(w[u]);
+                        const uint32_t mag = __float_as_uint(e[u]) & 0x7FFFFFFFu;
+                        lo_bits = min(lo_bits, mag); hi_bits = max(hi_bits, mag);
                     }
 #pragma unroll
                     for (int u = 0; u < kPipeUnroll; ++u) sts_f32(aw + u * sw, e[u]);
@@ -660,13 +711,17 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                     const float w = lds_f32(aw);
                     const float e = __fsub_rn(w, __fmul_rn(__fsub_rn(w, lds_f32(ab)), f));
                     changed |= __float_as_uint(e) != __float_as_uint(w);
+                    const uint32_t mag = __float_as_uint(e) & 0x7FFFFFFFu;
+                    lo_bits = min(lo_bits, mag); hi_bits = max(hi_bits, mag);
                     sts_f32(aw, e);
                     aw += sw; ab += sb;
                 }
             }
             {
                 const bool warp_changed = __any_sync(0xffffffffu, changed);
-                if (lane == 0) chg_s[s][cwarp] = warp_changed;
+                lo_bits = __reduce_min_sync(0xffffffffu, lo_bits);
+                hi_bits = __reduce_max_sync(0xffffffffu, hi_bits);
+                if (lane == 0) { chg_s[s][cwarp] = warp_changed; rng_s[s][cwarp] = make_uint2(lo_bits, hi_bits); }
             }
             consumer_sync();                  // whole neuron updated
             if (!__any_sync(0xffffffffu, lane < kPipeConsumerWarps && chg_s[s][lane] != 0)) {

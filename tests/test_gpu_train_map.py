@@ -80,14 +80,15 @@ def test_train_fused_and_split_update_agree(cuda, case, mode, monkeypatch):
     assert np.array_equal(out[0][1].view(np.uint32), out[1][1].view(np.uint32))
     assert np.array_equal(out[0][2], out[1][2])
     assert out[0][3] < out[1][3]          # the fused path really ran: two kernels less per image
-    # both paths see the same neurons with a non-zero factor; the fused one leaves neurons whose values
-    # did not change unwritten (far from the best matching unit of a 10 x 10 map the products vanish)
+    # the split path rewrites every neuron with a non-zero factor; the fused one does not even read neurons
+    # that provably cannot change and leaves neurons whose values did not change unwritten (far from the
+    # best matching unit of a 10 x 10 map the products vanish) -- with bit-identical maps, asserted above
     (read_f, written_f), (read_s, written_s) = out[0][4], out[1][4]
     want_read = sum(int((F[bmu] != 0).sum()) for bmu in out[0][0])
-    assert read_f == read_s == written_s == want_read
-    assert written_f <= read_f
+    assert read_s == written_s == want_read
+    assert written_f <= read_f <= read_s
     if N == 100:
-        assert written_f < read_f
+        assert written_f < read_s and read_f < read_s
 
 
 @pytest.mark.parametrize("case", TRAIN_CASES[:5])

@@ -269,19 +269,28 @@ def main():
     K = w["channels"] * w["ed_dim"] ** 2
     P = w["channels"] * w["neuron_dim"] ** 2
     nl = eng.count
-    # Per image, the update reads every neuron of this shard whose factor is not zero and writes back
-    # those in which at least one value changed (counted on the device), plus their operand rows.
+    # Algorithmic bytes of the update: every neuron of this shard with a non-zero factor for the image's best
+    # matching unit is read and written once (8 * N_upd * P, the reference rewrites all of them).  The kernel
+    # here moves fewer: it leaves out neurons that provably cannot change and does not write back neurons in
+    # which no value changed (both counted on the device) -- with bit-identical maps.
+    bmus = eng.bmu_log(prof_steps)
+    nz_rows = (F[:, eng.first:eng.first + nl] != 0).sum(1)
+    owned = bmus[bmus != 0xFFFFFFFF]
+    n_upd = float(nz_rows[owned].mean()) if (world == 1 and len(owned)) else float(nz_rows.mean())
     n_read = (stats1[0] - stats0[0]) / prof_steps
     n_written = (stats1[1] - stats0[1]) / prof_steps
     t_dist = phase_ms["distance"] / covered * 1e-3
     t_upd = phase_ms["update"] / covered * 1e-3
     dist_ops = 2.0 * nl * T * K
-    upd_bytes = 4.0 * P * n_read + (4.0 * P + K) * n_written
+    upd_bytes = 8.0 * n_upd * P
+    moved_bytes = 4.0 * P * n_read + (4.0 * P + K) * n_written
     int8_peak = 2.0 * peaks["bf16_tflops"]
     kernels = {
         "update_kernel": {"bound": "hbm", "achieved": upd_bytes / t_upd / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                           "frac": upd_bytes / t_upd / 1e9 / peaks["hbm_gbs"], "us_per_launch": t_upd * 1e6,
-                          "algorithmic_bytes": upd_bytes, "neurons_read": n_read, "neurons_written": n_written},
+                          "algorithmic_bytes": upd_bytes, "neurons_with_nonzero_factor": n_upd,
+                          "moved_bytes": moved_bytes, "moved_frac": moved_bytes / t_upd / 1e9 / peaks["hbm_gbs"],
+                          "neurons_read": n_read, "neurons_written": n_written},
         "distance_tc_kernel": {"bound": "tensor", "achieved": dist_ops / t_dist / 1e12, "peak": int8_peak,
                                "unit": "TOP/s", "frac": dist_ops / t_dist / 1e12 / int8_peak,
                                "us_per_launch": t_dist * 1e6, "algorithmic_ops": dist_ops,

@@ -77,6 +77,8 @@ def ref():
         r.ref_session_create.restype = C.c_void_p
         r.ref_session_create.argtypes = [C.c_void_p, C.c_int] + [C.c_uint32] * 7 + [C.c_int, C.c_int, C.c_float,
                                                                                    C.c_float, C.c_float, C.c_int]
+        r.ref_session_create_shape.restype = C.c_void_p
+        r.ref_session_create_shape.argtypes = r.ref_session_create.argtypes + [C.c_int]
         r.ref_session_train.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64]
         r.ref_session_map.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p,
                                       C.c_void_p]
@@ -113,13 +115,24 @@ def rotation_set(img, nd, R, flip):
 _QDT = {MODE_F32: np.float32, MODE_U16: np.uint16, MODE_U8: np.uint8}
 
 
-def crop_quantize(planes, ed, mode):
-    """planes: (n, C, nd, nd) float32 -> (n, C*ed*ed) operand of the mode's type."""
+SHAPE_QUADRATIC, SHAPE_CIRCULAR = 0, 1
+
+
+def circle_rows(nd, ed):
+    """Neuron-column span [begin, end) of every row of the circular distance region."""
+    jb = np.zeros(ed, np.uint32)
+    je = np.zeros(ed, np.uint32)
+    lib.pko_circle_rows(C.c_uint32(nd), C.c_uint32(ed), _fp(jb), _fp(je))
+    return jb, je
+
+
+def crop_quantize(planes, ed, mode, shape=SHAPE_QUADRATIC):
+    """planes: (n, C, nd, nd) float32 -> (n, C*ed*ed) operand of the mode's type (zeros outside a circular region)."""
     planes = np.ascontiguousarray(planes, dtype=np.float32)
     n, Cn, nd, _ = planes.shape
     out = np.empty((n, Cn * ed * ed), _QDT[mode])
-    lib.pko_crop_quantize(_fp(planes), C.c_uint32(n), C.c_uint32(Cn), C.c_uint32(nd), C.c_uint32(ed),
-                          C.c_int(mode), _fp(out))
+    lib.pko_crop_quantize_shape(_fp(planes), C.c_uint32(n), C.c_uint32(Cn), C.c_uint32(nd), C.c_uint32(ed),
+                                C.c_int(mode), C.c_int(shape), _fp(out))
     return out
 
 
@@ -194,7 +207,7 @@ def _shape(som, img):
     return N, Cn, img.shape[-1], som.shape[-1]
 
 
-def train_step(som, img, factors, ed, R, flip, mode):
+def train_step(som, img, factors, ed, R, flip, mode, shape=SHAPE_QUADRATIC):
     """One training step in place on som (N, C, nd, nd) or (N, nd, nd).
     Returns (best_rot[N], dist[N], bmu)."""
     assert som.dtype == np.float32 and som.flags.c_contiguous
@@ -204,21 +217,22 @@ def train_step(som, img, factors, ed, R, flip, mode):
     best = np.empty(N, np.uint32)
     dist = np.empty(N, np.float32)
     bmu = C.c_uint32(0)
-    rc = lib.pko_train_step(_fp(som), _fp(img), _fp(factors), C.c_uint32(N), C.c_uint32(Cn), C.c_uint32(idim),
-                            C.c_uint32(nd), C.c_uint32(ed), C.c_uint32(R), C.c_int(int(flip)), C.c_int(mode),
-                            _fp(best), _fp(dist), C.byref(bmu))
+    rc = lib.pko_train_step_shape(_fp(som), _fp(img), _fp(factors), C.c_uint32(N), C.c_uint32(Cn),
+                                  C.c_uint32(idim), C.c_uint32(nd), C.c_uint32(ed), C.c_uint32(R), C.c_int(int(flip)),
+                                  C.c_int(mode), C.c_int(shape), _fp(best), _fp(dist), C.byref(bmu))
     assert rc == 0
     return best, dist, bmu.value
 
 
-def map_image(som, img, ed, R, flip, mode):
+def map_image(som, img, ed, R, flip, mode, shape=SHAPE_QUADRATIC):
     som = np.ascontiguousarray(som, dtype=np.float32)
     img = np.ascontiguousarray(img, dtype=np.float32)
     N, Cn, idim, nd = _shape(som, img)
     dist = np.empty(N, np.float32)
     best = np.empty(N, np.uint32)
-    rc = lib.pko_map(_fp(som), _fp(img), C.c_uint32(N), C.c_uint32(Cn), C.c_uint32(idim), C.c_uint32(nd),
-                     C.c_uint32(ed), C.c_uint32(R), C.c_int(int(flip)), C.c_int(mode), _fp(dist), _fp(best))
+    rc = lib.pko_map_shape(_fp(som), _fp(img), C.c_uint32(N), C.c_uint32(Cn), C.c_uint32(idim), C.c_uint32(nd),
+                           C.c_uint32(ed), C.c_uint32(R), C.c_int(int(flip)), C.c_int(mode), C.c_int(shape),
+                           _fp(dist), _fp(best))
     assert rc == 0
     return dist, best
 
@@ -231,13 +245,13 @@ class RefSession:
     """One reference Trainer<...,false> or Mapper<...,false> bound to a SOM copy."""
 
     def __init__(self, som, som_layout, s0, s1, channels, idim, nd, ed, R, flip,
-                 func=FUNC_GAUSSIAN, p0=1.1, p1=0.2, max_dist=-1.0, for_map=False):
+                 func=FUNC_GAUSSIAN, p0=1.1, p1=0.2, max_dist=-1.0, for_map=False, shape=SHAPE_QUADRATIC):
         som = np.ascontiguousarray(som, dtype=np.float32)
         self.N = som.shape[0]
         self.som_shape = som.shape
         self.image_size = max(channels, 1) * idim * idim
-        self._h = ref().ref_session_create(_fp(som), som_layout, s0, s1, channels, idim, nd, ed, R, int(flip),
-                                           func, p0, p1, max_dist, int(for_map))
+        self._h = ref().ref_session_create_shape(_fp(som), som_layout, s0, s1, channels, idim, nd, ed, R, int(flip),
+                                                 func, p0, p1, max_dist, int(for_map), int(shape))
         if not self._h:
             raise RuntimeError("reference rejected the configuration")
 

@@ -73,16 +73,17 @@ struct SessionT : Session
     std::unique_ptr<Mapper<SL, DL, float, false>> mapper;
 
     SessionT(const float* som_in, uint32_t s0, uint32_t s1, uint32_t C, uint32_t id, uint32_t nd, uint32_t ed,
-             uint32_t R, bool flip, int func, float p0, float p1, float max_dist, bool for_map)
+             uint32_t R, bool flip, int func, float p0, float p1, float max_dist, bool for_map, int shape)
      : som(make_som_layout<SL>(s0, s1), make_data_layout<DL>(C, nd)),
        img_layout(make_data_layout<DL>(C, id))
     {
         std::memcpy(som.get_data_pointer(), som_in, som.size() * sizeof(float));
         if (for_map)
-            mapper.reset(new Mapper<SL, DL, float, false>(som, 0, R, flip, Interpolation::BILINEAR, ed));
+            mapper.reset(new Mapper<SL, DL, float, false>(som, 0, R, flip, Interpolation::BILINEAR, ed,
+                shape ? EuclideanDistanceShape::CIRCULAR : EuclideanDistanceShape::QUADRATIC));
         else
             trainer.reset(new Trainer<SL, DL, float, false>(som, make_func(func, p0, p1), 0, R, flip, max_dist,
-                Interpolation::BILINEAR, ed));
+                Interpolation::BILINEAR, ed, shape ? EuclideanDistanceShape::CIRCULAR : EuclideanDistanceShape::QUADRATIC));
     }
     void train(const float* img) override
     {
@@ -112,17 +113,23 @@ extern "C" {
 // som_layout: 0 cartesian-2d (s0 x s1), 1 hexagonal (side s0).  C == 0 selects
 // the 2-D data layout (one channel, CartesianLayout<2>); C >= 1 selects
 // CartesianLayout<3> with C channels.
-void* ref_session_create(const float* som, int som_layout, uint32_t s0, uint32_t s1, uint32_t C, uint32_t id,
-    uint32_t nd, uint32_t ed, uint32_t R, int flip, int func, float p0, float p1, float max_dist, int for_map)
+// shape: 0 quadratic, 1 circular distance region.
+void* ref_session_create_shape(const float* som, int som_layout, uint32_t s0, uint32_t s1, uint32_t C, uint32_t id,
+    uint32_t nd, uint32_t ed, uint32_t R, int flip, int func, float p0, float p1, float max_dist, int for_map, int shape)
 {
     try {
-        if (som_layout == 0 && C == 0) return new SessionT<CartesianLayout<2>, CartesianLayout<2>>(som, s0, s1, 1, id, nd, ed, R, flip, func, p0, p1, max_dist, for_map);
-        if (som_layout == 0) return new SessionT<CartesianLayout<2>, CartesianLayout<3>>(som, s0, s1, C, id, nd, ed, R, flip, func, p0, p1, max_dist, for_map);
-        if (C == 0) return new SessionT<HexagonalLayout, CartesianLayout<2>>(som, s0, s1, 1, id, nd, ed, R, flip, func, p0, p1, max_dist, for_map);
-        return new SessionT<HexagonalLayout, CartesianLayout<3>>(som, s0, s1, C, id, nd, ed, R, flip, func, p0, p1, max_dist, for_map);
+        if (som_layout == 0 && C == 0) return new SessionT<CartesianLayout<2>, CartesianLayout<2>>(som, s0, s1, 1, id, nd, ed, R, flip, func, p0, p1, max_dist, for_map, shape);
+        if (som_layout == 0) return new SessionT<CartesianLayout<2>, CartesianLayout<3>>(som, s0, s1, C, id, nd, ed, R, flip, func, p0, p1, max_dist, for_map, shape);
+        if (C == 0) return new SessionT<HexagonalLayout, CartesianLayout<2>>(som, s0, s1, 1, id, nd, ed, R, flip, func, p0, p1, max_dist, for_map, shape);
+        return new SessionT<HexagonalLayout, CartesianLayout<3>>(som, s0, s1, C, id, nd, ed, R, flip, func, p0, p1, max_dist, for_map, shape);
     } catch (std::exception const&) {
         return nullptr;
     }
+}
+void* ref_session_create(const float* som, int som_layout, uint32_t s0, uint32_t s1, uint32_t C, uint32_t id,
+    uint32_t nd, uint32_t ed, uint32_t R, int flip, int func, float p0, float p1, float max_dist, int for_map)
+{
+    return ref_session_create_shape(som, som_layout, s0, s1, C, id, nd, ed, R, flip, func, p0, p1, max_dist, for_map, 0);
 }
 void ref_session_train(void* s, const float* images, uint64_t n, uint64_t image_size)
 {

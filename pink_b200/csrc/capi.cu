@@ -91,8 +91,8 @@ int make_geometry(const pink_b200_config& c, Geometry* g)
         return fail(PINK_B200_EINVAL, "Euclidean distance dimension larger than neuron dimension");
     if (c.interpolation != PINK_B200_BILINEAR)
         return fail(PINK_B200_EINVAL, "generate_rotated_images: unknown interpolation type");
-    if (c.ed_shape != PINK_B200_QUADRATIC)
-        return fail(PINK_B200_EINVAL, "circular euclidean distance shape is not supported by this library");
+    if (c.ed_shape != PINK_B200_QUADRATIC && c.ed_shape != PINK_B200_CIRCULAR)
+        return fail(PINK_B200_EINVAL, "Unknown euclidean_distance_shape");
     if (c.dist_type > PINK_B200_UINT8) return fail(PINK_B200_EINVAL, "Unknown euclidean_distance_type");
 
     g->C = c.channels; g->id = c.image_dim; g->nd = c.neuron_dim; g->ed = c.ed_dim;
@@ -105,6 +105,7 @@ int make_geometry(const pink_b200_config& c, Geometry* g)
     g->P = (uint32_t)P; g->Pp = round_up(g->P, 4);
     g->K = (uint32_t)K;
     g->mode = (int)c.dist_type;
+    g->circle = nullptr;             // a context with a circular region uploads the table and sets this
     g->Kp = g->mode == kModeF32 ? round_up(g->K, 16) : round_up(g->K, 128);
     // s32 accumulators: K * 255^2 (uint8) and 2 * K * 255^2 (uint16 cross term) must stay below 2^31.
     if (g->mode == kModeU8 && g->K > 33025) return fail(PINK_B200_EINVAL, "uint8 distance supports at most 33025 elements");
@@ -124,6 +125,28 @@ size_t norm_bytes(const Geometry& g, size_t rows)
     return rows * (g.mode == kModeU16 ? 8 : 4);
 }
 
+// Column span of every row of a circular distance region, restating the reference's CPU functor
+// (src/ImageProcessingLib/circular_euclidean_distance.h:44-57): with center = nd / 2 and radius = ed / 2
+// (integer divisions), region row i covers the neuron columns round(center - delta) .. round(center + delta) - 1,
+// delta = sqrt(2 * radius * (i + 0.5) - (i + 0.5)^2) in double.  Returned in region-local columns
+// (neuron column - offset); rows whose radicand is negative (odd ed) are empty.  False when a span leaves
+// the ed x ed square the operands hold.
+bool circle_table(uint32_t nd, uint32_t ed, std::vector<ushort2>* out)
+{
+    const uint32_t center = nd / 2, radius = ed / 2, off = static_cast<uint32_t>((nd - ed) * 0.5);
+    out->assign(ed, make_ushort2(0, 0));
+    for (uint32_t i = 0; i < ed; ++i) {
+        const double arg = 2 * radius * (i + 0.5) - std::pow((i + 0.5), 2);
+        if (!(arg >= 0.0)) continue;
+        const double delta = std::sqrt(arg);
+        const double lo = std::round(center - delta), hi = std::round(center + delta);
+        if (!(hi > lo)) continue;
+        if (lo < off || hi > off + ed) return false;
+        (*out)[i] = make_ushort2((unsigned short)(lo - off), (unsigned short)(hi - off));
+    }
+    return true;
+}
+
 template <typename T>
 void free_dev(T*& p)
 {
@@ -134,7 +157,14 @@ void free_dev(T*& p)
 } // namespace
 
 namespace pinkb {
-int geometry_from_config(const pink_b200_config* cfg, Geometry* g) { return cfg && g ? make_geometry(*cfg, g) : fail(PINK_B200_EINVAL, "null argument"); }
+// Geometry for the single-stage entries, which keep no device table of a circular region.
+int geometry_from_config(const pink_b200_config* cfg, Geometry* g)
+{
+    if (!cfg || !g) return fail(PINK_B200_EINVAL, "null argument");
+    if (cfg->ed_shape == PINK_B200_CIRCULAR)
+        return fail(PINK_B200_EINVAL, "the single-stage entries support only the quadratic euclidean distance shape");
+    return make_geometry(*cfg, g);
+}
 int report_error(int code, const char* msg) { return fail(code, msg); }
 } // namespace pinkb
 
@@ -165,6 +195,7 @@ struct pink_b200_ctx
     XchgRecord* d_xchg = nullptr; XchgRecord* xchg_peer[kXchgMaxRanks] = {}; bool xchg_on = false; unsigned long long xchg_seq = 0;
     // value ranges for leaving out neurons that cannot change: per neuron {min |w|, max |w|}, per buffered image max |pixel|
     uint2* d_wrange = nullptr; uint32_t* d_rmax = nullptr;
+    ushort2* d_circle = nullptr;      // column spans of a circular distance region (null: quadratic)
     unsigned long long* d_stats = nullptr;   // [0] neurons with a non-zero factor, [1] neurons written back, summed over steps
     uint64_t launches = 0;            // kernels launched by this context so far
     bool fuse_update = false;         // the update kernel finds the best matching unit and its work list itself
@@ -521,6 +552,17 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
         CTX_TRY(cudaEventCreateWithFlags(&c->rotated[i], cudaEventDisableTiming));
         CTX_TRY(cudaEventCreateWithFlags(&c->rot_free[i], cudaEventDisableTiming));
     }
+    if (cfg->ed_shape == PINK_B200_CIRCULAR) {
+        std::vector<ushort2> spans;
+        if (!circle_table(g.nd, g.ed, &spans)) {
+            fail(PINK_B200_EINVAL, "circular euclidean distance region does not fit the euclidean distance square");
+            return bail(PINK_B200_EINVAL);
+        }
+        CTX_TRY(cudaMalloc(&c->d_circle, spans.size() * sizeof(ushort2)));
+        CTX_TRY(cudaMemcpyAsync(c->d_circle, spans.data(), spans.size() * sizeof(ushort2), cudaMemcpyHostToDevice, c->stream));
+        CTX_TRY(cudaStreamSynchronize(c->stream));   // spans goes out of scope
+        c->g.circle = c->d_circle;
+    }
     CTX_TRY(cudaMalloc(&c->d_som, (size_t)c->count * g.Pp * sizeof(float)));
     CTX_TRY(cudaMemsetAsync(c->d_som, 0, (size_t)c->count * g.Pp * sizeof(float), c->stream));
     CTX_TRY(cudaMalloc(&c->d_a0, operand_plane_bytes(g, c->count)));
@@ -582,6 +624,7 @@ int pink_b200_destroy(pink_b200_ctx* c)
     free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_base);
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
     free_dev(c->d_items); free_dev(c->d_nitems); free_dev(c->d_stats); free_dev(c->d_wrange); free_dev(c->d_rmax);
+    free_dev(c->d_circle);
     free_dev(c->d_pairs); free_dev(c->d_counts); free_dev(c->d_bmu_log); free_dev(c->d_status);
     free_dev(c->d_images[0]); free_dev(c->d_images[1]); free_dev(c->d_dist); free_dev(c->d_rot);
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
@@ -909,7 +952,7 @@ int pink_b200_op_rotate(const pink_b200_config* cfg, const float* dev_images, ui
 {
     if (!cfg || !dev_images || !dev_b0) return fail(PINK_B200_EINVAL, "null argument");
     Geometry g{};
-    int rc = make_geometry(*cfg, &g);
+    int rc = geometry_from_config(cfg, &g);
     if (rc) return rc;
     if (!dev_base && (size_t)g.P * sizeof(float) > 200 * 1024)
         return fail(PINK_B200_EINVAL, "dev_base is required when a base rotation does not fit shared memory");
@@ -929,7 +972,7 @@ int pink_b200_op_quantize_som(const pink_b200_config* cfg, const float* dev_som,
 {
     if (!cfg || !dev_som || !dev_a0) return fail(PINK_B200_EINVAL, "null argument");
     Geometry g{};
-    int rc = make_geometry(*cfg, &g);
+    int rc = geometry_from_config(cfg, &g);
     if (rc) return rc;
     if (g.P != g.Pp) return fail(PINK_B200_EINVAL, "this entry needs a neuron size that is a multiple of 4 floats");
     LAUNCH_TRY(launch_quantize_som(g, dev_som, n_neurons, dev_a0, dev_a1, dev_anorm, static_cast<cudaStream_t>(stream)));

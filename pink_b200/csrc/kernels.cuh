@@ -29,7 +29,19 @@ struct Geometry
                                 //   integer modes: multiple of 128 (bytes per plane row)
                                 //   float mode:    multiple of 16 floats
     int mode;
+    // Circular distance region (src/ImageProcessingLib/circular_euclidean_distance.h:36-60): device table of
+    // ed entries {first column, end column} of each region row, in region-local columns; null = the whole
+    // ed x ed square.  Operand elements outside the circle are written as zeros, which removes them from
+    // every term of the distance.
+    const ushort2* circle;
 };
+
+__device__ __forceinline__ bool in_region(const Geometry& g, uint32_t row, uint32_t col)
+{
+    if (!g.circle) return true;
+    const ushort2 r = g.circle[row];
+    return col >= r.x && col < r.y;
+}
 
 // Ordering code of a per-neuron minimum.  Integer modes: the exact integer sum
 // S; float mode: the IEEE bit pattern of the non-negative float sum.  A key

@@ -265,6 +265,17 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
                     const uint32_t r2 = __byte_perm(o[1], 0, 0x0123), r3 = __byte_perm(o[0], 0, 0x0123);
                     o[0] = r0; o[1] = r1; o[2] = r2; o[3] = r3;
                 }
+                if (g.circle) {                              // zero the bytes outside the circle's span of this row
+                    const ushort2 span = g.circle[i];
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        const int32_t c0 = (int32_t)jj + 4 * m;
+                        const int32_t lo = min(max((int32_t)span.x - c0, 0), 4), hi = min(max((int32_t)span.y - c0, 0), 4);
+                        uint32_t keep = 0;
+                        if (hi > lo) keep = (hi == 4 ? 0xFFFFFFFFu : (1u << (8 * hi)) - 1u) & ~((1u << (8 * lo)) - 1u);
+                        o[m] &= keep;
+                    }
+                }
 #pragma unroll
                 for (int m = 0; m < 4; ++m) acc = __dp4a(o[m], o[m], (uint32_t)acc);
                 reinterpret_cast<uint4*>(static_cast<uint8_t*>(b0) + orow * g.Kp)[gi] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -275,7 +286,7 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
 #pragma unroll
             for (uint32_t e = 0; e < kGroup; ++e) {
                 val[e] = 0;
-                if (k + e < g.K) val[e] = use_smem ? stage[s] : to_stage<MODE>(gbase[s]);
+                if (k + e < g.K && in_region(g, i, jj)) val[e] = use_smem ? stage[s] : to_stage<MODE>(gbase[s]);
                 ++jj; s += ay;
                 if (jj == g.ed) {
                     jj = 0; ++i;
@@ -355,7 +366,7 @@ quantize_som_kernel(Geometry g, const float* __restrict__ som, void* __restrict_
             if (k < g.K) {
                 uint32_t c = k / K1, r = k - c * K1;
                 uint32_t i = r / g.ed, jj = r - i * g.ed;
-                val[e] = src[c * P1 + (g.off + i) * g.nd + g.off + jj];
+                if (in_region(g, i, jj)) val[e] = src[c * P1 + (g.off + i) * g.nd + g.off + jj];
             }
         }
         if (MODE == kModeU8) {

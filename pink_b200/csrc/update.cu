@@ -146,7 +146,7 @@ inline uint32_t div_magic(uint32_t d) { return d == 1 ? 0u : (uint32_t)((1ull <<
 // Per neuron row (over all channels): where the row starts in the base
 // rotation under the neuron's best transform, and where it lands in the
 // distance operand (negative when the row lies outside the distance region).
-struct RowInfo { int32_t src; int32_t kk; };
+struct RowInfo { int32_t src; int32_t kk; uint32_t span; };   // span: region columns [low 16 bits, high 16 bits) of the row
 
 // One block per neuron of the shard.  The block looks up the best matching
 // unit and its own update factor, leaves at once when the factor is zero, and
@@ -194,6 +194,9 @@ update_kernel(Geometry g, UpdateArgs a, uint32_t stage_base, uint32_t magic_nd, 
         const uint32_t ci = x - g.off;                                   // unsigned wrap rejects x < off
         rowinfo[rr].src = (int32_t)(c * P1) + ax * (int32_t)x + a0;
         rowinfo[rr].kk = ci < g.ed ? (int32_t)(c * K1 + ci * g.ed) : -1;
+        uint32_t span = g.ed << 16;
+        if (g.circle && ci < g.ed) { const ushort2 r = g.circle[ci]; span = (uint32_t)r.x | ((uint32_t)r.y << 16); }
+        rowinfo[rr].span = span;
     }
     __syncthreads();
 
@@ -231,17 +234,18 @@ update_kernel(Geometry g, UpdateArgs a, uint32_t stage_base, uint32_t magic_nd, 
                 __stcs(p0 + (size_t)u * g.nd, nv);
                 if (in_col && ri.kk >= 0) {
                     const uint32_t kk = (uint32_t)ri.kk + cj;
+                    const float ov = (cj >= (ri.span & 0xFFFFu) && cj < (ri.span >> 16)) ? nv : 0.0f;   // zero outside a circular region
                     if (MODE == kModeU8) {
-                        const uint32_t qv = quant_u8(nv);
+                        const uint32_t qv = quant_u8(ov);
                         crop_s[kk] = (uint8_t)qv;
                         acc += qv * qv;
                     } else if (MODE == kModeU16) {
-                        const uint32_t qv = quant_u16(nv);
+                        const uint32_t qv = quant_u16(ov);
                         crop_s[kk] = (uint8_t)(qv >> 8);
                         crop_s[g.Kp + kk] = (uint8_t)(qv & 255);
                         acc += (unsigned long long)qv * qv;
                     } else {
-                        reinterpret_cast<float*>(crop_s)[kk] = nv;
+                        reinterpret_cast<float*>(crop_s)[kk] = ov;
                     }
                 }
             }
@@ -480,7 +484,7 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                 const uint32_t unit = ctid + k * kPipeConsumers;
                 const uint32_t kk = (unit / 32) * 128 + (unit % 32) + 32 * e;
                 const uint32_t c = kk / K1, rem = kk - c * K1, ci = rem / g.ed, cj = rem - ci * g.ed;
-                const bool ok = unit < nunit && kk < g.K;
+                const bool ok = unit < nunit && kk < g.K && in_region(g, ci, cj);   // outside a circular region: stays zero
                 un_src[k][e] = ok ? 4 * (c * P1 + (g.off + ci) * g.nd + g.off + cj) : 0u;   // byte offset in the neuron
                 un_dst[k][e] = ok ? kk : ~0u;
             }
@@ -792,7 +796,7 @@ cudaError_t update_classic(const Geometry& g, const UpdateArgs& a, cudaStream_t 
     if ((uint64_t)g.P * g.nd >= (1ull << 32)) return cudaErrorInvalidValue;   // multiply-high division range
     const size_t crop = MODE == kModeF32 ? (size_t)g.Kp * 4 : (MODE == kModeU16 ? (size_t)g.Kp * 2 : g.Kp);
     const size_t rows = (size_t)g.C * g.nd;
-    const size_t fixed = ((rows * 8 + 15) & ~size_t(15)) + ((crop + 15) & ~size_t(15));
+    const size_t fixed = ((rows * sizeof(RowInfo) + 15) & ~size_t(15)) + ((crop + 15) & ~size_t(15));
     const size_t staged = fixed + (size_t)g.P * 4;
     // The bulk copy needs a size that is a multiple of 16 bytes; otherwise (and
     // when a base rotation does not fit) the base is read through the cache.

@@ -35,6 +35,10 @@ STEP_CASES = [  # som layout, s0, s1, channels, image, neuron, ed, rotations, fl
     (0, 4, 4, 0, 24, 17, 8, 40, True, 3, 2, 1.5, 0.3, 2.5),
     (0, 3, 3, 0, 12, 12, 12, 4, False, 2, 3, 1.0, 0.0, -1.0),
 ]
+CIRCLE_CASES = [  # circular distance region, 2-D data layout: som layout, s0, s1, image, neuron, ed, rotations, flip, n images
+    (0, 3, 3, 32, 22, 16, 8, True, 3), (1, 3, 3, 40, 28, 20, 12, True, 3), (0, 2, 2, 64, 45, 32, 40, True, 2),
+    (0, 2, 3, 16, 12, 12, 4, False, 2),
+]
 FACTOR_CASES = [(0, 3, 4, 0, 1.1, 0.2, -1.0), (0, 10, 10, 0, 1.1, 0.2, 2.5), (1, 7, 7, 0, 2.0, 0.1, -1.0),
                 (1, 11, 11, 0, 3.0, 0.05, -1.0), (0, 5, 5, 2, 1.5, 0.3, -1.0), (0, 4, 4, 3, 1.0, 0.0, -1.0),
                 (0, 6, 3, 1, 1.3, 0.4, -1.0)]
@@ -73,6 +77,21 @@ def main():
         out["fac%d_out" % i] = O.ref_update_factors(lay, d0, d1, func, p0, p1, md)
     out["fill_seed1234"] = O.ref_fill_random_uniform(4096, 1234)
     out["fill_default"] = O.ref_fill_random_uniform(256, 5489)
+    # (appended after all other entries so that the random stream of the earlier ones does not change)
+    for i, (lay, s0, s1, idim, nd, ed, R, flip, n) in enumerate(CIRCLE_CASES):
+        N = s0 * s1 if lay == 0 else int(O.lib.pko_hexagonal_size(s0))
+        som = rng.random((N, 1, nd, nd), dtype=np.float32)
+        imgs = rng.random((n, 1, idim, idim), dtype=np.float32)
+        tr = O.RefSession(som, lay, s0, s1, 0, idim, nd, ed, R, flip, shape=O.SHAPE_CIRCULAR)
+        tr.train(imgs)
+        mp = O.RefSession(som, lay, s0, s1, 0, idim, nd, ed, R, flip, for_map=True, shape=O.SHAPE_CIRCULAR)
+        dist, rot = mp.map(imgs)
+        out["circ%d_cfg" % i] = np.array([lay, s0, s1, idim, nd, ed, R, int(flip), n])
+        out["circ%d_som" % i] = som
+        out["circ%d_imgs" % i] = imgs
+        out["circ%d_trained" % i] = tr.som()
+        out["circ%d_map_dist" % i] = dist
+        out["circ%d_map_rot" % i] = rot
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_cpu.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")

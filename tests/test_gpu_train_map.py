@@ -115,6 +115,54 @@ def test_train_float_mode(cuda, case):
             np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-7)
 
 
+CIRCLE_CASES = [
+    # layout, s0, s1, C, id, nd, ed, R, flip, n_images
+    (0, 3, 3, 1, 32, 22, 16, 8, True, 4),
+    (0, 10, 10, 1, 64, 44, 32, 40, True, 4),       # pipelined update kernel
+    (0, 2, 3, 2, 20, 15, 11, 12, True, 3),         # two channels, odd sizes: fallback update kernel
+]
+
+
+@pytest.mark.parametrize("case", CIRCLE_CASES)
+@pytest.mark.parametrize("mode", [2, 1, 0])
+def test_circular_distance_region(cuda, case, mode):
+    """EuclideanDistanceShape::CIRCULAR: training (integer modes bit-exact, float within tolerance with teacher
+    forcing) and mapping against the oracle, which is pinned to the reference's CPU code for this shape."""
+    import pink_b200.capi as capi
+    layout, s0, s1, C_, idim, nd, ed, R, flip, n = case
+    N = _som_size(layout, s0, s1)
+    rng = np.random.default_rng(1000 + nd + mode)
+    som0 = rng.random((N, C_, nd, nd), dtype=np.float32)
+    imgs = blob_images(n, idim, C_, seed=N + ed).reshape(n, C_, idim, idim)
+    F = O.update_factors(layout, s0, s1, O.FUNC_GAUSSIAN, 1.1, 0.2)
+    cfg = make_config(capi, N, C_, idim, nd, ed, R, flip, mode)
+    cfg.ed_shape = capi.CIRCULAR
+    with Context(capi, cfg) as ctx:
+        ctx.set_factors(F)
+        want = som0.copy()
+        if mode != 0:
+            ctx.set_som(som0)
+            want_bmu = [O.train_step(want, im, F, ed, R, flip, mode, shape=O.SHAPE_CIRCULAR)[2] for im in imgs]
+            log = ctx.train(imgs)
+            assert list(log) == want_bmu
+            assert np.array_equal(ctx.get_som(som0).view(np.uint32), want.view(np.uint32))
+        else:
+            for i in range(n):
+                ctx.set_som(want)
+                bmu = O.train_step(want, imgs[i], F, ed, R, flip, 0, shape=O.SHAPE_CIRCULAR)[2]
+                assert ctx.train(imgs[i:i + 1])[0] == bmu
+                np.testing.assert_allclose(ctx.get_som(som0), want, rtol=1e-5, atol=1e-7)
+        ctx.set_som(som0)
+        dist, rot = ctx.map(imgs)
+    for i in range(n):
+        wd, wr = O.map_image(som0, imgs[i], ed, R, flip, mode, shape=O.SHAPE_CIRCULAR)
+        if mode != 0:
+            assert np.array_equal(rot[i], wr)
+            assert np.array_equal(dist[i].view(np.uint32), wd.view(np.uint32))
+        else:
+            np.testing.assert_allclose(dist[i], wd, rtol=1e-5, atol=1e-7)
+
+
 MAP_CASES = [
     (0, 3, 3, 1, 16, 12, 7, 16, True, 5),
     (0, 4, 4, 1, 64, 44, 31, 360, True, 3),

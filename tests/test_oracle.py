@@ -201,6 +201,41 @@ def test_train_and_map_match_reference(i):
         assert np.array_equal(rot, GOLD["step%d_map_rot" % i][k])
 
 
+@pytest.mark.parametrize("i", range(4))
+def test_circular_region_matches_reference(i):
+    """Circular distance region (2-D data layout): trained map and mapping results of the reference's CPU
+    Trainer / Mapper with EuclideanDistanceShape::CIRCULAR, bit for bit."""
+    lay, s0, s1, idim, nd, ed, R, flip, n = (int(v) for v in GOLD["circ%d_cfg" % i])
+    som0, imgs = GOLD["circ%d_som" % i], GOLD["circ%d_imgs" % i]
+    F = O.update_factors(lay, s0, s1, O.FUNC_GAUSSIAN, 1.1, 0.2)
+    som = som0.copy()
+    for im in imgs:
+        O.train_step(som, im, F, ed, R, bool(flip), O.MODE_F32, shape=O.SHAPE_CIRCULAR)
+    assert np.array_equal(bits(som), bits(GOLD["circ%d_trained" % i].reshape(som.shape)))
+    for k, im in enumerate(imgs):
+        dist, rot = O.map_image(som0, im, ed, R, bool(flip), O.MODE_F32, shape=O.SHAPE_CIRCULAR)
+        assert np.array_equal(bits(dist), bits(GOLD["circ%d_map_dist" % i][k]))
+        assert np.array_equal(rot, GOLD["circ%d_map_rot" % i][k])
+
+
+def test_circular_region_literals():
+    """test/SelfOrganizingMapTest/euclidean_distance.cpp:71-89: the circle inscribed in a 200 x 200 region of a
+    300 x 300 neuron holds 31428 elements; test/SelfOrganizingMapTest/circular_ed.cpp:23-53: mapper known answers."""
+    jb, je = O.circle_rows(300, 200)
+    assert int((je - jb).sum()) == 31428
+    assert jb.min() >= 50 and je.max() <= 250          # the circle stays inside the centred region
+    img = np.zeros((4, 4), np.float32)
+    img.flat[4] = 1.0
+    som = np.zeros((4, 1, 4, 4), np.float32)
+    som.flat[4], som.flat[18], som.flat[43], som.flat[61] = 1.0, 0.5, 0.8, 0.3
+    dist, rot = O.map_image(som, img, 4, 4, False, O.MODE_F32, shape=O.SHAPE_CIRCULAR)
+    np.testing.assert_allclose(dist, [0.0, 0.5, 0.2, 0.7], atol=0.01)
+    assert list(rot) == [0, 1, 2, 3]
+    # integer modes on the masked operands: the same elements are kept
+    a = O.crop_quantize(np.ones((1, 1, 300, 300), np.float32), 200, O.MODE_U8, shape=O.SHAPE_CIRCULAR)
+    assert int((a != 0).sum()) == 31428
+
+
 @pytest.mark.parametrize("i", range(7))
 def test_update_factors_match_reference(i):
     lay, d0, d1, func = (int(v) for v in GOLD["fac%d_cfg" % i])

@@ -16,6 +16,7 @@
 #include <cstring>
 #include <functional>
 #include <memory>
+#include <sstream>
 #include <vector>
 #include <omp.h>
 
@@ -23,6 +24,7 @@
 #include "SelfOrganizingMapLib/HexagonalLayout.h"
 #include "SelfOrganizingMapLib/Data.h"
 #include "SelfOrganizingMapLib/SOM.h"
+#include "SelfOrganizingMapLib/DataIteratorShuffled.h"
 #include "SelfOrganizingMapLib/Trainer.h"
 #include "SelfOrganizingMapLib/Mapper.h"
 #include "SelfOrganizingMapLib/generate_rotated_images.h"
@@ -146,6 +148,19 @@ void ref_session_get_som(void* s, float* out)
 }
 void ref_session_get_counts(void* s, uint32_t* out) { static_cast<Session*>(s)->counts(out); }
 void ref_session_destroy(void* s) { delete static_cast<Session*>(s); }
+
+// Order in which the reference's shuffled iterator (SelfOrganizingMapLib/DataIteratorShuffled.h) presents
+// the n entries of a data file: built on an in-memory file whose entry i holds the value i.
+void ref_shuffled_order(uint32_t n, uint64_t seed, int shuffle, uint32_t* out)
+{
+    std::stringstream ss;
+    int header[7] = {2, 0, 0, (int)n, 0, 1, 1};
+    ss.write(reinterpret_cast<const char*>(header), sizeof(header));
+    for (uint32_t i = 0; i < n; ++i) { float v = (float)i; ss.write(reinterpret_cast<const char*>(&v), sizeof(float)); }
+    auto cur = DataIteratorShuffled<CartesianLayout<1>, float>(ss, seed, shuffle != 0);
+    auto end = DataIteratorShuffled<CartesianLayout<1>, float>(ss, true);
+    for (uint32_t k = 0; cur != end && k < n; ++cur, ++k) out[k] = (uint32_t)(*cur)[0];
+}
 
 // Rotation set through the reference's SpatialTransformer (C == 0: 2-D layout).
 void ref_rotation_set(const float* img, uint32_t C, uint32_t id, uint32_t nd, uint32_t R, int flip, float* out)

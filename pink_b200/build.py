@@ -46,7 +46,23 @@ def build(force=False, verbose=False):
     if force or procs or _stale(LIB, objs):
         cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-ldl"]
         subprocess.check_call(cmd)
+    build_cli(force)
     return LIB
+
+
+CLI = os.path.join(HERE, "Pink")
+
+
+def build_cli(force=False):
+    """The command line program (host C++ only) next to the library it drives."""
+    host = os.path.join(HERE, "host")
+    srcs = [os.path.join(host, "pink_cli.cpp"), os.path.join(host, "pink_files.hpp"),
+            os.path.join(HERE, "..", "include", "pink_b200.h")]
+    if force or _stale(CLI, srcs + [LIB]):
+        cxx = os.environ.get("CXX", "g++")
+        subprocess.check_call([cxx, "-O2", "-std=c++17", "-pthread", srcs[0], "-o", CLI, "-L" + HERE, "-lpink_b200",
+                               "-Wl,-rpath,$ORIGIN"])
+    return CLI
 
 
 if __name__ == "__main__":

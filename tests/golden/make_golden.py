@@ -92,6 +92,14 @@ def main():
         out["circ%d_trained" % i] = tr.som()
         out["circ%d_map_dist" % i] = dist
         out["circ%d_map_rot" % i] = rot
+    # order of the reference's shuffled data iterator (SelfOrganizingMapLib/DataIteratorShuffled.h:41-74)
+    import ctypes as C
+    r = O.ref()
+    r.ref_shuffled_order.argtypes = [C.c_uint32, C.c_uint64, C.c_int, C.c_void_p]
+    for n, seed in [(8, 1234), (100, 1234), (100, 1235), (1000, 7)]:
+        order = np.zeros(n, np.uint32)
+        r.ref_shuffled_order(n, seed, 1, order.ctypes.data)
+        out["order_%d_%d" % (n, seed)] = order
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_cpu.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")

@@ -76,3 +76,66 @@ def test_two_gpu_sharded_training_bit_exact(cuda, mode, exchange):
     else:
         assert np.array_equal(whole.view(np.uint32), want.view(np.uint32))
     assert counts.sum() == len(imgs) and all(counts[b] > 0 for b in bmus)
+
+
+def _silent_worker(rank, world, port, q):
+    """Rank 1 stops delivering records after two images; rank 0 trains a third and must get a time-out status
+    (not a hang) from its update kernel's bounded wait.  Rank 1 keeps its context until rank 0 is done, so that
+    rank 0's stores into rank 1's record ring stay valid."""
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import time
+    import torch
+    import torch.distributed as dist
+    from pink_b200 import capi, engine
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    N, idim, nd, ed, R = 12, 24, 16, 11, 8
+    rng = np.random.default_rng(3)
+    som = rng.random((N, 1, nd, nd), dtype=np.float32)
+    imgs = rng.random((3, 1, idim, idim), dtype=np.float32)
+    F = engine.update_factors(0, 4, 3, capi.FUNC_GAUSSIAN, 1.1, 0.2)
+    eng = engine.Engine(N, 1, idim, nd, ed, R, True, capi.UINT8, device=rank, rank=rank, world_size=world)
+    uid = [engine.Engine.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(uid, 0)
+    eng.comm_init(uid[0])
+    eng.set_som(som)
+    eng.set_update_factors(F)
+    eng.train(imgs[:2])
+    eng.synchronize()
+    dist.barrier()
+    outcome = None
+    if rank == 0:
+        t0 = time.time()
+        try:
+            eng.train(imgs[2:])
+            eng.synchronize()
+            outcome = "no error"
+        except capi.PinkError as ex:
+            outcome = (ex.code if hasattr(ex, "code") else None, str(ex), time.time() - t0)
+    dist.barrier()                       # rank 1 leaves only now, between steps, with nothing in flight
+    if rank == 0:
+        q.put((eng.exchange_kind(), outcome))
+    eng.close()
+    dist.destroy_process_group()
+
+
+def test_missing_rank_gives_a_timeout_status(cuda):
+    torch = cuda
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29850 + (os.getpid() % 100)
+    procs = [ctx.Process(target=_silent_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    kind, outcome = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert kind == 2                                         # peer-memory exchange
+    assert outcome != "no error"
+    assert "bounded device-side wait expired (code 13)" in outcome[1]
+    assert outcome[2] < 30                                   # seconds: a bounded wait, not a hang

@@ -49,23 +49,28 @@ constexpr uint32_t kThreads = 192;
 // PAIR: two CTAs of a cluster share one M=256 MMA (cta_group::2); each stages its own 128 neuron
 // rows and only half of the transform rows, which frees shared memory for deeper rings.
 template <int MODE, bool PAIR> struct TcCfg;
-template <> struct TcCfg<kModeU8, false>  { static constexpr uint32_t planes = 1, max_n = 256, stages = 4, cols = 256; };
-template <> struct TcCfg<kModeU16, false> { static constexpr uint32_t planes = 2, max_n = 128, stages = 3, cols = 512; };
-template <> struct TcCfg<kModeU8, true>   { static constexpr uint32_t planes = 1, max_n = 256, stages = 6, cols = 256; };
-template <> struct TcCfg<kModeU16, true>  { static constexpr uint32_t planes = 2, max_n = 128, stages = 4, cols = 512; };
+template <> struct TcCfg<kModeU8, false>  { static constexpr uint32_t planes = 1, max_n = 256, cols = 256; };
+template <> struct TcCfg<kModeU16, false> { static constexpr uint32_t planes = 2, max_n = 128, cols = 512; };
+template <> struct TcCfg<kModeU8, true>   { static constexpr uint32_t planes = 1, max_n = 256, cols = 256; };
+template <> struct TcCfg<kModeU16, true>  { static constexpr uint32_t planes = 2, max_n = 128, cols = 512; };
 
+// Shared memory of a CTA: barriers, the tensor-memory address and the per-column |b|^2 in the first
+// 4 KB, then the ring of stages.  A stage holds, per byte plane, the 128 neuron rows and this CTA's
+// transform rows of one 128-byte K slice; its size follows the tile width of the launch, and the
+// ring takes as many stages as fit (narrow tiles of small shards get a deeper ring, which is what
+// hides the load latency when the MMAs of a slice are short).
+constexpr uint32_t kMaxStages = 16;
 template <int MODE, bool PAIR>
 struct SmemLayout
 {
     using Cfg = TcCfg<MODE, PAIR>;
     static constexpr uint32_t a_bytes = kBlockM * kBlockK;            // per plane
-    static constexpr uint32_t b_bytes = Cfg::max_n / (PAIR ? 2 : 1) * kBlockK;   // per plane (capacity)
-    static constexpr uint32_t stage_bytes = Cfg::planes * (a_bytes + b_bytes);
-    static constexpr uint32_t ring_bytes = Cfg::stages * stage_bytes;
-    static constexpr uint32_t bar_off = ring_bytes;                   // full[stages], empty[stages], tmem_full
-    static constexpr uint32_t tmem_ptr_off = bar_off + (2 * Cfg::stages + 1) * 8;
-    static constexpr uint32_t nb_off = (tmem_ptr_off + 4 + 15) & ~15u; // per-column |b|^2 of this tile
-    static constexpr uint32_t total = nb_off + Cfg::max_n * 8 + 1024; // + slack for 1024-byte alignment
+    static constexpr uint32_t bar_off = 0;                            // full[kMaxStages], empty[kMaxStages], tmem_full
+    static constexpr uint32_t tmem_ptr_off = (2 * kMaxStages + 1) * 8;
+    static constexpr uint32_t nb_off = 512;                           // per-column |b|^2 of this tile, up to 256 x 8 bytes
+    static constexpr uint32_t ring_off = 4096;
+    static constexpr uint32_t ring_budget = 196 * 1024;
+    static constexpr uint32_t slack = 1024;                           // for the 1024-byte alignment of the base
 };
 
 struct TcParams
@@ -76,6 +81,7 @@ struct TcParams
     void* s_out;
     int* status;
     uint32_t n, T, num_kb, n_tile;
+    uint32_t stages, b_bytes;   // ring depth; bytes of this CTA's transform rows per plane and stage (multiple of 1024)
     uint32_t* tail_counter;     // nullable: block arrival counter (zero between launches) that enables the tail below
     BmuArgs tail;               // the last block to finish reduces the shard's keys to its record and publishes it
 };
@@ -97,8 +103,10 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::bar_off);
-    uint64_t* empty_bar = full_bar + Cfg::stages;
-    uint64_t* tmem_full_bar = empty_bar + Cfg::stages;
+    uint64_t* empty_bar = full_bar + kMaxStages;
+    uint64_t* tmem_full_bar = empty_bar + kMaxStages;
+    uint8_t* ring = smem + L::ring_off;
+    const uint32_t stage_bytes = Cfg::planes * (L::a_bytes + p.b_bytes);
     uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(smem + L::tmem_ptr_off);
     unsigned long long* nb_s = reinterpret_cast<unsigned long long*>(smem + L::nb_off);
 
@@ -113,7 +121,7 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
 
     if (threadIdx.x == 0) {
         // PAIR: both CTAs' producers arrive (with their byte counts) on the issuing CTA's full barriers
-        for (uint32_t s = 0; s < Cfg::stages; ++s) { mbar_init(&full_bar[s], PAIR ? 2 : 1); mbar_init(&empty_bar[s], 1); }
+        for (uint32_t s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], PAIR ? 2 : 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(tmem_full_bar, 1);
         mbar_fence_init();
         tma_prefetch_desc(&map_a0);
@@ -138,9 +146,9 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
         if (elect_one()) {
             const int32_t brow = (int32_t)(img * p.T + t0 + pair_rank * b_rows);
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
-                const uint32_t s = kb % Cfg::stages, ph = (kb / Cfg::stages) & 1;
+                const uint32_t s = kb % p.stages, ph = (kb / p.stages) & 1;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1)) { report(p.status, kDevTimeoutProducer); break; }
-                uint8_t* st = smem + s * L::stage_bytes;
+                uint8_t* st = ring + s * stage_bytes;
                 const int32_t kx = (int32_t)(kb * kBlockK);
                 if (PAIR) {
                     const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);      // the issuing CTA's barrier
@@ -149,7 +157,7 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     tma_load_2d_pair(st + Cfg::planes * L::a_bytes, &map_b0, bar, kx, brow);
                     if (MODE == kModeU16) {
                         tma_load_2d_pair(st + L::a_bytes, &map_a1, bar, kx, (int32_t)m0);
-                        tma_load_2d_pair(st + Cfg::planes * L::a_bytes + L::b_bytes, &map_b1, bar, kx, brow);
+                        tma_load_2d_pair(st + Cfg::planes * L::a_bytes + p.b_bytes, &map_b1, bar, kx, brow);
                     }
                 } else {
                     mbar_expect_tx(&full_bar[s], stage_tx);
@@ -157,7 +165,7 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     tma_load_2d(st + Cfg::planes * L::a_bytes, &map_b0, &full_bar[s], kx, brow);
                     if (MODE == kModeU16) {
                         tma_load_2d(st + L::a_bytes, &map_a1, &full_bar[s], kx, (int32_t)m0);
-                        tma_load_2d(st + Cfg::planes * L::a_bytes + L::b_bytes, &map_b1, &full_bar[s], kx, brow);
+                        tma_load_2d(st + Cfg::planes * L::a_bytes + p.b_bytes, &map_b1, &full_bar[s], kx, brow);
                     }
                 }
             }
@@ -180,10 +188,10 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
             };
             bool ok = true;
             for (uint32_t kb = 0; kb < p.num_kb && ok; ++kb) {
-                const uint32_t s = kb % Cfg::stages, ph = (kb / Cfg::stages) & 1;
+                const uint32_t s = kb % p.stages, ph = (kb / p.stages) & 1;
                 if (!mbar_wait(&full_bar[s], ph)) { report(p.status, kDevTimeoutMma); ok = false; break; }
                 tc_fence_after();
-                const uint32_t st = smem_u32(smem + s * L::stage_bytes);
+                const uint32_t st = smem_u32(ring + s * stage_bytes);
                 const uint64_t a_hi = make_sw128_kmajor_desc(st);
                 const uint64_t b_hi = make_sw128_kmajor_desc(st + Cfg::planes * L::a_bytes);
 #pragma unroll
@@ -194,7 +202,7 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                         mma(tmem_base, a_hi + adv, b_hi + adv, acc);
                     } else {
                         const uint64_t a_lo = make_sw128_kmajor_desc(st + L::a_bytes);
-                        const uint64_t b_lo = make_sw128_kmajor_desc(st + Cfg::planes * L::a_bytes + L::b_bytes);
+                        const uint64_t b_lo = make_sw128_kmajor_desc(st + Cfg::planes * L::a_bytes + p.b_bytes);
                         mma(tmem_base, a_hi + adv, b_hi + adv, acc);                         // hh
                         mma(tmem_base + Cfg::max_n, a_lo + adv, b_lo + adv, acc);            // ll
                         mma(tmem_base + 2 * Cfg::max_n, a_hi + adv, b_lo + adv, acc);        // cross
@@ -398,21 +406,27 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     static int attr_dev = -1;   // the opt-in shared-memory size is a per-device function attribute
     int dev = 0;
     cudaGetDevice(&dev);
+    constexpr uint32_t smem_max = L::ring_off + L::ring_budget + L::slack;
     if (dev != attr_dev) {
         cudaError_t e = cudaFuncSetAttribute(distance_tc_kernel<MODE, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)L::total);
+                                             (int)smem_max);
         if (e != cudaSuccess) { *why = "cudaFuncSetAttribute(distance_tc_kernel)"; return e; }
         attr_dev = dev;
     }
+    // ring: as many stages as fit the budget, no more than there are K slices
+    const uint32_t b_bytes = (b_box * kBlockK + 1023) & ~1023u;
+    const uint32_t stage_bytes = Cfg::planes * (L::a_bytes + b_bytes);
+    const uint32_t stages = std::max(2u, std::min(std::min(kMaxStages, L::ring_budget / stage_bytes), g.Kp / kBlockK));
     TcParams p;
     p.anorm = a.anorm; p.bnorm = a.bnorm; p.keys = a.keys; p.s_out = a.s_out; p.status = a.status;
     p.n = a.n; p.T = g.T; p.num_kb = g.Kp / kBlockK; p.n_tile = n_tile;
+    p.stages = stages; p.b_bytes = b_bytes;
     p.tail_counter = a.tail ? a.tail_counter : nullptr;
     if (a.tail) p.tail = *a.tail;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(m_tiles, n_tiles, a.n_img);
     cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = L::total;
+    cfg.dynamicSmemBytes = L::ring_off + stages * stage_bytes + L::slack;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;

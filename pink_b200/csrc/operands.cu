@@ -113,8 +113,9 @@ __device__ __forceinline__ typename StageType<MODE>::type to_stage(float v)
 constexpr uint32_t kRotMaxSlots = 8;          // column slots (of 32) per thread with hoisted column terms
 constexpr uint32_t kStagePad = 16;            // slack around the staged byte planes for aligned over-reads
 
+// (five blocks per SM: the kernel lives on many resident warps; rarely taken paths may spill instead)
 template <int MODE>
-__global__ void __launch_bounds__(kRotThreads)
+__global__ void __launch_bounds__(kRotThreads, 5)
 rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, uint32_t magic_nd, uint32_t magic_ed,
               const float* __restrict__ cs, const float* __restrict__ sn, float* __restrict__ base_out,
               void* __restrict__ b0, void* __restrict__ b1, void* __restrict__ bnorm, uint32_t* __restrict__ rmax)

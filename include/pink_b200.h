@@ -184,9 +184,12 @@ uint64_t pink_b200_launch_count(pink_b200_ctx* ctx);
 /* How the ranks exchange their best-matching-unit records every step (no
  * reference counterpart: the reference trains on one GPU).  PEER: each rank
  * stores its record into every rank's memory over NVLink and the update kernel
- * waits for them (ranks on one node, one GPU each); NCCL: an all-gather per
- * step; NONE: a single rank or no communicator yet. */
-enum { PINK_B200_EXCHANGE_NONE = 0, PINK_B200_EXCHANGE_NCCL = 1, PINK_B200_EXCHANGE_PEER = 2 };
+ * waits for them (ranks on one node, one GPU each); PEER_SHARED_ROTATION: the
+ * same, and the ranks also share the rotation work -- each computes the rotation
+ * sets of its part of every batch of images and copies them into all ranks'
+ * buffers; NCCL: an all-gather per step; NONE: a single rank or no communicator yet. */
+enum { PINK_B200_EXCHANGE_NONE = 0, PINK_B200_EXCHANGE_NCCL = 1, PINK_B200_EXCHANGE_PEER = 2,
+       PINK_B200_EXCHANGE_PEER_SHARED_ROTATION = 3 };
 int pink_b200_exchange_kind(pink_b200_ctx* ctx);
 
 /* Totals over all training steps of this context (this rank's shard): out[0] =

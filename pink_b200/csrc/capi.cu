@@ -196,6 +196,17 @@ struct pink_b200_ctx
     // value ranges for leaving out neurons that cannot change: per neuron {min |w|, max |w|}, per buffered image max |pixel|
     uint2* d_wrange = nullptr; uint32_t* d_rmax = nullptr;
     ushort2* d_circle = nullptr;      // column spans of a circular distance region (null: quadratic)
+    // Rotation sets computed in shares (world_size > 1 with peer memory): every rank rotates its part of a
+    // batch of images and copies the results into all ranks' transform buffers, which hold three batches.
+    bool rot_shared = false;
+    cudaStream_t bcast_stream = nullptr;
+    cudaEvent_t share_rotated = nullptr, bcast_done[3] = { nullptr, nullptr, nullptr };
+    unsigned long long* d_rotflag = nullptr;               // [3 batches][world]: batch number + 1 of the share that arrived
+    unsigned long long* peer_rotflag[kXchgMaxRanks] = {};
+    float* peer_base[kXchgMaxRanks] = {};
+    uint8_t* peer_b0[kXchgMaxRanks] = {}; uint8_t* peer_b1[kXchgMaxRanks] = {}; uint8_t* peer_bnorm[kXchgMaxRanks] = {};
+    uint32_t* peer_rmax[kXchgMaxRanks] = {};
+    uint64_t share_seq = 0;                                // batches handled so far (all ranks count alike)
     unsigned long long* d_stats = nullptr;   // [0] neurons with a non-zero factor, [1] neurons written back, summed over steps
     uint64_t launches = 0;            // kernels launched by this context so far
     bool fuse_update = false;         // the update kernel finds the best matching unit and its work list itself
@@ -347,8 +358,11 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
 
 // m sequential steps over images resident on the device.  `ready` (nullable) is
 // an event the rotation stream must wait for before reading the images.
+static int train_chunk_shared(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* log, cudaEvent_t ready);
+
 int train_chunk(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* log, cudaEvent_t ready)
 {
+    if (c->rot_shared) return train_chunk_shared(c, d_images, m, log, ready);
     const Geometry& g = c->g;
     const size_t esz = g.mode == kModeF32 ? 4 : 1, isz = c->image_size();
     for (uint64_t s0 = 0; s0 < m; s0 += kRotBatch) {
@@ -381,6 +395,91 @@ int train_chunk(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* l
     return PINK_B200_OK;
 }
 
+// The same over several ranks that share the rotation work (rot_shared): of every batch of kRotBatch images
+// a rank rotates a contiguous part, copies the results (base rotations, operand rows, norms, pixel maximum)
+// into every other rank's transform buffers on a copy stream, and then raises its flag in every rank's
+// flag row; a rank starts the steps of a batch when all flags of the batch are up.  The part of batch b + 1
+// is rotated before the steps of batch b, so that its copies travel while those steps run.  The buffers hold
+// three batches: the ranks are at most one step apart (they exchange a record every step), so a batch two
+// ahead never lands in memory a slower rank still reads.
+static int train_chunk_shared(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* log, cudaEvent_t ready)
+{
+    const Geometry& g = c->g;
+    const uint32_t W = c->cfg.world_size, rank = c->cfg.rank;
+    const size_t esz = g.mode == kModeF32 ? 4 : 1, isz = c->image_size(), nbase = g.q ? g.q : 1;
+    const size_t base_img = nbase * (size_t)g.P * sizeof(float), op_img = (size_t)g.T * g.Kp * esz;
+    const size_t norm_img = (size_t)g.T * (g.mode == kModeU16 ? 8 : 4);
+    if (ready) CU_TRY(cudaStreamWaitEvent(c->stream, ready, 0));
+    const uint64_t batches = (m + kRotBatch - 1) / kRotBatch;
+    auto produce = [&](uint64_t b) -> int {
+        const uint64_t seq = c->share_seq + b;
+        const uint32_t ring = (uint32_t)(seq % 3);
+        const size_t slot = (size_t)ring * kRotBatch;
+        const uint32_t cnt = (uint32_t)std::min<uint64_t>(kRotBatch, m - b * kRotBatch);
+        const uint32_t per = (cnt + W - 1) / W, lo = std::min(rank * per, cnt), hi = std::min(lo + per, cnt);
+        // the copies that last read this part of the buffers (three batches ago) are over
+        CU_TRY(cudaStreamWaitEvent(c->stream, c->bcast_done[ring], 0));
+        if (hi > lo) {
+            CU_TRY(cudaMemsetAsync(c->d_rmax + slot + lo, 0, (hi - lo) * sizeof(uint32_t), c->stream));
+            const size_t row0 = (slot + lo) * g.T;
+            cudaEvent_t* ev = nullptr;
+            if (c->prof_used < c->prof_cap && 2 * (c->prof_rot_used + 1) <= c->prof_rot_events.size())
+                ev = &c->prof_rot_events[2 * c->prof_rot_used++];
+            if (ev) CU_TRY(cudaEventRecord(ev[0], c->stream));
+            LAUNCH_TRY(launch_rotate(g, d_images + (b * kRotBatch + lo) * isz, hi - lo, c->d_cs, c->d_sn,
+                                     c->d_base + (slot + lo) * nbase * (size_t)g.P,
+                                     static_cast<uint8_t*>(c->d_b0) + row0 * g.Kp * esz,
+                                     c->d_b1 ? static_cast<uint8_t*>(c->d_b1) + row0 * g.Kp * esz : nullptr,
+                                     static_cast<uint8_t*>(c->d_bnorm) + row0 * (g.mode == kModeU16 ? 8 : 4),
+                                     c->stream, c->d_rmax + slot + lo));
+            c->launches += 1;
+            if (ev) CU_TRY(cudaEventRecord(ev[1], c->stream));
+        }
+        CU_TRY(cudaEventRecord(c->share_rotated, c->stream));
+        CU_TRY(cudaStreamWaitEvent(c->bcast_stream, c->share_rotated, 0));
+        if (hi > lo) {
+            const size_t first = slot + lo, n = hi - lo;
+            for (uint32_t p = 0; p < W; ++p) {
+                if (p == rank) continue;
+                CU_TRY(cudaMemcpyAsync(reinterpret_cast<uint8_t*>(c->peer_base[p]) + first * base_img,
+                                       reinterpret_cast<uint8_t*>(c->d_base) + first * base_img, n * base_img, cudaMemcpyDefault, c->bcast_stream));
+                CU_TRY(cudaMemcpyAsync(c->peer_b0[p] + first * op_img, static_cast<uint8_t*>(c->d_b0) + first * op_img, n * op_img,
+                                       cudaMemcpyDefault, c->bcast_stream));
+                if (c->d_b1)
+                    CU_TRY(cudaMemcpyAsync(c->peer_b1[p] + first * op_img, static_cast<uint8_t*>(c->d_b1) + first * op_img, n * op_img,
+                                           cudaMemcpyDefault, c->bcast_stream));
+                CU_TRY(cudaMemcpyAsync(c->peer_bnorm[p] + first * norm_img, static_cast<uint8_t*>(c->d_bnorm) + first * norm_img,
+                                       n * norm_img, cudaMemcpyDefault, c->bcast_stream));
+                CU_TRY(cudaMemcpyAsync(c->peer_rmax[p] + first, c->d_rmax + first, n * sizeof(uint32_t), cudaMemcpyDefault, c->bcast_stream));
+            }
+        }
+        LAUNCH_TRY(launch_flag_publish(c->peer_rotflag, W, ring * W + rank, seq + 1, c->bcast_stream));
+        c->launches += 1;
+        CU_TRY(cudaEventRecord(c->bcast_done[ring], c->bcast_stream));
+        return PINK_B200_OK;
+    };
+    int rc = produce(0);
+    if (rc) return rc;
+    for (uint64_t b = 0; b < batches; ++b) {
+        if (b + 1 < batches) { rc = produce(b + 1); if (rc) return rc; }
+        const uint64_t seq = c->share_seq + b;
+        const uint32_t ring = (uint32_t)(seq % 3);
+        const uint32_t cnt = (uint32_t)std::min<uint64_t>(kRotBatch, m - b * kRotBatch);
+        // This rank's own share of the batch must have left (copies and flag) before its steps begin: the
+        // update kernel fills every SM while it waits for the other ranks' records, and they wait for this
+        // flag -- whose kernel could then find no SM to run on.
+        CU_TRY(cudaStreamWaitEvent(c->stream, c->bcast_done[ring], 0));
+        LAUNCH_TRY(launch_flag_wait(c->d_rotflag + ring * W, W, rank, seq + 1, c->d_status, c->stream));
+        c->launches += 1;
+        for (uint32_t i = 0; i < cnt; ++i) {
+            rc = train_step(c, (size_t)ring * kRotBatch + i, log + b * kRotBatch + i);
+            if (rc) return rc;
+        }
+    }
+    c->share_seq += batches;
+    return PINK_B200_OK;
+}
+
 void release_peer_exchange(pink_b200_ctx* c)
 {
     for (uint32_t r = 0; r < kXchgMaxRanks; ++r) {
@@ -390,6 +489,21 @@ void release_peer_exchange(pink_b200_ctx* c)
     if (c->d_xchg) cudaFree(c->d_xchg);
     c->d_xchg = nullptr;
     c->xchg_on = false;
+    for (uint32_t r = 0; r < kXchgMaxRanks; ++r) {
+        if (r != c->cfg.rank) {
+            if (c->peer_rotflag[r]) cudaIpcCloseMemHandle(c->peer_rotflag[r]);
+            if (c->peer_base[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
+            if (c->peer_b0[r]) cudaIpcCloseMemHandle(c->peer_b0[r]);
+            if (c->peer_b1[r]) cudaIpcCloseMemHandle(c->peer_b1[r]);
+            if (c->peer_bnorm[r]) cudaIpcCloseMemHandle(c->peer_bnorm[r]);
+            if (c->peer_rmax[r]) cudaIpcCloseMemHandle(c->peer_rmax[r]);
+        }
+        c->peer_rotflag[r] = nullptr; c->peer_base[r] = nullptr; c->peer_b0[r] = nullptr; c->peer_b1[r] = nullptr;
+        c->peer_bnorm[r] = nullptr; c->peer_rmax[r] = nullptr;
+    }
+    if (c->d_rotflag) cudaFree(c->d_rotflag);
+    c->d_rotflag = nullptr;
+    c->rot_shared = false;
 }
 
 // Sets up the exchange of best-matching-unit records through peer memory: every rank
@@ -401,7 +515,8 @@ void release_peer_exchange(pink_b200_ctx* c)
 int setup_peer_exchange(pink_b200_ctx* c)
 {
     const uint32_t W = c->cfg.world_size, rank = c->cfg.rank;
-    struct Hello { cudaIpcMemHandle_t handle; char bus[32]; uint32_t want; uint32_t ok; };
+    // handles: 0 record ring; 1..6 the transform buffers and the flag rows of the shared rotation
+    struct Hello { cudaIpcMemHandle_t handle[7]; char bus[32]; uint32_t want; uint32_t share; uint32_t ok; };
     Hello mine{};
     std::vector<Hello> all(W);
     Hello* d_all = nullptr;
@@ -412,8 +527,23 @@ int setup_peer_exchange(pink_b200_ctx* c)
         CU_TRY(cudaMalloc(&c->d_xchg, bytes));
         CU_TRY(cudaMemsetAsync(c->d_xchg, 0, bytes, c->stream));
         CU_TRY(cudaStreamSynchronize(c->stream));          // zeroed before any rank can learn the handle
-        if (cudaIpcGetMemHandle(&mine.handle, c->d_xchg) != cudaSuccess) { cudaGetLastError(); mine.want = 0; }
+        if (cudaIpcGetMemHandle(&mine.handle[0], c->d_xchg) != cudaSuccess) { cudaGetLastError(); mine.want = 0; }
         if (cudaDeviceGetPCIBusId(mine.bus, sizeof(mine.bus), c->cfg.device) != cudaSuccess) { cudaGetLastError(); mine.want = 0; }
+    }
+    // Shared rotation: the transform buffers get their final size now (three training batches, or the mapping
+    // batch if that is larger) because the other ranks map them.  PINK_B200_REPLICATED_ROTATION
+    // (diagnostic switch) keeps every rank computing every rotation set.
+    mine.share = mine.want && !getenv("PINK_B200_REPLICATED_ROTATION");
+    if (mine.share) {
+        const size_t imgs = std::max<size_t>(3 * kRotBatch, c->map_batch);
+        int rc0 = ensure_transform_buffers(c, imgs, 3 * kRotBatch);
+        if (rc0) return rc0;
+        CU_TRY(cudaMalloc(&c->d_rotflag, 3 * W * sizeof(unsigned long long)));
+        CU_TRY(cudaMemsetAsync(c->d_rotflag, 0, 3 * W * sizeof(unsigned long long), c->stream));
+        CU_TRY(cudaStreamSynchronize(c->stream));
+        void* bufs[6] = { c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->d_rmax, c->d_rotflag };
+        for (int i = 0; i < 6; ++i)
+            if (bufs[i] && cudaIpcGetMemHandle(&mine.handle[1 + i], bufs[i]) != cudaSuccess) { cudaGetLastError(); mine.share = 0; }
     }
     CU_TRY(cudaMalloc(&d_all, W * sizeof(Hello)));
     auto gather = [&]() -> int {
@@ -425,30 +555,58 @@ int setup_peer_exchange(pink_b200_ctx* c)
     };
     int rc = gather();
     if (rc) { cudaFree(d_all); return rc; }
-    bool ok = true;
+    bool ok = true, share = true;
     for (uint32_t r = 0; r < W; ++r) {
         ok = ok && all[r].want;
+        share = share && all[r].share;
         for (uint32_t q = 0; q < r; ++q) ok = ok && std::strncmp(all[r].bus, all[q].bus, sizeof(mine.bus)) != 0;
     }
+    share = share && ok;
+    auto open = [&](const cudaIpcMemHandle_t& h, void** out) {
+        if (cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess) return true;
+        cudaGetLastError();
+        *out = nullptr;
+        return false;
+    };
     if (ok) {
         for (uint32_t r = 0; r < W && ok; ++r) {
             if (r == rank) { c->xchg_peer[r] = c->d_xchg; continue; }
             void* ptr = nullptr;
-            if (cudaIpcOpenMemHandle(&ptr, all[r].handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
-                cudaGetLastError();
-                ok = false;
-            } else {
-                c->xchg_peer[r] = static_cast<XchgRecord*>(ptr);
+            ok = open(all[r].handle[0], &ptr);
+            c->xchg_peer[r] = static_cast<XchgRecord*>(ptr);
+        }
+    }
+    if (share) {
+        for (uint32_t r = 0; r < W && share; ++r) {
+            if (r == rank) {
+                c->peer_base[r] = c->d_base; c->peer_b0[r] = static_cast<uint8_t*>(c->d_b0);
+                c->peer_b1[r] = static_cast<uint8_t*>(c->d_b1); c->peer_bnorm[r] = static_cast<uint8_t*>(c->d_bnorm);
+                c->peer_rmax[r] = c->d_rmax; c->peer_rotflag[r] = c->d_rotflag;
+                continue;
             }
+            void* p[6] = {};
+            for (int i = 0; i < 6 && share; ++i)
+                if (i != 2 || c->d_b1) share = open(all[r].handle[1 + i], &p[i]);
+            c->peer_base[r] = static_cast<float*>(p[0]); c->peer_b0[r] = static_cast<uint8_t*>(p[1]);
+            c->peer_b1[r] = static_cast<uint8_t*>(p[2]); c->peer_bnorm[r] = static_cast<uint8_t*>(p[3]);
+            c->peer_rmax[r] = static_cast<uint32_t*>(p[4]); c->peer_rotflag[r] = static_cast<unsigned long long*>(p[5]);
         }
     }
     mine.ok = ok;
+    mine.share = share;
     rc = gather();                                          // all ranks must agree on the way they exchange
     cudaFree(d_all);
     if (rc) return rc;
-    for (uint32_t r = 0; r < W; ++r) ok = ok && all[r].ok;
+    for (uint32_t r = 0; r < W; ++r) { ok = ok && all[r].ok; share = share && all[r].share; }
     c->xchg_on = ok;
-    if (!ok) release_peer_exchange(c);
+    if (!ok) { release_peer_exchange(c); return PINK_B200_OK; }
+    c->rot_shared = share && ok;
+    if (c->rot_shared) {
+        if (!c->bcast_stream) CU_TRY(cudaStreamCreateWithFlags(&c->bcast_stream, cudaStreamNonBlocking));
+        if (!c->share_rotated) CU_TRY(cudaEventCreateWithFlags(&c->share_rotated, cudaEventDisableTiming));
+        for (int i = 0; i < 3; ++i)
+            if (!c->bcast_done[i]) CU_TRY(cudaEventCreateWithFlags(&c->bcast_done[i], cudaEventDisableTiming));
+    }
     return PINK_B200_OK;
 }
 
@@ -576,8 +734,8 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     CTX_TRY(cudaMemsetAsync(c->d_pairs, 0xFF, W * sizeof(BmuPair), c->stream));
     CTX_TRY(cudaMalloc(&c->d_items, c->count * sizeof(UpdateItem)));
     CTX_TRY(cudaMemsetAsync(c->d_items, 0, c->count * sizeof(UpdateItem), c->stream));
-    CTX_TRY(cudaMalloc(&c->d_rmax, 2 * kRotBatch * sizeof(uint32_t)));
-    CTX_TRY(cudaMemsetAsync(c->d_rmax, 0, 2 * kRotBatch * sizeof(uint32_t), c->stream));
+    CTX_TRY(cudaMalloc(&c->d_rmax, 3 * kRotBatch * sizeof(uint32_t)));
+    CTX_TRY(cudaMemsetAsync(c->d_rmax, 0, 3 * kRotBatch * sizeof(uint32_t), c->stream));
     CTX_TRY(cudaMalloc(&c->d_stats, 2 * sizeof(unsigned long long)));
     CTX_TRY(cudaMemsetAsync(c->d_stats, 0, 2 * sizeof(unsigned long long), c->stream));
     // [0] work-list length, [1] block arrival counter of the update kernel, [2] of the distance kernel
@@ -618,6 +776,7 @@ int pink_b200_destroy(pink_b200_ctx* c)
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->copy_stream) cudaStreamSynchronize(c->copy_stream);
     if (c->rot_stream) cudaStreamSynchronize(c->rot_stream);
+    if (c->bcast_stream) cudaStreamSynchronize(c->bcast_stream);
     release_peer_exchange(c);
     if (c->comm && nccl().ok) nccl().CommDestroy(c->comm);
     free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
@@ -635,6 +794,9 @@ int pink_b200_destroy(pink_b200_ctx* c)
         if (c->rotated[i]) cudaEventDestroy(c->rotated[i]);
         if (c->rot_free[i]) cudaEventDestroy(c->rot_free[i]);
     }
+    if (c->bcast_stream) { cudaStreamSynchronize(c->bcast_stream); cudaStreamDestroy(c->bcast_stream); }
+    if (c->share_rotated) cudaEventDestroy(c->share_rotated);
+    for (int i = 0; i < 3; ++i) if (c->bcast_done[i]) cudaEventDestroy(c->bcast_done[i]);
     if (c->stream) cudaStreamDestroy(c->stream);
     if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     if (c->rot_stream && c->rot_stream != c->stream) cudaStreamDestroy(c->rot_stream);
@@ -873,6 +1035,7 @@ uint64_t pink_b200_launch_count(pink_b200_ctx* c) { return c ? c->launches : 0; 
 int pink_b200_exchange_kind(pink_b200_ctx* c)
 {
     if (!c || c->cfg.world_size == 1 || !c->comm) return PINK_B200_EXCHANGE_NONE;
+    if (c->rot_shared) return PINK_B200_EXCHANGE_PEER_SHARED_ROTATION;
     return c->xchg_on ? PINK_B200_EXCHANGE_PEER : PINK_B200_EXCHANGE_NCCL;
 }
 

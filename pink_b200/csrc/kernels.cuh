@@ -16,7 +16,7 @@ enum : int { kModeF32 = 0, kModeU16 = 1, kModeU8 = 2 };
 
 // Status codes a kernel may leave in the device status word.
 enum : int { kDevOk = 0, kDevTimeoutProducer = 1, kDevTimeoutMma = 2, kDevTimeoutEpilogue = 3,
-             kDevTimeoutUpdateProducer = 11, kDevTimeoutUpdateConsumer = 12, kDevTimeoutExchange = 13 };
+             kDevTimeoutUpdateProducer = 11, kDevTimeoutUpdateConsumer = 12, kDevTimeoutExchange = 13, kDevTimeoutRotation = 14 };
 
 struct Geometry
 {
@@ -176,6 +176,14 @@ cudaError_t launch_map_finalize(const Geometry& g, unsigned long long* keys, uin
                          float* dist, uint32_t* rot, cudaStream_t st);
 
 cudaError_t launch_fill_keys(unsigned long long* keys, size_t count, cudaStream_t st);
+
+// ---- rotation sets computed in shares by the ranks (see rotshare.cu) -----------------------
+// Stores `value` into entry `entry` of every rank's flag array (peer_flags[r], r < world <= kXchgMaxRanks).
+cudaError_t launch_flag_publish(unsigned long long* const* peer_flags, uint32_t world, uint32_t entry,
+                                unsigned long long value, cudaStream_t st);
+// Waits (bounded; status receives kDevTimeoutRotation on expiry) until row[r] holds `value` for every r != self.
+cudaError_t launch_flag_wait(const unsigned long long* row, uint32_t world, uint32_t self, unsigned long long value,
+                             int* status, cudaStream_t st);
 
 // Helpers of the C-ABI layer that entry points defined beside their kernels use:
 // validate a configuration into a Geometry (returns a PINK_B200_* status and sets

@@ -113,7 +113,7 @@ class Engine:
         capi.check(capi.lib.pink_b200_train_device(self._h, C.c_void_p(dev_ptr), n))
 
     def exchange_kind(self):
-        """0 none, 1 NCCL all-gather per step, 2 peer-memory stores."""
+        """0 none, 1 NCCL all-gather per step, 2 peer-memory stores, 3 peer-memory stores and shared rotation work."""
         return int(capi.lib.pink_b200_exchange_kind(self._h))
 
     def launch_count(self):

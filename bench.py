@@ -239,6 +239,7 @@ def main():
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    exchange_kind = eng.exchange_kind()
     launches0 = eng.launch_count()
     ms = timed(lambda s: step_dev(args.warmup + s), args.steps)
     launches = eng.launch_count() - launches0          # kernels of this library launched inside the timed region
@@ -302,8 +303,8 @@ def main():
     roof = dict(kernels[dominant])
     roof["kernel"] = dominant
     # dram__bytes_read + dram__bytes_write of one launch of that kernel, from the ncu capture summarised under profiles/
-    # (update: a step that rewrote few neurons; 139 MB when every neuron is rewritten)
-    roof["traffic"] = {"update_kernel": 98.84e6, "distance_tc_kernel": 17.41e6}[dominant] if world == 1 else None
+    # (update: a step that read about 1750 of the 2791 neurons and rewrote few; 139 MB when every neuron is rewritten)
+    roof["traffic"] = {"update_kernel": 58.84e6, "distance_tc_kernel": 17.41e6}[dominant] if world == 1 else None
     roof["peak_source"] = peaks["source"]
     roof["timing"] = "CUDA events around every launch in a separate profiled pass of %d steps" % covered
 
@@ -320,6 +321,8 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": {"workload": w["name"], "images_per_step": B, "parallelism": "neuron-shard x%d" % world,
+                       "exchange": {0: "none", 1: "nccl all-gather", 2: "peer-memory records",
+                                    3: "peer-memory records + shared rotation work"}[exchange_kind],
                        "l2": "every step trains on a different slice of a 134 MB image pool; SOM (90 MB) + operand "
                              "(11 MB) + batch (34 MB) exceed the 126 MB L2"},
             "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": B * isz * 4, "d2h_bytes_per_step": N * 4,

@@ -199,8 +199,8 @@ struct pink_b200_ctx
     // Rotation sets computed in shares (world_size > 1 with peer memory): every rank rotates its part of a
     // batch of images and copies the results into all ranks' transform buffers, which hold three batches.
     bool rot_shared = false;
-    cudaStream_t bcast_stream = nullptr;
-    cudaEvent_t share_rotated = nullptr, bcast_done[3] = { nullptr, nullptr, nullptr };
+    cudaStream_t bcast_stream = nullptr, peer_stream[kXchgMaxRanks] = {};   // one copy stream per destination rank, joined on bcast_stream
+    cudaEvent_t share_rotated = nullptr, bcast_done[3] = { nullptr, nullptr, nullptr }, peer_sent[kXchgMaxRanks] = {};
     unsigned long long* d_rotflag = nullptr;               // [3 batches][world]: batch number + 1 of the share that arrived
     unsigned long long* peer_rotflag[kXchgMaxRanks] = {};
     float* peer_base[kXchgMaxRanks] = {};
@@ -435,26 +435,31 @@ static int train_chunk_shared(pink_b200_ctx* c, const float* d_images, uint64_t 
             c->launches += 1;
             if (ev) CU_TRY(cudaEventRecord(ev[1], c->stream));
         }
+        // one stream per destination, so that the copies to different ranks use different copy engines and
+        // links at the same time; a destination's flag follows its copies in its stream
         CU_TRY(cudaEventRecord(c->share_rotated, c->stream));
-        CU_TRY(cudaStreamWaitEvent(c->bcast_stream, c->share_rotated, 0));
-        if (hi > lo) {
-            const size_t first = slot + lo, n = hi - lo;
-            for (uint32_t p = 0; p < W; ++p) {
-                if (p == rank) continue;
+        for (uint32_t p = 0; p < W; ++p) {
+            if (p == rank) continue;
+            cudaStream_t ps = c->peer_stream[p];
+            CU_TRY(cudaStreamWaitEvent(ps, c->share_rotated, 0));
+            if (hi > lo) {
+                const size_t first = slot + lo, n = hi - lo;
                 CU_TRY(cudaMemcpyAsync(reinterpret_cast<uint8_t*>(c->peer_base[p]) + first * base_img,
-                                       reinterpret_cast<uint8_t*>(c->d_base) + first * base_img, n * base_img, cudaMemcpyDefault, c->bcast_stream));
+                                       reinterpret_cast<uint8_t*>(c->d_base) + first * base_img, n * base_img, cudaMemcpyDefault, ps));
                 CU_TRY(cudaMemcpyAsync(c->peer_b0[p] + first * op_img, static_cast<uint8_t*>(c->d_b0) + first * op_img, n * op_img,
-                                       cudaMemcpyDefault, c->bcast_stream));
+                                       cudaMemcpyDefault, ps));
                 if (c->d_b1)
                     CU_TRY(cudaMemcpyAsync(c->peer_b1[p] + first * op_img, static_cast<uint8_t*>(c->d_b1) + first * op_img, n * op_img,
-                                           cudaMemcpyDefault, c->bcast_stream));
+                                           cudaMemcpyDefault, ps));
                 CU_TRY(cudaMemcpyAsync(c->peer_bnorm[p] + first * norm_img, static_cast<uint8_t*>(c->d_bnorm) + first * norm_img,
-                                       n * norm_img, cudaMemcpyDefault, c->bcast_stream));
-                CU_TRY(cudaMemcpyAsync(c->peer_rmax[p] + first, c->d_rmax + first, n * sizeof(uint32_t), cudaMemcpyDefault, c->bcast_stream));
+                                       n * norm_img, cudaMemcpyDefault, ps));
+                CU_TRY(cudaMemcpyAsync(c->peer_rmax[p] + first, c->d_rmax + first, n * sizeof(uint32_t), cudaMemcpyDefault, ps));
             }
+            LAUNCH_TRY(launch_flag_publish(&c->peer_rotflag[p], 1, ring * W + rank, seq + 1, ps));
+            c->launches += 1;
+            CU_TRY(cudaEventRecord(c->peer_sent[p], ps));
+            CU_TRY(cudaStreamWaitEvent(c->bcast_stream, c->peer_sent[p], 0));
         }
-        LAUNCH_TRY(launch_flag_publish(c->peer_rotflag, W, ring * W + rank, seq + 1, c->bcast_stream));
-        c->launches += 1;
         CU_TRY(cudaEventRecord(c->bcast_done[ring], c->bcast_stream));
         return PINK_B200_OK;
     };
@@ -603,6 +608,11 @@ int setup_peer_exchange(pink_b200_ctx* c)
     c->rot_shared = share && ok;
     if (c->rot_shared) {
         if (!c->bcast_stream) CU_TRY(cudaStreamCreateWithFlags(&c->bcast_stream, cudaStreamNonBlocking));
+        for (uint32_t r = 0; r < W; ++r) {
+            if (r == rank) continue;
+            if (!c->peer_stream[r]) CU_TRY(cudaStreamCreateWithFlags(&c->peer_stream[r], cudaStreamNonBlocking));
+            if (!c->peer_sent[r]) CU_TRY(cudaEventCreateWithFlags(&c->peer_sent[r], cudaEventDisableTiming));
+        }
         if (!c->share_rotated) CU_TRY(cudaEventCreateWithFlags(&c->share_rotated, cudaEventDisableTiming));
         for (int i = 0; i < 3; ++i)
             if (!c->bcast_done[i]) CU_TRY(cudaEventCreateWithFlags(&c->bcast_done[i], cudaEventDisableTiming));
@@ -776,6 +786,7 @@ int pink_b200_destroy(pink_b200_ctx* c)
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->copy_stream) cudaStreamSynchronize(c->copy_stream);
     if (c->rot_stream) cudaStreamSynchronize(c->rot_stream);
+    for (uint32_t r = 0; r < kXchgMaxRanks; ++r) if (c->peer_stream[r]) cudaStreamSynchronize(c->peer_stream[r]);
     if (c->bcast_stream) cudaStreamSynchronize(c->bcast_stream);
     release_peer_exchange(c);
     if (c->comm && nccl().ok) nccl().CommDestroy(c->comm);
@@ -793,6 +804,10 @@ int pink_b200_destroy(pink_b200_ctx* c)
         if (c->consumed[i]) cudaEventDestroy(c->consumed[i]);
         if (c->rotated[i]) cudaEventDestroy(c->rotated[i]);
         if (c->rot_free[i]) cudaEventDestroy(c->rot_free[i]);
+    }
+    for (uint32_t r = 0; r < kXchgMaxRanks; ++r) {
+        if (c->peer_stream[r]) { cudaStreamSynchronize(c->peer_stream[r]); cudaStreamDestroy(c->peer_stream[r]); }
+        if (c->peer_sent[r]) cudaEventDestroy(c->peer_sent[r]);
     }
     if (c->bcast_stream) { cudaStreamSynchronize(c->bcast_stream); cudaStreamDestroy(c->bcast_stream); }
     if (c->share_rotated) cudaEventDestroy(c->share_rotated);

@@ -1,8 +1,9 @@
 // C ABI of the library (declared in include/pink_b200.h): context state that
 // stands for the device members of the reference's Trainer<...,true> and
 // Mapper<...,true> objects (src/SelfOrganizingMapLib/Trainer.h:311-333,
-// Mapper.h:210-229), the per-image launch sequences, host<->device staging and
-// the NCCL exchange of the per-shard best matching unit.
+// Mapper.h:210-229), the per-image launch sequences, host<->device staging and,
+// with several ranks, the exchange of the per-shard best matching unit and of
+// the rotation sets (peer memory over NVLink; NCCL as fallback).
 #include "../../include/pink_b200.h"
 #include "kernels.cuh"
 

@@ -1,20 +1,22 @@
 // Best-matching-unit reduction, neighbourhood update and mapping epilogue.
 //
-// bmu_kernel replaces find_best_matching_neuron_kernel, a single-thread serial
-// scan followed by a device-to-host read (src/CudaLib/update_neurons.h:18-31,
-// :64-80), by one block-wide first-minimum reduction whose result stays on the
-// device.
-//
-// update_kernel replaces update_neurons_kernel (src/CudaLib/update_neurons.h:
-// 34-49) and, in the same pass, the next image's copy_and_transform_kernel over
-// the SOM (src/CudaLib/generate_euclidean_distance_matrix.h:64-84): one CTA per
-// neuron loads the base rotation its best transform derives from into shared
-// memory, applies  w <- w - (w - r) * f  with 128-bit loads and stores, reading
-// r through the quarter-turn/flip index permutation instead of from a
-// materialised T x P array, and re-emits the neuron's quantised distance
-// operand row and its sum of squares.  The difference, the product and the
-// final subtraction are rounded separately (never contracted to FMA), as in
-// the reference's CPU loop (src/SelfOrganizingMapLib/Trainer.h:167-179).
+// The reference finds the best matching unit with a single-thread serial scan
+// followed by a device-to-host read (find_best_matching_neuron_kernel,
+// src/CudaLib/update_neurons.h:18-31, :64-80) and then rewrites every neuron
+// (update_neurons_kernel, update_neurons.h:34-49); the next image's distance
+// step converts the whole map again (copy_and_transform_kernel,
+// src/CudaLib/generate_euclidean_distance_matrix.h:64-84).  Here one kernel per
+// image does all of it on the device: update_pipe_kernel reduces the per-neuron
+// minima to the best matching unit, derives the list of neurons to rewrite,
+// streams them through shared memory, applies  w <- w - (w - r) * f  reading r
+// through the quarter-turn/flip index permutation of a base rotation instead of
+// from a materialised T x P array, and re-emits each rewritten neuron's
+// quantised distance operand row and its sum of squares.  The difference, the
+// product and the final subtraction are rounded separately (never contracted to
+// FMA), as in the reference's CPU loop (src/SelfOrganizingMapLib/Trainer.h:167-179).
+// bmu_kernel, worklist_kernel and update_kernel (one block per listed neuron)
+// are the same steps as separate kernels, for neurons too large for the
+// pipelined kernel's shared-memory stages.
 #include "kernels.cuh"
 #include "ptx.cuh"
 #include "record.cuh"

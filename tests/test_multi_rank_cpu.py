@@ -1,7 +1,9 @@
 """The multi-GPU algorithm on CPU ranks (gloo, world_size 2 and 3): neurons sharded with the library's own
 shard_range, per-shard distances and first-minimum records from the oracle, one all-gather of the
-(code, neuron) records, lexicographic global minimum, shard-local update.  The concatenated result must equal
-the single-process oracle bit for bit, including the tie rule (lowest neuron index wins across shards)."""
+(code, neuron) records, lexicographic global minimum, shard-local update -- with the rotation sets either computed
+by every rank or in shares (each rank rotates a contiguous part of the images, the parts are gathered), as the
+GPU library does.  The concatenated result must equal the single-process oracle bit for bit, including the tie rule
+(lowest neuron index wins across shards)."""
 import os
 import sys
 
@@ -13,7 +15,7 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, mode, ret):
+def _worker(rank, world, port, mode, share, ret):
     sys.path.insert(0, ROOT)
     import torch
     import oracle as O
@@ -32,8 +34,17 @@ def _worker(rank, world, port, mode, ret):
     mine = som[first:first + count].copy()
     T = R * 2
     bmus = []
-    for img in imgs:
-        rot = O.rotation_set(img, nd, R, flip)                       # replicated on every rank
+    shared_rot = None
+    if share:
+        # the library's split of a batch: ceil(n / world) consecutive images per rank, the last ranks possibly none
+        per = (n_img + world - 1) // world
+        lo, hi = min(rank * per, n_img), min(rank * per + per, n_img)
+        parts = [None] * world
+        dist.all_gather_object(parts, [O.rotation_set(imgs[k], nd, R, flip) for k in range(lo, hi)])
+        shared_rot = [r for part in parts for r in part]
+        assert len(shared_rot) == n_img
+    for k, img in enumerate(imgs):
+        rot = shared_rot[k] if share else O.rotation_set(img, nd, R, flip)
         if mode == O.MODE_F32:
             d, best = O.distance_f32(mine, rot, ed)
             code = d.view(np.uint32).astype(np.uint64)               # non-negative floats order like their bits
@@ -56,14 +67,15 @@ def _worker(rank, world, port, mode, ret):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("share", [False, True])
 @pytest.mark.parametrize("world", [2, 3])
 @pytest.mark.parametrize("mode", [2, 0])
-def test_sharded_training_equals_single_process(world, mode):
+def test_sharded_training_equals_single_process(world, mode, share):
     import oracle as O
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + world * 10 + mode + (os.getpid() % 200)
-    procs = [ctx.Process(target=_worker, args=(r, world, port, mode, q)) for r in range(world)]
+    port = 29500 + world * 20 + mode * 2 + int(share) + (os.getpid() % 200)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, mode, share, q)) for r in range(world)]
     for p in procs:
         p.start()
     whole, bmus, som, imgs, F = q.get(timeout=120)

@@ -384,6 +384,24 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
         const uint32_t n = blockIdx.x + threadIdx.x * gridDim.x;
         items[threadIdx.x] = make_item(b, n, b.keys[n], 0.0f);
     }
+    // A consumer thread owns four consecutive neurons of every chunk of 4 * kPipeConsumers; with a single
+    // chunk (the usual case) their keys stay in registers, and with a single rank they are fetched here
+    // already, so that the load overlaps the barrier below.
+    constexpr uint32_t kChunk = 4 * kPipeConsumers;
+    const bool one_chunk = b.n <= kChunk;
+    unsigned long long kreg[4] = {~0ull, ~0ull, ~0ull, ~0ull};
+    auto load_keys = [&](uint32_t i0) {
+        if (i0 + 3 < b.n) {
+            const ulonglong2 k01 = *reinterpret_cast<const ulonglong2*>(b.keys + i0);
+            const ulonglong2 k23 = *reinterpret_cast<const ulonglong2*>(b.keys + i0 + 2);
+            kreg[0] = k01.x; kreg[1] = k01.y; kreg[2] = k23.x; kreg[3] = k23.y;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) kreg[e] = i0 + e < b.n ? b.keys[i0 + e] : ~0ull;
+        }
+    };
+    const bool keys_prefetched = warp != 0 && one_chunk && b.world == 1;
+    if (keys_prefetched) load_keys(4 * (threadIdx.x - 32));
     fence_async_smem();                   // zeroed operand staging visible to later bulk stores
     __syncthreads();
     const uint32_t plane_bytes = g.P * 4;
@@ -496,19 +514,6 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
         // ---- best matching unit: first minimum of (code, neuron) over the keys.  A thread owns four
         //      consecutive neurons of every chunk of 4 * kPipeConsumers; with a single chunk (the
         //      usual case) their keys stay in registers for the compaction below.
-        constexpr uint32_t kChunk = 4 * kPipeConsumers;
-        const bool one_chunk = b.n <= kChunk;
-        unsigned long long kreg[4] = {~0ull, ~0ull, ~0ull, ~0ull};
-        auto load_keys = [&](uint32_t i0) {
-            if (i0 + 3 < b.n) {
-                const ulonglong2 k01 = *reinterpret_cast<const ulonglong2*>(b.keys + i0);
-                const ulonglong2 k23 = *reinterpret_cast<const ulonglong2*>(b.keys + i0 + 2);
-                kreg[0] = k01.x; kreg[1] = k01.y; kreg[2] = k23.x; kreg[3] = k23.y;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) kreg[e] = i0 + e < b.n ? b.keys[i0 + e] : ~0ull;
-            }
-        };
         // neurons that provably keep every value (tiny factor against the spacing of their values) will count
         // as factor 0; their value ranges do not depend on the best matching unit and are fetched up front
         const bool can_skip = a.wrange != nullptr && a.rmax != nullptr;
@@ -530,7 +535,7 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
         if (b.world == 1) {
             for (uint32_t c0 = 0; c0 < b.n; c0 += kChunk) {
                 const uint32_t i0 = c0 + 4 * ctid;
-                load_keys(i0);
+                if (!keys_prefetched) load_keys(i0);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const unsigned long long code = kreg[e] >> b.shift;
@@ -669,9 +674,10 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                 __threadfence();
                 arrival = atomicAdd(b.arrive, 1u);
             }
+            // (no fence behind the counter: the other blocks' key reads were complete before they arrived, and
+            //  the reset and the re-armed keys only have to be visible to the next kernel)
             last_s = arrival == gridDim.x - 1;
             if (arrival == gridDim.x - 1) *b.arrive = 0;
-            __threadfence();
         }
         consumer_sync();
         if (last_s)

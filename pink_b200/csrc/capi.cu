@@ -537,9 +537,11 @@ int setup_peer_exchange(pink_b200_ctx* c)
         if (cudaDeviceGetPCIBusId(mine.bus, sizeof(mine.bus), c->cfg.device) != cudaSuccess) { cudaGetLastError(); mine.want = 0; }
     }
     // Shared rotation: the transform buffers get their final size now (three training batches, or the mapping
-    // batch if that is larger) because the other ranks map them.  PINK_B200_REPLICATED_ROTATION
-    // (diagnostic switch) keeps every rank computing every rotation set.
-    mine.share = mine.want && !getenv("PINK_B200_REPLICATED_ROTATION");
+    // batch if that is larger) because the other ranks map them.  On by default for two ranks only: measured
+    // on eight B200 the copies (164 MB per rank and batch in each direction) slow the other kernels down by
+    // more than the saved rotation work (18.4 k against 23.7 k images/s), on two it gains 6 %.
+    // PINK_B200_SHARED_ROTATION forces it on, PINK_B200_REPLICATED_ROTATION off (diagnostic switches).
+    mine.share = mine.want && !getenv("PINK_B200_REPLICATED_ROTATION") && (W <= 2 || getenv("PINK_B200_SHARED_ROTATION"));
     if (mine.share) {
         const size_t imgs = std::max<size_t>(3 * kRotBatch, c->map_batch);
         int rc0 = ensure_transform_buffers(c, imgs, 3 * kRotBatch);

@@ -146,6 +146,13 @@ int pink_b200_som_distances(uint32_t som_layout, uint32_t dim0, uint32_t dim1, f
 int pink_b200_update_factors(uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t func, float p0, float p1,
                              float max_update_distance, float* out);
 
+/* The same two tables for a three-dimensional cartesian SOM of dim0 x dim1 x dim2
+ * neurons (CartesianLayout<3>, CartesianLayout.h:116-123 for the position of an
+ * array index; the command line tool's --som-depth > 1, main_gpu.cu:24-25). */
+int pink_b200_som_distances_3d(uint32_t dim0, uint32_t dim1, uint32_t dim2, float* out);
+int pink_b200_update_factors_3d(uint32_t dim0, uint32_t dim1, uint32_t dim2, uint32_t func, float p0, float p1,
+                                float max_update_distance, float* out);
+
 /* ---- training --------------------------------------------------------------
  * n sequential training steps; image i+1 sees the SOM updated by image i.
  * Stands for n calls of Trainer<...,true>::operator() (Trainer.h:263-304).

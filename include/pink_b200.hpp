@@ -83,6 +83,16 @@ namespace detail {
 template <typename Layout> struct layout_id;
 template <uint8_t dim> struct layout_id<CartesianLayout<dim>> { static constexpr uint32_t value = PINK_B200_LAYOUT_CARTESIAN; };
 template <> struct layout_id<HexagonalLayout> { static constexpr uint32_t value = PINK_B200_LAYOUT_HEXAGONAL; };
+
+/// out[i * N + j] = map distance of neurons i and j
+inline int som_distances(CartesianLayout<1> const& l, float* out)
+{ return pink_b200_som_distances(PINK_B200_LAYOUT_CARTESIAN, l.m_dimension[0], 1, out); }
+inline int som_distances(CartesianLayout<2> const& l, float* out)
+{ return pink_b200_som_distances(PINK_B200_LAYOUT_CARTESIAN, l.m_dimension[0], l.m_dimension[1], out); }
+inline int som_distances(CartesianLayout<3> const& l, float* out)
+{ return pink_b200_som_distances_3d(l.m_dimension[0], l.m_dimension[1], l.m_dimension[2], out); }
+inline int som_distances(HexagonalLayout const& l, float* out)
+{ return pink_b200_som_distances(PINK_B200_LAYOUT_HEXAGONAL, l.m_dimension[0], l.m_dimension[1], out); }
 } // namespace detail
 
 /// one data entry (an image or a neuron)
@@ -258,12 +268,9 @@ public:
     {
         // update factor of neuron j when neuron i is the best matching unit: the distribution function of
         // their map distance, cut off at max_update_distance
-        static_assert(SOMLayout::dimensionality <= 2, "one- and two-dimensional SOM layouts only");
         const uint32_t n = som.get_number_of_neurons();
-        auto&& d = som.get_som_layout().get_dimension();
         std::vector<float> distance(static_cast<size_t>(n) * n);
-        detail::check(pink_b200_som_distances(detail::layout_id<SOMLayout>::value, d.front(),
-            SOMLayout::dimensionality > 1 ? d.back() : 1, distance.data()));
+        detail::check(detail::som_distances(som.get_som_layout(), distance.data()));
         m_update_factors.resize(distance.size());
         for (size_t i = 0; i < distance.size(); ++i)
             m_update_factors[i] = (max_update_distance <= 0 or distance[i] < max_update_distance)

@@ -48,6 +48,8 @@ def _load():
               "pko_mexican_hat", "pko_step"):
         getattr(lib, n).restype = C.c_float
     lib.pko_cartesian_distance.argtypes = [C.c_uint32] * 4
+    lib.pko_cartesian3_distance.restype = C.c_float
+    lib.pko_cartesian3_distance.argtypes = [C.c_uint32] * 5
     lib.pko_hexagonal_distance.argtypes = [C.c_uint32] * 3
     lib.pko_gaussian.argtypes = [C.c_float] * 3
     lib.pko_unity_gaussian.argtypes = [C.c_float] * 3
@@ -201,6 +203,15 @@ def update_factors(layout, dim0, dim1, func, p0, p1=0.0, max_update_distance=-1.
     return F
 
 
+def update_factors_3d(dims, func, p0, p1=0.0, max_update_distance=-1.0):
+    """Factor table of a three-dimensional cartesian SOM with dimensions dims = (dim0, dim1, dim2)."""
+    N = int(np.prod(dims))
+    F = np.empty((N, N), np.float32)
+    lib.pko_update_factors_3d(*[C.c_uint32(int(d)) for d in dims], C.c_int(func), C.c_float(p0), C.c_float(p1),
+                              C.c_float(max_update_distance), _fp(F))
+    return F
+
+
 def _shape(som, img):
     N = som.shape[0]
     Cn = 1 if img.ndim == 2 else img.shape[0]
@@ -299,6 +310,14 @@ def ref_update_factors(layout, dim0, dim1, func, p0, p1=0.0, max_update_distance
     N = dim0 * dim1 if layout == LAYOUT_CARTESIAN else int(lib.pko_hexagonal_size(C.c_uint32(dim0)))
     F = np.empty((N, N), np.float32)
     ref().ref_update_factors(layout, dim0, dim1, func, p0, p1, max_update_distance, _fp(F))
+    return F
+
+
+def ref_update_factors_3d(dims, func, p0, p1=0.0, max_update_distance=-1.0):
+    N = int(np.prod(dims))
+    F = np.empty((N, N), np.float32)
+    ref().ref_update_factors_3d(*[C.c_uint32(int(d)) for d in dims], C.c_int(func), C.c_float(p0), C.c_float(p1),
+                                C.c_float(max_update_distance), _fp(F))
     return F
 
 

@@ -216,6 +216,17 @@ void ref_update_factors(int som_layout, uint32_t s0, uint32_t s1, int func, floa
     }
 }
 
+void ref_update_factors_3d(uint32_t s0, uint32_t s1, uint32_t s2, int func, float p0, float p1, float max_dist, float* F)
+{
+    auto f = make_func(func, p0, p1);
+    CartesianLayout<3> l{{s0, s1, s2}};
+    uint32_t N = l.size();
+    for (uint32_t i = 0; i < N; ++i) for (uint32_t j = 0; j < N; ++j) {
+        float d = l.get_distance(i, j);
+        F[(size_t)i * N + j] = (max_dist <= 0 || d < max_dist) ? f(d) : 0.0f;
+    }
+}
+
 void ref_fill_random_uniform(float* a, uint64_t n, uint32_t seed) { fill_random_uniform(a, n, seed); }
 
 int ref_num_threads() { return omp_get_max_threads(); }

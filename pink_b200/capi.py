@@ -59,6 +59,9 @@ SYMBOLS = {
     "pink_b200_som_distances": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
     "pink_b200_update_factors": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
                                            C.c_float, C.c_void_p]),
+    "pink_b200_som_distances_3d": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
+    "pink_b200_update_factors_3d": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
+                                               C.c_float, C.c_void_p]),
     "pink_b200_operand_stride": (C.c_uint32, [C.c_uint32, C.c_uint32]),
     "pink_b200_op_rotate": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -96,6 +96,51 @@ int pink_b200_som_distances(uint32_t som_layout, uint32_t dim0, uint32_t dim1, f
     return PINK_B200_OK;
 }
 
+int pink_b200_som_distances_3d(uint32_t dim0, uint32_t dim1, uint32_t dim2, float* out)
+{
+    if (!out || dim0 == 0 || dim1 == 0 || dim2 == 0) return PINK_B200_EINVAL;
+    const uint32_t N = dim0 * dim1 * dim2;
+    // the reference's position of an array index, expression by expression
+    auto cell = [&](uint32_t i, uint32_t p[3]) {
+        p[2] = i / dim0 / dim1;
+        p[1] = (i - p[2] * dim0 * dim1) / dim1;
+        p[0] = i % dim1;
+    };
+    for (uint32_t i = 0; i < N; ++i)
+        for (uint32_t j = 0; j < N; ++j) {
+            uint32_t a[3], b[3];
+            cell(i, a);
+            cell(j, b);
+            float d = 0.0f;
+            for (int k = 0; k < 3; ++k) {
+                const float diff = static_cast<float>(a[k]) - static_cast<float>(b[k]);
+                d += static_cast<float>(static_cast<double>(diff) * static_cast<double>(diff));
+            }
+            out[(size_t)i * N + j] = std::sqrt(d);
+        }
+    return PINK_B200_OK;
+}
+
+static int apply_neighbourhood(size_t count, uint32_t func, float p0, float p1, float max_update_distance, float* out)
+{
+    for (size_t i = 0; i < count; ++i) {
+        const float d = out[i];
+        out[i] = (max_update_distance <= 0.0f || d < max_update_distance) ? neighbourhood(func, d, p0, p1) : 0.0f;
+    }
+    return PINK_B200_OK;
+}
+
+int pink_b200_update_factors_3d(uint32_t dim0, uint32_t dim1, uint32_t dim2, uint32_t func, float p0, float p1,
+                                float max_update_distance, float* out)
+{
+    if (func > PINK_B200_FUNC_STEP) return PINK_B200_EINVAL;
+    if (func == PINK_B200_FUNC_MEXICAN_HAT && p0 <= 0.0f) return PINK_B200_EINVAL;
+    int rc = pink_b200_som_distances_3d(dim0, dim1, dim2, out);
+    if (rc) return rc;
+    const size_t N = (size_t)dim0 * dim1 * dim2;
+    return apply_neighbourhood(N * N, func, p0, p1, max_update_distance, out);
+}
+
 int pink_b200_update_factors(uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t func, float p0, float p1,
                              float max_update_distance, float* out)
 {
@@ -104,11 +149,7 @@ int pink_b200_update_factors(uint32_t som_layout, uint32_t dim0, uint32_t dim1, 
     int rc = pink_b200_som_distances(som_layout, dim0, dim1, out);
     if (rc) return rc;
     const size_t N = pink_b200_som_size(som_layout, dim0, dim1);
-    for (size_t i = 0; i < N * N; ++i) {
-        const float d = out[i];
-        out[i] = (max_update_distance <= 0.0f || d < max_update_distance) ? neighbourhood(func, d, p0, p1) : 0.0f;
-    }
-    return PINK_B200_OK;
+    return apply_neighbourhood(N * N, func, p0, p1, max_update_distance, out);
 }
 
 } // extern "C"

@@ -268,7 +268,7 @@ Options parse(int argc, char** argv)
     if (o.som_width < 2) throw std::runtime_error("som-width must be > 1.");
     if (o.som_height < 1) throw std::runtime_error("som-height must be > 0.");
     if (o.som_depth < 1) throw std::runtime_error("som-depth must be > 0.");
-    if (o.som_depth != 1) throw std::runtime_error("three-dimensional SOM layouts are not supported by this program");
+    if (o.som_depth > 1 && o.som_height < 2) throw std::runtime_error("som-depth > 1 needs som-height > 1.");
     return o;
 }
 
@@ -323,10 +323,11 @@ int run(const Options& o)
     }
     if (ed_dim > neuron_dim) throw std::runtime_error("euclidean distance dimension must be equal or smaller than neuron dimension.");
 
-    const uint32_t n_neurons = pink_b200_som_size(o.layout, o.som_width, o.som_height);
+    const uint32_t n_neurons = pink_b200_som_size(o.layout, o.som_width, o.som_height) * o.som_depth;
     if (n_neurons == 0) throw std::runtime_error("the SOM has no neurons");
     std::vector<int> som_dims = {(int)o.som_width};
     if (o.som_height > 1 || o.layout == PINK_B200_LAYOUT_HEXAGONAL) som_dims.push_back((int)o.som_height);
+    if (o.som_depth > 1) som_dims.push_back((int)o.som_depth);
     std::vector<int> neuron_dims;
     if (data.dims.size() == 3) neuron_dims.push_back((int)channels);
     neuron_dims.push_back((int)neuron_dim);
@@ -372,8 +373,12 @@ int run(const Options& o)
 
     if (o.path == Options::TRAIN) {
         std::vector<float> factors((size_t)n_neurons * n_neurons);
-        check(pink_b200_update_factors(o.layout, o.som_width, o.som_height, o.func, o.sigma, o.damping, o.max_update_distance,
-                                       factors.data()));
+        if (o.som_depth > 1)
+            check(pink_b200_update_factors_3d(o.som_width, o.som_height, o.som_depth, o.func, o.sigma, o.damping,
+                                              o.max_update_distance, factors.data()));
+        else
+            check(pink_b200_update_factors(o.layout, o.som_width, o.som_height, o.func, o.sigma, o.damping,
+                                           o.max_update_distance, factors.data()));
         check(pink_b200_set_update_factors(ctx.get(), factors.data()));
         const uint64_t total = (uint64_t)entries * o.iterations;
         Progress progress(total, o.progress_prints);

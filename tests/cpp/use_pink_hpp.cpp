@@ -1,5 +1,5 @@
 // A small program written against the reference's class API (pink::SOM, pink::Data,
-// pink::Trainer<..., float, true>, pink::Mapper<..., float, true>): trains a 3 x 3 map on the
+// pink::Trainer<..., float, true>, pink::Mapper<..., float, true>): trains a 3 x 3 map (and a 2 x 2 x 2 map) on the
 // images of a binary file and prints the trained map, the update counts and the mapping of
 // the first image as text, which the test compares with the CPU oracle.
 #include "pink_b200.hpp"
@@ -54,6 +54,18 @@ int main(int argc, char** argv)
         } catch (pink::exception const& e) {
             std::printf("error %s\n", e.what());
         }
+
+        // a three-dimensional map (2 x 2 x 2 neurons) trained on the first two images
+        typedef CartesianLayout<3> L3;
+        std::vector<float> init3(init.begin(), init.begin() + 8 * nd * nd);
+        SOM<L3, L2, float> som3(L3{{2, 2, 2}}, L2{{nd, nd}}, init3);
+        Trainer<L3, L2, float, true> trainer3(som3, GaussianFunctor(1.1f, 0.2f), 0, rot, true, -1.0f, Interpolation::BILINEAR,
+            ed, EuclideanDistanceShape::QUADRATIC, 256, DataType::UINT8);
+        for (uint32_t i = 0; i < 2 && i < n; ++i) trainer3(images[i]);
+        trainer3.update_som();
+        std::printf("som3");
+        for (size_t i = 0; i < som3.size(); ++i) std::printf(" %08x", *reinterpret_cast<const uint32_t*>(som3.get_data_pointer() + i));
+        std::printf("\n");
         return 0;
     } catch (std::exception const& e) {
         std::fprintf(stderr, "exception: %s\n", e.what());

@@ -39,6 +39,8 @@ CIRCLE_CASES = [  # circular distance region, 2-D data layout: som layout, s0, s
     (0, 3, 3, 32, 22, 16, 8, True, 3), (1, 3, 3, 40, 28, 20, 12, True, 3), (0, 2, 2, 64, 45, 32, 40, True, 2),
     (0, 2, 3, 16, 12, 12, 4, False, 2),
 ]
+FACTOR_3D_CASES = [((2, 2, 2), 0, 1.1, 0.2, -1.0), ((3, 4, 2), 0, 1.1, 0.2, -1.0), ((4, 3, 5), 1, 1.5, 0.3, 2.5),
+                   ((5, 2, 3), 2, 1.3, 0.4, -1.0)]
 FACTOR_CASES = [(0, 3, 4, 0, 1.1, 0.2, -1.0), (0, 10, 10, 0, 1.1, 0.2, 2.5), (1, 7, 7, 0, 2.0, 0.1, -1.0),
                 (1, 11, 11, 0, 3.0, 0.05, -1.0), (0, 5, 5, 2, 1.5, 0.3, -1.0), (0, 4, 4, 3, 1.0, 0.0, -1.0),
                 (0, 6, 3, 1, 1.3, 0.4, -1.0)]
@@ -100,6 +102,11 @@ def main():
         order = np.zeros(n, np.uint32)
         r.ref_shuffled_order(n, seed, 1, order.ctypes.data)
         out["order_%d_%d" % (n, seed)] = order
+    # factor tables of three-dimensional cartesian SOMs (CartesianLayout<3>)
+    for i, (dims, func, p0, p1, md) in enumerate(FACTOR_3D_CASES):
+        out["fac3d%d_cfg" % i] = np.array(list(dims) + [func])
+        out["fac3d%d_par" % i] = np.array([p0, p1, md], np.float32)
+        out["fac3d%d_out" % i] = O.ref_update_factors_3d(dims, func, p0, p1, md)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_cpu.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")

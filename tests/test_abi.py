@@ -76,6 +76,22 @@ def test_host_update_factor_table_bit_exact(case):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("case", [((2, 2, 2), 0, 1.1, 0.2, -1.0), ((3, 4, 2), 0, 1.1, 0.2, 1.8), ((4, 3, 5), 2, 1.5, 0.3, -1.0),
+                                  ((6, 5, 4), 1, 2.0, 0.1, -1.0)])
+def test_host_update_factor_table_of_3d_soms_bit_exact(case):
+    dims, func, p0, p1, md = case
+    N = int(np.prod(dims))
+    got = np.empty((N, N), np.float32)
+    capi.check(capi.lib.pink_b200_update_factors_3d(*dims, func, p0, p1, md, got.ctypes.data))
+    want = O.update_factors_3d(dims, func, p0, p1, md)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    dist = np.empty((N, N), np.float32)
+    capi.check(capi.lib.pink_b200_som_distances_3d(*dims, dist.ctypes.data))
+    i, j = N - 1, 0
+    assert dist[i, j] == np.float32(O.lib.pko_cartesian3_distance(i, j, *dims))
+    assert capi.lib.pink_b200_update_factors_3d(0, 1, 1, 0, 1.0, 1.0, -1.0, got.ctypes.data) == capi.EINVAL
+
+
 def test_som_size_and_operand_stride():
     assert engine.som_size(capi.LAYOUT_HEXAGONAL, 61, 61) == 2791          # radius 30
     assert engine.som_size(capi.LAYOUT_CARTESIAN, 20, 20) == 400

@@ -76,3 +76,9 @@ def test_option_errors(pink, tmp_path):
     assert r.returncode != 0 and "Unknown execution path" in r.stderr
     r = subprocess.run([pink, "--train", str(tmp_path / "missing.bin"), "x"], capture_output=True, text=True)
     assert r.returncode != 0 and "Error opening" in r.stderr
+    r = subprocess.run([pink, "--layout", "hexagonal", "--som-width", "3", "--som-height", "3", "--som-depth", "2",
+                        "--train", "a", "b"], capture_output=True, text=True)
+    assert r.returncode != 0 and "For hexagonal layout som-depth must be equal to 1." in r.stderr
+    r = subprocess.run([pink, "--som-width", "3", "--som-height", "1", "--som-depth", "2", "--train", "a", "b"],
+                       capture_output=True, text=True)
+    assert r.returncode != 0 and "som-depth > 1 needs som-height > 1." in r.stderr

@@ -86,3 +86,27 @@ def test_hexagonal_map_from_file_init(cuda, tmp_path):
     got, dims, header = files.read_som_file(out)
     assert dims == [3, 3] and header == "# header kept\n# END OF HEADER\n"
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_three_dimensional_map(cuda, tmp_path):
+    """--som-depth > 1: a cartesian map of 3 x 2 x 2 neurons; the files carry three SOM dimensions."""
+    n, idim, nd, ed, R, dims, seed = 7, 16, 12, 7, 8, (3, 2, 2), 5
+    imgs = blob_images(n, idim, 1, seed=8).reshape(n, idim, idim)
+    data, som_path, map_path = (str(tmp_path / f) for f in ("data.bin", "som.bin", "map.bin"))
+    files.write_data_file(data, imgs)
+    common = ["--som-width", dims[0], "--som-height", dims[1], "--som-depth", dims[2], "--numrot", R, "-d", nd, "-e", ed,
+              "--seed", seed, "--euclidean-distance-type", "uint8"]
+    _run(*common, "--input-shuffle-off", "--init", "random", "--train", data, som_path)
+    N = int(np.prod(dims))
+    want = mt19937_uniform(N * nd * nd, seed).reshape(N, 1, nd, nd).copy()
+    F = O.update_factors_3d(dims, O.FUNC_GAUSSIAN, 1.1, 0.2)
+    for im in imgs:
+        O.train_step(want, im.reshape(1, idim, idim), F, ed, R, True, O.MODE_U8)
+    got, som_dims, _ = files.read_som_file(som_path)
+    assert som_dims == list(dims) and got.shape == (N, nd, nd)
+    assert np.array_equal(got.reshape(want.shape).view(np.uint32), want.view(np.uint32))
+    _run(*common, "--map", data, map_path, som_path)
+    dist, mdims = files.read_mapping_file(map_path)
+    assert mdims == list(dims) and dist.shape == (n, N)
+    wd, _ = O.map_image(want, imgs[0].reshape(1, idim, idim), ed, R, True, O.MODE_U8)
+    assert np.array_equal(dist[0].view(np.uint32), wd.view(np.uint32))

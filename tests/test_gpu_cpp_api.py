@@ -46,3 +46,8 @@ def test_program_against_the_class_api(cuda, tmp_path):
     assert np.array_equal(np.array([int(v, 16) for v in out["dist"]], np.uint32), wd.view(np.uint32))
     assert [int(v) for v in out["rot"]] == list(wr)
     assert error == "error Number of rotations must be 1 or larger then 1 and divisible by 4"
+    want3 = som0[:8].copy()
+    F3 = O.update_factors_3d((2, 2, 2), O.FUNC_GAUSSIAN, 1.1, 0.2)
+    for im in imgs[:2]:
+        O.train_step(want3, im.reshape(1, idim, idim), F3, ed, R, True, O.MODE_U8)
+    assert np.array_equal(np.array([int(v, 16) for v in out["som3"]], np.uint32), want3.view(np.uint32).ravel())

@@ -243,6 +243,13 @@ def test_update_factors_match_reference(i):
     assert np.array_equal(bits(O.update_factors(lay, d0, d1, func, p0, p1, md)), bits(GOLD["fac%d_out" % i]))
 
 
+@pytest.mark.parametrize("i", range(4))
+def test_update_factors_of_3d_soms_match_reference(i):
+    *dims, func = (int(v) for v in GOLD["fac3d%d_cfg" % i])
+    p0, p1, md = (float(v) for v in GOLD["fac3d%d_par" % i])
+    assert np.array_equal(bits(O.update_factors_3d(dims, func, p0, p1, md)), bits(GOLD["fac3d%d_out" % i]))
+
+
 @pytest.mark.skipif(not O.have_ref(), reason="reference-linked checker not built here")
 def test_live_reference_agrees_on_fresh_seed():
     """Where the reference-linked library exists, also compare on inputs that are not in the fixture."""

@@ -200,6 +200,7 @@ struct pink_b200_ctx
     // Rotation sets computed in shares (world_size > 1 with peer memory): every rank rotates its part of a
     // batch of images and copies the results into all ranks' transform buffers, which hold three batches.
     bool rot_shared = false;
+    uint32_t share_group = 0;                              // ranks that share one batch's rotation work (consecutive ranks)
     cudaStream_t bcast_stream = nullptr, peer_stream[kXchgMaxRanks] = {};   // one copy stream per destination rank, joined on bcast_stream
     cudaEvent_t share_rotated = nullptr, bcast_done[3] = { nullptr, nullptr, nullptr }, peer_sent[kXchgMaxRanks] = {};
     unsigned long long* d_rotflag = nullptr;               // [3 batches][world]: batch number + 1 of the share that arrived
@@ -407,6 +408,8 @@ static int train_chunk_shared(pink_b200_ctx* c, const float* d_images, uint64_t 
 {
     const Geometry& g = c->g;
     const uint32_t W = c->cfg.world_size, rank = c->cfg.rank;
+    // the ranks sharing with this one: [g0, g0 + G), this rank the gr-th of them
+    const uint32_t g0 = rank / c->share_group * c->share_group, G = std::min(c->share_group, W - g0), gr = rank - g0;
     const size_t esz = g.mode == kModeF32 ? 4 : 1, isz = c->image_size(), nbase = g.q ? g.q : 1;
     const size_t base_img = nbase * (size_t)g.P * sizeof(float), op_img = (size_t)g.T * g.Kp * esz;
     const size_t norm_img = (size_t)g.T * (g.mode == kModeU16 ? 8 : 4);
@@ -417,7 +420,7 @@ static int train_chunk_shared(pink_b200_ctx* c, const float* d_images, uint64_t 
         const uint32_t ring = (uint32_t)(seq % 3);
         const size_t slot = (size_t)ring * kRotBatch;
         const uint32_t cnt = (uint32_t)std::min<uint64_t>(kRotBatch, m - b * kRotBatch);
-        const uint32_t per = (cnt + W - 1) / W, lo = std::min(rank * per, cnt), hi = std::min(lo + per, cnt);
+        const uint32_t per = (cnt + G - 1) / G, lo = std::min(gr * per, cnt), hi = std::min(lo + per, cnt);
         // the copies that last read this part of the buffers (three batches ago) are over
         CU_TRY(cudaStreamWaitEvent(c->stream, c->bcast_done[ring], 0));
         if (hi > lo) {
@@ -439,7 +442,7 @@ static int train_chunk_shared(pink_b200_ctx* c, const float* d_images, uint64_t 
         // one stream per destination, so that the copies to different ranks use different copy engines and
         // links at the same time; a destination's flag follows its copies in its stream
         CU_TRY(cudaEventRecord(c->share_rotated, c->stream));
-        for (uint32_t p = 0; p < W; ++p) {
+        for (uint32_t p = g0; p < g0 + G; ++p) {
             if (p == rank) continue;
             cudaStream_t ps = c->peer_stream[p];
             CU_TRY(cudaStreamWaitEvent(ps, c->share_rotated, 0));
@@ -475,7 +478,7 @@ static int train_chunk_shared(pink_b200_ctx* c, const float* d_images, uint64_t 
         // update kernel fills every SM while it waits for the other ranks' records, and they wait for this
         // flag -- whose kernel could then find no SM to run on.
         CU_TRY(cudaStreamWaitEvent(c->stream, c->bcast_done[ring], 0));
-        LAUNCH_TRY(launch_flag_wait(c->d_rotflag + ring * W, W, rank, seq + 1, c->d_status, c->stream));
+        LAUNCH_TRY(launch_flag_wait(c->d_rotflag + ring * W + g0, G, gr, seq + 1, c->d_status, c->stream));
         c->launches += 1;
         for (uint32_t i = 0; i < cnt; ++i) {
             rc = train_step(c, (size_t)ring * kRotBatch + i, log + b * kRotBatch + i);
@@ -540,8 +543,18 @@ int setup_peer_exchange(pink_b200_ctx* c)
     // batch if that is larger) because the other ranks map them.  On by default for two ranks only: measured
     // on eight B200 the copies (164 MB per rank and batch in each direction) slow the other kernels down by
     // more than the saved rotation work (18.4 k against 23.7 k images/s), on two it gains 6 %.
-    // PINK_B200_SHARED_ROTATION forces it on, PINK_B200_REPLICATED_ROTATION off (diagnostic switches).
-    mine.share = mine.want && !getenv("PINK_B200_REPLICATED_ROTATION") && (W <= 2 || getenv("PINK_B200_SHARED_ROTATION"));
+    // PINK_B200_SHARED_ROTATION=<g> makes groups of g consecutive ranks share (0 or 1: all ranks),
+    // PINK_B200_REPLICATED_ROTATION switches it off (diagnostic switches).  `share` carries the group size.
+    uint32_t group = 0;
+    if (mine.want && !getenv("PINK_B200_REPLICATED_ROTATION")) {
+        if (const char* e = getenv("PINK_B200_SHARED_ROTATION")) {
+            const long v = std::atol(e);
+            group = v >= 2 ? (uint32_t)std::min<long>(v, W) : W;
+        } else if (W <= 2) {
+            group = W;
+        }
+    }
+    mine.share = group;
     if (mine.share) {
         const size_t imgs = std::max<size_t>(3 * kRotBatch, c->map_batch);
         int rc0 = ensure_transform_buffers(c, imgs, 3 * kRotBatch);
@@ -566,7 +579,7 @@ int setup_peer_exchange(pink_b200_ctx* c)
     bool ok = true, share = true;
     for (uint32_t r = 0; r < W; ++r) {
         ok = ok && all[r].want;
-        share = share && all[r].share;
+        share = share && all[r].share == group && group >= 2;
         for (uint32_t q = 0; q < r; ++q) ok = ok && std::strncmp(all[r].bus, all[q].bus, sizeof(mine.bus)) != 0;
     }
     share = share && ok;
@@ -601,11 +614,12 @@ int setup_peer_exchange(pink_b200_ctx* c)
         }
     }
     mine.ok = ok;
-    mine.share = share;
+    mine.share = share ? group : 0;
     rc = gather();                                          // all ranks must agree on the way they exchange
     cudaFree(d_all);
     if (rc) return rc;
-    for (uint32_t r = 0; r < W; ++r) { ok = ok && all[r].ok; share = share && all[r].share; }
+    for (uint32_t r = 0; r < W; ++r) { ok = ok && all[r].ok; share = share && all[r].share == group; }
+    c->share_group = group;
     c->xchg_on = ok;
     if (!ok) { release_peer_exchange(c); return PINK_B200_OK; }
     c->rot_shared = share && ok;

@@ -540,9 +540,11 @@ int setup_peer_exchange(pink_b200_ctx* c)
         if (cudaDeviceGetPCIBusId(mine.bus, sizeof(mine.bus), c->cfg.device) != cudaSuccess) { cudaGetLastError(); mine.want = 0; }
     }
     // Shared rotation: the transform buffers get their final size now (three training batches, or the mapping
-    // batch if that is larger) because the other ranks map them.  On by default for two ranks only: measured
-    // on eight B200 the copies (164 MB per rank and batch in each direction) slow the other kernels down by
-    // more than the saved rotation work (18.4 k against 23.7 k images/s), on two it gains 6 %.
+    // batch if that is larger) because the other ranks map them.  By default pairs of consecutive ranks share:
+    // measured on eight B200, pairs gain 7 % over every rank rotating everything (25.4 k against 23.8 k
+    // images/s) and on two B200 6 %, while sharing among all eight loses (18.4 k): the copies to seven
+    // destinations (164 MB per rank and batch in each direction) slow the other kernels down by more than the
+    // rotation work they save.
     // PINK_B200_SHARED_ROTATION=<g> makes groups of g consecutive ranks share (0 or 1: all ranks),
     // PINK_B200_REPLICATED_ROTATION switches it off (diagnostic switches).  `share` carries the group size.
     uint32_t group = 0;
@@ -550,8 +552,8 @@ int setup_peer_exchange(pink_b200_ctx* c)
         if (const char* e = getenv("PINK_B200_SHARED_ROTATION")) {
             const long v = std::atol(e);
             group = v >= 2 ? (uint32_t)std::min<long>(v, W) : W;
-        } else if (W <= 2) {
-            group = W;
+        } else {
+            group = std::min<uint32_t>(W, 2);
         }
     }
     mine.share = group;

@@ -109,6 +109,21 @@ int pink_b200_shard(const pink_b200_ctx* ctx, uint32_t* first, uint32_t* count);
 /* The same split as a pure host function (no context, no GPU). */
 int pink_b200_shard_range(uint32_t n_neurons, uint32_t world_size, uint32_t rank, uint32_t* first, uint32_t* count);
 
+/* Switches of a context, to be set after pink_b200_create and before pink_b200_comm_init /
+ * pink_b200_set_som (no reference counterpart: the reference has one fixed launch sequence).  Unknown
+ * names and values out of range return PINK_B200_EINVAL.
+ *   "step_kernel"          0 (default) whole batches of training steps in one persistent kernel where the
+ *                          geometry allows it; 1 two kernels per image (distance, update); 2 four kernels
+ *                          per image (distance, best matching unit, work list, update)
+ *   "exchange"             0 (default) per-rank records through peer memory where possible; 1 NCCL all-gather
+ *   "rotation_sharing"     -1 (default) pairs of ranks share the rotation work; 0 every rank rotates every
+ *                          image; g >= 2 groups of g consecutive ranks share
+ *   "rotation_overlap"     1 puts the rotation kernels on a second, low-priority stream (default 0)
+ *   "mma_pairs"            0 keeps the distance kernel from pairing blocks (default 1)
+ *   "exchange_timeout_ms"  wall-clock limit of every device-side wait for another rank (default 20000).  The
+ *                          ranks must enqueue each batch of steps within this time of one another. */
+int pink_b200_set_option(pink_b200_ctx* ctx, const char* name, long long value);
+
 /* ---- multi-GPU: one process per GPU, neuron shards, NCCL for the BMU exchange
  * (replaces the per-image cudaMemcpyPeer traffic of
  *  src/CudaLib/generate_euclidean_distance_matrix_first_step_multi_gpu.h:87-104,184-193). */
@@ -214,6 +229,13 @@ int pink_b200_get_update_stats(pink_b200_ctx* ctx, uint64_t* out);
  * use it to apportion time between kernels, not to measure throughput. */
 int pink_b200_profile_begin(pink_b200_ctx* ctx, uint32_t max_steps);
 int pink_b200_profile_end(pink_b200_ctx* ctx, double ms_sum[4], uint64_t* steps);
+/* After profile_end, for a context that trains with the persistent kernel (all zeros otherwise):
+ * out[0] = mean device time of one launch in microseconds (CUDA events), out[1] = mean images per launch,
+ * out[2..6] = mean microseconds per image, read from device-timer stamps of block 0, of: its own distance
+ * tiles (TMA + MMA + epilogue), waiting for the other blocks at the first grid barrier, best matching unit
+ * (+ exchange between ranks) and work list, rewriting its own neurons, waiting at the second grid barrier;
+ * out[7] unused. */
+int pink_b200_profile_detail(pink_b200_ctx* ctx, double out[8]);
 
 /* ---- single stages on device buffers (what the context calls internally) ---
  * Exposed for kernel-level parity tests and benchmarks.  `stream` is a
@@ -245,8 +267,10 @@ int pink_b200_op_rotate(const pink_b200_config* cfg, const float* dev_images, ui
  * call) lives in a fixed 32 KB device array inside the library, held by every GPU
  * that loads it until the process exits.  Limits and rules:
  *   - at most 16384 rotations (4096 per quadrant); more returns PINK_B200_EINVAL;
- *   - the first call on a device looks up the array's device address; make that
- *     first call before any stream capture begins;
+ *   - the first call on a device (and for each distance type) looks up the array's device address and
+ *     loads the kernel; that first call may allocate inside the CUDA driver (module loading), so make one
+ *     warm-up call per device and distance type before entering a region where allocation is forbidden;
+ *     only later calls are allocation-free;
  *   - all calls share the one array (each overwrites the part it uses), so two
  *     calls whose GPU work may overlap -- different streams or host threads --
  *     race; serialise them.  The call returns after its work on `stream` is done. */

@@ -37,6 +37,7 @@ SYMBOLS = {
     "pink_b200_shard": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     "pink_b200_shard_range": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32),
                                         C.POINTER(C.c_uint32)]),
+    "pink_b200_set_option": (C.c_int, [C.c_void_p, C.c_char_p, C.c_longlong]),
     "pink_b200_comm_unique_id": (C.c_int, [C.c_void_p]),
     "pink_b200_comm_init": (C.c_int, [C.c_void_p, C.c_void_p]),
     "pink_b200_set_som": (C.c_int, [C.c_void_p, C.c_void_p]),
@@ -55,6 +56,7 @@ SYMBOLS = {
     "pink_b200_get_update_stats": (C.c_int, [C.c_void_p, C.c_void_p]),
     "pink_b200_profile_begin": (C.c_int, [C.c_void_p, C.c_uint32]),
     "pink_b200_profile_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
+    "pink_b200_profile_detail": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
     "pink_b200_som_size": (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32]),
     "pink_b200_som_distances": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
     "pink_b200_update_factors": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,

@@ -212,6 +212,21 @@ struct pink_b200_ctx
     unsigned long long* d_stats = nullptr;   // [0] neurons with a non-zero factor, [1] neurons written back, summed over steps
     uint64_t launches = 0;            // kernels launched by this context so far
     bool fuse_update = false;         // the update kernel finds the best matching unit and its work list itself
+    // Whole batches of training steps in one persistent kernel (train_steps.cu) where the geometry allows it.
+    bool plan_ok = false;             // the persistent kernel can run this geometry
+    bool use_steps = false;           // ... and this context uses it (decided when training starts)
+    StepPlan plan{};
+    uint32_t* d_owners = nullptr;     // [plan.grid][plan.owned_per_block]: which block rewrites which neuron
+    StepCtrl* d_ctrl = nullptr;
+    unsigned long long* d_stamps = nullptr; size_t stamps_cap = 0;   // opt-in device-timer stamps, 8 per profiled step
+    std::vector<cudaEvent_t> prof_launch_events; size_t prof_launches = 0, prof_launch_images = 0;
+    // switches (pink_b200_set_option)
+    int opt_step_kernel = 0;          // 0 persistent kernel where possible, 1 two kernels per image, 2 split update path
+    int opt_exchange = 0;             // 0 peer memory where possible, 1 NCCL all-gather
+    int opt_rotation_sharing = -1;    // -1 pairs of ranks, 0 every rank rotates everything, g >= 2 groups of g ranks
+    int opt_mma_pairs = 1;
+    long long opt_exchange_timeout_ms = 20000;
+    bool failed = false;              // a device-side wait expired: the map may be inconsistent, training is refused
     uint32_t* d_counts = nullptr;
     uint32_t* d_bmu_log = nullptr; size_t bmu_log_cap = 0, bmu_log_n = 0;
     int* d_status = nullptr;
@@ -281,13 +296,15 @@ int check_status(pink_b200_ctx* c)
     CU_TRY(cudaMemcpyAsync(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
     if (st != kDevOk) {
-        cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream);
+        // Sticky: the steps after the expired wait ran on whatever state it left, and with several ranks
+        // the exchange counters no longer agree.  The context only answers get_som / destroy from here on.
+        c->failed = true;
         return fail(PINK_B200_ETIMEOUT, "a bounded device-side wait expired (code " + std::to_string(st) + ")");
     }
     return PINK_B200_OK;
 }
 
-constexpr uint32_t kRotBatch = 16;
+constexpr uint32_t kRotBatch = kStepBatchMax;
 
 // One training step on image `slot_img` of the transform buffers (its rotation
 // set is already there): distance + minimum over transforms, best matching
@@ -305,7 +322,7 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     da.b1 = c->d_b1 ? static_cast<uint8_t*>(c->d_b1) + row0 * g.Kp * esz : nullptr;
     da.bnorm = static_cast<uint8_t*>(c->d_bnorm) + row0 * (g.mode == kModeU16 ? 8 : 4);
     da.n_img = 1;
-    da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status;
+    da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status; da.single_cta = !c->opt_mma_pairs;
     BmuArgs ba{};
     ba.keys = c->d_keys; ba.n = c->count; ba.first_neuron = c->first; ba.shift = key_shift(g.mode);
     ba.pairs = c->d_pairs; ba.rank = c->cfg.rank; ba.world = c->cfg.world_size;
@@ -317,6 +334,7 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     ba.arrive = c->d_nitems + 1;
     ba.stats = c->d_stats;
     ba.status = c->d_status;
+    ba.xchg_timeout_ns = (unsigned long long)std::max<long long>(1, c->opt_exchange_timeout_ms) * 1000000ull;
     // Fused form: the update kernel reduces the keys (or the exchanged records) and derives its
     // work list itself; otherwise a reduction and a compaction kernel run in between.
     const bool fused = c->fuse_update;
@@ -358,12 +376,57 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     return PINK_B200_OK;
 }
 
+// cnt (<= kRotBatch) consecutive training steps on the images whose rotation sets start at image `slot_img`
+// of the transform buffers, in one launch of the persistent kernel.
+int train_steps_batch(pink_b200_ctx* c, size_t slot_img, uint32_t cnt, uint32_t* bmu_slots)
+{
+    const Geometry& g = c->g;
+    StepArgs a{};
+    a.a0 = c->d_a0; a.a1 = c->d_a1; a.anorm = c->d_anorm; a.n = c->count;
+    a.b0 = c->d_b0; a.b1 = c->d_b1; a.bnorm = c->d_bnorm;
+    a.b_rows = (uint32_t)(c->b_imgs * g.T);
+    a.b_row0 = (uint32_t)(slot_img * g.T);
+    a.keys = c->d_keys;
+    a.som = c->d_som;
+    a.base = c->d_base + slot_img * (g.q ? g.q : 1) * (size_t)g.P;
+    a.wrange = c->d_wrange;
+    a.rmax = c->d_wrange ? c->d_rmax + slot_img : nullptr;
+    a.factors = c->d_factors;
+    a.owners = c->d_owners;
+    a.n_img = cnt; a.first_neuron = c->first; a.rank = c->cfg.rank; a.world = c->cfg.world_size;
+    a.counts = c->d_counts; a.bmu_log = bmu_slots; a.stats = c->d_stats; a.status = c->d_status;
+    a.ctrl = c->d_ctrl;
+    a.stamps = nullptr;
+    if (c->cfg.world_size > 1) {
+        a.xchg_local = c->d_xchg;
+        for (uint32_t r = 0; r < c->cfg.world_size; ++r) a.xchg_peer[r] = c->xchg_peer[r];
+        a.xchg_seq0 = c->xchg_seq + 1;
+        c->xchg_seq += cnt;
+    }
+    a.xchg_timeout_ns = (unsigned long long)std::max<long long>(1, c->opt_exchange_timeout_ms) * 1000000ull;
+    cudaEvent_t* ev = nullptr;
+    if (c->prof_used < c->prof_cap) {
+        if (c->d_stamps && c->prof_used + cnt <= c->stamps_cap) a.stamps = c->d_stamps + 8 * c->prof_used;
+        if (2 * (c->prof_launches + 1) <= c->prof_launch_events.size()) ev = &c->prof_launch_events[2 * c->prof_launches];
+        c->prof_used += std::min<size_t>(cnt, c->prof_cap - c->prof_used);
+    }
+    CU_TRY(cudaMemsetAsync(c->d_ctrl, 0xFF, sizeof(StepCtrl), c->stream));
+    if (ev) CU_TRY(cudaEventRecord(ev[0], c->stream));
+    const char* why = "";
+    cudaError_t e = launch_train_steps(g, c->plan, a, c->stream, &why);
+    if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
+    if (ev) { CU_TRY(cudaEventRecord(ev[1], c->stream)); c->prof_launches += 1; c->prof_launch_images += cnt; }
+    c->launches += 1;
+    return PINK_B200_OK;
+}
+
 // m sequential steps over images resident on the device.  `ready` (nullable) is
 // an event the rotation stream must wait for before reading the images.
 static int train_chunk_shared(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* log, cudaEvent_t ready);
 
 int train_chunk(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* log, cudaEvent_t ready)
 {
+    if (m == 0) return PINK_B200_OK;
     if (c->rot_shared) return train_chunk_shared(c, d_images, m, log, ready);
     const Geometry& g = c->g;
     const size_t esz = g.mode == kModeF32 ? 4 : 1, isz = c->image_size();
@@ -388,9 +451,14 @@ int train_chunk(pink_b200_ctx* c, const float* d_images, uint64_t m, uint32_t* l
         if (ev) CU_TRY(cudaEventRecord(ev[1], c->rot_stream));
         CU_TRY(cudaEventRecord(c->rotated[slot ? 1 : 0], c->rot_stream));
         CU_TRY(cudaStreamWaitEvent(c->stream, c->rotated[slot ? 1 : 0], 0));
-        for (uint32_t i = 0; i < cnt; ++i) {
-            int rc = train_step(c, slot + i, log + s0 + i);
+        if (c->use_steps) {
+            int rc = train_steps_batch(c, slot, cnt, log + s0);
             if (rc) return rc;
+        } else {
+            for (uint32_t i = 0; i < cnt; ++i) {
+                int rc = train_step(c, slot + i, log + s0 + i);
+                if (rc) return rc;
+            }
         }
         CU_TRY(cudaEventRecord(c->rot_free[slot ? 1 : 0], c->stream));
     }
@@ -478,11 +546,17 @@ static int train_chunk_shared(pink_b200_ctx* c, const float* d_images, uint64_t 
         // update kernel fills every SM while it waits for the other ranks' records, and they wait for this
         // flag -- whose kernel could then find no SM to run on.
         CU_TRY(cudaStreamWaitEvent(c->stream, c->bcast_done[ring], 0));
-        LAUNCH_TRY(launch_flag_wait(c->d_rotflag + ring * W + g0, G, gr, seq + 1, c->d_status, c->stream));
+        LAUNCH_TRY(launch_flag_wait(c->d_rotflag + ring * W + g0, G, gr, seq + 1, c->d_status,
+                                    (unsigned long long)std::max<long long>(1, c->opt_exchange_timeout_ms) * 1000000ull, c->stream));
         c->launches += 1;
-        for (uint32_t i = 0; i < cnt; ++i) {
-            rc = train_step(c, (size_t)ring * kRotBatch + i, log + b * kRotBatch + i);
+        if (c->use_steps) {
+            rc = train_steps_batch(c, (size_t)ring * kRotBatch, cnt, log + b * kRotBatch);
             if (rc) return rc;
+        } else {
+            for (uint32_t i = 0; i < cnt; ++i) {
+                rc = train_step(c, (size_t)ring * kRotBatch + i, log + b * kRotBatch + i);
+                if (rc) return rc;
+            }
         }
     }
     c->share_seq += batches;
@@ -520,7 +594,7 @@ void release_peer_exchange(pink_b200_ctx* c)
 // and each rank maps the other ranks' arrays.  The exchange is switched on only if every
 // rank could map every array and no two ranks share a GPU (a kernel that waits for a peer's
 // record must never share its GPU with the kernel that writes it); otherwise the per-step
-// NCCL all-gather stays in use.  PINK_B200_NCCL_EXCHANGE (diagnostic switch) keeps NCCL too.
+// NCCL all-gather stays in use.  Option "exchange" = 1 keeps NCCL too.
 int setup_peer_exchange(pink_b200_ctx* c)
 {
     const uint32_t W = c->cfg.world_size, rank = c->cfg.rank;
@@ -530,7 +604,8 @@ int setup_peer_exchange(pink_b200_ctx* c)
     std::vector<Hello> all(W);
     Hello* d_all = nullptr;
     // (distance codes must leave room for the 8-bit tag of a record word: 65535^2 * K < 2^56)
-    mine.want = W <= kXchgMaxRanks && c->fuse_update && c->g.K < (1u << 24) && !getenv("PINK_B200_NCCL_EXCHANGE");
+    mine.want = W <= kXchgMaxRanks && (c->fuse_update || (c->plan_ok && c->opt_step_kernel == 0)) && c->g.K < (1u << 24)
+                && c->opt_exchange == 0;
     if (mine.want) {
         const size_t bytes = (size_t)kXchgSlots * W * sizeof(XchgRecord);
         CU_TRY(cudaMalloc(&c->d_xchg, bytes));
@@ -545,17 +620,11 @@ int setup_peer_exchange(pink_b200_ctx* c)
     // images/s) and on two B200 6 %, while sharing among all eight loses (18.4 k): the copies to seven
     // destinations (164 MB per rank and batch in each direction) slow the other kernels down by more than the
     // rotation work they save.
-    // PINK_B200_SHARED_ROTATION=<g> makes groups of g consecutive ranks share (0 or 1: all ranks),
-    // PINK_B200_REPLICATED_ROTATION switches it off (diagnostic switches).  `share` carries the group size.
+    // Option "rotation_sharing" (pink_b200_set_option): g >= 2 makes groups of g consecutive ranks share,
+    // 0 switches sharing off, -1 is this default.  `share` carries the group size.
     uint32_t group = 0;
-    if (mine.want && !getenv("PINK_B200_REPLICATED_ROTATION")) {
-        if (const char* e = getenv("PINK_B200_SHARED_ROTATION")) {
-            const long v = std::atol(e);
-            group = v >= 2 ? (uint32_t)std::min<long>(v, W) : W;
-        } else {
-            group = std::min<uint32_t>(W, 2);
-        }
-    }
+    if (mine.want && c->opt_rotation_sharing != 0)
+        group = c->opt_rotation_sharing >= 2 ? (uint32_t)std::min<long>(c->opt_rotation_sharing, W) : std::min<uint32_t>(W, 2);
     mine.share = group;
     if (mine.share) {
         const size_t imgs = std::max<size_t>(3 * kRotBatch, c->map_batch);
@@ -641,12 +710,16 @@ int setup_peer_exchange(pink_b200_ctx* c)
 
 int train_prepare(pink_b200_ctx* c, uint64_t n)
 {
+    if (c->failed)
+        return fail(PINK_B200_ESTATE, "an earlier device-side wait expired; the context no longer trains (read the map back or destroy it)");
     if (!c->have_som) return fail(PINK_B200_ESTATE, "pink_b200_set_som must be called before training");
     if (!c->have_factors) return fail(PINK_B200_ESTATE, "pink_b200_set_update_factors must be called before training");
     if (c->cfg.world_size > 1 && !c->comm)
         return fail(PINK_B200_ESTATE, "pink_b200_comm_init must be called before training with world_size > 1");
     int rc = ensure_transform_buffers(c, 2 * kRotBatch, 2 * kRotBatch);
     if (rc) return rc;
+    // the persistent kernel exchanges the ranks' records itself, through peer memory only
+    c->use_steps = c->plan_ok && c->opt_step_kernel == 0 && c->d_owners && (c->cfg.world_size == 1 || c->xchg_on);
     if (c->bmu_log_cap < n) {
         free_dev(c->d_bmu_log);
         CU_TRY(cudaMalloc(&c->d_bmu_log, n * sizeof(uint32_t)));
@@ -726,12 +799,16 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
         CTX_TRY(cudaStreamCreateWithPriority(&c->copy_stream, cudaStreamNonBlocking, hi));
         // The rotation kernels (16 images ahead) run on the training stream: on a stream of their own
         // their blocks keep the other kernels' blocks, which need a whole SM each, from starting, and the
-        // step gets slower (measured).  Diagnostic switches: PINK_B200_ROT_OVERLAP puts them on a second,
-        // low-priority stream anyway; PINK_B200_SPLIT_UPDATE keeps best-matching-unit reduction and work
-        // list in kernels of their own.
-        c->fuse_update = update_can_fuse(c->g) && !getenv("PINK_B200_SPLIT_UPDATE");
-        if (!getenv("PINK_B200_ROT_OVERLAP")) c->rot_stream = c->stream;
-        else CTX_TRY(cudaStreamCreateWithPriority(&c->rot_stream, cudaStreamNonBlocking, lo));
+        // step gets slower (measured).  Option "rotation_overlap" puts them on a second, low-priority
+        // stream anyway; option "step_kernel" selects the older launch sequences.
+        c->fuse_update = update_can_fuse(c->g);
+        c->rot_stream = c->stream;
+        const char* why_not = "";
+        c->plan_ok = step_plan(c->g, c->count, N, &c->plan, &why_not);
+        if (c->plan_ok) {
+            CTX_TRY(cudaMalloc(&c->d_ctrl, sizeof(StepCtrl)));
+            CTX_TRY(cudaMalloc(&c->d_owners, (size_t)c->plan.grid * c->plan.owned_per_block * sizeof(uint32_t)));
+        }
     }
     for (int i = 0; i < 2; ++i) {
         CTX_TRY(cudaEventCreateWithFlags(&c->copied[i], cudaEventDisableTiming));
@@ -813,7 +890,8 @@ int pink_b200_destroy(pink_b200_ctx* c)
     free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_base);
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
     free_dev(c->d_items); free_dev(c->d_nitems); free_dev(c->d_stats); free_dev(c->d_wrange); free_dev(c->d_rmax);
-    free_dev(c->d_circle);
+    free_dev(c->d_circle); free_dev(c->d_owners); free_dev(c->d_ctrl); free_dev(c->d_stamps);
+    for (cudaEvent_t e : c->prof_launch_events) cudaEventDestroy(e);
     free_dev(c->d_pairs); free_dev(c->d_counts); free_dev(c->d_bmu_log); free_dev(c->d_status);
     free_dev(c->d_images[0]); free_dev(c->d_images[1]); free_dev(c->d_dist); free_dev(c->d_rot);
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
@@ -843,6 +921,40 @@ int pink_b200_shard(const pink_b200_ctx* c, uint32_t* first, uint32_t* count)
     if (!c) return fail(PINK_B200_EINVAL, "null context");
     if (first) *first = c->first;
     if (count) *count = c->count;
+    return PINK_B200_OK;
+}
+
+int pink_b200_set_option(pink_b200_ctx* c, const char* name, long long value)
+{
+    if (!c || !name) return fail(PINK_B200_EINVAL, "null argument");
+    if (c->have_som || c->comm)
+        return fail(PINK_B200_ESTATE, "options must be set before pink_b200_comm_init and pink_b200_set_som");
+    const std::string key(name);
+    if (key == "step_kernel") {
+        if (value < 0 || value > 2) return fail(PINK_B200_EINVAL, "step_kernel must be 0, 1 or 2");
+        c->opt_step_kernel = (int)value;
+        c->fuse_update = update_can_fuse(c->g) && value != 2;
+    } else if (key == "exchange") {
+        if (value < 0 || value > 1) return fail(PINK_B200_EINVAL, "exchange must be 0 or 1");
+        c->opt_exchange = (int)value;
+    } else if (key == "rotation_sharing") {
+        if (value < -1 || value == 1) return fail(PINK_B200_EINVAL, "rotation_sharing must be -1, 0 or at least 2");
+        c->opt_rotation_sharing = (int)value;
+    } else if (key == "rotation_overlap") {
+        CU_TRY(cudaSetDevice(c->cfg.device));
+        if (value && c->rot_stream == c->stream) {
+            int lo = 0, hi = 0;
+            CU_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+            CU_TRY(cudaStreamCreateWithPriority(&c->rot_stream, cudaStreamNonBlocking, lo));
+        }
+    } else if (key == "mma_pairs") {
+        c->opt_mma_pairs = value != 0;
+    } else if (key == "exchange_timeout_ms") {
+        if (value < 1) return fail(PINK_B200_EINVAL, "exchange_timeout_ms must be positive");
+        c->opt_exchange_timeout_ms = value;
+    } else {
+        return fail(PINK_B200_EINVAL, "unknown option '" + key + "'");
+    }
     return PINK_B200_OK;
 }
 
@@ -882,7 +994,7 @@ int pink_b200_set_som(pink_b200_ctx* c, const float* host_som)
     CU_TRY(cudaMemcpy2DAsync(c->d_som, (size_t)g.Pp * sizeof(float), host_som + (size_t)c->first * g.P,
                              (size_t)g.P * sizeof(float), (size_t)g.P * sizeof(float), c->count,
                              cudaMemcpyHostToDevice, c->stream));
-    if (c->fuse_update && !c->d_wrange) CU_TRY(cudaMalloc(&c->d_wrange, (size_t)c->count * sizeof(uint2)));
+    if ((c->fuse_update || c->plan_ok) && !c->d_wrange) CU_TRY(cudaMalloc(&c->d_wrange, (size_t)c->count * sizeof(uint2)));
     LAUNCH_TRY(launch_quantize_som(g, c->d_som, c->count, c->d_a0, c->d_a1, c->d_anorm, c->stream, c->d_wrange));
     c->launches += 1;
     CU_TRY(cudaStreamSynchronize(c->stream));
@@ -914,6 +1026,13 @@ int pink_b200_set_update_factors(pink_b200_ctx* c, const float* host_factors)
     CU_TRY(cudaMemcpy2DAsync(c->d_factors, (size_t)c->count * sizeof(float), host_factors + c->first, N * sizeof(float),
                              (size_t)c->count * sizeof(float), N, cudaMemcpyHostToDevice, c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
+    if (c->plan_ok) {
+        // which block of the persistent kernel rewrites which neuron: spread every neighbourhood over the blocks
+        std::vector<uint32_t> owners((size_t)c->plan.grid * c->plan.owned_per_block);
+        step_assign_owners(host_factors, (uint32_t)N, c->first, c->count, c->plan, owners.data());
+        CU_TRY(cudaMemcpyAsync(c->d_owners, owners.data(), owners.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
+        CU_TRY(cudaStreamSynchronize(c->stream));
+    }
     c->have_factors = true;
     return PINK_B200_OK;
 }
@@ -986,7 +1105,7 @@ static int map_chunk(pink_b200_ctx* c, const float* d_images, uint32_t m, float*
     DistanceArgs da{};
     da.a0 = c->d_a0; da.a1 = c->d_a1; da.anorm = c->d_anorm; da.n = c->count;
     da.b0 = c->d_b0; da.b1 = c->d_b1; da.bnorm = c->d_bnorm; da.n_img = m;
-    da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status;
+    da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status; da.single_cta = !c->opt_mma_pairs;
     const char* why = "";
     cudaError_t e = launch_distance(g, da, c->stream, &why);
     if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
@@ -1098,8 +1217,20 @@ int pink_b200_profile_begin(pink_b200_ctx* c, uint32_t max_steps)
         CU_TRY(cudaEventCreate(&e));
         c->prof_rot_events.push_back(e);
     }
+    while (c->prof_launch_events.size() < (size_t)2 * (max_steps / kRotBatch + 2)) {
+        cudaEvent_t e;
+        CU_TRY(cudaEventCreate(&e));
+        c->prof_launch_events.push_back(e);
+    }
+    if (c->plan_ok && c->stamps_cap < max_steps) {
+        free_dev(c->d_stamps);
+        CU_TRY(cudaMalloc(&c->d_stamps, (size_t)max_steps * 8 * sizeof(unsigned long long)));
+        c->stamps_cap = max_steps;
+    }
+    if (c->d_stamps) CU_TRY(cudaMemsetAsync(c->d_stamps, 0, c->stamps_cap * 8 * sizeof(unsigned long long), c->stream));
     c->prof_cap = max_steps;
     c->prof_used = c->prof_rot_used = 0;
+    c->prof_launches = c->prof_launch_images = 0;
     return PINK_B200_OK;
 }
 
@@ -1115,14 +1246,48 @@ int pink_b200_profile_end(pink_b200_ctx* c, double ms_sum[4], uint64_t* steps)
         CU_TRY(cudaEventElapsedTime(&ms, c->prof_rot_events[2 * s], c->prof_rot_events[2 * s + 1]));
         ms_sum[0] += ms;
     }
-    for (size_t s = 0; s < c->prof_used; ++s)
-        for (int k = 0; k < 3; ++k) {
-            float ms = 0.f;
-            CU_TRY(cudaEventElapsedTime(&ms, c->prof_events[4 * s + k], c->prof_events[4 * s + k + 1]));
-            ms_sum[k + 1] += ms;
+    if (c->use_steps) {
+        // persistent kernel: the phases of a step are read from block 0's device-timer stamps
+        std::vector<unsigned long long> t(8 * c->prof_used);
+        if (c->prof_used) CU_TRY(cudaMemcpy(t.data(), c->d_stamps, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        for (size_t s = 0; s < c->prof_used; ++s) {
+            const unsigned long long* q = &t[8 * s];
+            ms_sum[1] += (double)(q[2] - q[0]) * 1e-6;      // distance phase up to the first grid barrier
+            ms_sum[2] += (double)(q[3] - q[2]) * 1e-6;      // best matching unit (+ exchange) and work list
+            ms_sum[3] += (double)(q[5] - q[3]) * 1e-6;      // update phase up to the second grid barrier
         }
+    } else {
+        for (size_t s = 0; s < c->prof_used; ++s)
+            for (int k = 0; k < 3; ++k) {
+                float ms = 0.f;
+                CU_TRY(cudaEventElapsedTime(&ms, c->prof_events[4 * s + k], c->prof_events[4 * s + k + 1]));
+                ms_sum[k + 1] += ms;
+            }
+    }
     *steps = c->prof_used;
-    c->prof_cap = c->prof_used = c->prof_rot_used = 0;
+    c->prof_cap = 0;                   // prof_used and the stamps stay readable for pink_b200_profile_detail
+    return PINK_B200_OK;
+}
+
+int pink_b200_profile_detail(pink_b200_ctx* c, double out[8])
+{
+    if (!c || !out) return fail(PINK_B200_EINVAL, "null argument");
+    for (int k = 0; k < 8; ++k) out[k] = 0.0;
+    if (!c->use_steps || c->prof_used == 0 || c->prof_launches == 0) return PINK_B200_OK;
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    double ms_total = 0.0;
+    for (size_t l = 0; l < c->prof_launches; ++l) {
+        float ms = 0.f;
+        CU_TRY(cudaEventElapsedTime(&ms, c->prof_launch_events[2 * l], c->prof_launch_events[2 * l + 1]));
+        ms_total += ms;
+    }
+    out[0] = 1e3 * ms_total / (double)c->prof_launches;
+    out[1] = (double)c->prof_launch_images / (double)c->prof_launches;
+    std::vector<unsigned long long> t(8 * c->prof_used);
+    CU_TRY(cudaMemcpy(t.data(), c->d_stamps, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    for (size_t s = 0; s < c->prof_used; ++s)
+        for (int k = 0; k < 5; ++k) out[2 + k] += (double)(t[8 * s + k + 1] - t[8 * s + k]) * 1e-3 / (double)c->prof_used;
     return PINK_B200_OK;
 }
 

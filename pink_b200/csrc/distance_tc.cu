@@ -30,12 +30,12 @@
 #include "kernels.cuh"
 #include "ptx.cuh"
 #include "record.cuh"
+#include "tensormap.cuh"
 
 #include <algorithm>
 #include <type_traits>
 #include <cstdlib>
 
-#include <cudaTypedefs.h>
 
 namespace pinkb {
 
@@ -340,34 +340,6 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
 
 // ------------------------------------------------------------------ host side --
 
-PFN_cuTensorMapEncodeTiled_v12000 encode_fn()
-{
-    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess
-            && qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
-    }
-    return fn;
-}
-
-// rows x row_bytes matrix of bytes, K-contiguous; box = 128 bytes x box_rows, 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows)
-{
-    auto fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = { row_bytes, rows };
-    cuuint64_t strides[1] = { row_bytes };
-    cuuint32_t box[2] = { kBlockK, box_rows };
-    cuuint32_t estr[2] = { 1, 1 };
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
-}
-
 template <int MODE, bool PAIR>
 cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why)
 {
@@ -444,12 +416,11 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
 }
 
 // CTA pairs halve the transform rows every SM pulls through its L2 port (the kernel's bound) as soon
-// as there are two neuron tiles to pair.  PINK_B200_SINGLE_CTA_MMA (diagnostic switch) keeps single CTAs.
+// as there are two neuron tiles to pair.  DistanceArgs::single_cta (diagnostic switch) keeps single CTAs.
 template <int MODE>
 cudaError_t launch_tc_any(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why)
 {
-    static const bool single = getenv("PINK_B200_SINGLE_CTA_MMA") != nullptr;
-    if (a.n > kBlockM && !single) return launch_tc<MODE, true>(g, a, st, why);
+    if (a.n > kBlockM && !a.single_cta) return launch_tc<MODE, true>(g, a, st, why);
     return launch_tc<MODE, false>(g, a, st, why);
 }
 

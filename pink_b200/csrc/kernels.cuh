@@ -16,7 +16,8 @@ enum : int { kModeF32 = 0, kModeU16 = 1, kModeU8 = 2 };
 
 // Status codes a kernel may leave in the device status word.
 enum : int { kDevOk = 0, kDevTimeoutProducer = 1, kDevTimeoutMma = 2, kDevTimeoutEpilogue = 3,
-             kDevTimeoutUpdateProducer = 11, kDevTimeoutUpdateConsumer = 12, kDevTimeoutExchange = 13, kDevTimeoutRotation = 14 };
+             kDevTimeoutUpdateProducer = 11, kDevTimeoutUpdateConsumer = 12, kDevTimeoutExchange = 13, kDevTimeoutRotation = 14,
+             kDevTimeoutGrid = 15 };
 
 struct Geometry
 {
@@ -81,6 +82,7 @@ struct DistanceArgs
     // Optional tail (one image, integer modes): the last block to finish reduces keys[0..n) to this
     // shard's record and publishes it as launch_bmu phase 1 would.  tail_counter: zeroed uint32.
     const struct BmuArgs* tail; uint32_t* tail_counter;
+    uint32_t single_cta;        // 1: never pair blocks for one M = 256 MMA (diagnostic)
 };
 // True when launch_distance honours DistanceArgs::tail for this geometry.
 bool distance_has_tail(const Geometry& g);
@@ -122,6 +124,7 @@ struct BmuArgs
     // peer-memory exchange (world > 1, xchg_seq != 0): this rank's record array and every rank's (own included)
     XchgRecord* xchg_local; XchgRecord* xchg_peer[kXchgMaxRanks]; unsigned long long xchg_seq;
     int* status;                      // device status word (receives a code if the wait for the records expires)
+    unsigned long long xchg_timeout_ns;   // wall-clock limit of the wait for the other ranks' records (0: a second)
 };
 // phase bit 0: reduce keys[0..n) to this shard's (code, first_neuron + argmin) record in pairs[rank];
 // phase bit 1: pick the global best matching unit from pairs, count the hit, re-arm the keys and emit
@@ -170,6 +173,63 @@ cudaError_t launch_update(const Geometry& g, const UpdateArgs& a, cudaStream_t s
 bool update_can_fuse(const Geometry& g);
 cudaError_t launch_update_fused(const Geometry& g, const UpdateArgs& a, const BmuArgs& b, cudaStream_t st, int* status);
 
+// ---- whole training steps of a batch of images in ONE persistent kernel (train_steps.cu) -------------
+// One block per SM stays resident for the whole batch and walks image by image through the phases
+// distance -> (grid barrier) -> best matching unit, work list, update -> (grid barrier), so that an
+// image costs no kernel launch, no set-up and no host round trip.  Integer distance modes only.
+constexpr uint32_t kStepBatchMax = 16;          // images per launch
+constexpr uint32_t kStepMaxOwned = 32;          // neurons one block may own
+
+// Control words of one launch; the host sets every byte to 0xFF before the launch.
+//   bmu_word[i]: minimum over all (neuron, transform tile) partial minima of image i of
+//                (code << s) | global neuron index, s = 32 (uint8) or 16 (uint16)
+//   bar:         arrival counter of the grid barriers (counts up from 0xFFFFFFFF, i.e. -1)
+struct StepCtrl { unsigned long long bmu_word[kStepBatchMax]; uint32_t bar; uint32_t pad; };
+
+// Launch shape and shared-memory layout, fixed per context.
+struct StepPlan
+{
+    uint32_t pair;                       // blocks work as cta_group::2 pairs in the distance phase
+    uint32_t grid;                       // blocks (all resident at once); even when pair
+    uint32_t n_tile, n_tiles, m_units;   // transform tile width, tiles per image, neuron tiles (pairs of tiles when pair)
+    uint32_t ring_stages, b_bytes;       // TMA ring of the distance phase
+    uint32_t upd_stages, upd_stage_bytes, upd_off_base;     // stages of the update phase: {neuron plane, base rotation plane}
+    uint32_t col_chunks, row_blocks, rows_per_block;        // consumer task grid per plane
+    uint32_t owned_per_block;            // length of a block's row in the ownership table
+    uint32_t smem_bytes;                 // dynamic shared memory
+};
+
+struct StepArgs
+{
+    // distance phase
+    void* a0; void* a1; void* anorm; uint32_t n;                       // SOM operand of this shard (rows are rewritten by the update phase)
+    const void* b0; const void* b1; const void* bnorm; uint32_t b_rows; // transform operand buffer (all rows) and its row count
+    uint32_t b_row0;                  // row of the first image's transform 0 in that buffer
+    unsigned long long* keys;         // [n], kKeyEmpty on entry and on exit
+    // update phase
+    float* som;                       // [n][Pp]
+    const float* base;                // base rotations of the first image; consecutive images follow
+    uint2* wrange; const uint32_t* rmax;   // nullable together: value ranges (see cannot_change); rmax[i] for image i
+    const float* factors;             // [N_global][n]
+    const uint32_t* owners;           // [grid][owned_per_block] local neuron indices, ~0u = none
+    // bookkeeping
+    uint32_t n_img, first_neuron, rank, world;
+    uint32_t* counts; uint32_t* bmu_log; unsigned long long* stats; int* status;
+    StepCtrl* ctrl;
+    unsigned long long* stamps;       // nullable: [n_img][8] device-timer stamps of block 0 (see train_steps.cu)
+    // peer-memory exchange of the shards' records (world > 1): as in BmuArgs; the record of image i carries xchg_seq0 + i
+    XchgRecord* xchg_local; XchgRecord* xchg_peer[kXchgMaxRanks]; unsigned long long xchg_seq0;
+    unsigned long long xchg_timeout_ns;   // wall-clock limit of the wait for the other ranks' records
+};
+
+// Fills `plan` and returns true when the persistent kernel can run this geometry on the current device.
+bool step_plan(const Geometry& g, uint32_t n_local, uint32_t n_global, StepPlan* plan, const char** why_not);
+// Which block updates which neuron: owners[b * owned_per_block + j], balanced so that the neurons close to any
+// best matching unit (large update factors) are spread over different blocks.  host_factors: [N][N] table.
+void step_assign_owners(const float* host_factors, uint32_t N, uint32_t first, uint32_t count, const StepPlan& plan,
+                        uint32_t* owners);
+cudaError_t launch_train_steps(const Geometry& g, const StepPlan& plan, const StepArgs& a, cudaStream_t st, const char** why);
+
 // ---- mapping epilogue -------------------------------------------------------
 // dist[i][n] = sqrt(reported distance), rot[i][n] = transform; re-arms the keys.
 cudaError_t launch_map_finalize(const Geometry& g, unsigned long long* keys, uint32_t n_img, uint32_t n,
@@ -181,9 +241,10 @@ cudaError_t launch_fill_keys(unsigned long long* keys, size_t count, cudaStream_
 // Stores `value` into entry `entry` of every rank's flag array (peer_flags[r], r < world <= kXchgMaxRanks).
 cudaError_t launch_flag_publish(unsigned long long* const* peer_flags, uint32_t world, uint32_t entry,
                                 unsigned long long value, cudaStream_t st);
-// Waits (bounded; status receives kDevTimeoutRotation on expiry) until row[r] holds `value` for every r != self.
+// Waits (at most timeout_ns of wall clock; status receives kDevTimeoutRotation on expiry) until row[r] holds
+// `value` for every r != self.
 cudaError_t launch_flag_wait(const unsigned long long* row, uint32_t world, uint32_t self, unsigned long long value,
-                             int* status, cudaStream_t st);
+                             int* status, unsigned long long timeout_ns, cudaStream_t st);
 
 // Helpers of the C-ABI layer that entry points defined beside their kernels use:
 // validate a configuration into a Geometry (returns a PINK_B200_* status and sets

@@ -19,6 +19,7 @@
 // float pixels are bit-identical to the CPU reference built without FMA.
 #include "../../include/pink_b200.h"
 #include "kernels.cuh"
+#include "quant.cuh"
 
 #include <type_traits>
 
@@ -27,22 +28,6 @@
 namespace pinkb {
 
 namespace {
-
-// Truncating conversion of v * 255 (v * 65535); float-to-integer cvt clamps to
-// the destination range, so one instruction both converts and saturates.
-__device__ __forceinline__ uint32_t quant_u8(float v)
-{
-    uint32_t q;
-    asm("cvt.rzi.u8.f32 %0, %1;" : "=r"(q) : "f"(__fmul_rn(v, 255.0f)));
-    return q;
-}
-
-__device__ __forceinline__ uint32_t quant_u16(float v)
-{
-    uint32_t q;
-    asm("cvt.rzi.u16.f32 %0, %1;" : "=r"(q) : "f"(__fmul_rn(v, 65535.0f)));
-    return q;
-}
 
 // Centre crop / zero pad (src/CudaLib/resize_kernel.h:15-32, integer margins).
 __device__ __forceinline__ float resize_pixel(const float* __restrict__ img, uint32_t id, uint32_t nd,

@@ -345,4 +345,41 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr)
                  :: "r"(bar_cluster_addr) : "memory");
 }
 
+
+// One arrival on a barrier given by its address in the cluster's shared window (own or peer CTA).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(bar_cluster_addr) : "memory");
+}
+
+// Order asynchronous-proxy accesses (TMA loads and stores, tensor-core operand reads) and generic-proxy
+// accesses of this thread, in every state space.  Needed where data written through one proxy is read
+// through the other inside ONE kernel: between kernels the launch boundary does it.
+__device__ __forceinline__ void fence_proxy_async_all()
+{
+    asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// Nanoseconds of the device-wide timer: wall-clock limits of waits on other blocks or other GPUs.
+__device__ __forceinline__ unsigned long long global_timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ int ld_relaxed_gpu_s32(const int* p)
+{
+    int v;
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 } // namespace pinkb

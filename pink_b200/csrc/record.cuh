@@ -63,6 +63,29 @@ __device__ __forceinline__ void block_argmin_keys(const unsigned long long* keys
     }
 }
 
+// v / d for v * d < 2^32 with magic = floor(2^32 / d) + 1; magic == 0 encodes the divisor 1.
+__device__ __forceinline__ uint32_t bmu_div(uint32_t v, uint32_t magic) { return magic ? __umulhi(v, magic) : v; }
+
+// Transform index -> base rotation and affine source map of a work-list entry.
+__device__ __forceinline__ UpdateItem make_item(const BmuArgs& a, uint32_t i, unsigned long long key, float f)
+{
+    const uint32_t t = (uint32_t)(key & ((1ull << a.shift) - 1));
+    const uint32_t fl = bmu_div(t, a.magic_R), r = t - fl * a.R;
+    const uint32_t jq = a.q ? bmu_div(r, a.magic_q) : 0;
+    const int32_t nd = (int32_t)a.nd, nd1 = nd - 1, sgn = fl ? -1 : 1;
+    UpdateItem it;
+    it.n = i;
+    it.tq = a.q ? r - jq * a.q : 0;
+    it.f = f;
+    switch (jq) {
+        case 0:  it.ax = sgn * nd;  it.ay = 1;   it.a0 = fl ? nd1 * nd : 0; break;
+        case 1:  it.ax = sgn;       it.ay = -nd; it.a0 = nd1 * nd + (fl ? nd1 : 0); break;
+        case 2:  it.ax = -sgn * nd; it.ay = -1;  it.a0 = fl ? nd1 : nd1 * nd + nd1; break;
+        default: it.ax = -sgn;      it.ay = nd;  it.a0 = fl ? 0 : nd1; break;
+    }
+    return it;
+}
+
 // Hands this rank's record (code, global neuron index) to the other ranks: into pairs[rank]
 // for a following all-gather, or -- peer-memory exchange -- thread r stores the two tagged words
 // into rank r's record array.  Called by all threads of the block; (code, neuron) block-uniform.

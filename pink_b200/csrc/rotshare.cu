@@ -5,6 +5,7 @@
 // before its distance kernels read the batch.  No reference counterpart (the reference trains on
 // one GPU).
 #include "kernels.cuh"
+#include "ptx.cuh"
 #include "record.cuh"
 
 namespace pinkb {
@@ -19,14 +20,16 @@ __global__ void flag_publish_kernel(FlagPeers peers, uint32_t world, uint32_t en
 }
 
 __global__ void flag_wait_kernel(const unsigned long long* row, uint32_t world, uint32_t self, unsigned long long value,
-                                 int* status)
+                                 int* status, unsigned long long timeout_ns)
 {
     bool seen = true;
     for (uint32_t r = threadIdx.x; r < world; r += 32) {
         if (r == self) continue;          // this rank's own share is ordered by its streams, never by a kernel waiting for a kernel
         bool ok = false;
-        for (uint32_t spin = 0; spin < (1u << 22); ++spin) {          // >= 128 ns each: gives up after roughly a second
+        const unsigned long long t_start = global_timer_ns();       // bounded by the wall clock
+        for (uint32_t spin = 0;; ++spin) {
             if (ld_relaxed_sys(row + r) == value) { ok = true; break; }
+            if ((spin & 31u) == 31u && global_timer_ns() - t_start > timeout_ns) break;
             __nanosleep(128);
         }
         seen = seen && ok;
@@ -48,9 +51,9 @@ cudaError_t launch_flag_publish(unsigned long long* const* peer_flags, uint32_t 
 }
 
 cudaError_t launch_flag_wait(const unsigned long long* row, uint32_t world, uint32_t self, unsigned long long value,
-                             int* status, cudaStream_t st)
+                             int* status, unsigned long long timeout_ns, cudaStream_t st)
 {
-    flag_wait_kernel<<<1, 32, 0, st>>>(row, world, self, value, status);
+    flag_wait_kernel<<<1, 32, 0, st>>>(row, world, self, value, status, timeout_ns ? timeout_ns : 1000000000ull);
     return cudaGetLastError();
 }
 

@@ -18,6 +18,7 @@
 // are the same steps as separate kernels, for neurons too large for the
 // pipelined kernel's shared-memory stages.
 #include "kernels.cuh"
+#include "quant.cuh"
 #include "ptx.cuh"
 #include "record.cuh"
 
@@ -28,26 +29,6 @@ namespace pinkb {
 
 namespace {
 
-// Truncating conversion of v * 255 (v * 65535); float-to-integer cvt clamps to
-// the destination range, so one instruction both converts and saturates.
-__device__ __forceinline__ uint32_t quant_u8(float v)
-{
-    uint32_t q;
-    asm("cvt.rzi.u8.f32 %0, %1;" : "=r"(q) : "f"(__fmul_rn(v, 255.0f)));
-    return q;
-}
-
-__device__ __forceinline__ uint32_t quant_u16(float v)
-{
-    uint32_t q;
-    asm("cvt.rzi.u16.f32 %0, %1;" : "=r"(q) : "f"(__fmul_rn(v, 65535.0f)));
-    return q;
-}
-
-constexpr uint32_t kXchgSpinLimit = 1u << 22;     // polls of >= 128 ns each: gives up after roughly a second
-
-// v / d for v * d < 2^32 with magic = floor(2^32 / d) + 1; magic == 0 encodes the divisor 1.
-__device__ __forceinline__ uint32_t bmu_div(uint32_t v, uint32_t magic) { return magic ? __umulhi(v, magic) : v; }
 
 constexpr int kBmuThreads = 512;
 
@@ -62,26 +43,6 @@ bmu_kernel(BmuArgs a)
     if (threadIdx.x == 0) { sc[0] = bc; sn[0] = bn == ~0ull ? ~0ull : bn + a.first_neuron; }
     __syncthreads();
     publish_record(a, sc[0], sn[0]);
-}
-
-// Transform index -> base rotation and affine source map of a work-list entry.
-__device__ __forceinline__ UpdateItem make_item(const BmuArgs& a, uint32_t i, unsigned long long key, float f)
-{
-    const uint32_t t = (uint32_t)(key & ((1ull << a.shift) - 1));
-    const uint32_t fl = bmu_div(t, a.magic_R), r = t - fl * a.R;
-    const uint32_t jq = a.q ? bmu_div(r, a.magic_q) : 0;
-    const int32_t nd = (int32_t)a.nd, nd1 = nd - 1, sgn = fl ? -1 : 1;
-    UpdateItem it;
-    it.n = i;
-    it.tq = a.q ? r - jq * a.q : 0;
-    it.f = f;
-    switch (jq) {
-        case 0:  it.ax = sgn * nd;  it.ay = 1;   it.a0 = fl ? nd1 * nd : 0; break;
-        case 1:  it.ax = sgn;       it.ay = -nd; it.a0 = nd1 * nd + (fl ? nd1 : 0); break;
-        case 2:  it.ax = -sgn * nd; it.ay = -1;  it.a0 = fl ? nd1 : nd1 * nd + nd1; break;
-        default: it.ax = -sgn;      it.ay = nd;  it.a0 = fl ? 0 : nd1; break;
-    }
-    return it;
 }
 
 constexpr int kListThreads = 256;
@@ -571,10 +532,15 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                 for (uint32_t r = lane; r < b.world; r += 32) {
                     unsigned long long w0 = 0, w1 = 0;
                     bool seen = false;
-                    for (uint32_t spin = 0; spin < kXchgSpinLimit; ++spin) {
+                    // bounded by the wall clock: the other ranks are separate processes whose launches may
+                    // lag behind by a host-side delay (file reads, first-launch module loading)
+                    const unsigned long long limit = b.xchg_timeout_ns ? b.xchg_timeout_ns : 1000000000ull;
+                    const unsigned long long t_start = global_timer_ns();
+                    for (uint32_t spin = 0;; ++spin) {
                         w0 = ld_relaxed_sys(&slot[r].w0);
                         w1 = ld_relaxed_sys(&slot[r].w1);
                         if ((w0 & 0xFFull) == tag && (w1 & 0xFFull) == tag) { seen = true; break; }
+                        if ((spin & 31u) == 31u && global_timer_ns() - t_start > limit) break;
                         __nanosleep(128);
                     }
                     // an absent neuron index (~0) lost its upper bits to the tag; restore it so it never wins

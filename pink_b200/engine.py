@@ -42,7 +42,7 @@ class Engine:
 
     def __init__(self, n_neurons, channels, image_dim, neuron_dim, ed_dim, n_rotations=360, use_flip=True,
                  dist_type=capi.UINT8, device=0, rank=0, world_size=1, max_batch=0,
-                 ed_shape=capi.QUADRATIC, interpolation=capi.BILINEAR):
+                 ed_shape=capi.QUADRATIC, interpolation=capi.BILINEAR, options=None):
         self.cfg = capi.Config(n_neurons, channels, image_dim, neuron_dim, ed_dim, ed_shape, n_rotations,
                                int(bool(use_flip)), dist_type, interpolation, device, rank, world_size, max_batch)
         self._h = C.c_void_p()
@@ -52,6 +52,12 @@ class Engine:
         self.first, self.count = first.value, count.value
         self.image_size = channels * image_dim * image_dim
         self.neuron_size = channels * neuron_dim * neuron_dim
+        for name, value in (options or {}).items():
+            self.set_option(name, value)
+
+    def set_option(self, name, value):
+        """Switches of the context (see pink_b200_set_option); before comm_init / set_som."""
+        capi.check(capi.lib.pink_b200_set_option(self._h, name.encode(), int(value)))
 
     # -- life cycle ---------------------------------------------------------
     def close(self):
@@ -161,6 +167,14 @@ class Engine:
         steps = C.c_uint64()
         capi.check(capi.lib.pink_b200_profile_end(self._h, ms, C.byref(steps)))
         return dict(zip(("rotate", "distance", "bmu", "update"), list(ms))), steps.value
+
+    def profile_detail(self):
+        """Persistent-kernel timing of the last profiled pass (see pink_b200_profile_detail)."""
+        out = (C.c_double * 8)()
+        capi.check(capi.lib.pink_b200_profile_detail(self._h, out))
+        keys = ("launch_us", "images_per_launch", "distance_own_us", "barrier1_wait_us", "bmu_list_us",
+                "update_own_us", "barrier2_wait_us")
+        return dict(zip(keys, list(out)[:7]))
 
     @property
     def stream(self):

@@ -15,10 +15,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _worker(rank, world, port, mode, exchange, q):
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    if exchange == "nccl":
-        os.environ["PINK_B200_NCCL_EXCHANGE"] = "1"
-    if exchange == "peer":
-        os.environ["PINK_B200_REPLICATED_ROTATION"] = "1"
+    options = {"nccl": {"exchange": 1}, "peer": {"rotation_sharing": 0}, "shared": {},
+               "two-kernel": {"step_kernel": 1}}[exchange]
     import torch
     import torch.distributed as dist
     from pink_b200 import capi, engine
@@ -31,7 +29,7 @@ def _worker(rank, world, port, mode, exchange, q):
     som[13] = som[4]                                   # identical neurons in different shards: BMU ties
     imgs = rng.random((n_img, 1, idim, idim), dtype=np.float32)
     F = engine.update_factors(lay, s0, s1, capi.FUNC_GAUSSIAN, 1.1, 0.2)
-    eng = engine.Engine(N, 1, idim, nd, ed, R, flip, mode, device=rank, rank=rank, world_size=world)
+    eng = engine.Engine(N, 1, idim, nd, ed, R, flip, mode, device=rank, rank=rank, world_size=world, options=options)
     uid = [engine.Engine.unique_id() if rank == 0 else None]
     dist.broadcast_object_list(uid, 0)
     eng.comm_init(uid[0])
@@ -51,7 +49,7 @@ def _worker(rank, world, port, mode, exchange, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["shared", "peer", "nccl"])
+@pytest.mark.parametrize("exchange", ["shared", "peer", "nccl", "two-kernel"])
 @pytest.mark.parametrize("mode", [2, 1, 0])
 def test_two_gpu_sharded_training_bit_exact(cuda, mode, exchange):
     torch = cuda
@@ -62,7 +60,7 @@ def test_two_gpu_sharded_training_bit_exact(cuda, mode, exchange):
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + 3 * mode + ["shared", "peer", "nccl"].index(exchange) + (os.getpid() % 100)
+    port = 29700 + 4 * mode + ["shared", "peer", "nccl", "two-kernel"].index(exchange) + (os.getpid() % 100)
     procs = [ctx.Process(target=_worker, args=(r, world, port, mode, exchange, q)) for r in range(world)]
     for p in procs:
         p.start()
@@ -70,7 +68,7 @@ def test_two_gpu_sharded_training_bit_exact(cuda, mode, exchange):
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    assert kind == {"shared": 3, "peer": 2, "nccl": 1}[exchange]      # the intended exchange really ran
+    assert kind == {"shared": 3, "peer": 2, "nccl": 1, "two-kernel": 3}[exchange]      # the intended exchange really ran
     want = som.copy()
     bmus = [O.train_step(want, im, F, 15, 40, True, mode)[2] for im in imgs]
     if mode == 0:        # float32 distances: same best matching units (no near-ties in this seed), same arithmetic

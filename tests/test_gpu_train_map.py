@@ -53,42 +53,49 @@ def test_train_integer_modes_bit_exact(cuda, case, mode):
     assert counts.sum() == n and all(counts[b] > 0 for b in want_bmu)
 
 
-@pytest.mark.parametrize("case", [TRAIN_CASES[0], TRAIN_CASES[4]])
+@pytest.mark.parametrize("case", [TRAIN_CASES[0], TRAIN_CASES[4], TRAIN_CASES[3]])
 @pytest.mark.parametrize("mode", [2, 1, 0])
-def test_train_fused_and_split_update_agree(cuda, case, mode, monkeypatch):
-    """The update kernel that finds the best matching unit and its work list itself and the path with
-    separate reduction and compaction kernels give the same SOM, BMU sequence and counters bit for bit."""
+def test_step_kernels_agree(cuda, case, mode):
+    """The three launch sequences of a training step -- whole batches in the persistent kernel, two kernels per
+    image (distance + an update kernel that finds the best matching unit and its work list itself), and four
+    kernels per image (distance, reduction, compaction, update) -- give the same SOM, BMU sequence and counters
+    bit for bit."""
     import pink_b200.capi as capi
     layout, s0, s1, C_, idim, nd, ed, R, flip, n = case
     N = _som_size(layout, s0, s1)
     rng = np.random.default_rng(77)
     som0 = rng.random((N, C_, nd, nd), dtype=np.float32)
+    n = 19                                              # more than one batch of the persistent kernel
     imgs = blob_images(n, idim, C_, seed=5).reshape(n, C_, idim, idim)
     F = O.update_factors(layout, s0, s1, O.FUNC_GAUSSIAN, 1.1, 0.2)
     out = []
-    for split in (False, True):
-        if split:
-            monkeypatch.setenv("PINK_B200_SPLIT_UPDATE", "1")
-        with Context(capi, make_config(capi, N, C_, idim, nd, ed, R, flip, mode)) as ctx:
+    for step_kernel in (0, 1, 2):
+        with Context(capi, make_config(capi, N, C_, idim, nd, ed, R, flip, mode), {"step_kernel": step_kernel}) as ctx:
             ctx.set_som(som0)
             ctx.set_factors(F)
             log = ctx.train(imgs)
             log2 = ctx.train(imgs[::-1].copy())
             out.append((list(log) + list(log2), ctx.get_som(som0).copy(), ctx.counts().copy(),
                         ctx.e.launch_count(), ctx.e.update_stats()))
-    assert out[0][0] == out[1][0]
-    assert np.array_equal(out[0][1].view(np.uint32), out[1][1].view(np.uint32))
-    assert np.array_equal(out[0][2], out[1][2])
-    assert out[0][3] < out[1][3]          # the fused path really ran: two kernels less per image
-    # the split path rewrites every neuron with a non-zero factor; the fused one does not even read neurons
-    # that provably cannot change and leaves neurons whose values did not change unwritten (far from the
-    # best matching unit of a 10 x 10 map the products vanish) -- with bit-identical maps, asserted above
-    (read_f, written_f), (read_s, written_s) = out[0][4], out[1][4]
+    for other in out[1:]:
+        assert out[0][0] == other[0]
+        assert np.array_equal(out[0][1].view(np.uint32), other[1].view(np.uint32))
+        assert np.array_equal(out[0][2], other[2])
+    # the intended sequences really ran: one launch per batch, two or four per image
+    if mode != 0 and (nd * nd) % 4 == 0:
+        assert out[0][3] < out[1][3]
+    assert out[1][3] <= out[2][3]
+    # the split path rewrites every neuron with a non-zero factor; the others do not even read neurons that
+    # provably cannot change and leave neurons whose values did not change unwritten (far from the best
+    # matching unit of a 10 x 10 map the products vanish) -- with bit-identical maps, asserted above
     want_read = sum(int((F[bmu] != 0).sum()) for bmu in out[0][0])
+    read_s, written_s = out[2][4]
     assert read_s == written_s == want_read
-    assert written_f <= read_f <= read_s
-    if N == 100:
-        assert written_f < read_s and read_f < read_s
+    for k in (0, 1):
+        read_f, written_f = out[k][4]
+        assert written_f <= read_f <= read_s
+    if N == 100 and mode != 0:
+        assert out[0][4][1] < read_s and out[0][4][0] < read_s
 
 
 @pytest.mark.parametrize("case", TRAIN_CASES[:5])

@@ -23,12 +23,12 @@ def split_key(keys, mode):
 class Context:
     """Test-side wrapper of pink_b200.engine.Engine keyed by a prepared Config."""
 
-    def __init__(self, capi, cfg):
+    def __init__(self, capi, cfg, options=None):
         from pink_b200.engine import Engine
         self.cfg = cfg
         self.e = Engine(cfg.n_neurons, cfg.channels, cfg.image_dim, cfg.neuron_dim, cfg.ed_dim, cfg.n_rotations,
                         cfg.use_flip, cfg.dist_type, cfg.device, cfg.rank, cfg.world_size, cfg.max_batch,
-                        cfg.ed_shape, cfg.interpolation)
+                        cfg.ed_shape, cfg.interpolation, options=options)
         self.first, self.count = self.e.first, self.e.count
 
     def set_som(self, som):

@@ -1,23 +1,26 @@
 #!/usr/bin/env python
 """Benchmark of the rotation/flip-invariant SOM hot path on B200.
 
-Workload (the large hexagonal SOM the scaling target is quoted on): hexagonal
-SOM of radius 30 (2,791 neurons), 128x128 single-channel images, 90x90
-neurons, 64x64 distance region, 720 rotations + flip (1,440 transforms), uint8
-distance, Gaussian neighbourhood sigma 3.0 / damping 0.05, random-uniform SOM,
-synthetic Gaussian-blob images.  One step = sequential training on one batch
-of images (image i+1 sees the SOM updated by image i).
+Headline workload (the large hexagonal SOM the scaling target is quoted on): hexagonal
+SOM of radius 30 (2,791 neurons), 128x128 single-channel images, 90x90 neurons, 64x64
+distance region, 720 rotations + flip (1,440 transforms), uint8 distance, Gaussian
+neighbourhood sigma 3.0 / damping 0.05, random-uniform SOM, synthetic Gaussian-blob
+images.  One step = sequential training on one batch of images (image i+1 sees the SOM
+updated by image i).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B]
   python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
   python bench.py --impl reference ...     # the reference's CPU path on the host cores
 
-Prints ONE JSON line (rank 0).  `value` is images/s with the image batches
-resident in HBM; `e2e` is the same metric through the host-buffer entry point
-(pinned host images copied in, BMU hit counters copied out, every step).
-With N > 1 the neurons are sharded over the ranks (strong scaling): every rank
-sees every image, computes distances for its shard, the shards' best matching
-units are exchanged, and each rank updates its own neurons.
+Prints ONE JSON line (rank 0).  `value` is training images/s with the image batches
+resident in HBM; `e2e` is the same metric through the host-buffer entry point (pinned host
+images copied in, BMU hit counters copied out, every step).  With N > 1 the neurons are
+sharded over the ranks (strong scaling): every rank sees every image, computes distances
+for its shard, the shards' best matching units are exchanged, and each rank updates its
+own neurons.  Extra blocks of the line: `check` (checksums of a fixed untimed training
+prefix, identical for every N), `roofline` / `kernels` / `timeline` (per-phase device
+times of a profiled pass), `map` (mapping images/s, images sharded over the ranks),
+`other_configs` (the smaller training configurations, one GPU), `cpu_baseline`.
 """
 import argparse
 import json
@@ -26,16 +29,39 @@ import subprocess
 import sys
 import threading
 import time
+import zlib
 
 import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-WORKLOAD = dict(name="hex-r30 SOM (2791 neurons) train, 128x128 images, 90x90 neurons, 64x64 ED, 720 rot + flip, uint8",
-                som_layout=1, som_dim=61, channels=1, image_dim=128, neuron_dim=90, ed_dim=64,
-                rotations=720, flip=True, sigma=3.0, damping=0.05)
+FLOAT, UINT16, UINT8 = 0, 1, 2
+WORKLOADS = {
+    "C4": dict(name="hex-r30 SOM (2791 neurons) train, 128x128 images, 90x90 neurons, 64x64 ED, 720 rot + flip, uint8",
+               som_layout=1, som_dim=61, channels=1, image_dim=128, neuron_dim=90, ed_dim=64,
+               rotations=720, flip=True, sigma=3.0, damping=0.05, mode=UINT8, seed=1004),
+    "C1": dict(name="10x10 SOM train, 64x64 images, 44x44 neurons, 31x31 ED, 360 rot + flip, uint8",
+               som_layout=0, som_dim=10, channels=1, image_dim=64, neuron_dim=44, ed_dim=31,
+               rotations=360, flip=True, sigma=1.1, damping=0.2, mode=UINT8, seed=1001),
+    "C2": dict(name="20x20 SOM map, 128x128 images, 90x90 neurons, 64x64 ED, 360 rot + flip, float32",
+               som_layout=0, som_dim=20, channels=1, image_dim=128, neuron_dim=90, ed_dim=64,
+               rotations=360, flip=True, sigma=1.1, damping=0.2, mode=FLOAT, seed=1002),
+    "C3": dict(name="40x40 SOM train, 2x150x150 images, 2x106x106 neurons, 75x75 ED, 360 rot + flip, uint16",
+               som_layout=0, som_dim=40, channels=2, image_dim=150, neuron_dim=106, ed_dim=75,
+               rotations=360, flip=True, sigma=2.0, damping=0.1, mode=UINT16, seed=1003),
+}
+WORKLOAD = WORKLOADS["C4"]
 POOL_IMAGES = 2048          # distinct synthetic images; steps take consecutive, wrapping slices of the pool
+CHECK_IMAGES = 64           # untimed prefix whose results are checksummed
+
+
+def som_size(w):
+    """Neurons of the SOM grid: dim x dim (cartesian) or the hexagon of side dim (3 r (r + 1) + 1, r = (dim - 1) / 2)."""
+    if w["som_layout"] == 0:
+        return w["som_dim"] ** 2
+    r = (w["som_dim"] - 1) // 2
+    return 3 * r * (r + 1) + 1
 
 
 def measured_peaks():
@@ -45,6 +71,22 @@ def measured_peaks():
             p = json.load(f)
         return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], source="measured")
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+def tracked_figure(name, key):
+    """A figure quoted from a tracked summary under profiles/ (lines `key = value`), or None."""
+    path = os.path.join(ROOT, "profiles", name)
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        for line in f:
+            parts = line.split("=")
+            if len(parts) == 2 and parts[0].strip() == key:
+                try:
+                    return float(parts[1].split()[0])
+                except ValueError:
+                    return None
+    return None
 
 
 class ClockSampler(threading.Thread):
@@ -78,69 +120,60 @@ class ClockSampler(threading.Thread):
                     reasons=reasons, samples=len(sm))
 
 
-def make_inputs(w):
+def make_inputs(w, n_images=POOL_IMAGES):
+    """Seeded inputs of a workload: (N, SOM [N][P], images [n][C*id*id]).  Pure numpy: loads no compiled library."""
     from pink_b200.synthetic import blob_images, mt19937_uniform
-    from pink_b200 import engine
-    N = engine.som_size(w["som_layout"], w["som_dim"], w["som_dim"])
+    N = som_size(w)
     P = w["channels"] * w["neuron_dim"] ** 2
     som = mt19937_uniform(N * P, 1234).reshape(N, P)
-    pool = blob_images(POOL_IMAGES, w["image_dim"], w["channels"], seed=1004).reshape(POOL_IMAGES, -1)
+    pool = blob_images(n_images, w["image_dim"], w["channels"], seed=w["seed"]).reshape(n_images, -1)
     return N, som, pool
 
 
-def cpu_baseline(w, N, som, pool, budget_s=12.0, max_images=4):
-    """Times the reference's CPU training step (float32, its only CPU mode) on the first images of the workload."""
-    import oracle as O
+# ---------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's own CPU Trainer on the host cores
+# ---------------------------------------------------------------------------------------------
+
+def reference_stepper(w, N, som, pool):
+    """Returns (step(i), kind, cores).  All host threads are used whatever the launcher exported."""
     threads = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(threads)          # torch.distributed.run exports 1
+    import oracle as O
     if O.have_ref():
-        kind = "reference"
+        O.ref().ref_set_num_threads(threads)
         sess = O.RefSession(som.reshape(N, w["channels"], w["neuron_dim"], w["neuron_dim"]), w["som_layout"],
                             w["som_dim"], w["som_dim"], 0 if w["channels"] == 1 else w["channels"], w["image_dim"],
                             w["neuron_dim"], w["ed_dim"], w["rotations"], w["flip"], O.FUNC_GAUSSIAN, w["sigma"],
                             w["damping"])
-        step = lambda i: sess.train(pool[i:i + 1])
-        cores = int(O.ref().ref_num_threads())
-    else:
-        kind = "port"
-        F = O.update_factors(w["som_layout"], w["som_dim"], w["som_dim"], O.FUNC_GAUSSIAN, w["sigma"], w["damping"])
-        s = som.reshape(N, w["channels"], w["neuron_dim"], w["neuron_dim"]).copy()
-        img_shape = (w["channels"], w["image_dim"], w["image_dim"])
-        step = lambda i: O.train_step(s, pool[i].reshape(img_shape), F, w["ed_dim"], w["rotations"], w["flip"], 0)
-        cores = 1
+        n = len(pool)
+        return (lambda i: sess.train(pool[i % n:i % n + 1])), "reference", int(O.ref().ref_num_threads())
+    F = O.update_factors(w["som_layout"], w["som_dim"], w["som_dim"], O.FUNC_GAUSSIAN, w["sigma"], w["damping"])
+    s = som.reshape(N, w["channels"], w["neuron_dim"], w["neuron_dim"]).copy()
+    shape = (w["channels"], w["image_dim"], w["image_dim"])
+    n = len(pool)
+    return (lambda i: O.train_step(s, pool[i % n].reshape(shape), F, w["ed_dim"], w["rotations"], w["flip"], 0)), "port", 1
+
+
+def cpu_baseline(w, N, som, pool, budget_s=12.0, max_images=4):
+    """Times the reference's CPU training step (float32, its only CPU mode) on the first images of the workload."""
+    step, kind, cores = reference_stepper(w, N, som, pool)
     t0 = time.perf_counter()
     n = 0
     while n < max_images and (n == 0 or time.perf_counter() - t0 < budget_s):
         step(n)
         n += 1
     dt = time.perf_counter() - t0
-    return dict(value=n / dt, unit="images/s", cores=cores, kind=kind, host_cpus=threads,
+    return dict(value=n / dt, unit="images/s", cores=cores, kind=kind, host_cpus=os.cpu_count() or 1,
                 sample="first %d images of the workload, float32 distance (the reference has no integer CPU mode), "
                        "%.1f s wall" % (n, dt))
 
 
 def run_reference(args, w):
     """The reference's own CPU implementation on the host cores; one step = one image."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    import oracle as O
-    N, som, pool = make_inputs(w)
-    if O.have_ref():
-        kind = "reference"
-        sess = O.RefSession(som.reshape(N, w["channels"], w["neuron_dim"], w["neuron_dim"]), w["som_layout"],
-                            w["som_dim"], w["som_dim"], 0 if w["channels"] == 1 else w["channels"], w["image_dim"],
-                            w["neuron_dim"], w["ed_dim"], w["rotations"], w["flip"], O.FUNC_GAUSSIAN, w["sigma"],
-                            w["damping"])
-        step = lambda i: sess.train(pool[i % POOL_IMAGES:i % POOL_IMAGES + 1])
-        cores = int(O.ref().ref_num_threads())
-    else:
-        kind = "port"
-        F = O.update_factors(w["som_layout"], w["som_dim"], w["som_dim"], O.FUNC_GAUSSIAN, w["sigma"], w["damping"])
-        s = som.reshape(N, w["channels"], w["neuron_dim"], w["neuron_dim"]).copy()
-        shape = (w["channels"], w["image_dim"], w["image_dim"])
-        step = lambda i: O.train_step(s, pool[i % POOL_IMAGES].reshape(shape), F, w["ed_dim"], w["rotations"],
-                                      w["flip"], 0)
-        cores = 1
+    N, som, pool = make_inputs(w, 64)
+    step, kind, cores = reference_stepper(w, N, som, pool)
     for i in range(args.warmup):
         step(i)
     t0 = time.perf_counter()
@@ -148,7 +181,7 @@ def run_reference(args, w):
         step(args.warmup + i)
     dt = time.perf_counter() - t0
     v = args.steps / dt
-    sample = "1 image per step, float32 distance (the reference's CPU path has no integer mode)"
+    sample = "1 image per step, float32 distance (the reference's CPU path has no integer mode), %d threads" % cores
     print(json.dumps({
         "impl": "reference", "metric": "train_images_per_sec", "value": v, "unit": "images/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
@@ -159,6 +192,37 @@ def run_reference(args, w):
     }))
 
 
+# ---------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------
+
+def crc(a):
+    return "%08x" % (zlib.crc32(np.ascontiguousarray(a).tobytes()) & 0xFFFFFFFF)
+
+
+def training_check(eng, som, pool, n_images, reduce=None):
+    """Trains the first n_images of the pool on the seeded SOM and returns checksums of the BMU sequence, the hit
+    counters and the trained SOM.  uint8 training is bit-exact, so the values do not depend on the number of
+    ranks.  reduce(array, op): combines the ranks' partial results ("min" / "sum"); None for a single rank."""
+    eng.set_som(som)
+    counts0 = eng.update_counts().astype(np.int64)       # the counters run over the context's whole life
+    eng.train(pool[:n_images])
+    eng.synchronize()
+    bmus = eng.bmu_log(n_images).astype(np.int64)        # 0xFFFFFFFF where another rank owns the unit
+    counts = eng.update_counts().astype(np.int64) - counts0
+    part = eng.get_som(np.zeros_like(som))
+    if reduce is not None:
+        bmus, counts, part = reduce(bmus, "min"), reduce(counts, "sum"), reduce(part, "sum")
+    return {"images": n_images, "bmu_crc32": crc(bmus.astype(np.uint32)), "counts_crc32": crc(counts.astype(np.uint32)),
+            "som_crc32": crc(part.astype(np.float32)), "bmu_first8": [int(b) for b in bmus[:8]]}
+
+
+def make_engine(w, N, device, rank=0, world=1, max_batch=0, options=None):
+    from pink_b200 import engine
+    return engine.Engine(N, w["channels"], w["image_dim"], w["neuron_dim"], w["ed_dim"], w["rotations"], w["flip"],
+                         w["mode"], device=device, rank=rank, world_size=world, max_batch=max_batch, options=options)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -167,12 +231,15 @@ def main():
     ap.add_argument("--batch", type=int, default=512, help="images per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the map / other-configuration blocks")
+    ap.add_argument("--option", action="append", default=[], help="context switch name=value (see pink_b200_set_option)")
     args = ap.parse_args()
     w = WORKLOAD
     if args.impl == "reference":
         return run_reference(args, w)
     if args.warmup < 3:
         args.warmup = 3
+    options = {k: int(v) for k, v in (o.split("=") for o in args.option)}
 
     import torch
     import torch.distributed as dist
@@ -181,27 +248,40 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            sys.exit("bench.py --gpus %d must be launched with torch.distributed.run (one rank per GPU)" % args.gpus)
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        sys.exit("bench.py --gpus %d must be launched with torch.distributed.run (one rank per GPU)" % args.gpus)
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def reduce(a, op):
+        if world == 1:
+            return a
+        t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        dist.all_reduce(t, op=dist.ReduceOp.MIN if op == "min" else dist.ReduceOp.SUM)
+        return t.cpu().numpy()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
 
     N, som, pool = make_inputs(w)
     F = engine.update_factors(w["som_layout"], w["som_dim"], w["som_dim"], capi.FUNC_GAUSSIAN, w["sigma"], w["damping"])
     B = args.batch
     isz = pool.shape[1]
-    eng = engine.Engine(N, w["channels"], w["image_dim"], w["neuron_dim"], w["ed_dim"], w["rotations"], w["flip"],
-                        capi.UINT8, device=local, rank=rank, world_size=world, max_batch=B)
+    eng = make_engine(w, N, local, rank, world, B, options)
     if world > 1:
         uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
             uid.copy_(torch.frombuffer(bytearray(engine.Engine.unique_id()), dtype=torch.uint8))
         dist.broadcast(uid, 0)
         eng.comm_init(bytes(uid.cpu().numpy()))
-    eng.set_som(som)
     eng.set_update_factors(F)
+
+    # ---- untimed: a fixed training prefix whose results must not depend on the number of ranks -----------
+    check = training_check(eng, som, pool, CHECK_IMAGES, reduce if world > 1 else None)
 
     d_pool = torch.from_numpy(pool).cuda()
     h_pool = torch.from_numpy(pool).pin_memory()
@@ -211,27 +291,21 @@ def main():
     def slice_ptr(t, step):
         return t.data_ptr() + (step % n_slices) * B * isz * 4
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
+    def timed(fn, steps, sync, ev_stream):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
+        e0.record(ev_stream)
         for s in range(steps):
             fn(s)
-        e1.record(stream)
-        eng.synchronize()
+        e1.record(ev_stream)
+        sync()
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    # ---- device-resident throughput -----------------------------------------
+    # ---- device-resident training throughput ---------------------------------------------------------------
     step_dev = lambda s: eng.train_device(slice_ptr(d_pool, s), B)
     for s in range(args.warmup):
         step_dev(s)
@@ -241,12 +315,12 @@ def main():
         time.sleep(0.3)
     exchange_kind = eng.exchange_kind()
     launches0 = eng.launch_count()
-    ms = timed(lambda s: step_dev(args.warmup + s), args.steps)
+    ms = timed(lambda s: step_dev(args.warmup + s), args.steps, eng.synchronize, stream)
     launches = eng.launch_count() - launches0          # kernels of this library launched inside the timed region
     clocks = sampler.stop() if rank == 0 else None
     value = args.steps * B / (ms * 1e-3)
 
-    # ---- end to end: pinned host images in, BMU hit counters out, every step --
+    # ---- end to end: pinned host images in, BMU hit counters out, every step -------------------------------
     counts = np.empty(N, np.uint32)
 
     def step_e2e(s):
@@ -254,15 +328,16 @@ def main():
         capi.check(capi.lib.pink_b200_get_update_counts(eng._h, counts.ctypes.data))
     for s in range(3):
         step_e2e(s)
-    ms_e2e = timed(step_e2e, args.steps)
+    ms_e2e = timed(step_e2e, args.steps, eng.synchronize, stream)
     e2e = args.steps * B / (ms_e2e * 1e-3)
 
-    # ---- per-kernel device time (separate profiled pass of the same workload) --
+    # ---- per-phase device time (separate profiled pass of the same workload) -------------------------------
     prof_steps = min(B, 256)
     stats0 = eng.update_stats()
     eng.profile_begin(prof_steps)
     eng.train_device(slice_ptr(d_pool, 1), prof_steps)
     phase_ms, covered = eng.profile_end()
+    detail = eng.profile_detail()
     stats1 = eng.update_stats()
 
     peaks = measured_peaks()
@@ -270,43 +345,75 @@ def main():
     K = w["channels"] * w["ed_dim"] ** 2
     P = w["channels"] * w["neuron_dim"] ** 2
     nl = eng.count
-    # Algorithmic bytes of the update: every neuron of this shard with a non-zero factor for the image's best
-    # matching unit is read and written once (8 * N_upd * P, the reference rewrites all of them).  The kernel
-    # here moves fewer: it leaves out neurons that provably cannot change and does not write back neurons in
-    # which no value changed (both counted on the device) -- with bit-identical maps.
-    bmus = eng.bmu_log(prof_steps)
-    nz_rows = (F[:, eng.first:eng.first + nl] != 0).sum(1)
-    owned = bmus[bmus != 0xFFFFFFFF]
-    n_upd = float(nz_rows[owned].mean()) if (world == 1 and len(owned)) else float(nz_rows.mean())
+    # Update traffic.  Algorithmic (what the reference's kernel moves): every neuron of this shard with a non-zero
+    # factor for the image's best matching unit is read and written once, 8 * N_upd * P.  Moved: the kernel leaves
+    # out neurons that provably cannot change and does not write back neurons in which no value changed (both
+    # counted on the device), with bit-identical maps: 4 P per neuron read + (4 P + K) per neuron written.
+    bmus = reduce(eng.bmu_log(prof_steps).astype(np.int64), "min")
+    nz_rows = (F[:, eng.neurons] != 0).sum(1)
+    n_upd = float(nz_rows[bmus[bmus < N]].mean())
     n_read = (stats1[0] - stats0[0]) / prof_steps
     n_written = (stats1[1] - stats0[1]) / prof_steps
     t_dist = phase_ms["distance"] / covered * 1e-3
+    t_bmu = phase_ms["bmu"] / covered * 1e-3
     t_upd = phase_ms["update"] / covered * 1e-3
+    t_rot = phase_ms["rotate"] / covered * 1e-3
     dist_ops = 2.0 * nl * T * K
     upd_bytes = 8.0 * n_upd * P
     moved_bytes = 4.0 * P * n_read + (4.0 * P + K) * n_written
     int8_peak = 2.0 * peaks["bf16_tflops"]
+    mma_peak = tracked_figure("mma_i8_peak.txt", "mma_only_tops")
+    fused = detail["launch_us"] > 0                  # the persistent kernel ran: phases come from device-timer stamps
+    timing = ("device-timer stamps of block 0 inside the persistent kernel, each phase up to and including its grid "
+              "barrier, %d steps" % covered) if fused else \
+             ("CUDA events around every launch in a separate profiled pass of %d steps" % covered)
     kernels = {
-        "update_kernel": {"bound": "hbm", "achieved": upd_bytes / t_upd / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                          "frac": upd_bytes / t_upd / 1e9 / peaks["hbm_gbs"], "us_per_launch": t_upd * 1e6,
-                          "algorithmic_bytes": upd_bytes, "neurons_with_nonzero_factor": n_upd,
-                          "moved_bytes": moved_bytes, "moved_frac": moved_bytes / t_upd / 1e9 / peaks["hbm_gbs"],
-                          "neurons_read": n_read, "neurons_written": n_written},
-        "distance_tc_kernel": {"bound": "tensor", "achieved": dist_ops / t_dist / 1e12, "peak": int8_peak,
-                               "unit": "TOP/s", "frac": dist_ops / t_dist / 1e12 / int8_peak,
-                               "us_per_launch": t_dist * 1e6, "algorithmic_ops": dist_ops,
-                               "peak_note": "int8 peak taken as 2 x the %s bf16 cuBLAS figure" % peaks["source"]},
-        "rotate_kernel": {"us_per_launch": phase_ms["rotate"] / covered * 1e3},
-        "bmu_kernel+exchange": {"us_per_launch": phase_ms["bmu"] / covered * 1e3},
+        "update": {"bound": "hbm", "achieved": moved_bytes / t_upd / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                   "frac": moved_bytes / t_upd / 1e9 / peaks["hbm_gbs"], "us_per_image": t_upd * 1e6,
+                   "moved_bytes": moved_bytes, "neurons_read": n_read, "neurons_written": n_written,
+                   "effective_bytes": upd_bytes, "effective_frac": upd_bytes / t_upd / 1e9 / peaks["hbm_gbs"],
+                   "neurons_with_nonzero_factor": n_upd,
+                   "note": "achieved / frac use the bytes the kernel moves; effective_* the 8 * N_upd * P the "
+                           "reference's kernel would move for the same step"},
+        "distance": {"bound": "tensor", "achieved": dist_ops / t_dist / 1e12, "peak": int8_peak, "unit": "TOP/s",
+                     "frac": dist_ops / t_dist / 1e12 / int8_peak, "us_per_image": t_dist * 1e6,
+                     "algorithmic_ops": dist_ops,
+                     "peak_note": "int8 peak taken as 2 x the %s bf16 cuBLAS figure" % peaks["source"],
+                     "frac_of_mma_only_peak": (dist_ops / t_dist / 1e12 / mma_peak) if mma_peak else None,
+                     "mma_only_peak_tops": mma_peak},
+        "bmu+exchange+list": {"us_per_image": t_bmu * 1e6},
+        "rotate": {"us_per_image": t_rot * 1e6},
     }
-    dominant = "update_kernel" if t_upd >= t_dist else "distance_tc_kernel"
-    roof = dict(kernels[dominant])
-    roof["kernel"] = dominant
-    # dram__bytes_read + dram__bytes_write of one launch of that kernel, from the ncu capture summarised under profiles/
-    # (update: a step that read about 1750 of the 2791 neurons and rewrote few; 139 MB when every neuron is rewritten)
-    roof["traffic"] = {"update_kernel": 58.84e6, "distance_tc_kernel": 17.41e6}[dominant] if world == 1 else None
+    roof = dict(kernels["update"] if t_upd >= t_dist else kernels["distance"])
+    roof["kernel"] = ("train_steps_kernel, " if fused else "") + ("update phase" if t_upd >= t_dist else "distance phase")
     roof["peak_source"] = peaks["source"]
-    roof["timing"] = "CUDA events around every launch in a separate profiled pass of %d steps" % covered
+    roof["timing"] = timing
+    # DRAM bytes of one image's share of a launch, from the tracked ncu summary, scaled by the bytes the live pass moved
+    cap_traffic = tracked_figure("train_steps_kernel_u8_c4.txt", "dram_bytes_per_image")
+    cap_moved = tracked_figure("train_steps_kernel_u8_c4.txt", "moved_bytes_per_image")
+    roof["traffic"] = cap_traffic * moved_bytes / cap_moved if (cap_traffic and cap_moved and world == 1) else None
+    roof["traffic_note"] = ("profiles/train_steps_kernel_u8_c4.txt (dram__bytes_read + write per image of a captured "
+                            "launch), scaled by moved_bytes live / captured") if roof["traffic"] else None
+    timeline = None
+    if fused:
+        sol_us = dist_ops / (int8_peak * 1e12) * 1e6 + moved_bytes / (peaks["hbm_gbs"] * 1e9) * 1e6
+        per_image = detail["launch_us"] / max(detail["images_per_launch"], 1.0)
+        timeline = dict(detail)
+        timeline.update({"us_per_image_in_kernel": per_image, "rotate_us_per_image": t_rot * 1e6,
+                         "step_us_per_image_measured": ms / args.steps * 1e3 / B,
+                         "speed_of_light_us_per_image": sol_us, "frac_of_speed_of_light": sol_us / per_image,
+                         "note": "launch_us: CUDA events around one launch of the persistent kernel; speed of light = "
+                                 "distance ops / int8 peak + moved update bytes / HBM peak (the phases depend on each "
+                                 "other and cannot overlap)"})
+
+    # ---- mapping throughput: images sharded over the ranks, one whole-SOM context per rank -----------------
+    extras = {}
+    if not args.no_extras:
+        eng.close()
+        eng = None
+        extras["map"] = bench_map(torch, dist, barrier, rank, world, local, som, pool)
+        if world == 1:
+            extras["other_configs"] = bench_other_configs(torch, local)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -323,20 +430,102 @@ def main():
             "config": {"workload": w["name"], "images_per_step": B, "parallelism": "neuron-shard x%d" % world,
                        "exchange": {0: "none", 1: "nccl all-gather", 2: "peer-memory records",
                                     3: "peer-memory records + shared rotation work"}[exchange_kind],
+                       "options": options,
                        "l2": "every step trains on a different slice of a 134 MB image pool; SOM (90 MB) + operand "
                              "(11 MB) + batch (34 MB) exceed the 126 MB L2"},
             "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": B * isz * 4, "d2h_bytes_per_step": N * 4,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches,
             "clocks": clocks,
+            "check": check,
             "roofline": roof,
             "kernels": kernels,
+            "timeline": timeline,
             "cpu_baseline": cpu,
         }
+        line.update(extras)
         print(json.dumps(line))
-    eng.close()
+    if eng is not None:
+        eng.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_map(torch, dist, barrier, rank, world, local, som4, pool4):
+    """Mapping images/s of C4 (uint8) and C2 (float32): every rank holds the whole SOM and maps its share of the
+    images (round robin); device-resident and through host buffers (pinned images in, results out)."""
+    out = {}
+    for key, n_img in (("C4", 2048), ("C2", 2048)):
+        w = WORKLOADS[key]
+        if key == "C4":
+            N, som, pool = som_size(w), som4, pool4
+        else:
+            N, som, pool = make_inputs(w, n_img)
+        mine = np.ascontiguousarray(pool[rank::world])
+        n = len(mine)
+        eng = make_engine(w, N, local)
+        eng.set_som(som)
+        d_img = torch.from_numpy(mine).cuda()
+        d_dist = torch.empty((n, N), dtype=torch.float32, device="cuda")
+        d_rot = torch.empty((n, N), dtype=torch.int32, device="cuda")
+        h_img = torch.from_numpy(mine).pin_memory()
+        h_dist = torch.empty((n, N), dtype=torch.float32).pin_memory()
+        h_rot = torch.empty((n, N), dtype=torch.int32).pin_memory()
+        from pink_b200 import capi
+        dev = lambda: eng.map_device(d_img.data_ptr(), n, d_dist.data_ptr(), d_rot.data_ptr())
+        host = lambda: capi.check(capi.lib.pink_b200_map(eng._h, h_img.data_ptr(), n, h_dist.data_ptr(), h_rot.data_ptr()))
+        res = {}
+        for name, fn in (("value", dev), ("e2e", host)):
+            fn()
+            eng.synchronize()
+            reps = 3
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                fn()
+            eng.synchronize()
+            barrier()
+            dt = torch.tensor([time.perf_counter() - t0], device="cuda")
+            if world > 1:
+                dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            res[name] = reps * len(pool) / float(dt.item())
+        T = w["rotations"] * (2 if w["flip"] else 1)
+        K = w["channels"] * w["ed_dim"] ** 2
+        res.update({"unit": "images/s", "workload": w["name"], "images": len(pool), "sharding": "images round robin x%d" % world,
+                    "distance_ops_per_image": 2.0 * N * T * K,
+                    "timing": "host clock around %d whole passes, synchronised on both sides, max over ranks" % reps})
+        out[key] = res
+        eng.close()
+    return out
+
+
+def bench_other_configs(torch, local):
+    """Training images/s of the smaller configurations (one GPU, device-resident images)."""
+    from pink_b200 import capi, engine
+    out = {}
+    for key, n_img in (("C1", 2000), ("C3", 256)):
+        w = WORKLOADS[key]
+        N, som, pool = make_inputs(w, n_img)
+        F = engine.update_factors(w["som_layout"], w["som_dim"], w["som_dim"], capi.FUNC_GAUSSIAN, w["sigma"], w["damping"])
+        eng = make_engine(w, N, local)
+        eng.set_som(som)
+        eng.set_update_factors(F)
+        d_pool = torch.from_numpy(pool).cuda()
+        eng.train_device(d_pool.data_ptr(), n_img)
+        eng.synchronize()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.train_device(d_pool.data_ptr(), n_img)
+        eng.synchronize()
+        dt = time.perf_counter() - t0
+        eng.profile_begin(min(n_img, 128))
+        eng.train_device(d_pool.data_ptr(), min(n_img, 128))
+        phase_ms, covered = eng.profile_end()
+        out[key] = {"value": n_img / dt, "unit": "images/s", "workload": w["name"], "images": n_img,
+                    "phase_us_per_image": {k: v / covered * 1e3 for k, v in phase_ms.items()},
+                    "persistent_kernel": eng.profile_detail()["launch_us"] > 0}
+        eng.close()
+    return out
 
 
 if __name__ == "__main__":

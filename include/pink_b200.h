@@ -102,11 +102,15 @@ const char* pink_b200_version(void);
 int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out);
 int pink_b200_destroy(pink_b200_ctx* ctx);
 
-/* Neurons [first, first+count) of the SOM live on this context's device:
- * N/world (+1 for the first N % world ranks), contiguous, as the reference's
- * multi-GPU split (src/CudaLib/generate_euclidean_distance_matrix_first_step_multi_gpu.h:65-77). */
+/* The neurons that live on this context's device: global neurons first + j * stride, j < count, with
+ * stride = pink_b200_shard_stride(ctx).  count is N/world (+1 for the first N % world ranks), the sizes of
+ * the reference's multi-GPU split (src/CudaLib/generate_euclidean_distance_matrix_first_step_multi_gpu.h:65-77).
+ * By default the shards are interleaved (first = rank, stride = world_size), so that the neurons around any best
+ * matching unit -- the ones an image rewrites -- are spread evenly over the ranks; option "sharding" = 1 selects
+ * the reference's contiguous ranges (stride 1).  Mapping results are in this local order. */
 int pink_b200_shard(const pink_b200_ctx* ctx, uint32_t* first, uint32_t* count);
-/* The same split as a pure host function (no context, no GPU). */
+uint32_t pink_b200_shard_stride(const pink_b200_ctx* ctx);
+/* The reference's contiguous split as a pure host function (no context, no GPU). */
 int pink_b200_shard_range(uint32_t n_neurons, uint32_t world_size, uint32_t rank, uint32_t* first, uint32_t* count);
 
 /* Switches of a context, to be set after pink_b200_create and before pink_b200_comm_init /
@@ -115,6 +119,7 @@ int pink_b200_shard_range(uint32_t n_neurons, uint32_t world_size, uint32_t rank
  *   "step_kernel"          0 (default) whole batches of training steps in one persistent kernel where the
  *                          geometry allows it; 1 two kernels per image (distance, update); 2 four kernels
  *                          per image (distance, best matching unit, work list, update)
+ *   "sharding"             0 (default) interleaved neuron shards, 1 contiguous ranges as in the reference
  *   "exchange"             0 (default) per-rank records through peer memory where possible; 1 NCCL all-gather
  *   "rotation_sharing"     -1 (default) pairs of ranks share the rotation work; 0 every rank rotates every
  *                          image; g >= 2 groups of g consecutive ranks share
@@ -139,7 +144,7 @@ int pink_b200_comm_init(pink_b200_ctx* ctx, const void* id128);
  * shard) and build the distance operand.  Stands for the device copy taken at
  * construction, Trainer.h:219 / Mapper.h:140. */
 int pink_b200_set_som(pink_b200_ctx* ctx, const float* host_som);
-/* Write this rank's shard into rows [first, first+count) of host_som ([N][P]);
+/* Write this rank's shard into its rows (first + j * stride) of host_som ([N][P]);
  * other rows are left untouched.  Stands for Trainer::update_som(), Trainer.h:306-309. */
 int pink_b200_get_som(pink_b200_ctx* ctx, float* host_som);
 /* Upload the N x N update-factor table F[bmu * N + n] the reference builds on
@@ -236,6 +241,13 @@ int pink_b200_profile_end(pink_b200_ctx* ctx, double ms_sum[4], uint64_t* steps)
  * (+ exchange between ranks) and work list, rewriting its own neurons, waiting at the second grid barrier;
  * out[7] unused. */
 int pink_b200_profile_detail(pink_b200_ctx* ctx, double out[8]);
+/* The raw stamps behind it, [steps][blocks][12] words: nanoseconds of the device timer when (0) the image began,
+ * (1) the block had reduced its own distance tiles, (2) it had passed the first grid barrier, (3) its work
+ * list was built, (4) its own neurons were rewritten and stored, (5) it had passed the second grid barrier;
+ * (6) neuron planes it rewrote, (7) distance tiles it computed; inside the phases: (8) first operand slice
+ * arrived, (9) last MMA issued, (10) accumulators complete, (11) first neuron plane arrived.  *blocks and
+ * *steps are always set; `out` may be NULL to ask for the sizes only. */
+int pink_b200_profile_stamps(pink_b200_ctx* ctx, uint64_t* out, uint64_t capacity, uint32_t* blocks, uint64_t* steps);
 
 /* ---- single stages on device buffers (what the context calls internally) ---
  * Exposed for kernel-level parity tests and benchmarks.  `stream` is a

@@ -28,9 +28,18 @@ def build(force=False):
     if force or not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(src):
         subprocess.check_call(["make", "-C", _HERE, "libpink_oracle.so"], stdout=subprocess.DEVNULL)
     shim = os.path.join(_HERE, "ref_shim.cpp")
-    if os.path.isdir(os.environ.get("PINK_REF", "/root/reference") + "/src"):
+    tree = reference_tree()
+    if tree:
         if force or not os.path.exists(_REF) or os.path.getmtime(_REF) < os.path.getmtime(shim):
-            subprocess.check_call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
+            subprocess.check_call(["make", "-C", _HERE, "ref", "PINK_REF=" + tree], stdout=subprocess.DEVNULL)
+
+
+def reference_tree():
+    """The reference's source tree: $PINK_REF, else a directory `reference` beside this repository; None if absent."""
+    for cand in (os.environ.get("PINK_REF"), os.path.join(_HERE, "..", "..", "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src", "SelfOrganizingMapLib")):
+            return os.path.abspath(cand)
+    return None
 
 
 def _fp(a):
@@ -91,6 +100,7 @@ def ref():
         r.ref_update_factors.argtypes = [C.c_int, C.c_uint32, C.c_uint32, C.c_int, C.c_float, C.c_float, C.c_float,
                                          C.c_void_p]
         r.ref_fill_random_uniform.argtypes = [C.c_void_p, C.c_uint64, C.c_uint32]
+        r.ref_set_num_threads.argtypes = [C.c_int]
         _ref = r
     return _ref
 

@@ -231,4 +231,7 @@ void ref_fill_random_uniform(float* a, uint64_t n, uint32_t seed) { fill_random_
 
 int ref_num_threads() { return omp_get_max_threads(); }
 
+// Launchers such as torch.distributed.run export OMP_NUM_THREADS=1; a timed baseline sets its thread count itself.
+void ref_set_num_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+
 } // extern "C"

@@ -35,6 +35,7 @@ SYMBOLS = {
     "pink_b200_create": (C.c_int, [C.POINTER(Config), C.POINTER(C.c_void_p)]),
     "pink_b200_destroy": (C.c_int, [C.c_void_p]),
     "pink_b200_shard": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
+    "pink_b200_shard_stride": (C.c_uint32, [C.c_void_p]),
     "pink_b200_shard_range": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32),
                                         C.POINTER(C.c_uint32)]),
     "pink_b200_set_option": (C.c_int, [C.c_void_p, C.c_char_p, C.c_longlong]),
@@ -57,6 +58,8 @@ SYMBOLS = {
     "pink_b200_profile_begin": (C.c_int, [C.c_void_p, C.c_uint32]),
     "pink_b200_profile_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "pink_b200_profile_detail": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
+    "pink_b200_profile_stamps": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32),
+                                           C.POINTER(C.c_uint64)]),
     "pink_b200_som_size": (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32]),
     "pink_b200_som_distances": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
     "pink_b200_update_factors": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,

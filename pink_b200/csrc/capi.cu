@@ -173,7 +173,7 @@ struct pink_b200_ctx
 {
     pink_b200_config cfg{};
     Geometry g{};
-    uint32_t first = 0, count = 0;
+    uint32_t first = 0, count = 0, stride = 1;    // local neuron j is global neuron first + j * stride
     uint32_t train_batch = 0, map_batch = 0;
     cudaStream_t stream = nullptr, copy_stream = nullptr, rot_stream = nullptr;
     cudaEvent_t copied[2] = { nullptr, nullptr }, consumed[2] = { nullptr, nullptr };
@@ -324,7 +324,7 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     da.n_img = 1;
     da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status; da.single_cta = !c->opt_mma_pairs;
     BmuArgs ba{};
-    ba.keys = c->d_keys; ba.n = c->count; ba.first_neuron = c->first; ba.shift = key_shift(g.mode);
+    ba.keys = c->d_keys; ba.n = c->count; ba.first_neuron = c->first; ba.neuron_stride = c->stride; ba.shift = key_shift(g.mode);
     ba.pairs = c->d_pairs; ba.rank = c->cfg.rank; ba.world = c->cfg.world_size;
     ba.factors = c->d_factors; ba.items = c->d_items; ba.n_items = c->d_nitems;
     ba.counts = c->d_counts; ba.bmu_log = bmu_slot;
@@ -393,7 +393,7 @@ int train_steps_batch(pink_b200_ctx* c, size_t slot_img, uint32_t cnt, uint32_t*
     a.rmax = c->d_wrange ? c->d_rmax + slot_img : nullptr;
     a.factors = c->d_factors;
     a.owners = c->d_owners;
-    a.n_img = cnt; a.first_neuron = c->first; a.rank = c->cfg.rank; a.world = c->cfg.world_size;
+    a.n_img = cnt; a.first_neuron = c->first; a.neuron_stride = c->stride; a.rank = c->cfg.rank; a.world = c->cfg.world_size;
     a.counts = c->d_counts; a.bmu_log = bmu_slots; a.stats = c->d_stats; a.status = c->d_status;
     a.ctrl = c->d_ctrl;
     a.stamps = nullptr;
@@ -406,7 +406,7 @@ int train_steps_batch(pink_b200_ctx* c, size_t slot_img, uint32_t cnt, uint32_t*
     a.xchg_timeout_ns = (unsigned long long)std::max<long long>(1, c->opt_exchange_timeout_ms) * 1000000ull;
     cudaEvent_t* ev = nullptr;
     if (c->prof_used < c->prof_cap) {
-        if (c->d_stamps && c->prof_used + cnt <= c->stamps_cap) a.stamps = c->d_stamps + 8 * c->prof_used;
+        if (c->d_stamps && c->prof_used + cnt <= c->stamps_cap) a.stamps = c->d_stamps + (size_t)kStepStampWords * c->plan.grid * c->prof_used;
         if (2 * (c->prof_launches + 1) <= c->prof_launch_events.size()) ev = &c->prof_launch_events[2 * c->prof_launches];
         c->prof_used += std::min<size_t>(cnt, c->prof_cap - c->prof_used);
     }
@@ -768,7 +768,11 @@ int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
     const uint32_t W = cfg->world_size, N = cfg->n_neurons;
     const uint32_t base = N / W, extra = N % W;
     c->count = base + (cfg->rank < extra ? 1 : 0);
-    c->first = cfg->rank * base + (cfg->rank < extra ? cfg->rank : extra);
+    // Interleaved shards (rank r holds neurons r, r + W, r + 2W, ...): the neighbourhood of any best matching unit
+    // then spreads evenly over the ranks, so every rank has the same share of every image's update.  The sizes are
+    // those of the reference's contiguous split (option "sharding" = 1 selects that one).
+    c->first = cfg->rank; c->stride = W;
+    (void)extra;
     c->train_batch = cfg->max_batch ? cfg->max_batch : 256;
     {
         // Mapping batch: bound the transform operand of one batch to about 1 GiB.
@@ -924,6 +928,8 @@ int pink_b200_shard(const pink_b200_ctx* c, uint32_t* first, uint32_t* count)
     return PINK_B200_OK;
 }
 
+uint32_t pink_b200_shard_stride(const pink_b200_ctx* c) { return c ? c->stride : 0; }
+
 int pink_b200_set_option(pink_b200_ctx* c, const char* name, long long value)
 {
     if (!c || !name) return fail(PINK_B200_EINVAL, "null argument");
@@ -934,6 +940,11 @@ int pink_b200_set_option(pink_b200_ctx* c, const char* name, long long value)
         if (value < 0 || value > 2) return fail(PINK_B200_EINVAL, "step_kernel must be 0, 1 or 2");
         c->opt_step_kernel = (int)value;
         c->fuse_update = update_can_fuse(c->g) && value != 2;
+    } else if (key == "sharding") {
+        if (value < 0 || value > 1) return fail(PINK_B200_EINVAL, "sharding must be 0 or 1");
+        const uint32_t W = c->cfg.world_size, N = c->cfg.n_neurons, base = N / W, extra = N % W, r = c->cfg.rank;
+        if (value == 1) { c->first = r * base + (r < extra ? r : extra); c->stride = 1; }
+        else { c->first = r; c->stride = W; }
     } else if (key == "exchange") {
         if (value < 0 || value > 1) return fail(PINK_B200_EINVAL, "exchange must be 0 or 1");
         c->opt_exchange = (int)value;
@@ -992,7 +1003,7 @@ int pink_b200_set_som(pink_b200_ctx* c, const float* host_som)
     // while its DMA is still in flight on the legacy stream, which the
     // context's non-blocking stream does not wait for.
     CU_TRY(cudaMemcpy2DAsync(c->d_som, (size_t)g.Pp * sizeof(float), host_som + (size_t)c->first * g.P,
-                             (size_t)g.P * sizeof(float), (size_t)g.P * sizeof(float), c->count,
+                             (size_t)c->stride * g.P * sizeof(float), (size_t)g.P * sizeof(float), c->count,
                              cudaMemcpyHostToDevice, c->stream));
     if ((c->fuse_update || c->plan_ok) && !c->d_wrange) CU_TRY(cudaMalloc(&c->d_wrange, (size_t)c->count * sizeof(uint2)));
     LAUNCH_TRY(launch_quantize_som(g, c->d_som, c->count, c->d_a0, c->d_a1, c->d_anorm, c->stream, c->d_wrange));
@@ -1009,7 +1020,7 @@ int pink_b200_get_som(pink_b200_ctx* c, float* host_som)
     CU_TRY(cudaSetDevice(c->cfg.device));
     int rc = check_status(c);
     if (rc) return rc;
-    CU_TRY(cudaMemcpy2DAsync(host_som + (size_t)c->first * g.P, (size_t)g.P * sizeof(float), c->d_som,
+    CU_TRY(cudaMemcpy2DAsync(host_som + (size_t)c->first * g.P, (size_t)c->stride * g.P * sizeof(float), c->d_som,
                              (size_t)g.Pp * sizeof(float), (size_t)g.P * sizeof(float), c->count,
                              cudaMemcpyDeviceToHost, c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
@@ -1023,13 +1034,21 @@ int pink_b200_set_update_factors(pink_b200_ctx* c, const float* host_factors)
     CU_TRY(cudaStreamSynchronize(c->stream));
     const size_t N = c->cfg.n_neurons;
     if (!c->d_factors) CU_TRY(cudaMalloc(&c->d_factors, N * c->count * sizeof(float)));
-    CU_TRY(cudaMemcpy2DAsync(c->d_factors, (size_t)c->count * sizeof(float), host_factors + c->first, N * sizeof(float),
-                             (size_t)c->count * sizeof(float), N, cudaMemcpyHostToDevice, c->stream));
-    CU_TRY(cudaStreamSynchronize(c->stream));
+    {
+        // this shard's columns of the table, gathered on the host: F[b][first + j * stride]
+        std::vector<float> cols(N * c->count);
+        for (size_t b = 0; b < N; ++b) {
+            const float* row = host_factors + b * N + c->first;
+            float* out = cols.data() + b * c->count;
+            for (size_t j = 0; j < c->count; ++j) out[j] = row[j * c->stride];
+        }
+        CU_TRY(cudaMemcpyAsync(c->d_factors, cols.data(), cols.size() * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+        CU_TRY(cudaStreamSynchronize(c->stream));
+    }
     if (c->plan_ok) {
         // which block of the persistent kernel rewrites which neuron: spread every neighbourhood over the blocks
         std::vector<uint32_t> owners((size_t)c->plan.grid * c->plan.owned_per_block);
-        step_assign_owners(host_factors, (uint32_t)N, c->first, c->count, c->plan, owners.data());
+        step_assign_owners(host_factors, (uint32_t)N, c->first, c->stride, c->count, c->plan, owners.data());
         CU_TRY(cudaMemcpyAsync(c->d_owners, owners.data(), owners.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
         CU_TRY(cudaStreamSynchronize(c->stream));
     }
@@ -1224,10 +1243,10 @@ int pink_b200_profile_begin(pink_b200_ctx* c, uint32_t max_steps)
     }
     if (c->plan_ok && c->stamps_cap < max_steps) {
         free_dev(c->d_stamps);
-        CU_TRY(cudaMalloc(&c->d_stamps, (size_t)max_steps * 8 * sizeof(unsigned long long)));
+        CU_TRY(cudaMalloc(&c->d_stamps, (size_t)max_steps * c->plan.grid * kStepStampWords * sizeof(unsigned long long)));
         c->stamps_cap = max_steps;
     }
-    if (c->d_stamps) CU_TRY(cudaMemsetAsync(c->d_stamps, 0, c->stamps_cap * 8 * sizeof(unsigned long long), c->stream));
+    if (c->d_stamps) CU_TRY(cudaMemsetAsync(c->d_stamps, 0, c->stamps_cap * c->plan.grid * kStepStampWords * sizeof(unsigned long long), c->stream));
     c->prof_cap = max_steps;
     c->prof_used = c->prof_rot_used = 0;
     c->prof_launches = c->prof_launch_images = 0;
@@ -1248,10 +1267,11 @@ int pink_b200_profile_end(pink_b200_ctx* c, double ms_sum[4], uint64_t* steps)
     }
     if (c->use_steps) {
         // persistent kernel: the phases of a step are read from block 0's device-timer stamps
-        std::vector<unsigned long long> t(8 * c->prof_used);
+        const size_t per_step = (size_t)kStepStampWords * c->plan.grid;
+        std::vector<unsigned long long> t(per_step * c->prof_used);
         if (c->prof_used) CU_TRY(cudaMemcpy(t.data(), c->d_stamps, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
         for (size_t s = 0; s < c->prof_used; ++s) {
-            const unsigned long long* q = &t[8 * s];
+            const unsigned long long* q = &t[per_step * s];
             ms_sum[1] += (double)(q[2] - q[0]) * 1e-6;      // distance phase up to the first grid barrier
             ms_sum[2] += (double)(q[3] - q[2]) * 1e-6;      // best matching unit (+ exchange) and work list
             ms_sum[3] += (double)(q[5] - q[3]) * 1e-6;      // update phase up to the second grid barrier
@@ -1284,10 +1304,26 @@ int pink_b200_profile_detail(pink_b200_ctx* c, double out[8])
     }
     out[0] = 1e3 * ms_total / (double)c->prof_launches;
     out[1] = (double)c->prof_launch_images / (double)c->prof_launches;
-    std::vector<unsigned long long> t(8 * c->prof_used);
+    const size_t per_step = (size_t)kStepStampWords * c->plan.grid;
+    std::vector<unsigned long long> t(per_step * c->prof_used);
     CU_TRY(cudaMemcpy(t.data(), c->d_stamps, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     for (size_t s = 0; s < c->prof_used; ++s)
-        for (int k = 0; k < 5; ++k) out[2 + k] += (double)(t[8 * s + k + 1] - t[8 * s + k]) * 1e-3 / (double)c->prof_used;
+        for (int k = 0; k < 5; ++k)
+            out[2 + k] += (double)(t[per_step * s + k + 1] - t[per_step * s + k]) * 1e-3 / (double)c->prof_used;
+    return PINK_B200_OK;
+}
+
+int pink_b200_profile_stamps(pink_b200_ctx* c, uint64_t* out, uint64_t capacity, uint32_t* blocks, uint64_t* steps)
+{
+    if (!c || !blocks || !steps) return fail(PINK_B200_EINVAL, "null argument");
+    *blocks = c->use_steps ? c->plan.grid : 0;
+    *steps = c->use_steps ? c->prof_used : 0;
+    const uint64_t words = (uint64_t)kStepStampWords * *blocks * *steps;
+    if (!out || words == 0) return PINK_B200_OK;
+    if (capacity < words) return fail(PINK_B200_EINVAL, "buffer too small for the stamps");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    CU_TRY(cudaMemcpy(out, c->d_stamps, words * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     return PINK_B200_OK;
 }
 

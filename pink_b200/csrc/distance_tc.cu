@@ -331,7 +331,7 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
             unsigned long long bc, bn;
             block_argmin_keys(p.tail.keys, p.tail.n, p.tail.shift, kThreads, tc_s, tn_s, bc, bn);
             __syncthreads();
-            if (threadIdx.x == 0) { tc_s[0] = bc; tn_s[0] = bn == ~0ull ? ~0ull : bn + p.tail.first_neuron; }
+            if (threadIdx.x == 0) { tc_s[0] = bc; tn_s[0] = bn == ~0ull ? ~0ull : shard_global(p.tail.first_neuron, p.tail.neuron_stride, bn); }
             __syncthreads();
             publish_record(p.tail, tc_s[0], tn_s[0]);
         }

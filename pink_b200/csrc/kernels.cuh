@@ -112,6 +112,7 @@ constexpr uint32_t kXchgMaxRanks = 16;
 struct BmuArgs
 {
     unsigned long long* keys; uint32_t n, first_neuron, shift;   // this shard's per-neuron minima (re-armed in phase 2)
+    uint32_t neuron_stride;           // local neuron j is global neuron first_neuron + j * neuron_stride
     BmuPair* pairs; uint32_t rank, world;                        // per-rank records (world entries)
     const float* factors;             // [N_global][n] update factors, column = local neuron
     UpdateItem* items; uint32_t* n_items;   // out: neurons with a non-zero factor, ascending, and their number
@@ -179,6 +180,7 @@ cudaError_t launch_update_fused(const Geometry& g, const UpdateArgs& a, const Bm
 // image costs no kernel launch, no set-up and no host round trip.  Integer distance modes only.
 constexpr uint32_t kStepBatchMax = 16;          // images per launch
 constexpr uint32_t kStepMaxOwned = 32;          // neurons one block may own
+constexpr uint32_t kStepStampWords = 12;        // opt-in timeline words per image and block
 
 // Control words of one launch; the host sets every byte to 0xFF before the launch.
 //   bmu_word[i]: minimum over all (neuron, transform tile) partial minima of image i of
@@ -213,10 +215,10 @@ struct StepArgs
     const float* factors;             // [N_global][n]
     const uint32_t* owners;           // [grid][owned_per_block] local neuron indices, ~0u = none
     // bookkeeping
-    uint32_t n_img, first_neuron, rank, world;
+    uint32_t n_img, first_neuron, neuron_stride, rank, world;   // local neuron j is global neuron first_neuron + j * neuron_stride
     uint32_t* counts; uint32_t* bmu_log; unsigned long long* stats; int* status;
     StepCtrl* ctrl;
-    unsigned long long* stamps;       // nullable: [n_img][8] device-timer stamps of block 0 (see train_steps.cu)
+    unsigned long long* stamps;       // nullable: [n_img][grid][kStepStampWords] device-timer stamps of every block (see train_steps.cu)
     // peer-memory exchange of the shards' records (world > 1): as in BmuArgs; the record of image i carries xchg_seq0 + i
     XchgRecord* xchg_local; XchgRecord* xchg_peer[kXchgMaxRanks]; unsigned long long xchg_seq0;
     unsigned long long xchg_timeout_ns;   // wall-clock limit of the wait for the other ranks' records
@@ -226,8 +228,8 @@ struct StepArgs
 bool step_plan(const Geometry& g, uint32_t n_local, uint32_t n_global, StepPlan* plan, const char** why_not);
 // Which block updates which neuron: owners[b * owned_per_block + j], balanced so that the neurons close to any
 // best matching unit (large update factors) are spread over different blocks.  host_factors: [N][N] table.
-void step_assign_owners(const float* host_factors, uint32_t N, uint32_t first, uint32_t count, const StepPlan& plan,
-                        uint32_t* owners);
+void step_assign_owners(const float* host_factors, uint32_t N, uint32_t first, uint32_t stride, uint32_t count,
+                        const StepPlan& plan, uint32_t* owners);
 cudaError_t launch_train_steps(const Geometry& g, const StepPlan& plan, const StepArgs& a, cudaStream_t st, const char** why);
 
 // ---- mapping epilogue -------------------------------------------------------

@@ -5,6 +5,19 @@
 
 namespace pinkb {
 
+// Global index of local neuron j of a shard, and the inverse test: does the shard (first, stride, n) hold global neuron g?
+__device__ __forceinline__ unsigned long long shard_global(uint32_t first, uint32_t stride, unsigned long long j)
+{
+    return first + j * stride;
+}
+
+__device__ __forceinline__ bool shard_owns(uint32_t first, uint32_t stride, uint32_t n, uint32_t g)
+{
+    if (g < first) return false;
+    const uint32_t d = g - first;
+    return d % stride == 0 && d / stride < n;
+}
+
 // Lexicographic order of (distance code, neuron index): lowest distance, then lowest index.
 __device__ __forceinline__ bool pair_less(unsigned long long c0, unsigned long long n0,
                                           unsigned long long c1, unsigned long long n1)

@@ -46,7 +46,7 @@ namespace pinkb {
 namespace {
 
 constexpr uint32_t kMT = 512;                          // threads per block
-constexpr uint32_t kEpiWarps = 8;                      // warps 2..9 read the accumulators (two per lane quadrant)
+constexpr uint32_t kEpiWarps = 12;                     // warps 2..13 read the accumulators (three per lane quadrant)
 constexpr uint32_t kEpiThreads = kEpiWarps * 32;
 constexpr uint32_t kConsWarps = kMT / 32 - 1;          // warps 1..15 update neurons; warp 0 moves the data
 constexpr uint32_t kConsThreads = kConsWarps * 32;
@@ -60,6 +60,7 @@ constexpr int kMaxTasks = 2;                           // (row block, column) ta
 constexpr int kMaxUnits = 4;                           // operand groups of four elements per consumer thread and plane
 constexpr uint32_t kRegionBudget = 208 * 1024;         // shared memory the two phases use in turn
 constexpr unsigned long long kGridWaitNs = 2000000000ull;   // a grid barrier gives up after two seconds
+constexpr uint32_t kStampWords = kStepStampWords;
 
 template <int MODE> struct StepCfg;
 template <> struct StepCfg<kModeU8>  { static constexpr uint32_t planes = 1, max_n = 256, cols = 256, word_shift = 32; };
@@ -153,12 +154,14 @@ __device__ __forceinline__ void grid_sync(const StepArgs& a, StepShared& sh, uin
     __syncthreads();
 }
 
-// Device-timer stamps of block 0 (opt-in): 0 image begins, 1 its own distance tiles are reduced, 2 all blocks'
-// are (first grid barrier passed), 3 work list built, 4 its own neurons are rewritten and stored, 5 all blocks'
-// are (second grid barrier passed).
+// Device-timer stamps of every block (opt-in), eight words per image and block: 0 image begins, 1 the block's
+// own distance tiles are reduced, 2 all blocks' are (first grid barrier passed), 3 work list built, 4 its own
+// neurons are rewritten and stored, 5 all blocks' are (second grid barrier passed), 6 planes it rewrote,
+// 7 distance tiles it computed, 8 first operand slice arrived (MMA thread), 9 last MMA issued, 10 accumulators
+// complete (seen by an epilogue thread), 11 first neuron plane arrived (seen by a consumer thread).
 __device__ __forceinline__ void stamp(const StepArgs& a, uint32_t img, uint32_t k, uint32_t thread)
 {
-    if (a.stamps && blockIdx.x == 0 && threadIdx.x == thread) a.stamps[(size_t)img * 8 + k] = global_timer_ns();
+    if (a.stamps && threadIdx.x == thread) a.stamps[((size_t)img * gridDim.x + blockIdx.x) * kStampWords + k] = global_timer_ns();
 }
 
 template <int MODE, bool PAIR>
@@ -247,6 +250,8 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
         }
     }
     const bool can_skip = a.wrange != nullptr && a.rmax != nullptr;
+    // the neuron lane j of warp 1 looks after in every image's work list (static ownership)
+    const uint32_t own_n = (warp == 1 && lane < pl.owned_per_block) ? a.owners[(size_t)blockIdx.x * pl.owned_per_block + lane] : ~0u;
     uint32_t upd_base = 0;                // planes this block has streamed so far (stage and parity of the next one)
 
     for (uint32_t img = 0; img < a.n_img; ++img) {
@@ -314,6 +319,7 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                         const uint32_t it = idn * num_kb + kb;
                         const uint32_t s = it % pl.ring_stages, ph = (it / pl.ring_stages) & 1;
                         if (!step_wait(&sh.full_bar[s], ph, sh, a.status)) { step_fail(sh, a.status, kDevTimeoutMma); ok = false; break; }
+                        if (k == 0 && kb == 0) stamp(a, img, 8, 32);
                         tc_fence_after();
                         const uint32_t st = smem_u32(region + s * ring_stage_bytes);
                         const uint64_t a_hi = make_sw128_kmajor_desc(st);
@@ -337,20 +343,21 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     }
                     if (!ok) break;
                     commit(&sh.tmem_full);               // accumulators of this tile complete
+                    stamp(a, img, 9, 32);
                 }
             }
             __syncwarp();
         } else if (warp < 2 + kEpiWarps) {
             // ----------------------------------------------------------- epilogue --
-            // Two warps share a lane quadrant of the tensor memory and split the tile's columns; a thread
-            // owns one neuron row of its half: S = |a|^2 + |b|^2 - 2ab per column, first minimum, one
+            // Three warps share a lane quadrant of the tensor memory and split the tile's columns; a thread
+            // owns one neuron row of its third: S = |a|^2 + |b|^2 - 2ab per column, first minimum, one
             // atomicMin per row into the per-neuron key, one per warp into the image's unit word.
             val_t* nbv = reinterpret_cast<val_t*>(sh.nb);
             const uint32_t et = threadIdx.x - 64;
-            const uint32_t quad = warp & 3, half = (warp - 2) >> 2;
+            const uint32_t quad = warp & 3, part = (warp - 2) >> 2;          // part 0..2 of the tile's columns
             const uint32_t row = quad * 32 + lane;
-            const uint32_t chunks = pl.n_tile / 16, chunks_lo = (chunks + 1) / 2;
-            const uint32_t c_lo = half ? chunks_lo * 16 : 0u, c_hi_tile = half ? pl.n_tile : chunks_lo * 16;
+            const uint32_t chunks = pl.n_tile / 16;
+            const uint32_t c_lo = (chunks * part / 3) * 16, c_hi_tile = (chunks * (part + 1) / 3) * 16;
             const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
             uint32_t k = 0;
             for (uint32_t item = unit; item < n_items; item += n_units, ++k) {
@@ -365,30 +372,34 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                 const val_t na = n < a.n ? __ldcg(static_cast<const val_t*>(a.anorm) + n) : val_t(0);
                 epilogue_sync();                          // nbv visible to all epilogue warps
                 const uint32_t c_hi = min(c_hi_tile, ncols);
+                // Per column only the part of S that depends on it is formed, D = |b|^2 - 2ab (uint8: exact as a signed
+                // 32-bit value, because S = |a|^2 + D and |a|^2 both lie in [0, 2^31)); |a|^2 is added to the winner.
+                using cmp_t = typename std::conditional<MODE == kModeU8, int32_t, long long>::type;
+                constexpr cmp_t kNever = MODE == kModeU8 ? (cmp_t)0x7FFFFFFF : (cmp_t)0x7FFFFFFFFFFFFFFFll;
                 constexpr int kChains = 4;
-                val_t best[kChains];
+                cmp_t best[kChains];
                 uint32_t bcol[kChains];
 #pragma unroll
-                for (int c = 0; c < kChains; ++c) { best[c] = ~val_t(0); bcol[c] = 0; }
+                for (int c = 0; c < kChains; ++c) { best[c] = kNever; bcol[c] = 0; }
                 const bool ready = step_wait(&sh.tmem_full, idn & 1, sh, a.status);
                 if (ready) {
+                    stamp(a, img, 10, 64);
                     tc_fence_after();
                     auto reduce = [&](uint32_t c0, const uint32_t (&x0)[16], const uint32_t (&x1)[16], const uint32_t (&x2)[16]) {
-                        val_t sv[16];
+                        cmp_t sv[16];
 #pragma unroll
                         for (uint32_t j = 0; j < 16; ++j) {
                             if (MODE == kModeU8) {
-                                // exact: 0 <= S < 2^31 although the intermediates wrap modulo 2^32
-                                sv[j] = (uint32_t)(na + nbv[c0 + j]) - 2u * x0[j];
+                                sv[j] = (cmp_t)(int32_t)((uint32_t)nbv[c0 + j] - 2u * x0[j]);
                             } else {
                                 const unsigned long long dot = ((unsigned long long)x0[j] << 16)
                                                              + ((unsigned long long)x2[j] << 8) + x1[j];
-                                sv[j] = na + nbv[c0 + j] - 2ull * dot;
+                                sv[j] = (cmp_t)((unsigned long long)nbv[c0 + j] - 2ull * dot);
                             }
                         }
                         if (c0 + 16 > c_hi) {                     // ragged last chunk: columns beyond T never win
 #pragma unroll
-                            for (uint32_t j = 0; j < 16; ++j) if (c0 + j >= c_hi) sv[j] = ~val_t(0);
+                            for (uint32_t j = 0; j < 16; ++j) if (c0 + j >= c_hi) sv[j] = kNever;
                         }
 #pragma unroll
                         for (uint32_t j = 0; j < 16; ++j)
@@ -421,16 +432,17 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                 } else {
                     step_fail(sh, a.status, kDevTimeoutEpilogue);
                 }
-                // first minimum over the chains: lowest S, then lowest column
-                val_t best_s = best[0];
+                // first minimum over the chains: lowest value, then lowest column
+                cmp_t best_d = best[0];
                 uint32_t best_c = bcol[0];
 #pragma unroll
                 for (int c = 1; c < kChains; ++c)
-                    if (best[c] < best_s || (best[c] == best_s && bcol[c] < best_c)) { best_s = best[c]; best_c = bcol[c]; }
+                    if (best[c] < best_d || (best[c] == best_d && bcol[c] < best_c)) { best_d = best[c]; best_c = bcol[c]; }
                 unsigned long long cand = ~0ull;              // (S, global neuron) of this row, ordered like the unit word
-                if (n < a.n && best_s != ~val_t(0)) {
+                if (n < a.n && ready && c_lo < c_hi) {
+                    const val_t best_s = (val_t)(na + (val_t)best_d);
                     atomicMin(&a.keys[n], ((unsigned long long)best_s << key_shift(MODE)) | (unsigned long long)(t0 + best_c));
-                    cand = ((unsigned long long)best_s << Cfg::word_shift) | (unsigned long long)(a.first_neuron + n);
+                    cand = ((unsigned long long)best_s << Cfg::word_shift) | shard_global(a.first_neuron, a.neuron_stride, n);
                 }
                 for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_down_sync(0xffffffffu, cand, o));
                 if (lane == 0 && cand != ~0ull) atomicMin(&a.ctrl->bmu_word[img], cand);
@@ -450,6 +462,7 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
 
         // ===================================================================== update phase ====
         if (warp == 1) {
+            const uint32_t rmax_bits = can_skip ? a.rmax[img] : 0u;
             // ---- best matching unit: the image's word, or the first minimum over the ranks' words
             const unsigned long long word = __ldcg(&a.ctrl->bmu_word[img]);
             unsigned long long bc = word == ~0ull ? ~0ull : word >> Cfg::word_shift;
@@ -497,24 +510,23 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
             const uint32_t bmu = (uint32_t)bn;              // ~0u: no best matching unit
             const bool have_bmu = bn != ~0ull && !step_aborted(sh);
             if (blockIdx.x == 0 && lane == 0) {
-                if (have_bmu && bmu >= a.first_neuron && bmu - a.first_neuron < a.n) {    // this rank owns the unit
+                if (have_bmu && shard_owns(a.first_neuron, a.neuron_stride, a.n, bmu)) {    // this rank owns the unit
                     atomicAdd(&a.counts[bmu], 1u);
                     if (a.bmu_log) a.bmu_log[img] = bmu;
                 }
             }
             // ---- work list: the neurons this block owns whose factor is not zero and whose values can change
-            const uint32_t n = lane < pl.owned_per_block ? a.owners[(size_t)blockIdx.x * pl.owned_per_block + lane] : ~0u;
+            const uint32_t n = own_n;
             const bool valid = n < a.n;
             float f = 0.0f;
             unsigned long long key = 0;
             if (valid) {
+                // three independent loads (one memory round trip)
                 key = __ldcg(&a.keys[n]);
-                a.keys[n] = kKeyEmpty;                       // re-armed for the next image's distance phase
+                const uint2 r = can_skip ? __ldcg(&a.wrange[n]) : make_uint2(0u, 0u);
                 if (have_bmu) f = a.factors[(size_t)bmu * a.n + n];
-                if (can_skip && f != 0.0f) {
-                    const uint2 r = __ldcg(&a.wrange[n]);
-                    if (cannot_change(f, r.x, r.y, a.rmax[img])) f = 0.0f;
-                }
+                a.keys[n] = kKeyEmpty;                       // re-armed for the next image's distance phase
+                if (can_skip && f != 0.0f && cannot_change(f, r.x, r.y, rmax_bits)) f = 0.0f;
             }
             const uint32_t ballot = __ballot_sync(0xffffffffu, f != 0.0f);
             if (f != 0.0f) {
@@ -612,6 +624,7 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                 // (no early exit on a failed wait: every consumer warp must reach the barriers below the same
                 //  number of times; after a failure all later waits return at once and the results are void anyway)
                 if (!step_wait(&sh.upd_full[s], ph, sh, a.status)) step_fail(sh, a.status, kDevTimeoutUpdateConsumer);
+                if (jx == 0) stamp(a, img, 11, 32);
                 const uint32_t som_a = smem_u32(region) + s * pl.upd_stage_bytes;        // shared-window byte addresses
                 const uint32_t base_a = som_a + pl.upd_off_base;
                 const Entry e = sh.entries[jx];
@@ -698,6 +711,10 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
         }
         upd_base += M;
         stamp(a, img, 4, 0);
+        if (a.stamps && threadIdx.x == 1) {
+            a.stamps[((size_t)img * gridDim.x + blockIdx.x) * kStampWords + 6] = M;
+            a.stamps[((size_t)img * gridDim.x + blockIdx.x) * kStampWords + 7] = my_items;
+        }
         grid_sync(a, sh, (2 * img + 2) * gridDim.x);
         stamp(a, img, 5, 0);
     }
@@ -817,7 +834,8 @@ bool step_plan(const Geometry& g, uint32_t n_local, uint32_t n_global, StepPlan*
 // i and m are rewritten together.  The neighbourhood of any best matching unit then spreads over the
 // blocks almost evenly (measured on a hexagonal map of 2791 neurons, sigma 3: at most 5-7 neurons of a
 // block among the ~700-1000 neurons an image rewrites, against 7-9 for a round-robin assignment).
-void step_assign_owners(const float* F, uint32_t N, uint32_t first, uint32_t count, const StepPlan& pl, uint32_t* owners)
+void step_assign_owners(const float* F, uint32_t N, uint32_t first, uint32_t stride, uint32_t count, const StepPlan& pl,
+                        uint32_t* owners)
 {
     const uint32_t G = pl.grid, J = pl.owned_per_block;
     std::fill(owners, owners + (size_t)G * J, ~0u);
@@ -825,8 +843,8 @@ void step_assign_owners(const float* F, uint32_t N, uint32_t first, uint32_t cou
     std::vector<double> score(G);
     for (uint32_t i = 0; i < count; ++i) {
         std::fill(score.begin(), score.end(), 0.0);
-        const float* row = F + (size_t)(first + i) * N + first;
-        for (uint32_t m = 0; m < i; ++m) score[color[m]] += std::fabs((double)row[m]);
+        const float* row = F + (size_t)(first + (size_t)i * stride) * N + first;
+        for (uint32_t m = 0; m < i; ++m) score[color[m]] += std::fabs((double)row[(size_t)m * stride]);
         uint32_t best = G;
         for (uint32_t c = 0; c < G; ++c) {
             if (load[c] >= J) continue;

@@ -40,7 +40,7 @@ bmu_kernel(BmuArgs a)
     unsigned long long bc, bn;
     block_argmin_keys(a.keys, a.n, a.shift, kBmuThreads, sc, sn, bc, bn);
     __syncthreads();
-    if (threadIdx.x == 0) { sc[0] = bc; sn[0] = bn == ~0ull ? ~0ull : bn + a.first_neuron; }
+    if (threadIdx.x == 0) { sc[0] = bc; sn[0] = bn == ~0ull ? ~0ull : shard_global(a.first_neuron, a.neuron_stride, bn); }
     __syncthreads();
     publish_record(a, sc[0], sn[0]);
 }
@@ -65,7 +65,7 @@ worklist_kernel(BmuArgs a)
             if (pair_less(a.pairs[r].code, a.pairs[r].neuron, bc, bn)) { bc = a.pairs[r].code; bn = a.pairs[r].neuron; }
         const uint32_t bmu = (uint32_t)bn;
         bmu_s = bmu;
-        if (blockIdx.x == 0 && bmu >= a.first_neuron && bmu - a.first_neuron < a.n) {   // this rank owns the unit
+        if (blockIdx.x == 0 && shard_owns(a.first_neuron, a.neuron_stride, a.n, bmu)) {   // this rank owns the unit
             atomicAdd(&a.counts[bmu], 1u);
             if (a.bmu_log) *a.bmu_log = bmu;
         }
@@ -518,7 +518,7 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
                     const unsigned long long oc = __shfl_down_sync(0xffffffffu, bc, o), on = __shfl_down_sync(0xffffffffu, bn, o);
                     if (pair_less(oc, on, bc, bn)) { bc = oc; bn = on; }
                 }
-                bn += b.first_neuron;
+                bn = shard_global(b.first_neuron, b.neuron_stride, bn);
             } else if (b.xchg_seq == 0) {
                 // lexicographic minimum over the per-rank records: lowest distance, then lowest neuron index
                 bc = b.pairs[0].code; bn = b.pairs[0].neuron;
@@ -561,7 +561,7 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             if (lane == 0) {
                 const uint32_t bmu = (uint32_t)bn;          // ~0u: no best matching unit (exchange failed)
                 bmu_s = bmu;
-                if (blockIdx.x == 0 && bmu >= b.first_neuron && bmu - b.first_neuron < b.n) {   // this rank owns the unit
+                if (blockIdx.x == 0 && shard_owns(b.first_neuron, b.neuron_stride, b.n, bmu)) {   // this rank owns the unit
                     atomicAdd(&b.counts[bmu], 1u);
                     if (b.bmu_log) *b.bmu_log = bmu;
                 }

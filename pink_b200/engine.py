@@ -52,12 +52,25 @@ class Engine:
         self.first, self.count = first.value, count.value
         self.image_size = channels * image_dim * image_dim
         self.neuron_size = channels * neuron_dim * neuron_dim
+        self._read_shard()
         for name, value in (options or {}).items():
             self.set_option(name, value)
 
     def set_option(self, name, value):
         """Switches of the context (see pink_b200_set_option); before comm_init / set_som."""
         capi.check(capi.lib.pink_b200_set_option(self._h, name.encode(), int(value)))
+        self._read_shard()
+
+    def _read_shard(self):
+        first, count = C.c_uint32(), C.c_uint32()
+        capi.check(capi.lib.pink_b200_shard(self._h, C.byref(first), C.byref(count)))
+        self.first, self.count = first.value, count.value
+        self.stride = int(capi.lib.pink_b200_shard_stride(self._h))
+
+    @property
+    def neurons(self):
+        """Global indices of this context's neurons, in its local order."""
+        return self.first + self.stride * np.arange(self.count)
 
     # -- life cycle ---------------------------------------------------------
     def close(self):
@@ -175,6 +188,15 @@ class Engine:
         keys = ("launch_us", "images_per_launch", "distance_own_us", "barrier1_wait_us", "bmu_list_us",
                 "update_own_us", "barrier2_wait_us")
         return dict(zip(keys, list(out)[:7]))
+
+    def profile_stamps(self):
+        """Raw device-timer stamps of the last profiled pass: uint64 array [steps][blocks][12]."""
+        blocks, steps = C.c_uint32(), C.c_uint64()
+        capi.check(capi.lib.pink_b200_profile_stamps(self._h, None, 0, C.byref(blocks), C.byref(steps)))
+        out = np.zeros((steps.value, blocks.value, 12), np.uint64)
+        if out.size:
+            capi.check(capi.lib.pink_b200_profile_stamps(self._h, _vp(out), out.size, C.byref(blocks), C.byref(steps)))
+        return out
 
     @property
     def stream(self):

@@ -16,7 +16,7 @@ def _worker(rank, world, port, mode, exchange, q):
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     options = {"nccl": {"exchange": 1}, "peer": {"rotation_sharing": 0}, "shared": {},
-               "two-kernel": {"step_kernel": 1}}[exchange]
+               "two-kernel": {"step_kernel": 1}, "contiguous": {"sharding": 1}}[exchange]
     import torch
     import torch.distributed as dist
     from pink_b200 import capi, engine
@@ -41,15 +41,20 @@ def _worker(rank, world, port, mode, exchange, q):
     part = eng.get_som(np.zeros_like(som))
     counts = eng.update_counts()
     out = [None] * world
-    dist.all_gather_object(out, (eng.first, eng.count, part[eng.first:eng.first + eng.count], counts))
+    dist.all_gather_object(out, (eng.neurons, part[eng.neurons], counts))
     if rank == 0:
-        whole = np.concatenate([p[2] for p in sorted(out, key=lambda p: p[0])])
-        q.put((whole, sum(p[3] for p in out), som, imgs, F, kind))
+        whole = np.zeros_like(som)
+        seen = np.zeros(N, int)
+        for neurons, rows, _ in out:
+            whole[neurons] = rows
+            seen[neurons] += 1
+        assert (seen == 1).all()                       # the shards partition the map
+        q.put((whole, sum(p[2] for p in out), som, imgs, F, kind))
     eng.close()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["shared", "peer", "nccl", "two-kernel"])
+@pytest.mark.parametrize("exchange", ["shared", "peer", "nccl", "two-kernel", "contiguous"])
 @pytest.mark.parametrize("mode", [2, 1, 0])
 def test_two_gpu_sharded_training_bit_exact(cuda, mode, exchange):
     torch = cuda
@@ -60,7 +65,7 @@ def test_two_gpu_sharded_training_bit_exact(cuda, mode, exchange):
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + 4 * mode + ["shared", "peer", "nccl", "two-kernel"].index(exchange) + (os.getpid() % 100)
+    port = 29700 + 5 * mode + ["shared", "peer", "nccl", "two-kernel", "contiguous"].index(exchange) + (os.getpid() % 100)
     procs = [ctx.Process(target=_worker, args=(r, world, port, mode, exchange, q)) for r in range(world)]
     for p in procs:
         p.start()
@@ -68,7 +73,7 @@ def test_two_gpu_sharded_training_bit_exact(cuda, mode, exchange):
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    assert kind == {"shared": 3, "peer": 2, "nccl": 1, "two-kernel": 3}[exchange]      # the intended exchange really ran
+    assert kind == {"shared": 3, "peer": 2, "nccl": 1, "two-kernel": 3, "contiguous": 3}[exchange]      # the intended exchange really ran
     want = som.copy()
     bmus = [O.train_step(want, im, F, 15, 40, True, mode)[2] for im in imgs]
     if mode == 0:        # float32 distances: same best matching units (no near-ties in this seed), same arithmetic

@@ -249,6 +249,38 @@ int pink_b200_profile_detail(pink_b200_ctx* ctx, double out[8]);
  * *steps are always set; `out` may be NULL to ask for the sizes only. */
 int pink_b200_profile_stamps(pink_b200_ctx* ctx, uint64_t* out, uint64_t capacity, uint32_t* blocks, uint64_t* steps);
 
+/* ---- one process, several GPUs ------------------------------------------------
+ * The reference's Trainer / Mapper use every visible GPU of the process on their own
+ * (src/CudaLib/CudaLib.cu:56-76; neurons split over the GPUs with a host thread per extra GPU,
+ * src/CudaLib/generate_euclidean_distance_matrix_first_step_multi_gpu.h:47-196).  A group is that for this
+ * library: it owns one context per device and drives them from host threads of its own.
+ *   training: the neurons are sharded over the devices (rank r on devices[r]) and the shards' records are
+ *             exchanged through peer memory, as between processes;
+ *   mapping:  every device holds the whole map and the images of a call are dealt to the devices in contiguous
+ *             ranges; results are in the order of the images.  No communication.
+ * `devices` lists CUDA ordinals; NULL takes the visible sm_100 devices (at most n_devices of them when n_devices
+ * is not 0).  cfg->device, rank and world_size are ignored.  SOM, factors, counters and results are those of
+ * the WHOLE map: a caller never sees the shards. */
+typedef struct pink_b200_group pink_b200_group;
+int pink_b200_device_count(void);                  /* visible sm_100 devices */
+int pink_b200_group_create(const pink_b200_config* cfg, const int32_t* devices, uint32_t n_devices, pink_b200_group** out);
+int pink_b200_group_destroy(pink_b200_group* group);
+uint32_t pink_b200_group_size(const pink_b200_group* group);
+int pink_b200_group_set_option(pink_b200_group* group, const char* name, long long value);
+int pink_b200_group_set_som(pink_b200_group* group, const float* host_som);
+int pink_b200_group_get_som(pink_b200_group* group, float* host_som);
+int pink_b200_group_set_update_factors(pink_b200_group* group, const float* host_factors);
+int pink_b200_group_train(pink_b200_group* group, const float* host_images, uint64_t n);
+int pink_b200_group_get_update_counts(pink_b200_group* group, uint32_t* host_counts);
+int pink_b200_group_synchronize(pink_b200_group* group);
+int pink_b200_group_map(pink_b200_group* group, const float* host_images, uint64_t n, float* host_dist, uint32_t* host_rot);
+
+/* Page-locked host memory for image and result buffers (the copies of pink_b200_train / pink_b200_map then run
+ * asynchronously at full speed; pageable memory works too, slower).  The reference reads every image into
+ * pageable memory (src/SelfOrganizingMapLib/DataIterator.h). */
+int pink_b200_host_alloc(void** out, uint64_t bytes);
+int pink_b200_host_free(void* ptr);
+
 /* ---- single stages on device buffers (what the context calls internally) ---
  * Exposed for kernel-level parity tests and benchmarks.  `stream` is a
  * cudaStream_t (NULL = default stream).  Operand layout: integer modes use

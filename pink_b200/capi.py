@@ -60,6 +60,20 @@ SYMBOLS = {
     "pink_b200_profile_detail": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
     "pink_b200_profile_stamps": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32),
                                            C.POINTER(C.c_uint64)]),
+    "pink_b200_device_count": (C.c_int, []),
+    "pink_b200_group_create": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_uint32, C.POINTER(C.c_void_p)]),
+    "pink_b200_group_destroy": (C.c_int, [C.c_void_p]),
+    "pink_b200_group_size": (C.c_uint32, [C.c_void_p]),
+    "pink_b200_group_set_option": (C.c_int, [C.c_void_p, C.c_char_p, C.c_longlong]),
+    "pink_b200_group_set_som": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "pink_b200_group_get_som": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "pink_b200_group_set_update_factors": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "pink_b200_group_train": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64]),
+    "pink_b200_group_get_update_counts": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "pink_b200_group_synchronize": (C.c_int, [C.c_void_p]),
+    "pink_b200_group_map": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),
+    "pink_b200_host_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_uint64]),
+    "pink_b200_host_free": (C.c_int, [C.c_void_p]),
     "pink_b200_som_size": (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32]),
     "pink_b200_som_distances": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
     "pink_b200_update_factors": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,

@@ -12,6 +12,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <dlfcn.h>
+#include <unistd.h>
 #include <nccl.h>
 #include <new>
 #include <string>
@@ -194,6 +195,7 @@ struct pink_b200_ctx
     UpdateItem* d_items = nullptr; uint32_t* d_nitems = nullptr;   // per-step work list of the update
     // records of the ranks' best matching units exchanged by peer stores (world_size > 1, all ranks on one node)
     XchgRecord* d_xchg = nullptr; XchgRecord* xchg_peer[kXchgMaxRanks] = {}; bool xchg_on = false; unsigned long long xchg_seq = 0;
+    bool peer_in_process[kXchgMaxRanks] = {};   // rank r lives in this process: its buffers are reached by plain peer access
     // value ranges for leaving out neurons that cannot change: per neuron {min |w|, max |w|}, per buffered image max |pixel|
     uint2* d_wrange = nullptr; uint32_t* d_rmax = nullptr;
     ushort2* d_circle = nullptr;      // column spans of a circular distance region (null: quadratic)
@@ -566,14 +568,14 @@ static int train_chunk_shared(pink_b200_ctx* c, const float* d_images, uint64_t 
 void release_peer_exchange(pink_b200_ctx* c)
 {
     for (uint32_t r = 0; r < kXchgMaxRanks; ++r) {
-        if (c->xchg_peer[r] && c->xchg_peer[r] != c->d_xchg) cudaIpcCloseMemHandle(c->xchg_peer[r]);
+        if (c->xchg_peer[r] && c->xchg_peer[r] != c->d_xchg && !c->peer_in_process[r]) cudaIpcCloseMemHandle(c->xchg_peer[r]);
         c->xchg_peer[r] = nullptr;
     }
     if (c->d_xchg) cudaFree(c->d_xchg);
     c->d_xchg = nullptr;
     c->xchg_on = false;
     for (uint32_t r = 0; r < kXchgMaxRanks; ++r) {
-        if (r != c->cfg.rank) {
+        if (r != c->cfg.rank && !c->peer_in_process[r]) {
             if (c->peer_rotflag[r]) cudaIpcCloseMemHandle(c->peer_rotflag[r]);
             if (c->peer_base[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
             if (c->peer_b0[r]) cudaIpcCloseMemHandle(c->peer_b0[r]);
@@ -599,18 +601,24 @@ int setup_peer_exchange(pink_b200_ctx* c)
 {
     const uint32_t W = c->cfg.world_size, rank = c->cfg.rank;
     // handles: 0 record ring; 1..6 the transform buffers and the flag rows of the shared rotation
-    struct Hello { cudaIpcMemHandle_t handle[7]; char bus[32]; uint32_t want; uint32_t share; uint32_t ok; };
+    // (pid, device, ptr: ranks that live in one process -- a group driving several GPUs -- cannot open each other's
+    //  IPC handles; they enable peer access and use the device pointers themselves)
+    struct Hello { cudaIpcMemHandle_t handle[7]; void* ptr[7]; char bus[32]; long long pid; int device;
+                   uint32_t want; uint32_t share; uint32_t ok; };
     Hello mine{};
     std::vector<Hello> all(W);
     Hello* d_all = nullptr;
     // (distance codes must leave room for the 8-bit tag of a record word: 65535^2 * K < 2^56)
     mine.want = W <= kXchgMaxRanks && (c->fuse_update || (c->plan_ok && c->opt_step_kernel == 0)) && c->g.K < (1u << 24)
                 && c->opt_exchange == 0;
+    mine.pid = (long long)getpid();
+    mine.device = c->cfg.device;
     if (mine.want) {
         const size_t bytes = (size_t)kXchgSlots * W * sizeof(XchgRecord);
         CU_TRY(cudaMalloc(&c->d_xchg, bytes));
         CU_TRY(cudaMemsetAsync(c->d_xchg, 0, bytes, c->stream));
         CU_TRY(cudaStreamSynchronize(c->stream));          // zeroed before any rank can learn the handle
+        mine.ptr[0] = c->d_xchg;
         if (cudaIpcGetMemHandle(&mine.handle[0], c->d_xchg) != cudaSuccess) { cudaGetLastError(); mine.want = 0; }
         if (cudaDeviceGetPCIBusId(mine.bus, sizeof(mine.bus), c->cfg.device) != cudaSuccess) { cudaGetLastError(); mine.want = 0; }
     }
@@ -634,8 +642,10 @@ int setup_peer_exchange(pink_b200_ctx* c)
         CU_TRY(cudaMemsetAsync(c->d_rotflag, 0, 3 * W * sizeof(unsigned long long), c->stream));
         CU_TRY(cudaStreamSynchronize(c->stream));
         void* bufs[6] = { c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->d_rmax, c->d_rotflag };
-        for (int i = 0; i < 6; ++i)
+        for (int i = 0; i < 6; ++i) {
+            mine.ptr[1 + i] = bufs[i];
             if (bufs[i] && cudaIpcGetMemHandle(&mine.handle[1 + i], bufs[i]) != cudaSuccess) { cudaGetLastError(); mine.share = 0; }
+        }
     }
     CU_TRY(cudaMalloc(&d_all, W * sizeof(Hello)));
     auto gather = [&]() -> int {
@@ -654,8 +664,24 @@ int setup_peer_exchange(pink_b200_ctx* c)
         for (uint32_t q = 0; q < r; ++q) ok = ok && std::strncmp(all[r].bus, all[q].bus, sizeof(mine.bus)) != 0;
     }
     share = share && ok;
-    auto open = [&](const cudaIpcMemHandle_t& h, void** out) {
-        if (cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess) return true;
+    auto open = [&](uint32_t r, int i, void** out) {
+        if (all[r].pid == mine.pid) {
+            // same process: direct peer access to the other rank's device
+            int can = 0;
+            if (cudaDeviceCanAccessPeer(&can, c->cfg.device, all[r].device) == cudaSuccess && can) {
+                const cudaError_t e = cudaDeviceEnablePeerAccess(all[r].device, 0);
+                if (e == cudaSuccess || e == cudaErrorPeerAccessAlreadyEnabled) {
+                    cudaGetLastError();
+                    *out = all[r].ptr[i];
+                    c->peer_in_process[r] = true;
+                    return true;
+                }
+            }
+            cudaGetLastError();
+            *out = nullptr;
+            return false;
+        }
+        if (cudaIpcOpenMemHandle(out, all[r].handle[i], cudaIpcMemLazyEnablePeerAccess) == cudaSuccess) return true;
         cudaGetLastError();
         *out = nullptr;
         return false;
@@ -664,7 +690,7 @@ int setup_peer_exchange(pink_b200_ctx* c)
         for (uint32_t r = 0; r < W && ok; ++r) {
             if (r == rank) { c->xchg_peer[r] = c->d_xchg; continue; }
             void* ptr = nullptr;
-            ok = open(all[r].handle[0], &ptr);
+            ok = open(r, 0, &ptr);
             c->xchg_peer[r] = static_cast<XchgRecord*>(ptr);
         }
     }
@@ -678,7 +704,7 @@ int setup_peer_exchange(pink_b200_ctx* c)
             }
             void* p[6] = {};
             for (int i = 0; i < 6 && share; ++i)
-                if (i != 2 || c->d_b1) share = open(all[r].handle[1 + i], &p[i]);
+                if (i != 2 || c->d_b1) share = open(r, 1 + i, &p[i]);
             c->peer_base[r] = static_cast<float*>(p[0]); c->peer_b0[r] = static_cast<uint8_t*>(p[1]);
             c->peer_b1[r] = static_cast<uint8_t*>(p[2]); c->peer_bnorm[r] = static_cast<uint8_t*>(p[3]);
             c->peer_rmax[r] = static_cast<uint32_t*>(p[4]); c->peer_rotflag[r] = static_cast<unsigned long long*>(p[5]);

@@ -354,7 +354,7 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     // tiles spread over all SMs finish sooner.  Below 32 columns the neuron tile dominates and nothing is gained.
     uint32_t tiles = (g.T + Cfg::max_n - 1) / Cfg::max_n;
     {
-        static int sm_dev = -1, sms = 0;
+        static thread_local int sm_dev = -1, sms = 0;
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev != sm_dev) { cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); sm_dev = dev; }
@@ -375,7 +375,7 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     else { ma1 = ma0; mb1 = mb0; }
     if (!ok) { *why = "cuTensorMapEncodeTiled failed"; return cudaErrorInvalidValue; }
 
-    static int attr_dev = -1;   // the opt-in shared-memory size is a per-device function attribute
+    static thread_local int attr_dev = -1;   // the opt-in shared-memory size is a per-device function attribute
     int dev = 0;
     cudaGetDevice(&dev);
     constexpr uint32_t smem_max = L::ring_off + L::ring_budget + L::slack;

@@ -413,8 +413,8 @@ cudaError_t rotate_dispatch(const Geometry& g, const float* images, uint32_t n_i
     uint32_t use_smem = smem <= kRotateSmemLimit;
     if (!use_smem) smem = 0;
     // Dynamic shared memory above 48 KB is an opt-in, per-device function attribute.
-    static int attr_dev = -1;
-    static size_t attr_bytes = 0;
+    static thread_local int attr_dev = -1;
+    static thread_local size_t attr_bytes = 0;
     int dev = 0;
     cudaGetDevice(&dev);
     if (smem > 48 * 1024 && (dev != attr_dev || smem > attr_bytes)) {

@@ -777,8 +777,8 @@ cudaError_t update_classic(const Geometry& g, const UpdateArgs& a, cudaStream_t 
     const uint32_t stage_base = staged <= 200 * 1024 && (g.P & 3) == 0;
     const size_t smem = stage_base ? staged : fixed;
     // Dynamic shared memory above 48 KB is an opt-in, per-device function attribute.
-    static int attr_dev = -1;
-    static size_t attr_bytes = 0;
+    static thread_local int attr_dev = -1;
+    static thread_local size_t attr_bytes = 0;
     int dev = 0;
     cudaGetDevice(&dev);
     if (smem > 48 * 1024 && (dev != attr_dev || smem > attr_bytes)) {
@@ -794,7 +794,7 @@ cudaError_t update_classic(const Geometry& g, const UpdateArgs& a, cudaStream_t 
 
 int device_sm_count()
 {
-    static int dev_cached = -1, sms = 0;
+    static thread_local int dev_cached = -1, sms = 0;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev != dev_cached) {
@@ -851,8 +851,8 @@ cudaError_t update_dispatch(const Geometry& g, const UpdateArgs& a, const BmuArg
     if ((uint64_t)a.n * grid >= (1ull << 32)) return cudaErrorInvalidValue;   // multiply-high division range
     pp.magic_grid = div_magic(grid);
     const size_t smem = (size_t)pp.stages * stage;
-    static int attr_dev = -1;
-    static size_t attr_bytes = 0;
+    static thread_local int attr_dev = -1;
+    static thread_local size_t attr_bytes = 0;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev != attr_dev || smem > attr_bytes) {

@@ -85,7 +85,8 @@ class Engine:
         self.close()
 
     def __del__(self):
-        self.close()
+        if capi is not None:          # interpreter shutdown may have cleared the module
+            self.close()
 
     # -- multi-GPU ----------------------------------------------------------
     @staticmethod
@@ -201,3 +202,81 @@ class Engine:
     @property
     def stream(self):
         return capi.lib.pink_b200_stream(self._h)
+
+
+class Group:
+    """All (or the listed) GPUs of this process behind one object: neuron-sharded training, image-sharded mapping
+    (pink_b200_group_*).  Arrays are those of the whole map."""
+
+    def __init__(self, n_neurons, channels, image_dim, neuron_dim, ed_dim, n_rotations=360, use_flip=True,
+                 dist_type=capi.UINT8, devices=None, max_devices=0, ed_shape=capi.QUADRATIC,
+                 interpolation=capi.BILINEAR, options=None):
+        self.cfg = capi.Config(n_neurons, channels, image_dim, neuron_dim, ed_dim, ed_shape, n_rotations,
+                               int(bool(use_flip)), dist_type, interpolation, 0, 0, 1, 0)
+        self._h = C.c_void_p()
+        if devices is not None:
+            arr = (C.c_int32 * len(devices))(*devices)
+            capi.check(capi.lib.pink_b200_group_create(C.byref(self.cfg), arr, len(devices), C.byref(self._h)))
+        else:
+            capi.check(capi.lib.pink_b200_group_create(C.byref(self.cfg), None, max_devices, C.byref(self._h)))
+        self.size = int(capi.lib.pink_b200_group_size(self._h))
+        self.image_size = channels * image_dim * image_dim
+        self.neuron_size = channels * neuron_dim * neuron_dim
+        for name, value in (options or {}).items():
+            capi.check(capi.lib.pink_b200_group_set_option(self._h, name.encode(), int(value)))
+
+    def close(self):
+        if self._h:
+            capi.lib.pink_b200_group_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        if capi is not None:
+            self.close()
+
+    def set_som(self, som):
+        som = np.ascontiguousarray(som, dtype=np.float32)
+        if som.size != self.cfg.n_neurons * self.neuron_size:
+            raise ValueError("SOM has %d elements, expected %d" % (som.size, self.cfg.n_neurons * self.neuron_size))
+        capi.check(capi.lib.pink_b200_group_set_som(self._h, _vp(som)))
+
+    def get_som(self, out):
+        assert out.dtype == np.float32 and out.flags.c_contiguous
+        capi.check(capi.lib.pink_b200_group_get_som(self._h, _vp(out)))
+        return out
+
+    def set_update_factors(self, F):
+        F = np.ascontiguousarray(F, dtype=np.float32)
+        if F.size != self.cfg.n_neurons ** 2:
+            raise ValueError("update factor table must be N x N")
+        capi.check(capi.lib.pink_b200_group_set_update_factors(self._h, _vp(F)))
+
+    def train(self, images):
+        images = np.ascontiguousarray(images, dtype=np.float32)
+        if images.size % self.image_size:
+            raise ValueError("image buffer is not a whole number of images")
+        capi.check(capi.lib.pink_b200_group_train(self._h, _vp(images), images.size // self.image_size))
+
+    def synchronize(self):
+        capi.check(capi.lib.pink_b200_group_synchronize(self._h))
+
+    def update_counts(self):
+        out = np.empty(self.cfg.n_neurons, np.uint32)
+        capi.check(capi.lib.pink_b200_group_get_update_counts(self._h, _vp(out)))
+        return out
+
+    def map(self, images):
+        images = np.ascontiguousarray(images, dtype=np.float32)
+        if images.size % self.image_size:
+            raise ValueError("image buffer is not a whole number of images")
+        n = images.size // self.image_size
+        dist = np.empty((n, self.cfg.n_neurons), np.float32)
+        rot = np.empty((n, self.cfg.n_neurons), np.uint32)
+        capi.check(capi.lib.pink_b200_group_map(self._h, _vp(images), n, _vp(dist), _vp(rot)))
+        return dist, rot

@@ -302,6 +302,29 @@ struct Progress
     }
 };
 
+// Page-locked host array (pink_b200_host_alloc); falls back to nothing: allocation failure is an error.
+template <typename T>
+class PinnedBuffer
+{
+public:
+    explicit PinnedBuffer(size_t n) : n_(n)
+    {
+        void* p = nullptr;
+        check(pink_b200_host_alloc(&p, (uint64_t)n * sizeof(T)));
+        p_ = static_cast<T*>(p);
+    }
+    PinnedBuffer(PinnedBuffer&& o) noexcept : p_(o.p_), n_(o.n_) { o.p_ = nullptr; }
+    PinnedBuffer(const PinnedBuffer&) = delete;
+    PinnedBuffer& operator=(const PinnedBuffer&) = delete;
+    ~PinnedBuffer() { pink_b200_host_free(p_); }
+    T* data() { return p_; }
+    T& operator[](size_t i) { return p_[i]; }
+    size_t size() const { return n_; }
+private:
+    T* p_ = nullptr;
+    size_t n_ = 0;
+};
+
 int run(const Options& o)
 {
     std::ifstream ifs(o.data_file, std::ios::binary);
@@ -362,13 +385,19 @@ int run(const Options& o)
     cfg.n_neurons = n_neurons; cfg.channels = channels; cfg.image_dim = image_dim; cfg.neuron_dim = neuron_dim;
     cfg.ed_dim = ed_dim; cfg.ed_shape = o.ed_shape; cfg.n_rotations = o.rotations; cfg.use_flip = o.use_flip;
     cfg.dist_type = o.dist_type; cfg.interpolation = PINK_B200_BILINEAR; cfg.device = 0; cfg.rank = 0; cfg.world_size = 1;
-    pink_b200_ctx* raw = nullptr;
-    check(pink_b200_create(&cfg, &raw));
-    std::unique_ptr<pink_b200_ctx, int (*)(pink_b200_ctx*)> ctx(raw, pink_b200_destroy);
-    check(pink_b200_set_som(ctx.get(), som.data()));
+    // every visible GPU takes part, as in the reference (src/CudaLib/CudaLib.cu:56-76): training shards the neurons
+    // over them, mapping the images
+    pink_b200_group* raw = nullptr;
+    check(pink_b200_group_create(&cfg, nullptr, 0, &raw));
+    std::unique_ptr<pink_b200_group, int (*)(pink_b200_group*)> ctx(raw, pink_b200_group_destroy);
+    const uint32_t n_gpus = pink_b200_group_size(ctx.get());
+    if (o.verbose) std::printf("  GPUs in use: %u\n", n_gpus);
+    check(pink_b200_group_set_som(ctx.get(), som.data()));
 
-    const size_t batch = 256;                                 // images per host buffer
-    std::vector<float> buffers[2] = {std::vector<float>(batch * data.entry_floats), std::vector<float>(batch * data.entry_floats)};
+    // images per host buffer; mapping deals a buffer over the GPUs, so it grows with their number
+    const size_t batch = o.path == Options::TRAIN ? 256 : 256 * (size_t)n_gpus;
+    // page-locked staging: the copies to the devices run asynchronously while the reader thread fills the other buffer
+    PinnedBuffer<float> buffers[2] = {PinnedBuffer<float>(batch * data.entry_floats), PinnedBuffer<float>(batch * data.entry_floats)};
     const uint32_t entries = (uint32_t)data.entries;
 
     if (o.path == Options::TRAIN) {
@@ -379,7 +408,7 @@ int run(const Options& o)
         else
             check(pink_b200_update_factors(o.layout, o.som_width, o.som_height, o.func, o.sigma, o.damping,
                                            o.max_update_distance, factors.data()));
-        check(pink_b200_set_update_factors(ctx.get(), factors.data()));
+        check(pink_b200_group_set_update_factors(ctx.get(), factors.data()));
         const uint64_t total = (uint64_t)entries * o.iterations;
         Progress progress(total, o.progress_prints);
         std::vector<uint64_t> stores;
@@ -387,7 +416,7 @@ int run(const Options& o)
         size_t store_idx = 0, keep_count = 0;
         uint64_t done = 0;
         auto store_map = [&](const std::string& path) {
-            check(pink_b200_get_som(ctx.get(), som.data()));
+            check(pink_b200_group_get_som(ctx.get(), som.data()));
             write_som_file(path, som_text_header, som_dims, neuron_dims, som.data(), som.size());
         };
         for (uint32_t it = 0; it < o.iterations; ++it) {
@@ -414,7 +443,8 @@ int run(const Options& o)
                 if (k + 1 < chunks.size())
                     reader = std::thread(load_entries, std::ref(reader_stream), std::cref(data), std::cref(order), chunks[k + 1].first,
                                          chunks[k + 1].second, buffers[(k + 1) & 1].data());
-                check(pink_b200_train(ctx.get(), buffers[k & 1].data(), chunks[k].second));
+                check(pink_b200_group_train(ctx.get(), buffers[k & 1].data(), chunks[k].second));
+                check(pink_b200_group_synchronize(ctx.get()));      // the reader thread refills this buffer next
                 done += chunks[k].second;
                 if (reader.joinable()) reader.join();
                 progress.advance(done);
@@ -436,7 +466,7 @@ int run(const Options& o)
         std::printf("done.\n");
         if (o.verbose) {
             std::vector<uint32_t> counts(n_neurons);
-            check(pink_b200_get_update_counts(ctx.get(), counts.data()));
+            check(pink_b200_group_get_update_counts(ctx.get(), counts.data()));
             std::printf("\n  Number of updates of each neuron:\n\n");
             for (uint32_t i = 0; i < n_neurons; ++i) std::printf("%u%s", counts[i], (i + 1) % o.som_width ? " " : "\n");
             std::printf("\n");
@@ -453,8 +483,8 @@ int run(const Options& o)
         }
         std::vector<uint32_t> order(entries);
         std::iota(order.begin(), order.end(), 0u);
-        std::vector<float> dist(batch * n_neurons);
-        std::vector<uint32_t> rot(batch * n_neurons);
+        PinnedBuffer<float> dist(batch * n_neurons);
+        PinnedBuffer<uint32_t> rot(batch * n_neurons);
         Progress progress(entries, o.progress_prints);
         const float angle_step = static_cast<float>(2.0 * M_PI) / o.rotations;
         std::ifstream reader_stream(o.data_file, std::ios::binary);
@@ -465,7 +495,7 @@ int run(const Options& o)
             if (first + count < entries)
                 reader = std::thread(load_entries, std::ref(reader_stream), std::cref(data), std::cref(order), first + count,
                                      std::min<size_t>(batch, entries - first - count), buffers[(k + 1) & 1].data());
-            check(pink_b200_map(ctx.get(), buffers[k & 1].data(), count, dist.data(), rot.data()));
+            check(pink_b200_group_map(ctx.get(), buffers[k & 1].data(), count, dist.data(), rot.data()));
             result.write(reinterpret_cast<const char*>(dist.data()), (std::streamsize)(count * n_neurons * sizeof(float)));
             if (o.write_rot_flip) {
                 for (size_t i = 0; i < count * n_neurons; ++i) {

@@ -47,6 +47,7 @@ def build(force=False, verbose=False):
         cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-ldl"]
         subprocess.check_call(cmd)
     build_cli(force)
+    build_module(force)
     return LIB
 
 
@@ -63,6 +64,25 @@ def build_cli(force=False):
         subprocess.check_call([cxx, "-O2", "-std=c++17", "-pthread", srcs[0], "-o", CLI, "-L" + HERE, "-lpink_b200",
                                "-Wl,-rpath,$ORIGIN"])
     return CLI
+
+
+def module_path():
+    import sysconfig
+    return os.path.join(HERE, "_pink" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_module(force=False):
+    """The compiled Python module `_pink` (pybind11) next to the library it binds."""
+    import sysconfig
+    import pybind11
+    src = os.path.join(HERE, "host", "pink_module.cpp")
+    out = module_path()
+    if force or _stale(out, [src, os.path.join(HERE, "..", "include", "pink_b200.h"), LIB]):
+        cxx = os.environ.get("CXX", "g++")
+        subprocess.check_call([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+                               "-I" + sysconfig.get_paths()["include"], "-I" + pybind11.get_include(), src, "-o", out,
+                               "-L" + HERE, "-lpink_b200", "-Wl,-rpath,$ORIGIN"])
+    return out
 
 
 if __name__ == "__main__":

@@ -7,6 +7,7 @@
 #include "../../include/pink_b200.h"
 #include "kernels.cuh"
 
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -1355,7 +1356,26 @@ int pink_b200_profile_stamps(pink_b200_ctx* c, uint64_t* out, uint64_t capacity,
 
 // ---- single stages ---------------------------------------------------------------
 
-static int* g_op_status = nullptr;   // device status word shared by the single-stage entries
+// device status word of the single-stage entries, one per device (a kernel may only be handed memory of its own GPU)
+constexpr int kOpMaxDevices = 64;
+static std::atomic<int*> g_op_status[kOpMaxDevices];
+
+static int op_status_word(int** out)
+{
+    int dev = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kOpMaxDevices) return fail(PINK_B200_EINVAL, "device ordinal out of range");
+    int* p = g_op_status[dev].load(std::memory_order_acquire);
+    if (!p) {
+        int* fresh = nullptr;
+        CU_TRY(cudaMalloc(&fresh, sizeof(int)));
+        CU_TRY(cudaMemset(fresh, 0, sizeof(int)));
+        if (g_op_status[dev].compare_exchange_strong(p, fresh, std::memory_order_acq_rel)) p = fresh;
+        else cudaFree(fresh);                      // another thread was first
+    }
+    *out = p;
+    return PINK_B200_OK;
+}
 
 static int stage_tables(const Geometry& g, float** d_cs, float** d_sn, cudaStream_t st)
 {
@@ -1363,11 +1383,17 @@ static int stage_tables(const Geometry& g, float** d_cs, float** d_sn, cudaStrea
     std::vector<float> cs(nq), sn(nq);
     const float step = static_cast<float>(2 * M_PI) / g.R;
     for (uint32_t t = 0; t < nq; ++t) { const float a = t * step; cs[t] = std::cos(a); sn[t] = std::sin(a); }
-    CU_TRY(cudaMalloc(d_cs, nq * sizeof(float)));
-    CU_TRY(cudaMalloc(d_sn, nq * sizeof(float)));
-    CU_TRY(cudaMemcpyAsync(*d_cs, cs.data(), nq * sizeof(float), cudaMemcpyHostToDevice, st));
-    CU_TRY(cudaMemcpyAsync(*d_sn, sn.data(), nq * sizeof(float), cudaMemcpyHostToDevice, st));
-    CU_TRY(cudaStreamSynchronize(st));
+    *d_cs = *d_sn = nullptr;
+    cudaError_t e = cudaMalloc(d_cs, nq * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(d_sn, nq * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemcpyAsync(*d_cs, cs.data(), nq * sizeof(float), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(*d_sn, sn.data(), nq * sizeof(float), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+        cudaFree(*d_cs); cudaFree(*d_sn);          // nothing leaks on the error paths
+        *d_cs = *d_sn = nullptr;
+        return fail(PINK_B200_ECUDA, std::string("staging the rotation tables: ") + cudaGetErrorString(e));
+    }
     return PINK_B200_OK;
 }
 
@@ -1417,8 +1443,11 @@ int pink_b200_op_distance(uint32_t dist_type, uint32_t n_neurons, uint32_t n_tra
     Geometry g{};
     g.mode = (int)dist_type;
     g.T = n_transforms; g.K = K; g.Kp = pink_b200_operand_stride(K, dist_type);
-    if (!g_op_status) { CU_TRY(cudaMalloc(&g_op_status, sizeof(int))); CU_TRY(cudaMemset(g_op_status, 0, sizeof(int))); }
-    int* d_status = g_op_status;
+    int* d_status = nullptr;
+    {
+        const int rc = op_status_word(&d_status);
+        if (rc) return rc;
+    }
     DistanceArgs da{};
     da.a0 = dev_a0; da.a1 = dev_a1; da.anorm = dev_anorm; da.n = n_neurons;
     da.b0 = dev_b0; da.b1 = dev_b1; da.bnorm = dev_bnorm; da.n_img = n_img;
@@ -1431,12 +1460,15 @@ int pink_b200_op_distance(uint32_t dist_type, uint32_t n_neurons, uint32_t n_tra
 
 int pink_b200_op_status(void)
 {
-    if (!g_op_status) return PINK_B200_OK;
+    int dev = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    int* word = (dev >= 0 && dev < kOpMaxDevices) ? g_op_status[dev].load(std::memory_order_acquire) : nullptr;
+    if (!word) return PINK_B200_OK;
     int st = 0;
     CU_TRY(cudaDeviceSynchronize());
-    CU_TRY(cudaMemcpy(&st, g_op_status, sizeof(int), cudaMemcpyDeviceToHost));
+    CU_TRY(cudaMemcpy(&st, word, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != kDevOk) {
-        cudaMemset(g_op_status, 0, sizeof(int));
+        cudaMemset(word, 0, sizeof(int));
         return fail(PINK_B200_ETIMEOUT, "a bounded device-side wait expired (code " + std::to_string(st) + ")");
     }
     return PINK_B200_OK;

@@ -21,6 +21,7 @@
 #include "kernels.cuh"
 #include "quant.cuh"
 
+#include <atomic>
 #include <type_traits>
 
 #include <cmath>
@@ -484,19 +485,21 @@ static __device__ __align__(256) float g_rotate_scratch[2 * kStaticMaxQuadrant];
 cudaError_t rotate_scratch_address(float** out)
 {
     constexpr int kMaxDevices = 64;
-    static float* addr[kMaxDevices] = {};
+    static std::atomic<float*> addr[kMaxDevices];        // first calls may come from several host threads
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-    if (!addr[dev]) {
+    float* known = addr[dev].load(std::memory_order_acquire);
+    if (!known) {
         // In host code the array's name is only a handle; the kernels need its device address.
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_rotate_scratch);
         if (e != cudaSuccess) return e;
-        addr[dev] = static_cast<float*>(p);
+        known = static_cast<float*>(p);
+        addr[dev].store(known, std::memory_order_release);   // every thread looks up the same address
     }
-    *out = addr[dev];
+    *out = known;
     return cudaSuccess;
 }
 

@@ -1,4 +1,5 @@
-"""The reference's Python-level tests and usage, run against pink_b200.pink (same names, keywords and results).
+"""The reference's Python-level tests and usage, run against both front-ends of the library -- the compiled
+pybind11 module pink_b200._pink and its ctypes/numpy mirror pink_b200.pink (same names, keywords and results).
 Sources: test/SelfOrganizingMapTest/Trainer.cpp, Mapper.cpp; test/CudaTest/mapper.cu, compare_trainer_cpu.cu,
 compare_trainer_mixed.cu; test/PythonBindingTest/DynamicTrainer.cpp; python/pink/train.py."""
 import numpy as np
@@ -9,6 +10,12 @@ import oracle as O
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["pink_b200._pink", "pink_b200.pink"])
+def pink(request):
+    import importlib
+    return importlib.import_module(request.param)
+
+
 class StepFunctor:                      # src/UtilitiesLib/DistributionFunctor.cpp:14-22
     def __init__(self, value):
         self.value = value
@@ -17,9 +24,8 @@ class StepFunctor:                      # src/UtilitiesLib/DistributionFunctor.c
         return 1.0 if d <= self.value else 0.0
 
 
-def test_trainer_num_rot(cuda):
+def test_trainer_num_rot(cuda, pink):
     """test/SelfOrganizingMapTest/Trainer.cpp:22-42"""
-    import pink_b200.pink as pink
     som = pink.SOM(np.zeros((2, 2, 2, 2), np.float32))
     for R in (0, 3, 90):
         with pytest.raises(RuntimeError, match="Number of rotations"):
@@ -28,9 +34,8 @@ def test_trainer_num_rot(cuda):
         pink.Trainer(som, number_of_rotations=R, use_flip=False, max_update_distance=1.0, euclidean_distance_dim=2)
 
 
-def test_trainer_cartesian_2d_float_step_function(cuda):
+def test_trainer_cartesian_2d_float_step_function(cuda, pink):
     """test/SelfOrganizingMapTest/Trainer.cpp:66-88: expected neuron {6, 7, 10, 11}."""
-    import pink_b200.pink as pink
     som = pink.SOM(np.zeros((1, 1, 2, 2), np.float32))
     trainer = pink.Trainer(som, StepFunctor(10.0), 0, 1, False, 0.0, pink.Interpolation.BILINEAR,
                            euclidean_distance_dim=2, euclidean_distance_type=pink.DataType.FLOAT)
@@ -39,9 +44,8 @@ def test_trainer_cartesian_2d_float_step_function(cuda):
     assert np.array(som, copy=False).ravel().tolist() == [6.0, 7.0, 10.0, 11.0]
 
 
-def test_trainer_cartesian_3d(cuda):
+def test_trainer_cartesian_3d(cuda, pink):
     """test/SelfOrganizingMapTest/Trainer.cpp:90-151"""
-    import pink_b200.pink as pink
     raw = np.zeros((2, 2, 2, 2, 2), np.float32)
     raw[0, 1] = np.array([4, 3, 2, 1, 8, 7, 6, 5], np.float32).reshape(2, 2, 2)
     som = pink.SOM(raw, neuron_layout="cartesian-3d")
@@ -56,9 +60,8 @@ def test_trainer_cartesian_3d(cuda):
 @pytest.mark.parametrize("dtype", ["FLOAT", "UINT8", "UINT16"])
 @pytest.mark.parametrize("row", [(1, 2, 2, 2, 1, False), (1, 3, 3, 2, 1, False), (1, 3, 3, 2, 360, False),
                                  (2, 3, 3, 2, 360, False), (2, 3, 3, 2, 360, True)])
-def test_mapper_exact_values(cuda, row, dtype):
+def test_mapper_exact_values(cuda, pink, row, dtype):
     """test/CudaTest/mapper.cu:55-120: image 0 against SOM 1 maps to exactly 2.0 in all three modes."""
-    import pink_b200.pink as pink
     som_dim, nd, idim, ed, R, flip = row
     som = pink.SOM(np.ones((som_dim, som_dim, nd, nd), np.float32))
     mapper = pink.Mapper(som, 0, R, flip, pink.Interpolation.BILINEAR, euclidean_distance_dim=ed,
@@ -69,9 +72,8 @@ def test_mapper_exact_values(cuda, row, dtype):
 
 @pytest.mark.parametrize("row", [(1, 2, 2, 2, 1, False, 0.0, 0.5, 1.0), (1, 2, 2, 2, 1, False, 0.5, 0.5, 0.0),
                                  (2, 3, 5, 2, 360, True, 0.0, 1.0, 2.0), (1, 3, 5, 2, 360, False, 1.0, 0.0, 2.0)])
-def test_mapper_float_table(cuda, row):
+def test_mapper_float_table(cuda, pink, row):
     """test/SelfOrganizingMapTest/Mapper.cpp:80-98 (float)."""
-    import pink_b200.pink as pink
     som_dim, nd, idim, ed, R, flip, nv, iv, want = row
     som = pink.SOM(np.full((som_dim, som_dim, nd, nd), nv, np.float32))
     mapper = pink.Mapper(som, number_of_rotations=R, use_flip=flip, euclidean_distance_dim=ed,
@@ -86,10 +88,9 @@ COMPARE = [(2, 2, 2, 2, 1, False), (2, 2, 2, 2, 4, False), (2, 2, 2, 2, 8, True)
 
 
 @pytest.mark.parametrize("p", COMPARE)
-def test_compare_trainer_with_reference_cpu(cuda, p):
+def test_compare_trainer_with_reference_cpu(cuda, pink, p):
     """test/CudaTest/compare_trainer_cpu.cu:49-98: one step, random image and SOM, GPU float against the
     reference CPU path within 1e-4 absolute (here: the oracle, which equals the reference CPU bit for bit)."""
-    import pink_b200.pink as pink
     som_dim, idim, nd, ed, R, flip = p
     rng = np.random.default_rng(sum(p))
     img = rng.random((idim, idim), dtype=np.float32)
@@ -105,10 +106,9 @@ def test_compare_trainer_with_reference_cpu(cuda, p):
 
 
 @pytest.mark.parametrize("p", COMPARE[:8])
-def test_compare_trainer_mixed_precision(cuda, p):
+def test_compare_trainer_mixed_precision(cuda, pink, p):
     """test/CudaTest/compare_trainer_mixed.cu:49-93: float and uint8 training agree within 1e-4 (same BMU and
     best rotations) for one step on random inputs."""
-    import pink_b200.pink as pink
     som_dim, idim, nd, ed, R, flip = p
     rng = np.random.default_rng(sum(p) + 1)
     img = rng.random((idim, idim), dtype=np.float32)
@@ -125,10 +125,9 @@ def test_compare_trainer_mixed_precision(cuda, p):
 
 
 @pytest.mark.parametrize("layout,shape", [("cartesian-2d", (3, 3, 12, 12)), ("hexagonal-2d", (19, 12, 12))])
-def test_dynamic_trainer_layouts_like_train_py(cuda, layout, shape):
+def test_dynamic_trainer_layouts_like_train_py(cuda, pink, layout, shape):
     """test/PythonBindingTest/DynamicTrainer.cpp:29-73 and python/pink/train.py:103-118: cartesian and hexagonal
     SOMs, uint8, several images; here also checked against the oracle."""
-    import pink_b200.pink as pink
     rng = np.random.default_rng(5)
     som0 = rng.random(shape, dtype=np.float32)
     imgs = rng.random((5, 16, 16), dtype=np.float32)
@@ -150,9 +149,8 @@ def test_dynamic_trainer_layouts_like_train_py(cuda, layout, shape):
     assert trainer.get_update_info().sum() == 5
 
 
-def test_python_callable_distribution_function(cuda):
+def test_python_callable_distribution_function(cuda, pink):
     """Any Python callable works as distribution_function (pybind11/functional.h in the reference)."""
-    import pink_b200.pink as pink
     som0 = np.random.default_rng(1).random((3, 3, 8, 8), dtype=np.float32)
     img = np.random.default_rng(2).random((10, 10), dtype=np.float32)
     g = pink.GaussianFunctor(1.3, 0.4)
@@ -165,11 +163,12 @@ def test_python_callable_distribution_function(cuda):
     assert np.array_equal(np.array(a), np.array(b))
 
 
-def test_error_texts(cuda):
-    import pink_b200.pink as pink
+def test_error_texts(cuda, pink):
     som = pink.SOM(np.zeros((2, 2, 4, 4), np.float32))
-    with pytest.raises(RuntimeError, match="euclidean_distance_dim not defined"):
+    with pytest.raises((RuntimeError, TypeError)):      # the reference's binding has no default for it: TypeError there
         pink.Trainer(som)
+    with pytest.raises(RuntimeError, match="euclidean_distance_dim not defined"):
+        pink.Trainer(som, euclidean_distance_dim=0)
     with pytest.raises(RuntimeError, match="data-type not supported"):
         pink.SOM(np.zeros((2, 2, 4, 4)), data_type="float64")
     with pytest.raises(RuntimeError, match="is not supported"):

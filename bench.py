@@ -231,7 +231,7 @@ def main():
     ap.add_argument("--batch", type=int, default=512, help="images per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-extras", action="store_true", help="skip the map / other-configuration blocks")
+    ap.add_argument("--no-extras", action="store_true", help="skip the map / other-configuration / reference-GPU blocks")
     ap.add_argument("--option", action="append", default=[], help="context switch name=value (see pink_b200_set_option)")
     args = ap.parse_args()
     w = WORKLOAD
@@ -414,6 +414,7 @@ def main():
         extras["map"] = bench_map(torch, dist, barrier, rank, world, local, som, pool)
         if world == 1:
             extras["other_configs"] = bench_other_configs(torch, local)
+            extras["reference_gpu"] = bench_reference_gpu(w, som, pool)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -496,6 +497,27 @@ def bench_map(torch, dist, barrier, rank, world, local, som4, pool4):
                     "timing": "host clock around %d whole passes, synchronised on both sides, max over ranks" % reps})
         out[key] = res
         eng.close()
+    return out
+
+
+def bench_reference_gpu(w, som, pool, n_images=24):
+    """The reference's own CUDA path (unmodified, compiled for sm_100a) on the same GPU and workload: images/s of its
+    Trainer and Mapper, uint8 distances, on the first images of the pool.  Runs in a child process."""
+    import oracle as O
+    if not O.have_ref_cuda():
+        return {"unavailable": "the reference's CUDA path was not built (its source tree was absent at build time)"}
+    N = som_size(w)
+    out = {"workload": w["name"], "images": n_images, "unit": "images/s",
+           "note": "reference Trainer / Mapper with UseGPU = true, one visible GPU, wall clock of its own loop after one warm-up step"}
+    args = (som.reshape(N, w["neuron_dim"], w["neuron_dim"]), pool[:n_images].reshape(n_images, w["image_dim"], w["image_dim"]),
+            w["som_layout"], w["som_dim"], w["som_dim"], w["image_dim"], w["neuron_dim"], w["ed_dim"], w["rotations"], w["flip"], w["mode"])
+    for task in ("train", "map"):
+        try:
+            r = O.ref_cuda_run(task, *args, sigma=w["sigma"], damping=w["damping"], timeout=240)
+            out[task] = n_images / float(r["seconds"])
+        except Exception as ex:
+            out[task] = None
+            out[task + "_error"] = str(ex)[:300]
     return out
 
 

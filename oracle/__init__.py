@@ -16,6 +16,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = os.path.join(_HERE, "libpink_oracle.so")
 _REF = os.path.join(_HERE, "_ref", "libpink_ref.so")
+_REF_CUDA = os.path.join(_HERE, "_ref", "libpink_ref_cuda.so")
 
 MODE_F32, MODE_U16, MODE_U8 = 0, 1, 2
 FUNC_GAUSSIAN, FUNC_UNITY_GAUSSIAN, FUNC_MEXICAN_HAT, FUNC_STEP = 0, 1, 2, 3
@@ -30,8 +31,11 @@ def build(force=False):
     shim = os.path.join(_HERE, "ref_shim.cpp")
     tree = reference_tree()
     if tree:
-        if force or not os.path.exists(_REF) or os.path.getmtime(_REF) < os.path.getmtime(shim):
-            subprocess.check_call(["make", "-C", _HERE, "ref", "PINK_REF=" + tree], stdout=subprocess.DEVNULL)
+        cuda_shim = os.path.join(_HERE, "ref_cuda_shim.cu")
+        stale = lambda lib, src: not os.path.exists(lib) or os.path.getmtime(lib) < os.path.getmtime(src)
+        if force or stale(_REF, shim) or stale(_REF_CUDA, cuda_shim):
+            subprocess.check_call(["make", "-C", _HERE, "ref", "PINK_REF=" + tree], stdout=subprocess.DEVNULL,
+                                  stderr=subprocess.DEVNULL)
 
 
 def reference_tree():
@@ -335,3 +339,38 @@ def ref_fill_random_uniform(n, seed=5489):
     a = np.empty(n, np.float32)
     ref().ref_fill_random_uniform(_fp(a), n, seed)
     return a
+
+
+# ---------------------------------------------------------------------------
+# the reference's own CUDA path, run in a process of its own
+# ---------------------------------------------------------------------------
+
+def have_ref_cuda():
+    return os.path.exists(_REF_CUDA)
+
+
+def ref_cuda_run(task, som, images, som_layout, s0, s1, idim, nd, ed, R, flip, mode, sigma=1.1, damping=0.2,
+                 timeout=300):
+    """Runs the reference's CUDA Trainer (task "train") or Mapper (task "map") on ONE visible GPU in a child process
+    (oracle/ref_cuda_worker.py): a failure of that code cannot take the caller's CUDA context with it, and the
+    reference's multi-GPU branch is never reached.  som: (N, nd, nd); images: (n, idim, idim).
+    Returns a dict: "seconds" (wall time of the n steps after one untimed warm-up step), "som" (train) or
+    "dist", "rot" (map).  Raises RuntimeError with the child's output when it fails or runs out of time."""
+    import sys
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        inp, out = os.path.join(tmp, "in.npz"), os.path.join(tmp, "out.npz")
+        np.savez(inp, som=np.ascontiguousarray(som, dtype=np.float32), images=np.ascontiguousarray(images, dtype=np.float32),
+                 cfg=np.array([som_layout, s0, s1, idim, nd, ed, R, int(flip), mode], np.int64),
+                 fcfg=np.array([sigma, damping], np.float64), task=np.array(task))
+        env = dict(os.environ)
+        env["CUDA_VISIBLE_DEVICES"] = env.get("CUDA_VISIBLE_DEVICES", "0").split(",")[0] or "0"
+        try:
+            proc = subprocess.run([sys.executable, os.path.join(_HERE, "ref_cuda_worker.py"), inp, out], env=env,
+                                  capture_output=True, text=True, timeout=timeout)
+        except subprocess.TimeoutExpired:
+            raise RuntimeError("the reference's CUDA path did not finish within %d s" % timeout)
+        if proc.returncode != 0 or not os.path.exists(out):
+            raise RuntimeError("the reference's CUDA path failed (exit %d): %s" % (proc.returncode, (proc.stdout + proc.stderr)[-600:]))
+        with np.load(out) as z:
+            return {k: z[k] for k in z.files}

@@ -278,7 +278,8 @@ def main():
             uid.copy_(torch.frombuffer(bytearray(engine.Engine.unique_id()), dtype=torch.uint8))
         dist.broadcast(uid, 0)
         eng.comm_init(bytes(uid.cpu().numpy()))
-    eng.set_update_factors(F)
+    # one factor per distance class of the grid; F (the N x N table of the same factors) only serves the accounting below
+    eng.set_update_function(w["som_layout"], w["som_dim"], w["som_dim"], capi.FUNC_GAUSSIAN, w["sigma"], w["damping"])
 
     # ---- untimed: a fixed training prefix whose results must not depend on the number of ranks -----------
     check = training_check(eng, som, pool, CHECK_IMAGES, reduce if world > 1 else None)
@@ -528,10 +529,9 @@ def bench_other_configs(torch, local):
     for key, n_img in (("C1", 2000), ("C3", 256)):
         w = WORKLOADS[key]
         N, som, pool = make_inputs(w, n_img)
-        F = engine.update_factors(w["som_layout"], w["som_dim"], w["som_dim"], capi.FUNC_GAUSSIAN, w["sigma"], w["damping"])
         eng = make_engine(w, N, local)
         eng.set_som(som)
-        eng.set_update_factors(F)
+        eng.set_update_function(w["som_layout"], w["som_dim"], w["som_dim"], capi.FUNC_GAUSSIAN, w["sigma"], w["damping"])
         d_pool = torch.from_numpy(pool).cuda()
         eng.train_device(d_pool.data_ptr(), n_img)
         eng.synchronize()

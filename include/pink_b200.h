@@ -166,6 +166,25 @@ int pink_b200_som_distances(uint32_t som_layout, uint32_t dim0, uint32_t dim1, f
 int pink_b200_update_factors(uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t func, float p0, float p1,
                              float max_update_distance, float* out);
 
+/* The same without an N x N table (no reference counterpart; the reference evaluates its distribution function N^2
+ * times and keeps N^2 floats, Trainer.h:69-76 -- 7.8 million calls and 31 MB for 2,791 neurons).  The map distance of
+ * two neurons takes few distinct values: it depends only on the absolute coordinate differences (cartesian grids of
+ * up to three dimensions; dim2 = 1 for two) or is the hop count (hexagonal; dim2 = 1).  pink_b200_distance_classes
+ * returns their number and (if `distances` is not NULL) the distance of every class; a caller with its own
+ * distribution function evaluates it once per class, applies the max_update_distance cut-off and hands the result to
+ * pink_b200_set_update_lut.  pink_b200_update_lut does that for the built-in functors, pink_b200_set_update_function
+ * both steps.  The factors are identical to the table's, bit for bit.  pink_b200_som_coordinates: the grid
+ * position (x, y, z, 0 -- hexagonal: axial q, r) of every neuron as int16[N][4]. */
+uint32_t pink_b200_distance_classes(uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t dim2, float* distances,
+                                    uint32_t capacity);
+int pink_b200_som_coordinates(uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t dim2, int16_t* out);
+int pink_b200_update_lut(uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t dim2, uint32_t func, float p0, float p1,
+                         float max_update_distance, float* lut, uint32_t capacity);
+int pink_b200_set_update_lut(pink_b200_ctx* ctx, uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                             const float* host_lut, uint32_t n_classes);
+int pink_b200_set_update_function(pink_b200_ctx* ctx, uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                                  uint32_t func, float p0, float p1, float max_update_distance);
+
 /* The same two tables for a three-dimensional cartesian SOM of dim0 x dim1 x dim2
  * neurons (CartesianLayout<3>, CartesianLayout.h:116-123 for the position of an
  * array index; the command line tool's --som-depth > 1, main_gpu.cu:24-25). */
@@ -270,6 +289,8 @@ int pink_b200_group_set_option(pink_b200_group* group, const char* name, long lo
 int pink_b200_group_set_som(pink_b200_group* group, const float* host_som);
 int pink_b200_group_get_som(pink_b200_group* group, float* host_som);
 int pink_b200_group_set_update_factors(pink_b200_group* group, const float* host_factors);
+int pink_b200_group_set_update_lut(pink_b200_group* group, uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                                   const float* host_lut, uint32_t n_classes);
 int pink_b200_group_train(pink_b200_group* group, const float* host_images, uint64_t n);
 int pink_b200_group_get_update_counts(pink_b200_group* group, uint32_t* host_counts);
 int pink_b200_group_synchronize(pink_b200_group* group);

@@ -84,15 +84,12 @@ template <typename Layout> struct layout_id;
 template <uint8_t dim> struct layout_id<CartesianLayout<dim>> { static constexpr uint32_t value = PINK_B200_LAYOUT_CARTESIAN; };
 template <> struct layout_id<HexagonalLayout> { static constexpr uint32_t value = PINK_B200_LAYOUT_HEXAGONAL; };
 
-/// out[i * N + j] = map distance of neurons i and j
-inline int som_distances(CartesianLayout<1> const& l, float* out)
-{ return pink_b200_som_distances(PINK_B200_LAYOUT_CARTESIAN, l.m_dimension[0], 1, out); }
-inline int som_distances(CartesianLayout<2> const& l, float* out)
-{ return pink_b200_som_distances(PINK_B200_LAYOUT_CARTESIAN, l.m_dimension[0], l.m_dimension[1], out); }
-inline int som_distances(CartesianLayout<3> const& l, float* out)
-{ return pink_b200_som_distances_3d(l.m_dimension[0], l.m_dimension[1], l.m_dimension[2], out); }
-inline int som_distances(HexagonalLayout const& l, float* out)
-{ return pink_b200_som_distances(PINK_B200_LAYOUT_HEXAGONAL, l.m_dimension[0], l.m_dimension[1], out); }
+/// (layout id, dim0, dim1, dim2) of a map layout as the C ABI's per-distance-class functions want it
+inline std::array<uint32_t, 4> grid_of(CartesianLayout<1> const& l) { return {PINK_B200_LAYOUT_CARTESIAN, l.m_dimension[0], 1, 1}; }
+inline std::array<uint32_t, 4> grid_of(CartesianLayout<2> const& l) { return {PINK_B200_LAYOUT_CARTESIAN, l.m_dimension[0], l.m_dimension[1], 1}; }
+inline std::array<uint32_t, 4> grid_of(CartesianLayout<3> const& l)
+{ return {PINK_B200_LAYOUT_CARTESIAN, l.m_dimension[0], l.m_dimension[1], l.m_dimension[2]}; }
+inline std::array<uint32_t, 4> grid_of(HexagonalLayout const& l) { return {PINK_B200_LAYOUT_HEXAGONAL, l.m_dimension[0], l.m_dimension[1], 1}; }
 } // namespace detail
 
 /// one data entry (an image or a neuron)
@@ -267,12 +264,15 @@ public:
        m_update_info(som.get_number_of_neurons(), 0)
     {
         // update factor of neuron j when neuron i is the best matching unit: the distribution function of
-        // their map distance, cut off at max_update_distance
-        const uint32_t n = som.get_number_of_neurons();
-        std::vector<float> distance(static_cast<size_t>(n) * n);
-        detail::check(detail::som_distances(som.get_som_layout(), distance.data()));
-        m_update_factors.resize(distance.size());
-        for (size_t i = 0; i < distance.size(); ++i)
+        // their map distance, cut off at max_update_distance -- evaluated once per distinct distance of the
+        // grid (the reference calls it N^2 times, Trainer.h:69-76; the factors are the same)
+        m_grid = detail::grid_of(som.get_som_layout());
+        const uint32_t classes = pink_b200_distance_classes(m_grid[0], m_grid[1], m_grid[2], m_grid[3], nullptr, 0);
+        if (classes == 0) throw exception("unsupported SOM layout");
+        std::vector<float> distance(classes);
+        pink_b200_distance_classes(m_grid[0], m_grid[1], m_grid[2], m_grid[3], distance.data(), classes);
+        m_update_factors.resize(classes);
+        for (uint32_t i = 0; i < classes; ++i)
             m_update_factors[i] = (max_update_distance <= 0 or distance[i] < max_update_distance)
                                 ? distribution_function(distance[i]) : 0.0f;
     }
@@ -281,7 +281,8 @@ public:
     {
         const bool first = m_session.get() == nullptr;
         pink_b200_ctx* ctx = m_session.context(data, m_som.get_data_pointer());
-        if (first) detail::check(pink_b200_set_update_factors(ctx, m_update_factors.data()));
+        if (first) detail::check(pink_b200_set_update_lut(ctx, m_grid[0], m_grid[1], m_grid[2], m_grid[3], m_update_factors.data(),
+                                                          static_cast<uint32_t>(m_update_factors.size())));
         detail::check(pink_b200_train(ctx, data.get_data_pointer(), 1));
     }
 
@@ -299,7 +300,8 @@ public:
 private:
     SOMType& m_som;
     detail::Session<SOMLayout, DataLayout> m_session;
-    std::vector<float> m_update_factors;
+    std::array<uint32_t, 4> m_grid{};
+    std::vector<float> m_update_factors;        // one factor per distance class of the grid
     std::vector<uint32_t> m_update_info;
 };
 

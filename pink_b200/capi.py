@@ -78,6 +78,15 @@ SYMBOLS = {
     "pink_b200_som_distances": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
     "pink_b200_update_factors": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
                                            C.c_float, C.c_void_p]),
+    "pink_b200_distance_classes": (C.c_uint32, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32]),
+    "pink_b200_som_coordinates": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
+    "pink_b200_update_lut": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
+                                       C.c_float, C.c_void_p, C.c_uint32]),
+    "pink_b200_set_update_lut": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32]),
+    "pink_b200_set_update_function": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                                C.c_float, C.c_float, C.c_float]),
+    "pink_b200_group_set_update_lut": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
+                                                 C.c_uint32]),
     "pink_b200_som_distances_3d": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]),
     "pink_b200_update_factors_3d": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
                                                C.c_float, C.c_void_p]),

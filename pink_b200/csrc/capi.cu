@@ -188,7 +188,9 @@ struct pink_b200_ctx
     float* d_som = nullptr;
     void *d_a0 = nullptr, *d_a1 = nullptr, *d_anorm = nullptr;
     float *d_cs = nullptr, *d_sn = nullptr;
-    float* d_factors = nullptr;
+    float* d_factors = nullptr;       // this shard's columns of an N x N factor table, or ...
+    short4* d_coords = nullptr; float* d_lut = nullptr;   // ... grid positions of all neurons + one factor per distance class
+    FactorSource factor_source{};
     float* d_base = nullptr;   size_t base_imgs = 0;
     void *d_b0 = nullptr, *d_b1 = nullptr, *d_bnorm = nullptr; size_t b_imgs = 0;
     unsigned long long* d_keys = nullptr; size_t key_imgs = 0;
@@ -329,7 +331,7 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     BmuArgs ba{};
     ba.keys = c->d_keys; ba.n = c->count; ba.first_neuron = c->first; ba.neuron_stride = c->stride; ba.shift = key_shift(g.mode);
     ba.pairs = c->d_pairs; ba.rank = c->cfg.rank; ba.world = c->cfg.world_size;
-    ba.factors = c->d_factors; ba.items = c->d_items; ba.n_items = c->d_nitems;
+    ba.factors = c->factor_source; ba.items = c->d_items; ba.n_items = c->d_nitems;
     ba.counts = c->d_counts; ba.bmu_log = bmu_slot;
     ba.R = g.R; ba.q = g.q; ba.nd = g.nd;
     ba.magic_R = g.R == 1 ? 0u : (uint32_t)((1ull << 32) / g.R) + 1;
@@ -394,7 +396,7 @@ int train_steps_batch(pink_b200_ctx* c, size_t slot_img, uint32_t cnt, uint32_t*
     a.base = c->d_base + slot_img * (g.q ? g.q : 1) * (size_t)g.P;
     a.wrange = c->d_wrange;
     a.rmax = c->d_wrange ? c->d_rmax + slot_img : nullptr;
-    a.factors = c->d_factors;
+    a.factors = c->factor_source;
     a.owners = c->d_owners;
     a.n_img = cnt; a.first_neuron = c->first; a.neuron_stride = c->stride; a.rank = c->cfg.rank; a.world = c->cfg.world_size;
     a.counts = c->d_counts; a.bmu_log = bmu_slots; a.stats = c->d_stats; a.status = c->d_status;
@@ -918,7 +920,7 @@ int pink_b200_destroy(pink_b200_ctx* c)
     release_peer_exchange(c);
     if (c->comm && nccl().ok) nccl().CommDestroy(c->comm);
     free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
-    free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_base);
+    free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_coords); free_dev(c->d_lut); free_dev(c->d_base);
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
     free_dev(c->d_items); free_dev(c->d_nitems); free_dev(c->d_stats); free_dev(c->d_wrange); free_dev(c->d_rmax);
     free_dev(c->d_circle); free_dev(c->d_owners); free_dev(c->d_ctrl); free_dev(c->d_stamps);
@@ -1060,6 +1062,7 @@ int pink_b200_set_update_factors(pink_b200_ctx* c, const float* host_factors)
     CU_TRY(cudaSetDevice(c->cfg.device));
     CU_TRY(cudaStreamSynchronize(c->stream));
     const size_t N = c->cfg.n_neurons;
+    free_dev(c->d_lut);
     if (!c->d_factors) CU_TRY(cudaMalloc(&c->d_factors, N * c->count * sizeof(float)));
     {
         // this shard's columns of the table, gathered on the host: F[b][first + j * stride]
@@ -1075,12 +1078,70 @@ int pink_b200_set_update_factors(pink_b200_ctx* c, const float* host_factors)
     if (c->plan_ok) {
         // which block of the persistent kernel rewrites which neuron: spread every neighbourhood over the blocks
         std::vector<uint32_t> owners((size_t)c->plan.grid * c->plan.owned_per_block);
-        step_assign_owners(host_factors, (uint32_t)N, c->first, c->stride, c->count, c->plan, owners.data());
+        step_assign_owners([&](uint32_t i, uint32_t m) { return host_factors[(size_t)i * N + m]; }, c->first, c->stride,
+                           c->count, c->plan, owners.data());
         CU_TRY(cudaMemcpyAsync(c->d_owners, owners.data(), owners.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
         CU_TRY(cudaStreamSynchronize(c->stream));
     }
+    c->factor_source = FactorSource{};
+    c->factor_source.table = c->d_factors;
     c->have_factors = true;
     return PINK_B200_OK;
+}
+
+int pink_b200_set_update_lut(pink_b200_ctx* c, uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                             const float* host_lut, uint32_t n_classes)
+{
+    if (!c || !host_lut) return fail(PINK_B200_EINVAL, "null argument");
+    const uint32_t want = pink_b200_distance_classes(som_layout, dim0, dim1, dim2, nullptr, 0);
+    if (want == 0 || want != n_classes) return fail(PINK_B200_EINVAL, "the table does not have one entry per distance class of this SOM layout");
+    const uint32_t N = c->cfg.n_neurons;
+    const uint64_t size = som_layout == PINK_B200_LAYOUT_HEXAGONAL ? pink_b200_som_size(som_layout, dim0, dim1)
+                                                                   : (uint64_t)dim0 * dim1 * dim2;
+    if (size != N) return fail(PINK_B200_EINVAL, "the SOM layout does not have the context's number of neurons");
+    std::vector<int16_t> coords((size_t)4 * N);
+    if (pink_b200_som_coordinates(som_layout, dim0, dim1, dim2, coords.data()) != PINK_B200_OK)
+        return fail(PINK_B200_EINVAL, "unsupported SOM layout");
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    free_dev(c->d_factors); free_dev(c->d_lut);
+    if (!c->d_coords) CU_TRY(cudaMalloc(&c->d_coords, (size_t)N * sizeof(short4)));
+    CU_TRY(cudaMalloc(&c->d_lut, (size_t)n_classes * sizeof(float)));
+    CU_TRY(cudaMemcpyAsync(c->d_coords, coords.data(), (size_t)N * sizeof(short4), cudaMemcpyHostToDevice, c->stream));
+    CU_TRY(cudaMemcpyAsync(c->d_lut, host_lut, (size_t)n_classes * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    const bool hex = som_layout == PINK_B200_LAYOUT_HEXAGONAL;
+    if (c->plan_ok) {
+        auto cls = [&](uint32_t i, uint32_t m) -> uint32_t {
+            const int dx = coords[4 * i] - coords[4 * m], dy = coords[4 * i + 1] - coords[4 * m + 1], dz = coords[4 * i + 2] - coords[4 * m + 2];
+            if (hex) return ((dx >= 0) == (dy >= 0)) ? (uint32_t)std::abs(dx + dy) : (uint32_t)std::max(std::abs(dx), std::abs(dy));
+            return ((uint32_t)std::abs(dz) * dim0 + (uint32_t)std::abs(dy)) * dim1 + (uint32_t)std::abs(dx);
+        };
+        std::vector<uint32_t> owners((size_t)c->plan.grid * c->plan.owned_per_block);
+        step_assign_owners([&](uint32_t i, uint32_t m) { return host_lut[cls(i, m)]; }, c->first, c->stride, c->count, c->plan,
+                           owners.data());
+        CU_TRY(cudaMemcpyAsync(c->d_owners, owners.data(), owners.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
+        CU_TRY(cudaStreamSynchronize(c->stream));
+    }
+    c->factor_source = FactorSource{};
+    c->factor_source.coords = c->d_coords;
+    c->factor_source.lut = c->d_lut;
+    c->factor_source.hexagonal = hex;
+    c->factor_source.dim0 = dim0; c->factor_source.dim1 = dim1;
+    c->have_factors = true;
+    return PINK_B200_OK;
+}
+
+int pink_b200_set_update_function(pink_b200_ctx* c, uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                                  uint32_t func, float p0, float p1, float max_update_distance)
+{
+    if (!c) return fail(PINK_B200_EINVAL, "null argument");
+    const uint32_t n = pink_b200_distance_classes(som_layout, dim0, dim1, dim2, nullptr, 0);
+    if (n == 0) return fail(PINK_B200_EINVAL, "unsupported SOM layout");
+    std::vector<float> lut(n);
+    if (pink_b200_update_lut(som_layout, dim0, dim1, dim2, func, p0, p1, max_update_distance, lut.data(), n) != PINK_B200_OK)
+        return fail(PINK_B200_EINVAL, "unsupported neighbourhood function");
+    return pink_b200_set_update_lut(c, som_layout, dim0, dim1, dim2, lut.data(), n);
 }
 
 int pink_b200_train_device(pink_b200_ctx* c, const float* dev_images, uint64_t n)

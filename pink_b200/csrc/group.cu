@@ -30,7 +30,8 @@ struct pink_b200_group
     std::vector<pink_b200_ctx*> map;        // whole-SOM contexts, created on first use (one device: the training context)
     std::vector<std::pair<std::string, long long>> options;
     std::vector<float> som;                 // host copy of the whole map: source for contexts created later
-    std::vector<float> factors;
+    std::vector<float> factors;             // N x N table, or (lut_layout[0] != ~0u) one value per distance class
+    uint32_t lut_layout[4] = {~0u, 0, 0, 0};
     bool have_som = false, have_factors = false;
     bool train_has_som = false, train_has_factors = false, map_has_som = false;
     bool som_stale = false;                 // the training contexts hold a newer map than `som`
@@ -95,7 +96,11 @@ int ensure_train(pink_b200_group* g)
         g->train_has_som = true;
     }
     if (!g->train_has_factors && g->have_factors) {
-        int rc = for_each_device(W, [&](size_t d) { return pink_b200_set_update_factors(g->train[d], g->factors.data()); });
+        int rc = for_each_device(W, [&](size_t d) {
+            if (g->lut_layout[0] == ~0u) return pink_b200_set_update_factors(g->train[d], g->factors.data());
+            return pink_b200_set_update_lut(g->train[d], g->lut_layout[0], g->lut_layout[1], g->lut_layout[2], g->lut_layout[3],
+                                            g->factors.data(), (uint32_t)g->factors.size());
+        });
         if (rc != PINK_B200_OK) return rc;
         g->train_has_factors = true;
     }
@@ -251,6 +256,21 @@ int pink_b200_group_set_update_factors(pink_b200_group* g, const float* host_fac
     if (!g || !host_factors) return report_error(PINK_B200_EINVAL, "null argument");
     const size_t n = (size_t)g->cfg.n_neurons * g->cfg.n_neurons;
     g->factors.assign(host_factors, host_factors + n);
+    g->lut_layout[0] = ~0u;
+    g->have_factors = true;
+    g->train_has_factors = false;
+    if (!g->train.empty()) return ensure_train(g);
+    return PINK_B200_OK;
+}
+
+int pink_b200_group_set_update_lut(pink_b200_group* g, uint32_t som_layout, uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                                   const float* host_lut, uint32_t n_classes)
+{
+    if (!g || !host_lut) return report_error(PINK_B200_EINVAL, "null argument");
+    if (pink_b200_distance_classes(som_layout, dim0, dim1, dim2, nullptr, 0) != n_classes || n_classes == 0)
+        return report_error(PINK_B200_EINVAL, "the table does not have one entry per distance class of this SOM layout");
+    g->factors.assign(host_lut, host_lut + n_classes);
+    g->lut_layout[0] = som_layout; g->lut_layout[1] = dim0; g->lut_layout[2] = dim1; g->lut_layout[3] = dim2;
     g->have_factors = true;
     g->train_has_factors = false;
     if (!g->train.empty()) return ensure_train(g);

@@ -6,6 +6,7 @@
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
+#include <functional>
 
 struct pink_b200_config;
 
@@ -89,6 +90,30 @@ bool distance_has_tail(const Geometry& g);
 // Returns cudaSuccess or the launch / tensor-map error; *why receives a static message.
 cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why);
 
+// ---- update factors ----------------------------------------------------------------
+// Either the N x N table of the reference (Trainer.h:69-76), this shard's columns of it, or -- for the grid layouts,
+// where the map distance takes few distinct values -- one value per distance class: lut[class(coords[bmu], coords[n])].
+struct FactorSource
+{
+    const float* table;         // [N_global][n_local], column = local neuron; null when the classes are used
+    const short4* coords;       // [N_global] grid position of every neuron (cartesian: x, y, z; hexagonal: axial q, r)
+    const float* lut;           // [classes]
+    uint32_t hexagonal, dim0, dim1;
+};
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float factor_of(const FactorSource& fs, uint32_t bmu, uint32_t local, uint32_t global, uint32_t n_local)
+{
+    if (fs.table) return fs.table[(size_t)bmu * n_local + local];
+    const short4 a = fs.coords[bmu], b = fs.coords[global];
+    const int dx = a.x - b.x, dy = a.y - b.y, dz = a.z - b.z;
+    uint32_t cls;
+    if (fs.hexagonal) cls = ((dx >= 0) == (dy >= 0)) ? (uint32_t)abs(dx + dy) : (uint32_t)max(abs(dx), abs(dy));
+    else cls = ((uint32_t)abs(dz) * fs.dim0 + (uint32_t)abs(dy)) * fs.dim1 + (uint32_t)abs(dx);
+    return fs.lut[cls];
+}
+#endif
+
 // ---- best matching unit and work list of the update ----------------------------
 // One neuron the update must rewrite: local index, update factor, and its best
 // transform decoded into the base rotation tq and the affine map
@@ -114,7 +139,7 @@ struct BmuArgs
     unsigned long long* keys; uint32_t n, first_neuron, shift;   // this shard's per-neuron minima (re-armed in phase 2)
     uint32_t neuron_stride;           // local neuron j is global neuron first_neuron + j * neuron_stride
     BmuPair* pairs; uint32_t rank, world;                        // per-rank records (world entries)
-    const float* factors;             // [N_global][n] update factors, column = local neuron
+    FactorSource factors;             // update factors of (best matching unit, neuron)
     UpdateItem* items; uint32_t* n_items;   // out: neurons with a non-zero factor, ascending, and their number
     uint32_t* counts;                 // [N_global] BMU hit counters (incremented by the owner)
     uint32_t* bmu_log;                // nullable: receives the global BMU index of this step
@@ -212,7 +237,7 @@ struct StepArgs
     float* som;                       // [n][Pp]
     const float* base;                // base rotations of the first image; consecutive images follow
     uint2* wrange; const uint32_t* rmax;   // nullable together: value ranges (see cannot_change); rmax[i] for image i
-    const float* factors;             // [N_global][n]
+    FactorSource factors;             // update factors of (best matching unit, neuron)
     const uint32_t* owners;           // [grid][owned_per_block] local neuron indices, ~0u = none
     // bookkeeping
     uint32_t n_img, first_neuron, neuron_stride, rank, world;   // local neuron j is global neuron first_neuron + j * neuron_stride
@@ -227,9 +252,10 @@ struct StepArgs
 // Fills `plan` and returns true when the persistent kernel can run this geometry on the current device.
 bool step_plan(const Geometry& g, uint32_t n_local, uint32_t n_global, StepPlan* plan, const char** why_not);
 // Which block updates which neuron: owners[b * owned_per_block + j], balanced so that the neurons close to any
-// best matching unit (large update factors) are spread over different blocks.  host_factors: [N][N] table.
-void step_assign_owners(const float* host_factors, uint32_t N, uint32_t first, uint32_t stride, uint32_t count,
-                        const StepPlan& plan, uint32_t* owners);
+// best matching unit (large update factors) are spread over different blocks.
+// closeness(i, m): update factor between global neurons i and m (any symmetric non-negative measure of nearness).
+void step_assign_owners(const std::function<float(uint32_t, uint32_t)>& closeness, uint32_t first, uint32_t stride,
+                        uint32_t count, const StepPlan& plan, uint32_t* owners);
 cudaError_t launch_train_steps(const Geometry& g, const StepPlan& plan, const StepArgs& a, cudaStream_t st, const char** why);
 
 // ---- mapping epilogue -------------------------------------------------------

@@ -266,12 +266,17 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     const uint32_t mu = item % pl.m_units, nt = item / pl.m_units;
                     const int32_t m0 = (int32_t)((PAIR ? 2 * mu + pair_rank : mu) * kBlockM);
                     const int32_t brow = (int32_t)(a.b_row0 + img * g.T + nt * pl.n_tile + pair_rank * b_rows);
+                    // Tiles that share neuron rows (or transform rows) run at the same time on other SMs.  Each starts
+                    // its walk over K at a different slice, so that they do not all ask the same L2 lines for the same
+                    // bytes at the same moment; integer accumulation does not depend on the order.
+                    const uint32_t k_first = (uint32_t)(((uint64_t)item * num_kb) / n_items);
                     for (uint32_t kb = 0; kb < num_kb; ++kb) {
                         const uint32_t it = (img * my_items + k) * num_kb + kb;
                         const uint32_t s = it % pl.ring_stages, ph = (it / pl.ring_stages) & 1;
                         if (!step_wait(&sh.empty_bar[s], ph ^ 1, sh, a.status)) { step_fail(sh, a.status, kDevTimeoutProducer); break; }
                         uint8_t* st = region + s * ring_stage_bytes;
-                        const int32_t kx = (int32_t)(kb * kBlockK);
+                        const uint32_t kb_at = kb + k_first < num_kb ? kb + k_first : kb + k_first - num_kb;
+                        const int32_t kx = (int32_t)(kb_at * kBlockK);
                         if (PAIR) {
                             const uint32_t bar = map_to_cta(smem_u32(&sh.full_bar[s]), 0);     // the issuing block's barrier
                             mbar_expect_tx_cluster(bar, stage_tx);
@@ -524,7 +529,7 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                 // three independent loads (one memory round trip)
                 key = __ldcg(&a.keys[n]);
                 const uint2 r = can_skip ? __ldcg(&a.wrange[n]) : make_uint2(0u, 0u);
-                if (have_bmu) f = a.factors[(size_t)bmu * a.n + n];
+                if (have_bmu) f = factor_of(a.factors, bmu, n, (uint32_t)shard_global(a.first_neuron, a.neuron_stride, n), a.n);
                 a.keys[n] = kKeyEmpty;                       // re-armed for the next image's distance phase
                 if (can_skip && f != 0.0f && cannot_change(f, r.x, r.y, rmax_bits)) f = 0.0f;
             }
@@ -631,8 +636,12 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                 const float f = e.f;
                 // -- w <- w - (w - r) * f over the whole plane, kUnroll rows per step:
                 //    all loads, then the arithmetic, then the stores; no predicates in the steady loop
-                bool changed = false;
-                uint32_t lo_bits = 0xFFFFFFFFu, hi_bits = 0u;           // min |w|, max |w| of the new values, as bit patterns
+                // What is tracked per element costs issue slots (the loop is issue-bound): one LOP3 for "did any bit
+                // change", two integer min / max for the value range.  The range is taken over the bit patterns as
+                // SIGNED integers: for non-negative floats that is the order of the values; a negative value (or
+                // NaN) shows as a negative minimum, and the neuron then simply gets no "cannot change" guarantee.
+                uint32_t diff_bits = 0;
+                int32_t lo_i = 0x7FFFFFFF, hi_i = (int32_t)0x80000000;
                 const uint32_t sw = nd * 4;                             // byte step of a neuron row
                 const int32_t sb = e.ax * 4;                            // byte step of the base rotation per neuron row
 #pragma unroll
@@ -646,9 +655,8 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
 #pragma unroll
                         for (int u = 0; u < kUnroll; ++u) {
                             o[u] = __fsub_rn(w[u], __fmul_rn(__fsub_rn(w[u], rv[u]), f));
-                            changed |= __float_as_uint(o[u]) != __float_as_uint(w[u]);
-                            const uint32_t mag = __float_as_uint(o[u]) & 0x7FFFFFFFu;
-                            lo_bits = min(lo_bits, mag); hi_bits = max(hi_bits, mag);
+                            diff_bits |= __float_as_uint(o[u]) ^ __float_as_uint(w[u]);
+                            lo_i = min(lo_i, __float_as_int(o[u])); hi_i = max(hi_i, __float_as_int(o[u]));
                         }
 #pragma unroll
                         for (int u = 0; u < kUnroll; ++u) sts_f32(aw + u * sw, o[u]);
@@ -657,17 +665,19 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     for (uint32_t i = 0; i < tk_tail[k]; ++i) {
                         const float w = lds_f32(aw);
                         const float o = __fsub_rn(w, __fmul_rn(__fsub_rn(w, lds_f32(ab)), f));
-                        changed |= __float_as_uint(o) != __float_as_uint(w);
-                        const uint32_t mag = __float_as_uint(o) & 0x7FFFFFFFu;
-                        lo_bits = min(lo_bits, mag); hi_bits = max(hi_bits, mag);
+                        diff_bits |= __float_as_uint(o) ^ __float_as_uint(w);
+                        lo_i = min(lo_i, __float_as_int(o)); hi_i = max(hi_i, __float_as_int(o));
                         sts_f32(aw, o);
                         aw += sw; ab += sb;
                     }
                 }
                 {
-                    const bool warp_changed = __any_sync(0xffffffffu, changed);
-                    lo_bits = __reduce_min_sync(0xffffffffu, lo_bits);
-                    hi_bits = __reduce_max_sync(0xffffffffu, hi_bits);
+                    const bool warp_changed = __any_sync(0xffffffffu, diff_bits != 0u);
+                    lo_i = __reduce_min_sync(0xffffffffu, lo_i);
+                    hi_i = __reduce_max_sync(0xffffffffu, hi_i);
+                    // (idle warps keep the neutral range: minimum 0x7FFFFFFF, maximum below zero -> shown as 0)
+                    const uint32_t lo_bits = lo_i < 0 ? 0u : (uint32_t)lo_i;
+                    const uint32_t hi_bits = lo_i < 0 ? 0xFFFFFFFFu : (hi_i < 0 ? 0u : (uint32_t)hi_i);
                     if (lane == 0) { sh.chg_s[s][cwarp] = warp_changed; sh.rng_s[s][cwarp] = make_uint2(lo_bits, hi_bits); }
                 }
                 consumer_sync();                  // whole plane updated, flags of all warps written
@@ -830,12 +840,12 @@ bool step_plan(const Geometry& g, uint32_t n_local, uint32_t n_global, StepPlan*
 }
 
 // Greedy assignment in index order: a neuron goes to the block (with room left) whose neurons so far are
-// farthest from it, closeness measured by the update factors themselves -- F[i][m] is large exactly when
+// farthest from it, closeness measured by the update factors themselves -- the factor of (i, m) is large exactly when
 // i and m are rewritten together.  The neighbourhood of any best matching unit then spreads over the
 // blocks almost evenly (measured on a hexagonal map of 2791 neurons, sigma 3: at most 5-7 neurons of a
 // block among the ~700-1000 neurons an image rewrites, against 7-9 for a round-robin assignment).
-void step_assign_owners(const float* F, uint32_t N, uint32_t first, uint32_t stride, uint32_t count, const StepPlan& pl,
-                        uint32_t* owners)
+void step_assign_owners(const std::function<float(uint32_t, uint32_t)>& closeness, uint32_t first, uint32_t stride,
+                        uint32_t count, const StepPlan& pl, uint32_t* owners)
 {
     const uint32_t G = pl.grid, J = pl.owned_per_block;
     std::fill(owners, owners + (size_t)G * J, ~0u);
@@ -843,8 +853,8 @@ void step_assign_owners(const float* F, uint32_t N, uint32_t first, uint32_t str
     std::vector<double> score(G);
     for (uint32_t i = 0; i < count; ++i) {
         std::fill(score.begin(), score.end(), 0.0);
-        const float* row = F + (size_t)(first + (size_t)i * stride) * N + first;
-        for (uint32_t m = 0; m < i; ++m) score[color[m]] += std::fabs((double)row[(size_t)m * stride]);
+        const uint32_t gi = first + i * stride;
+        for (uint32_t m = 0; m < i; ++m) score[color[m]] += std::fabs((double)closeness(gi, first + m * stride));
         uint32_t best = G;
         for (uint32_t c = 0; c < G; ++c) {
             if (load[c] >= J) continue;

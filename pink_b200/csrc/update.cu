@@ -71,12 +71,13 @@ worklist_kernel(BmuArgs a)
         }
     }
     __syncthreads();
-    const float* frow = a.factors + (size_t)bmu_s * a.n;
+    const uint32_t bmu_row = bmu_s;
+    auto fac = [&](uint32_t j) { return factor_of(a.factors, bmu_row, j, (uint32_t)shard_global(a.first_neuron, a.neuron_stride, j), a.n); };
     const uint32_t start = blockIdx.x * kListThreads, i = start + threadIdx.x;
-    const float f = i < a.n ? frow[i] : 0.0f;
+    const float f = i < a.n ? fac(i) : 0.0f;
     const unsigned long long key = i < a.n ? a.keys[i] : 0ull;
     uint32_t pre = 0;                                   // non-zero factors before this block, counted per warp
-    for (uint32_t j = threadIdx.x; j < start; j += kListThreads) pre += __popc(__ballot_sync(0xffffffffu, frow[j] != 0.0f));
+    for (uint32_t j = threadIdx.x; j < start; j += kListThreads) pre += __popc(__ballot_sync(0xffffffffu, fac(j) != 0.0f));
     const uint32_t ballot = __ballot_sync(0xffffffffu, f != 0.0f);
     if (lane == 0) { warp_cnt[warp] = __popc(ballot); warp_pre[warp] = pre; }
     __syncthreads();
@@ -579,9 +580,10 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             arrival = atomicAdd(b.arrive, 1u);
         }
         const bool have_bmu = bmu_s != ~0u;
-        const float* frow = b.factors + (have_bmu ? (size_t)bmu_s * b.n : 0);
+        const uint32_t bmu_row = have_bmu ? bmu_s : 0u;
+        auto fac = [&](uint32_t j) { return factor_of(b.factors, bmu_row, j, (uint32_t)shard_global(b.first_neuron, b.neuron_stride, j), b.n); };
         if (ctid < m_fixed) {
-            float ff = have_bmu ? frow[items[ctid].n] : 0.0f;
+            float ff = have_bmu ? fac(items[ctid].n) : 0.0f;
             if (can_skip && ff != 0.0f) {
                 const uint2 r = a.wrange[items[ctid].n];
                 if (cannot_change(ff, r.x, r.y, rmax_bits)) ff = 0.0f;
@@ -594,7 +596,7 @@ update_pipe_kernel(Geometry g, UpdateArgs a, PipeParams pp, BmuArgs b)
             float f[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                f[e] = (have_bmu && i0 + e < b.n && i0 + e >= n_fixed) ? frow[i0 + e] : 0.0f;
+                f[e] = (have_bmu && i0 + e < b.n && i0 + e >= n_fixed) ? fac(i0 + e) : 0.0f;
             }
             if (can_skip) {
                 if (!one_chunk) load_ranges(i0);

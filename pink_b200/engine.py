@@ -37,6 +37,16 @@ def update_factors(layout, dim0, dim1, func=capi.FUNC_GAUSSIAN, p0=1.1, p1=0.2, 
     return F
 
 
+def distance_classes(layout, dim0, dim1, dim2=1):
+    """Distances of the distinct map-distance classes of a SOM grid (float32 array, class order)."""
+    n = int(capi.lib.pink_b200_distance_classes(layout, dim0, dim1, dim2, None, 0))
+    if n == 0:
+        raise capi.PinkError(capi.EINVAL, "unsupported SOM layout")
+    d = np.empty(n, np.float32)
+    capi.lib.pink_b200_distance_classes(layout, dim0, dim1, dim2, _vp(d), n)
+    return d
+
+
 class Engine:
     """Device state of one trainer/mapper (one neuron shard when world_size > 1)."""
 
@@ -117,6 +127,17 @@ class Engine:
         if F.size != self.cfg.n_neurons ** 2:
             raise ValueError("update factor table must be N x N")
         capi.check(capi.lib.pink_b200_set_update_factors(self._h, _vp(F)))
+
+    def set_update_function(self, layout, dim0, dim1, func=capi.FUNC_GAUSSIAN, p0=1.1, p1=0.2, max_update_distance=-1.0,
+                            dim2=1):
+        """Built-in neighbourhood function, one factor per distance class (no N x N table)."""
+        capi.check(capi.lib.pink_b200_set_update_function(self._h, layout, dim0, dim1, dim2, func, p0, p1,
+                                                          max_update_distance))
+
+    def set_update_lut(self, layout, dim0, dim1, lut, dim2=1):
+        """One factor per distance class (order of distance_classes()), e.g. of a Python callable."""
+        lut = np.ascontiguousarray(lut, dtype=np.float32)
+        capi.check(capi.lib.pink_b200_set_update_lut(self._h, layout, dim0, dim1, dim2, _vp(lut), lut.size))
 
     # -- training -----------------------------------------------------------
     def _n_images(self, size):

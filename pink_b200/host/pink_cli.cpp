@@ -401,14 +401,14 @@ int run(const Options& o)
     const uint32_t entries = (uint32_t)data.entries;
 
     if (o.path == Options::TRAIN) {
-        std::vector<float> factors((size_t)n_neurons * n_neurons);
-        if (o.som_depth > 1)
-            check(pink_b200_update_factors_3d(o.som_width, o.som_height, o.som_depth, o.func, o.sigma, o.damping,
-                                              o.max_update_distance, factors.data()));
-        else
-            check(pink_b200_update_factors(o.layout, o.som_width, o.som_height, o.func, o.sigma, o.damping,
-                                           o.max_update_distance, factors.data()));
-        check(pink_b200_group_set_update_factors(ctx.get(), factors.data()));
+        // one update factor per distinct map distance of the grid (the reference fills an N x N table, Trainer.h:69-76)
+        const uint32_t depth = o.som_depth > 1 ? o.som_depth : 1;
+        const uint32_t classes = pink_b200_distance_classes(o.layout, o.som_width, o.som_height, depth, nullptr, 0);
+        if (classes == 0) throw std::runtime_error("unsupported SOM layout");
+        std::vector<float> factors(classes);
+        check(pink_b200_update_lut(o.layout, o.som_width, o.som_height, depth, o.func, o.sigma, o.damping,
+                                   o.max_update_distance, factors.data(), classes));
+        check(pink_b200_group_set_update_lut(ctx.get(), o.layout, o.som_width, o.som_height, depth, factors.data(), classes));
         const uint64_t total = (uint64_t)entries * o.iterations;
         Progress progress(total, o.progress_prints);
         std::vector<uint64_t> stores;

@@ -203,26 +203,20 @@ public:
             EuclideanDistanceShape shape, DataType type)
      : m_session(som, number_of_rotations, use_flip, interpolation, use_gpu, euclidean_distance_dim, shape, type)
     {
-        // F[i][j] = f(distance(i, j)) if max_update_distance <= 0 or distance < max_update_distance, else 0
+        // factor(i, j) = f(distance(i, j)) if max_update_distance <= 0 or distance < max_update_distance, else 0
         // (TrainerCommon, src/SelfOrganizingMapLib/Trainer.h:69-76).  The callable is evaluated once per
-        // DISTINCT distance -- a SOM grid has few -- which gives the table N^2 calls would give.
-        const size_t N = som.n_neurons;
-        std::vector<float> distance(N * N);
-        check(pink_b200_som_distances(som.layout, som.dim0, som.dim1, distance.data()));
-        m_factors.resize(N * N);
-        std::map<float, float> lut;
+        // DISTINCT map distance -- a SOM grid has few -- and the library looks the factor up by distance class:
+        // the same factors as N^2 calls give, without an N x N table.
+        const uint32_t classes = pink_b200_distance_classes(som.layout, som.dim0, som.dim1, 1, nullptr, 0);
+        std::vector<float> distance(classes);
+        pink_b200_distance_classes(som.layout, som.dim0, som.dim1, 1, distance.data(), classes);
+        m_factors.resize(classes);
         const bool native = py::isinstance<GaussianFunctor>(distribution_function);
         const GaussianFunctor* g = native ? distribution_function.cast<const GaussianFunctor*>() : nullptr;
-        for (size_t i = 0; i < distance.size(); ++i) {
-            const float d = distance[i];
-            auto it = lut.find(d);
-            if (it == lut.end()) {
-                float f = 0.0f;
-                if (max_update_distance <= 0 || d < max_update_distance)
-                    f = native ? (*g)(d) : distribution_function(d).cast<float>();
-                it = lut.emplace(d, f).first;
-            }
-            m_factors[i] = it->second;
+        for (uint32_t c = 0; c < classes; ++c) {
+            const float d = distance[c];
+            m_factors[c] = (max_update_distance <= 0 || d < max_update_distance)
+                         ? (native ? (*g)(d) : distribution_function(d).cast<float>()) : 0.0f;
         }
     }
 
@@ -260,7 +254,11 @@ public:
 private:
     void prepare(const std::vector<uint32_t>& image_shape)
     {
-        if (m_session.open(image_shape)) check(pink_b200_set_update_factors(m_session.ctx(), m_factors.data()));
+        if (m_session.open(image_shape)) {
+            const SOM& som = m_session.som();
+            check(pink_b200_set_update_lut(m_session.ctx(), som.layout, som.dim0, som.dim1, 1, m_factors.data(),
+                                           (uint32_t)m_factors.size()));
+        }
     }
     Session m_session;
     std::vector<float> m_factors;

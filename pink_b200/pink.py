@@ -199,28 +199,30 @@ class Trainer(_Common):
                  euclidean_distance_type=DataType.UINT8):
         super().__init__(som, number_of_rotations, use_flip, interpolation, use_gpu, euclidean_distance_dim,
                          euclidean_distance_shape, euclidean_distance_type)
-        self._factors = self._update_factors(distribution_function, float(max_update_distance))
+        self._lut = self._update_lut(distribution_function, float(max_update_distance))
 
-    def _update_factors(self, func, max_update_distance):
-        """F[i, j] = func(distance(i, j)) if max_update_distance <= 0 or distance < max_update_distance, else 0
-        (TrainerCommon, src/SelfOrganizingMapLib/Trainer.h:69-76).  The built-in Gaussian is evaluated by the
-        library in float32 exactly as the reference does; any other callable is called once per distinct
-        distance (a SOM grid has few), which gives the same table as calling it N^2 times."""
+    def _update_lut(self, func, max_update_distance):
+        """factor(i, j) = func(distance(i, j)) if max_update_distance <= 0 or distance < max_update_distance, else 0
+        (TrainerCommon, src/SelfOrganizingMapLib/Trainer.h:69-76) -- held as one value per DISTINCT map distance (a
+        SOM grid has few), which gives the factors N^2 evaluations would give without an N x N table.  The built-in
+        Gaussian is evaluated by the library in float32 exactly as the reference does; any other callable is
+        called once per distinct distance."""
         s = self._som
         if type(func) is GaussianFunctor:
-            return engine.update_factors(s._layout, s._dim0, s._dim1, capi.FUNC_GAUSSIAN, func.sigma, func.damping,
-                                         max_update_distance)
-        N = s.number_of_neurons
-        dist = np.empty((N, N), np.float32)
-        capi.check(capi.lib.pink_b200_som_distances(s._layout, s._dim0, s._dim1, dist.ctypes.data))
-        values, inverse = np.unique(dist, return_inverse=True)
-        table = np.array([func(float(v)) for v in values], np.float32)
+            n = capi.lib.pink_b200_distance_classes(s._layout, s._dim0, s._dim1, 1, None, 0)
+            lut = np.empty(n, np.float32)
+            capi.check(capi.lib.pink_b200_update_lut(s._layout, s._dim0, s._dim1, 1, capi.FUNC_GAUSSIAN, func.sigma,
+                                                     func.damping, max_update_distance, lut.ctypes.data, n))
+            return lut
+        dist = engine.distance_classes(s._layout, s._dim0, s._dim1)
+        lut = np.array([func(float(v)) for v in dist], np.float32)
         if max_update_distance > 0:
-            table[values >= np.float32(max_update_distance)] = 0.0
-        return table[inverse].reshape(N, N)
+            lut[dist >= np.float32(max_update_distance)] = 0.0
+        return lut
 
     def _configure(self):
-        self._eng.set_update_factors(self._factors)
+        s = self._som
+        self._eng.set_update_lut(s._layout, s._dim0, s._dim1, self._lut)
 
     def __call__(self, data):
         self._engine(data).train(np.asarray(data))

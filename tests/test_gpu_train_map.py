@@ -228,3 +228,29 @@ def test_config_errors_match_reference_messages():
     cfg = make_config(capi, 4, 1, 8, 4, 5, 4, False, 2)
     assert capi.lib.pink_b200_create(C.byref(cfg), C.byref(h)) == capi.EINVAL
     assert b"Euclidean distance dimension larger than neuron dimension" in capi.lib.pink_b200_last_error()
+
+
+@pytest.mark.parametrize("case", [TRAIN_CASES[2], TRAIN_CASES[4], TRAIN_CASES[3]])
+@pytest.mark.parametrize("step_kernel", [0, 1, 2])
+def test_factors_per_distance_class_equal_the_table(cuda, case, step_kernel):
+    """pink_b200_set_update_function (one factor per distinct map distance, looked up on the device from the neurons'
+    grid positions) trains the same map, bit for bit, as the N x N factor table -- in every launch sequence."""
+    import pink_b200.capi as capi
+    layout, s0, s1, C_, idim, nd, ed, R, flip, n = case
+    N = _som_size(layout, s0, s1)
+    rng = np.random.default_rng(5)
+    som0 = rng.random((N, C_, nd, nd), dtype=np.float32)
+    imgs = blob_images(9, idim, C_, seed=8).reshape(9, C_, idim, idim)
+    F = O.update_factors(layout, s0, s1, O.FUNC_GAUSSIAN, 1.1, 0.2, 2.5)          # with a max_update_distance cut-off
+    out = []
+    for classes in (False, True):
+        with Context(capi, make_config(capi, N, C_, idim, nd, ed, R, flip, 2), {"step_kernel": step_kernel}) as ctx:
+            ctx.set_som(som0)
+            if classes:
+                ctx.e.set_update_function(layout, s0, s1, capi.FUNC_GAUSSIAN, 1.1, 0.2, 2.5)
+            else:
+                ctx.set_factors(F)
+            log = ctx.train(imgs)
+            out.append((list(log), ctx.get_som(som0).copy()))
+    assert out[0][0] == out[1][0]
+    assert np.array_equal(out[0][1].view(np.uint32), out[1][1].view(np.uint32))

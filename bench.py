@@ -233,10 +233,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the map / other-configuration / reference-GPU blocks")
     ap.add_argument("--option", action="append", default=[], help="context switch name=value (see pink_b200_set_option)")
+    ap.add_argument("--only", default=None, help="profiling aid: run one small pass of map-C4, map-C2, train-C1 or train-C3 "
+                                                 "(few images, no timing contract) and print its figures")
+    ap.add_argument("--images", type=int, default=64, help="images of an --only pass")
     args = ap.parse_args()
     w = WORKLOAD
     if args.impl == "reference":
         return run_reference(args, w)
+    if args.only:
+        return run_only(args)
     if args.warmup < 3:
         args.warmup = 3
     options = {k: int(v) for k, v in (o.split("=") for o in args.option)}
@@ -363,7 +368,13 @@ def main():
     upd_bytes = 8.0 * n_upd * P
     moved_bytes = 4.0 * P * n_read + (4.0 * P + K) * n_written
     int8_peak = 2.0 * peaks["bf16_tflops"]
-    mma_peak = tracked_figure("mma_i8_peak.txt", "mma_only_tops")
+    mma_peak = None                                  # tcgen05.mma kind::i8 alone on resident operands, measured now
+    if world == 1:
+        import ctypes
+        tops = ctypes.c_double(0.0)
+        pair_opt = dict(o.split("=") for o in args.option).get("mma_pairs", "1") != "0"
+        capi.check(capi.lib.pink_b200_mma_i8_peak(local, 240, 1 if pair_opt else 0, ctypes.byref(tops)))
+        mma_peak = tops.value
     fused = detail["launch_us"] > 0                  # the persistent kernel ran: phases come from device-timer stamps
     timing = ("device-timer stamps of block 0 inside the persistent kernel, each phase up to and including its grid "
               "barrier, %d steps" % covered) if fused else \
@@ -381,7 +392,9 @@ def main():
                      "algorithmic_ops": dist_ops,
                      "peak_note": "int8 peak taken as 2 x the %s bf16 cuBLAS figure" % peaks["source"],
                      "frac_of_mma_only_peak": (dist_ops / t_dist / 1e12 / mma_peak) if mma_peak else None,
-                     "mma_only_peak_tops": mma_peak},
+                     "mma_only_peak_tops": mma_peak,
+                     "mma_only_peak_note": "pink_b200_mma_i8_peak: the same instruction shape back to back on operands "
+                                           "resident in shared memory, one CTA pair per SM, no loads and no epilogue"},
         "bmu+exchange+list": {"us_per_image": t_bmu * 1e6},
         "rotate": {"us_per_image": t_rot * 1e6},
     }
@@ -415,6 +428,7 @@ def main():
         extras["map"] = bench_map(torch, dist, barrier, rank, world, local, som, pool)
         if world == 1:
             extras["other_configs"] = bench_other_configs(torch, local)
+            extras["distance_sweep"] = bench_distance_sweep(torch)
             extras["reference_gpu"] = bench_reference_gpu(w, som, pool)
 
     cpu = None
@@ -451,6 +465,42 @@ def main():
         eng.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_only(args):
+    """One small pass of one configuration's path (for profilers: few launches, little memory)."""
+    import torch
+    from pink_b200 import capi
+    torch.cuda.set_device(0)
+    kind, key = args.only.split("-")
+    w = WORKLOADS[key]
+    N, som, pool = make_inputs(w, args.images)
+    eng = make_engine(w, N, 0, options={k: int(v) for k, v in (o.split("=") for o in args.option)})
+    eng.set_som(som)
+    d_img = torch.from_numpy(pool).cuda()
+    out = {"only": args.only, "workload": w["name"], "images": args.images}
+    if kind == "map":
+        d_dist = torch.empty((args.images, N), dtype=torch.float32, device="cuda")
+        d_rot = torch.empty((args.images, N), dtype=torch.int32, device="cuda")
+        for rep in range(2):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            eng.map_device(d_img.data_ptr(), args.images, d_dist.data_ptr(), d_rot.data_ptr())
+            eng.synchronize()
+            out["images_per_s"] = args.images / (time.perf_counter() - t0)
+        if w["mode"] == 0:
+            out["filter"] = eng.map_filter_stats()
+    else:
+        eng.set_update_function(w["som_layout"], w["som_dim"], w["som_dim"], capi.FUNC_GAUSSIAN, w["sigma"], w["damping"])
+        for rep in range(2):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            eng.train_device(d_img.data_ptr(), args.images)
+            eng.synchronize()
+            out["images_per_s"] = args.images / (time.perf_counter() - t0)
+        out["update_stats"] = eng.update_stats()
+    eng.close()
+    print(json.dumps(out))
 
 
 def bench_map(torch, dist, barrier, rank, world, local, som4, pool4):
@@ -496,8 +546,66 @@ def bench_map(torch, dist, barrier, rank, world, local, som4, pool4):
         res.update({"unit": "images/s", "workload": w["name"], "images": len(pool), "sharding": "images round robin x%d" % world,
                     "distance_ops_per_image": 2.0 * N * T * K,
                     "timing": "host clock around %d whole passes, synchronised on both sides, max over ranks" % reps})
+        if w["mode"] == 0:
+            st = eng.map_filter_stats()              # float32: tensor-core estimate + exact pass
+            res["filter"] = {"exact_sums_per_neuron_and_image": st["pairs_exact"] * w["rotations"] * (2 if w["flip"] else 1)
+                             / max(st["pairs_estimated"], 1.0), "worst_estimate_error": st["worst_estimate_error"],
+                             "error_bound": st["error_bound"]}
         out[key] = res
         eng.close()
+    return out
+
+
+def bench_distance_sweep(torch):
+    """Distance kernel alone over the grid of shapes BASELINE.json names (neurons x region size x rotations, all three
+    distance types): 2 * N * T * K multiply-adds per image and second, operands resident, 8 images per launch."""
+    import ctypes
+    from pink_b200 import capi
+    out = {"unit": "Tera multiply-add operations/s (2 * N * T * K per image)", "images_per_launch": 8,
+           "timing": "CUDA events around 3 launches after one warm-up launch", "shapes": []}
+    n_img = 8
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    for mode, name in ((2, "uint8"), (1, "uint16"), (0, "float32")):
+        rates = []
+        for N in (400, 1600, 2791):
+            for K in (44 * 44, 64 * 64, 90 * 90):
+                for R in (90, 360, 720):
+                    T = 2 * R
+                    Kp = capi.lib.pink_b200_operand_stride(K, mode)
+
+                    def planes(rows):
+                        if mode == 0:
+                            x = torch.rand((rows, Kp), device="cuda", generator=gen)
+                            x[:, K:] = 0
+                            return x, None, None
+                        hi = torch.randint(0, 256, (rows, Kp), dtype=torch.uint8, device="cuda", generator=gen)
+                        hi[:, K:] = 0
+                        if mode == 2:
+                            return hi, None, (hi.to(torch.int64) ** 2).sum(1).to(torch.int32)
+                        lo = torch.randint(0, 256, (rows, Kp), dtype=torch.uint8, device="cuda", generator=gen)
+                        lo[:, K:] = 0
+                        v = hi.to(torch.int64) * 256 + lo.to(torch.int64)
+                        return hi, lo, (v * v).sum(1)
+                    a0, a1, an = planes(N)
+                    b0, b1, bn = planes(n_img * T)
+                    keys = torch.full((n_img, N), -1, dtype=torch.int64, device="cuda")
+                    call = lambda: capi.check(capi.lib.pink_b200_op_distance(mode, N, T, K, ptr(a0), ptr(a1), ptr(an), ptr(b0),
+                                                                             ptr(b1), ptr(bn), n_img, ptr(keys), None, None))
+                    call()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(3):
+                        call()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    capi.check(capi.lib.pink_b200_op_status())
+                    rate = 3 * n_img * 2.0 * N * T * K / (e0.elapsed_time(e1) * 1e-3) / 1e12
+                    rates.append(rate)
+                    out["shapes"].append([name, N, K, R, round(rate, 1)])
+        rates.sort()
+        out[name] = {"min": rates[0], "median": rates[len(rates) // 2], "max": rates[-1]}
     return out
 
 
@@ -519,6 +627,15 @@ def bench_reference_gpu(w, som, pool, n_images=24):
         except Exception as ex:
             out[task] = None
             out[task + "_error"] = str(ex)[:300]
+    if out.get("train") is None and out.get("map") is None:
+        return out                        # its uint8 run failed: the float run is not tried
+    for task in ("train", "map"):         # the same geometry with float distances (the reference's default type)
+        try:
+            r = O.ref_cuda_run(task, *(args[:-1] + (0,)), sigma=w["sigma"], damping=w["damping"], timeout=240)
+            out[task + "_float"] = n_images / float(r["seconds"])
+        except Exception as ex:
+            out[task + "_float"] = None
+            out[task + "_float_error"] = str(ex)[:300]
     return out
 
 

@@ -125,6 +125,12 @@ int pink_b200_shard_range(uint32_t n_neurons, uint32_t world_size, uint32_t rank
  *                          image; g >= 2 groups of g consecutive ranks share
  *   "rotation_overlap"     1 puts the rotation kernels on a second, low-priority stream (default 0)
  *   "mma_pairs"            0 keeps the distance kernel from pairing blocks (default 1)
+ *   "f32_filter"           0 maps float32 distances with the all-pairs exact kernel instead of the tensor-core
+ *                          estimate + exact pass (default 1)
+ *   "cooperative_launch"   0 launches the persistent kernel without the cooperative attribute (default 1).  Its
+ *                          blocks wait for one another, so this is only for a device with nothing else running,
+ *                          under a profiler that refuses cooperative launches; a block that is not resident
+ *                          ends the batch with PINK_B200_ETIMEOUT instead of a hang
  *   "exchange_timeout_ms"  wall-clock limit of every device-side wait for another rank (default 20000).  The
  *                          ranks must enqueue each batch of steps within this time of one another. */
 int pink_b200_set_option(pink_b200_ctx* ctx, const char* name, long long value);
@@ -267,6 +273,19 @@ int pink_b200_profile_detail(pink_b200_ctx* ctx, double out[8]);
  * arrived, (9) last MMA issued, (10) accumulators complete, (11) first neuron plane arrived.  *blocks and
  * *steps are always set; `out` may be NULL to ask for the sizes only. */
 int pink_b200_profile_stamps(pink_b200_ctx* ctx, uint64_t* out, uint64_t capacity, uint32_t* blocks, uint64_t* steps);
+
+/* float32 mapping runs as an estimate of all N x T distances on the tensor cores followed by exact sums for the
+ * transforms the estimate cannot rule out (option "f32_filter" = 0 computes all of them exactly instead; the
+ * results are the same up to the summation order of the exact sums).  out[0] = pairs estimated so far,
+ * out[1] = exact sums formed, out[2] = largest |estimate - exact| / (|a|^2 + |b|^2) seen among those,
+ * out[3] = the error bound the selection assumes for that ratio. */
+int pink_b200_map_filter_stats(pink_b200_ctx* ctx, double out[4]);
+
+/* Ceiling of the integer tensor pipe as the distance kernels drive it: tera-operations per second of
+ * tcgen05.mma kind::i8 (128 rows x n columns per CTA; pair != 0: CTA pairs, 256 x n per instruction) issued
+ * back to back on operands already in shared memory, one CTA (pair) per SM.  n: multiple of 16, 16..256.
+ * A measuring aid: the distance kernels' rates are quoted against it. */
+int pink_b200_mma_i8_peak(int device, uint32_t n, int pair, double* tops);
 
 /* ---- one process, several GPUs ------------------------------------------------
  * The reference's Trainer / Mapper use every visible GPU of the process on their own

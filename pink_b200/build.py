@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpink_b200.so")
-SOURCES = ["capi.cu", "operands.cu", "distance_tc.cu", "distance_f32.cu", "update.cu", "train_steps.cu", "rotshare.cu", "group.cu", "host_tables.cpp"]
+SOURCES = ["capi.cu", "operands.cu", "distance_tc.cu", "distance_f32.cu", "filter_f32.cu", "update.cu", "train_steps.cu", "rotshare.cu", "group.cu", "mma_peak.cu", "host_tables.cpp"]
 HEADERS = ["kernels.cuh", "ptx.cuh", "record.cuh", "quant.cuh", "tensormap.cuh", os.path.join("..", "..", "include", "pink_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]

@@ -60,6 +60,8 @@ SYMBOLS = {
     "pink_b200_profile_detail": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
     "pink_b200_profile_stamps": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32),
                                            C.POINTER(C.c_uint64)]),
+    "pink_b200_map_filter_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
+    "pink_b200_mma_i8_peak": (C.c_int, [C.c_int, C.c_uint32, C.c_int, C.POINTER(C.c_double)]),
     "pink_b200_device_count": (C.c_int, []),
     "pink_b200_group_create": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_uint32, C.POINTER(C.c_void_p)]),
     "pink_b200_group_destroy": (C.c_int, [C.c_void_p]),

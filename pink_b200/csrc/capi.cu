@@ -109,7 +109,7 @@ int make_geometry(const pink_b200_config& c, Geometry* g)
     g->K = (uint32_t)K;
     g->mode = (int)c.dist_type;
     g->circle = nullptr;             // a context with a circular region uploads the table and sets this
-    g->Kp = g->mode == kModeF32 ? round_up(g->K, 16) : round_up(g->K, 128);
+    g->Kp = g->mode == kModeF32 ? round_up(g->K, 32) : round_up(g->K, 128);   // float: one 128-byte slice of the filter's TF32 planes
     // s32 accumulators: K * 255^2 (uint8) and 2 * K * 255^2 (uint16 cross term) must stay below 2^31.
     if (g->mode == kModeU8 && g->K > 33025) return fail(PINK_B200_EINVAL, "uint8 distance supports at most 33025 elements");
     if (g->mode == kModeU16 && g->K > 16512) return fail(PINK_B200_EINVAL, "uint16 distance supports at most 16512 elements");
@@ -230,6 +230,14 @@ struct pink_b200_ctx
     int opt_exchange = 0;             // 0 peer memory where possible, 1 NCCL all-gather
     int opt_rotation_sharing = -1;    // -1 pairs of ranks, 0 every rank rotates everything, g >= 2 groups of g ranks
     int opt_mma_pairs = 1;
+    int opt_cooperative = 1;          // 0: persistent kernel launched without the cooperative attribute
+    int opt_f32_filter = 1;           // float32 mapping: tensor-core estimate + exact pass where the geometry allows it
+    // float32 mapping filter: TF32 word planes and float norms of the SOM operand (valid while the SOM is unchanged)
+    // and of one mapping batch of transforms, the estimate matrix and the pass's counters
+    float* d_af_hi = nullptr; float* d_af_lo = nullptr; float* d_af_norm = nullptr; bool af_valid = false;
+    float* d_bf_hi = nullptr; float* d_bf_lo = nullptr; float* d_bf_norm = nullptr; float* d_est = nullptr; size_t filter_imgs = 0;
+    unsigned long long* d_filter_stats = nullptr;     // {exact evaluations, bits of the largest estimate error seen}
+    unsigned long long filter_pairs = 0;              // (neuron, transform) pairs estimated so far
     long long opt_exchange_timeout_ms = 20000;
     bool failed = false;              // a device-side wait expired: the map may be inconsistent, training is refused
     uint32_t* d_counts = nullptr;
@@ -402,6 +410,7 @@ int train_steps_batch(pink_b200_ctx* c, size_t slot_img, uint32_t cnt, uint32_t*
     a.counts = c->d_counts; a.bmu_log = bmu_slots; a.stats = c->d_stats; a.status = c->d_status;
     a.ctrl = c->d_ctrl;
     a.stamps = nullptr;
+    a.plain_launch = c->opt_cooperative ? 0u : 1u;
     if (c->cfg.world_size > 1) {
         a.xchg_local = c->d_xchg;
         for (uint32_t r = 0; r < c->cfg.world_size; ++r) a.xchg_peer[r] = c->xchg_peer[r];
@@ -742,6 +751,7 @@ int train_prepare(pink_b200_ctx* c, uint64_t n)
     if (c->failed)
         return fail(PINK_B200_ESTATE, "an earlier device-side wait expired; the context no longer trains (read the map back or destroy it)");
     if (!c->have_som) return fail(PINK_B200_ESTATE, "pink_b200_set_som must be called before training");
+    c->af_valid = false;                 // training rewrites the SOM operand: the mapping filter's planes are rebuilt on demand
     if (!c->have_factors) return fail(PINK_B200_ESTATE, "pink_b200_set_update_factors must be called before training");
     if (c->cfg.world_size > 1 && !c->comm)
         return fail(PINK_B200_ESTATE, "pink_b200_comm_init must be called before training with world_size > 1");
@@ -922,6 +932,8 @@ int pink_b200_destroy(pink_b200_ctx* c)
     free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
     free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_coords); free_dev(c->d_lut); free_dev(c->d_base);
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
+    free_dev(c->d_af_hi); free_dev(c->d_af_lo); free_dev(c->d_af_norm); free_dev(c->d_bf_hi); free_dev(c->d_bf_lo);
+    free_dev(c->d_bf_norm); free_dev(c->d_est); free_dev(c->d_filter_stats);
     free_dev(c->d_items); free_dev(c->d_nitems); free_dev(c->d_stats); free_dev(c->d_wrange); free_dev(c->d_rmax);
     free_dev(c->d_circle); free_dev(c->d_owners); free_dev(c->d_ctrl); free_dev(c->d_stamps);
     for (cudaEvent_t e : c->prof_launch_events) cudaEventDestroy(e);
@@ -989,6 +1001,10 @@ int pink_b200_set_option(pink_b200_ctx* c, const char* name, long long value)
         }
     } else if (key == "mma_pairs") {
         c->opt_mma_pairs = value != 0;
+    } else if (key == "f32_filter") {
+        c->opt_f32_filter = value != 0;
+    } else if (key == "cooperative_launch") {
+        c->opt_cooperative = value != 0;
     } else if (key == "exchange_timeout_ms") {
         if (value < 1) return fail(PINK_B200_EINVAL, "exchange_timeout_ms must be positive");
         c->opt_exchange_timeout_ms = value;
@@ -1039,6 +1055,7 @@ int pink_b200_set_som(pink_b200_ctx* c, const float* host_som)
     c->launches += 1;
     CU_TRY(cudaStreamSynchronize(c->stream));
     c->have_som = true;
+    c->af_valid = false;
     return PINK_B200_OK;
 }
 
@@ -1205,19 +1222,104 @@ int pink_b200_get_bmu_log(pink_b200_ctx* c, uint32_t* host_bmus, uint64_t n)
     return PINK_B200_OK;
 }
 
+// Bound of the estimate's error relative to |a|^2 + |b|^2 (derived in filter_f32.cu): 3 * K / 16 * 2^-23 + 2^-17
+static float filter_eps(uint32_t K) { return (float)(3.0 * K / 16.0 * 1.1920928955078125e-7 + 7.62939453125e-6); }
+
+// float32 mapping through the tensor-core filter: possible when the exact pass's candidate lists fit shared memory
+static bool map_uses_filter(const pink_b200_ctx* c)
+{
+    return c->g.mode == kModeF32 && c->opt_f32_filter && c->g.Kp % 32 == 0 && c->g.T <= 12800;
+}
+
+static int ensure_filter_buffers(pink_b200_ctx* c, size_t imgs)
+{
+    const Geometry& g = c->g;
+    if (!c->d_af_hi) {
+        const size_t elems = (size_t)c->count * g.Kp;
+        CU_TRY(cudaMalloc(&c->d_af_hi, elems * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_af_lo, elems * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_af_norm, (size_t)c->count * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_filter_stats, 2 * sizeof(unsigned long long)));
+        CU_TRY(cudaMemsetAsync(c->d_filter_stats, 0, 2 * sizeof(unsigned long long), c->stream));
+        c->af_valid = false;
+    }
+    if (c->filter_imgs < imgs) {
+        free_dev(c->d_bf_hi); free_dev(c->d_bf_lo); free_dev(c->d_bf_norm); free_dev(c->d_est);
+        const size_t rows = imgs * g.T;
+        CU_TRY(cudaMalloc(&c->d_bf_hi, rows * g.Kp * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_bf_lo, rows * g.Kp * sizeof(float)));
+        // the rotation kernel writes K values per row; the padding up to Kp stays zero
+        CU_TRY(cudaMemsetAsync(c->d_bf_hi, 0, rows * g.Kp * sizeof(float), c->stream));
+        CU_TRY(cudaMemsetAsync(c->d_bf_lo, 0, rows * g.Kp * sizeof(float), c->stream));
+        CU_TRY(cudaMalloc(&c->d_bf_norm, rows * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_est, rows * c->count * sizeof(float)));
+        c->filter_imgs = imgs;
+    }
+    return PINK_B200_OK;
+}
+
 static int map_chunk(pink_b200_ctx* c, const float* d_images, uint32_t m, float* d_dist, uint32_t* d_rot)
 {
     const Geometry& g = c->g;
-    LAUNCH_TRY(launch_rotate(g, d_images, m, c->d_cs, c->d_sn, base_fits_smem(g) ? nullptr : c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream));
+    const bool filter = map_uses_filter(c);
+    if (filter) {
+        int rc = ensure_filter_buffers(c, c->map_batch);
+        if (rc) return rc;
+        // the rotation kernel also writes the estimate's TF32 planes and norms of the transforms
+        LAUNCH_TRY(launch_rotate(g, d_images, m, c->d_cs, c->d_sn, base_fits_smem(g) ? nullptr : c->d_base, c->d_b0, c->d_bf_hi,
+                                 c->d_bf_norm, c->stream, nullptr, c->d_bf_lo));
+    } else {
+        LAUNCH_TRY(launch_rotate(g, d_images, m, c->d_cs, c->d_sn, base_fits_smem(g) ? nullptr : c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream));
+    }
     DistanceArgs da{};
     da.a0 = c->d_a0; da.a1 = c->d_a1; da.anorm = c->d_anorm; da.n = c->count;
     da.b0 = c->d_b0; da.b1 = c->d_b1; da.bnorm = c->d_bnorm; da.n_img = m;
     da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status; da.single_cta = !c->opt_mma_pairs;
     const char* why = "";
+    if (filter) {
+        // estimate of every pair on the tensor cores, then exact sums for the transforms it cannot rule out
+        const float* A = static_cast<const float*>(c->d_a0);
+        const float* B = static_cast<const float*>(c->d_b0);
+        if (!c->af_valid) {
+            LAUNCH_TRY(launch_split_tf32(A, c->count, g.Kp, c->d_af_hi, c->d_af_lo, c->d_af_norm, c->stream));
+            c->af_valid = true;
+            c->launches += 1;
+        }
+        da.a0 = c->d_af_hi; da.a1 = c->d_af_lo; da.anorm = c->d_af_norm;
+        da.b0 = c->d_bf_hi; da.b1 = c->d_bf_lo; da.bnorm = c->d_bf_norm;
+        da.s_out = c->d_est;
+        cudaError_t e = launch_distance_tf32(g, da, c->stream, &why);
+        if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
+        const float eps = filter_eps(g.K);
+        LAUNCH_TRY(launch_refine_f32(g, A, c->d_af_norm, c->count, B, c->d_bf_norm, m, c->d_est, eps, c->d_keys,
+                                     c->d_filter_stats, c->stream));
+        c->filter_pairs += (unsigned long long)m * c->count * g.T;
+        LAUNCH_TRY(launch_map_finalize(g, c->d_keys, m, c->count, d_dist, d_rot, c->stream));
+        c->launches += 4;                 // rotation set, estimate, exact pass, epilogue
+        return PINK_B200_OK;
+    }
     cudaError_t e = launch_distance(g, da, c->stream, &why);
     if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
     LAUNCH_TRY(launch_map_finalize(g, c->d_keys, m, c->count, d_dist, d_rot, c->stream));
     c->launches += 3;                 // rotation set, distance, epilogue
+    return PINK_B200_OK;
+}
+
+int pink_b200_map_filter_stats(pink_b200_ctx* c, double out[4])
+{
+    if (!c || !out) return fail(PINK_B200_EINVAL, "null argument");
+    out[0] = (double)c->filter_pairs; out[1] = 0.0; out[2] = 0.0;
+    out[3] = (double)filter_eps(c->g.K);
+    if (!c->d_filter_stats) return PINK_B200_OK;
+    CU_TRY(cudaSetDevice(c->cfg.device));
+    unsigned long long h[2] = { 0, 0 };
+    CU_TRY(cudaMemcpyAsync(h, c->d_filter_stats, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    const uint32_t bits = (uint32_t)h[1];
+    float worst;
+    std::memcpy(&worst, &bits, sizeof(worst));
+    out[1] = (double)h[0];
+    out[2] = (double)worst;
     return PINK_B200_OK;
 }
 

@@ -19,16 +19,24 @@ namespace pinkb {
 
 namespace {
 
-constexpr int kBK = 16;
 
-template <int BM, int BN, int TM, int TN>
-__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+// A thread's TM neurons are TM/4 groups of four consecutive rows, the groups BM/(TM/4) rows apart (likewise its
+// transforms): the float4 reads of a quarter warp then cover 32 consecutive shared-memory words (transforms) or
+// one word group (neurons, broadcast) -- no bank conflicts.
+template <int BM, int BN, int TM, int TN, int kBK>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN), 512 / ((BM / TM) * (BN / TN)))
 distance_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, uint32_t n, uint32_t T, uint32_t Kp,
                     unsigned long long* __restrict__ keys, float* __restrict__ s_out)
 {
     constexpr int TX = BN / TN, TY = BM / TM, NT = TX * TY;
-    __shared__ __align__(16) float As[2][kBK][BM + 4];
-    __shared__ __align__(16) float Bs[2][kBK][BN + 4];
+    constexpr int GM = TM / 4, GN = TN / 4;                 // groups of four per thread
+    constexpr int SM_ = BM / GM, SN_ = BN / GN;             // distance between a thread's groups
+    constexpr int A_ELEMS = BM * kBK / 4, B_ELEMS = BN * kBK / 4;           // float4 per slice
+    constexpr int A_PER = (A_ELEMS + NT - 1) / NT, B_PER = (B_ELEMS + NT - 1) / NT;
+    constexpr bool A_EVEN = A_ELEMS % NT == 0, B_EVEN = B_ELEMS % NT == 0;
+    static_assert(TX == 16 && NT % 32 == 0 && TM % 4 == 0 && TN % 4 == 0 && kBK % 4 == 0, "thread layout");
+    __shared__ __align__(16) float As[2][kBK][BM];
+    __shared__ __align__(16) float Bs[2][kBK][BN];
 
     const uint32_t img = blockIdx.z;
     const uint32_t m0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
@@ -41,43 +49,63 @@ distance_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, ui
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
 
-    // Each row contributes kBK floats = 4 float4 per slice.
-    constexpr int A_VEC = BM * kBK / 4, B_VEC = BN * kBK / 4;
-    auto load_slice = [&](int buf, uint32_t k0) {
-        for (int v = threadIdx.x; v < A_VEC; v += NT) {
-            int r = v / (kBK / 4), c4 = v % (kBK / 4);
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (m0 + r < n) x = __ldg(reinterpret_cast<const float4*>(A + (size_t)(m0 + r) * Kp + k0) + c4);
-            As[buf][c4 * 4 + 0][r] = x.x; As[buf][c4 * 4 + 1][r] = x.y;
-            As[buf][c4 * 4 + 2][r] = x.z; As[buf][c4 * 4 + 3][r] = x.w;
+    // Slice loads: consecutive threads take consecutive rows (one float4 = four k of one row each), so that the
+    // transposing stores of a warp fall into 32 consecutive words.  Rows beyond the operand read row 0 (their
+    // results are never stored).
+    // Element e of a slice = float4 (four k) of row e % rows, k group e / rows; thread t takes e = t, t + NT, ...
+    float4 ra[A_PER], rb[B_PER];
+    auto fetch = [&](uint32_t kb) {                       // global -> registers (in flight during the math)
+#pragma unroll
+        for (int v = 0; v < A_PER; ++v) {
+            const int e = threadIdx.x + v * NT, row = e % BM, kq = e / BM;
+            if (A_EVEN || e < A_ELEMS)
+                ra[v] = __ldg(reinterpret_cast<const float4*>(A + (size_t)(m0 + row < n ? m0 + row : 0u) * Kp + kb * kBK) + kq);
         }
-        for (int v = threadIdx.x; v < B_VEC; v += NT) {
-            int r = v / (kBK / 4), c4 = v % (kBK / 4);
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t0 + r < T) x = __ldg(reinterpret_cast<const float4*>(Bi + (size_t)(t0 + r) * Kp + k0) + c4);
-            Bs[buf][c4 * 4 + 0][r] = x.x; Bs[buf][c4 * 4 + 1][r] = x.y;
-            Bs[buf][c4 * 4 + 2][r] = x.z; Bs[buf][c4 * 4 + 3][r] = x.w;
+#pragma unroll
+        for (int v = 0; v < B_PER; ++v) {
+            const int e = threadIdx.x + v * NT, row = e % BN, kq = e / BN;
+            if (B_EVEN || e < B_ELEMS)
+                rb[v] = __ldg(reinterpret_cast<const float4*>(Bi + (size_t)(t0 + row < T ? t0 + row : 0u) * Kp + kb * kBK) + kq);
+        }
+    };
+    auto stash = [&](int buf) {                           // registers -> shared memory, k-major
+#pragma unroll
+        for (int v = 0; v < A_PER; ++v) {
+            const int e = threadIdx.x + v * NT, row = e % BM, kq = e / BM;
+            if (A_EVEN || e < A_ELEMS) {
+                float* d = &As[buf][kq * 4][row];
+                d[0] = ra[v].x; d[BM] = ra[v].y; d[2 * BM] = ra[v].z; d[3 * BM] = ra[v].w;
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < B_PER; ++v) {
+            const int e = threadIdx.x + v * NT, row = e % BN, kq = e / BN;
+            if (B_EVEN || e < B_ELEMS) {
+                float* d = &Bs[buf][kq * 4][row];
+                d[0] = rb[v].x; d[BN] = rb[v].y; d[2 * BN] = rb[v].z; d[3 * BN] = rb[v].w;
+            }
         }
     };
 
     const uint32_t nk = Kp / kBK;
-    load_slice(0, 0);
+    fetch(0);
+    stash(0);
     __syncthreads();
     for (uint32_t kb = 0; kb < nk; ++kb) {
         const int cur = kb & 1;
-        if (kb + 1 < nk) load_slice(cur ^ 1, (kb + 1) * kBK);
+        if (kb + 1 < nk) fetch(kb + 1);
 #pragma unroll
         for (int k = 0; k < kBK; ++k) {
             float a[TM], b[TN];
 #pragma unroll
-            for (int i = 0; i < TM; i += 4) {
-                float4 x = *reinterpret_cast<const float4*>(&As[cur][k][ty * TM + i]);
-                a[i] = x.x; a[i + 1] = x.y; a[i + 2] = x.z; a[i + 3] = x.w;
+            for (int gi = 0; gi < GM; ++gi) {
+                float4 x = *reinterpret_cast<const float4*>(&As[cur][k][gi * SM_ + ty * 4]);
+                a[gi * 4] = x.x; a[gi * 4 + 1] = x.y; a[gi * 4 + 2] = x.z; a[gi * 4 + 3] = x.w;
             }
 #pragma unroll
-            for (int j = 0; j < TN; j += 4) {
-                float4 x = *reinterpret_cast<const float4*>(&Bs[cur][k][tx * TN + j]);
-                b[j] = x.x; b[j + 1] = x.y; b[j + 2] = x.z; b[j + 3] = x.w;
+            for (int gj = 0; gj < GN; ++gj) {
+                float4 x = *reinterpret_cast<const float4*>(&Bs[cur][k][gj * SN_ + tx * 4]);
+                b[gj * 4] = x.x; b[gj * 4 + 1] = x.y; b[gj * 4 + 2] = x.z; b[gj * 4 + 3] = x.w;
             }
 #pragma unroll
             for (int i = 0; i < TM; ++i)
@@ -87,17 +115,19 @@ distance_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, ui
                     acc[i][j] = fmaf(d, d, acc[i][j]);
                 }
         }
+        if (kb + 1 < nk) stash(cur ^ 1);                  // the other buffer: last read before the previous barrier
         __syncthreads();
     }
 
-    // First minimum over this thread's transforms, then across the TX threads of the row.
+    // First minimum over this thread's transforms (ascending), then across the TX threads of the row: keys are
+    // compared whole, so the lowest transform wins among equal distances whatever the order of the merge.
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
-        const uint32_t nn = m0 + ty * TM + i;
+        const uint32_t nn = m0 + (i / 4) * SM_ + ty * 4 + (i % 4);
         unsigned long long best = kKeyEmpty;
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
-            const uint32_t t = t0 + tx * TN + j;
+            const uint32_t t = t0 + (j / 4) * SN_ + tx * 4 + (j % 4);
             if (t < T) {
                 unsigned long long key = ((unsigned long long)__float_as_uint(acc[i][j]) << 32) | t;
                 best = key < best ? key : best;
@@ -115,6 +145,13 @@ distance_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, ui
 
 } // namespace
 
+template <int BM>
+static void launch_rows(const float* A, const float* B, float* s_out, const Geometry& g, const DistanceArgs& a, cudaStream_t st)
+{
+    dim3 grid((a.n + BM - 1) / BM, (g.T + 127) / 128, a.n_img);
+    distance_f32_kernel<BM, 128, 8, 8, 8><<<grid, (BM / 8) * 16, 0, st>>>(A, B, a.n, g.T, g.Kp, a.keys, s_out);
+}
+
 cudaError_t launch_distance_f32(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why)
 {
     const float* A = static_cast<const float*>(a.a0);
@@ -122,11 +159,22 @@ cudaError_t launch_distance_f32(const Geometry& g, const DistanceArgs& a, cudaSt
     float* s_out = static_cast<float*>(a.s_out);
     const uint64_t big = (uint64_t)((a.n + 127) / 128) * ((g.T + 127) / 128) * a.n_img;
     if (big >= 148) {
-        dim3 grid((a.n + 127) / 128, (g.T + 127) / 128, a.n_img);
-        distance_f32_kernel<128, 128, 8, 8><<<grid, 256, 0, st>>>(A, B, a.n, g.T, g.Kp, a.keys, s_out);
+        // neuron tile height: the one of 128, 112, 96, 80, 64 rows that pads the shard least (ties: the tallest)
+        uint32_t best = 128, waste = UINT32_MAX;
+        for (uint32_t bm = 128; bm >= 64; bm -= 16) {
+            const uint32_t w = (a.n + bm - 1) / bm * bm - a.n;
+            if (w < waste) { waste = w; best = bm; }
+        }
+        switch (best) {
+        case 128: launch_rows<128>(A, B, s_out, g, a, st); break;
+        case 112: launch_rows<112>(A, B, s_out, g, a, st); break;
+        case 96: launch_rows<96>(A, B, s_out, g, a, st); break;
+        case 80: launch_rows<80>(A, B, s_out, g, a, st); break;
+        default: launch_rows<64>(A, B, s_out, g, a, st); break;
+        }
     } else {
         dim3 grid((a.n + 63) / 64, (g.T + 63) / 64, a.n_img);
-        distance_f32_kernel<64, 64, 4, 4><<<grid, 256, 0, st>>>(A, B, a.n, g.T, g.Kp, a.keys, s_out);
+        distance_f32_kernel<64, 64, 4, 4, 16><<<grid, 256, 0, st>>>(A, B, a.n, g.T, g.Kp, a.keys, s_out);
     }
     *why = "distance_f32_kernel launch";
     return cudaGetLastError();

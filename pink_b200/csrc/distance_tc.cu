@@ -19,6 +19,13 @@
 //   hh = ah.bh,  ll = al.bl,  cross = ah.bl + al.bh,
 //   a.b = 65536*hh + 256*cross + ll        (combined in 64-bit integers).
 //
+// float32 mapping uses the same pipeline as a filter (kModeTf32): the operands are split into two TF32 words per
+// value (a = ah + al with ah = the top 19 bits of a), the dot product is assembled as ah.bh + ah.bl + al.bh in
+// float accumulators (kind::tf32; one for the even and one for the odd K steps), and the estimate
+// |a|^2 + |b|^2 - 2 a.b of every (neuron, transform) pair is
+// written out; an exact pass over the few transforms per neuron that the estimate cannot rule out follows
+// (filter_f32.cu).
+//
 // A CTA computes a 128-neuron x n_tile-transform tile.  The kernel is bound by the operand bytes an
 // SM pulls from L2, so two CTAs of a cluster work as a pair where possible (tcgen05 cta_group::2:
 // one M=256 MMA over both CTAs' neuron rows; each CTA stages only half of the transform rows; the
@@ -53,6 +60,8 @@ template <> struct TcCfg<kModeU8, false>  { static constexpr uint32_t planes = 1
 template <> struct TcCfg<kModeU16, false> { static constexpr uint32_t planes = 2, max_n = 128, cols = 512; };
 template <> struct TcCfg<kModeU8, true>   { static constexpr uint32_t planes = 1, max_n = 256, cols = 256; };
 template <> struct TcCfg<kModeU16, true>  { static constexpr uint32_t planes = 2, max_n = 128, cols = 512; };
+template <> struct TcCfg<kModeTf32, false> { static constexpr uint32_t planes = 2, max_n = 256, cols = 512; };
+template <> struct TcCfg<kModeTf32, true>  { static constexpr uint32_t planes = 2, max_n = 256, cols = 512; };
 
 // Shared memory of a CTA: barriers, the tensor-memory address and the per-column |b|^2 in the first
 // 4 KB, then the ring of stages.  A stage holds, per byte plane, the 128 neuron rows and this CTA's
@@ -126,7 +135,7 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
         mbar_fence_init();
         tma_prefetch_desc(&map_a0);
         tma_prefetch_desc(&map_b0);
-        if (MODE == kModeU16) { tma_prefetch_desc(&map_a1); tma_prefetch_desc(&map_b1); }
+        if (Cfg::planes == 2) { tma_prefetch_desc(&map_a1); tma_prefetch_desc(&map_b1); }
     }
     if (warp == 1) {
         if (PAIR) { tmem_alloc_pair(tmem_ptr_s, Cfg::cols); tmem_relinquish_pair(); }
@@ -155,7 +164,7 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     mbar_expect_tx_cluster(bar, stage_tx);
                     tma_load_2d_pair(st, &map_a0, bar, kx, (int32_t)m0);
                     tma_load_2d_pair(st + Cfg::planes * L::a_bytes, &map_b0, bar, kx, brow);
-                    if (MODE == kModeU16) {
+                    if (Cfg::planes == 2) {
                         tma_load_2d_pair(st + L::a_bytes, &map_a1, bar, kx, (int32_t)m0);
                         tma_load_2d_pair(st + Cfg::planes * L::a_bytes + p.b_bytes, &map_b1, bar, kx, brow);
                     }
@@ -163,7 +172,7 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     mbar_expect_tx(&full_bar[s], stage_tx);
                     tma_load_2d(st, &map_a0, &full_bar[s], kx, (int32_t)m0);
                     tma_load_2d(st + Cfg::planes * L::a_bytes, &map_b0, &full_bar[s], kx, brow);
-                    if (MODE == kModeU16) {
+                    if (Cfg::planes == 2) {
                         tma_load_2d(st + L::a_bytes, &map_a1, &full_bar[s], kx, (int32_t)m0);
                         tma_load_2d(st + Cfg::planes * L::a_bytes + p.b_bytes, &map_b1, &full_bar[s], kx, brow);
                     }
@@ -173,10 +182,13 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer --
         if (pair_rank == 0 && elect_one()) {
-            const uint32_t idesc = make_idesc_u8(PAIR ? 2 * kBlockM : kBlockM, p.n_tile);
+            const uint32_t idesc = MODE == kModeTf32 ? make_idesc_tf32(PAIR ? 2 * kBlockM : kBlockM, p.n_tile)
+                                                     : make_idesc_u8(PAIR ? 2 * kBlockM : kBlockM, p.n_tile);
             // PAIR: one instruction computes both CTAs' tiles; completion is signalled to both
             auto mma = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t acc) {
-                if (PAIR) umma_i8_pair(d, a, b, idesc, acc); else umma_i8(d, a, b, idesc, acc);
+                if (MODE == kModeTf32) { if (PAIR) umma_tf32_pair(d, a, b, idesc, acc); else umma_tf32(d, a, b, idesc, acc); }
+                else if (PAIR) umma_i8_pair(d, a, b, idesc, acc);
+                else umma_i8(d, a, b, idesc, acc);
             };
             auto commit = [&](uint64_t* bar) {
                 if (PAIR) {
@@ -200,6 +212,16 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     const uint32_t acc = (kb | k) != 0;
                     if (MODE == kModeU8) {
                         mma(tmem_base, a_hi + adv, b_hi + adv, acc);
+                    } else if (MODE == kModeTf32) {
+                        // the main and the cross terms share an accumulator (the cross terms are 2^-10 of the main
+                        // term); even and odd K steps go to two accumulators, which halves the number of
+                        // additions -- and with it the rounding -- each running sum sees
+                        const uint64_t a_lo = make_sw128_kmajor_desc(st + L::a_bytes);
+                        const uint64_t b_lo = make_sw128_kmajor_desc(st + Cfg::planes * L::a_bytes + p.b_bytes);
+                        const uint32_t d = tmem_base + (k & 1u) * Cfg::max_n;
+                        mma(d, a_hi + adv, b_hi + adv, (kb | (k >> 1)) != 0);
+                        mma(d, a_hi + adv, b_lo + adv, 1u);
+                        mma(d, a_lo + adv, b_hi + adv, 1u);
                     } else {
                         const uint64_t a_lo = make_sw128_kmajor_desc(st + L::a_bytes);
                         const uint64_t b_lo = make_sw128_kmajor_desc(st + Cfg::planes * L::a_bytes + p.b_bytes);
@@ -218,7 +240,8 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
         // A thread owns one neuron row (TMEM lane) and walks the tile's columns in chunks of 16: the
         // next chunk's tcgen05.ld is in flight while the current one is reduced, and four independent
         // (minimum, column) chains keep the compare/select latency off the critical path.
-        using val_t = typename std::conditional<MODE == kModeU8, uint32_t, unsigned long long>::type;
+        using val_t = typename std::conditional<MODE == kModeU8, uint32_t,
+                      typename std::conditional<MODE == kModeTf32, float, unsigned long long>::type>::type;
         val_t* nbv = reinterpret_cast<val_t*>(nb_s);         // |b|^2 per column of this tile
         const uint32_t et = threadIdx.x - 64;               // 0..127
         const uint32_t quad = warp & 3;                      // TMEM lane quadrant this warp may read
@@ -237,12 +260,13 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
         val_t best[kChains];
         uint32_t bcol[kChains];
 #pragma unroll
-        for (int c = 0; c < kChains; ++c) { best[c] = ~val_t(0); bcol[c] = 0; }
+        for (int c = 0; c < kChains; ++c) { best[c] = MODE == kModeTf32 ? val_t(0) : val_t(~0ull); bcol[c] = 0; }
         if (mbar_wait(tmem_full_bar, 0)) {
             tc_fence_after();
             const uint32_t lane_addr = tmem_base + ((quad * 32u) << 16);
             auto load = [&](uint32_t c0, uint32_t (&x0)[16], uint32_t (&x1)[16], uint32_t (&x2)[16]) {
                 tmem_ld_32x16(lane_addr + c0, x0);
+                if (MODE == kModeTf32) tmem_ld_32x16(lane_addr + Cfg::max_n + c0, x1);
                 if (MODE == kModeU16) {
                     tmem_ld_32x16(lane_addr + Cfg::max_n + c0, x1);
                     tmem_ld_32x16(lane_addr + 2 * Cfg::max_n + c0, x2);
@@ -250,24 +274,50 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
             };
             auto wait = [&](uint32_t (&x0)[16], uint32_t (&x1)[16], uint32_t (&x2)[16]) {
                 tmem_ld_wait_on(x0);
+                if (MODE == kModeTf32) tmem_ld_wait_on(x1);
                 if (MODE == kModeU16) { tmem_ld_wait_on(x1); tmem_ld_wait_on(x2); }
             };
             auto reduce = [&](uint32_t c0, const uint32_t (&x0)[16], const uint32_t (&x1)[16], const uint32_t (&x2)[16]) {
                 val_t sv[16];
+                if (MODE == kModeTf32) {
+                    // the estimate of every pair goes out (row-major per neuron: 64 contiguous bytes per thread
+                    // and chunk); nothing is reduced here
+                    if (n < p.n) {
+                        float* dst = static_cast<float*>(p.s_out) + ((size_t)img * p.n + n) * p.T + t0 + c0;
+#pragma unroll
+                        for (uint32_t j = 0; j < 16; j += 4) {
+                            float4 o;
+                            o.x = fmaxf((float)na + (float)nbv[c0 + j] - 2.0f * (__uint_as_float(x0[j]) + __uint_as_float(x1[j])), 0.0f);
+                            o.y = fmaxf((float)na + (float)nbv[c0 + j + 1] - 2.0f * (__uint_as_float(x0[j + 1]) + __uint_as_float(x1[j + 1])), 0.0f);
+                            o.z = fmaxf((float)na + (float)nbv[c0 + j + 2] - 2.0f * (__uint_as_float(x0[j + 2]) + __uint_as_float(x1[j + 2])), 0.0f);
+                            o.w = fmaxf((float)na + (float)nbv[c0 + j + 3] - 2.0f * (__uint_as_float(x0[j + 3]) + __uint_as_float(x1[j + 3])), 0.0f);
+                            // rows of T floats: 16-byte stores only where every row starts on a 16-byte boundary
+                            if ((p.T & 3u) == 0 && c0 + j + 4 <= ncols) *reinterpret_cast<float4*>(dst + j) = o;
+                            else {
+                                if (c0 + j < ncols) dst[j] = o.x;
+                                if (c0 + j + 1 < ncols) dst[j + 1] = o.y;
+                                if (c0 + j + 2 < ncols) dst[j + 2] = o.z;
+                                if (c0 + j + 3 < ncols) dst[j + 3] = o.w;
+                            }
+                        }
+                    }
+                } else {
 #pragma unroll
                 for (uint32_t j = 0; j < 16; ++j) {
                     if (MODE == kModeU8) {
                         // exact: 0 <= S < 2^31 although the intermediates wrap modulo 2^32
                         sv[j] = (uint32_t)(na + nbv[c0 + j]) - 2u * x0[j];
-                    } else {
+                    } else if (MODE == kModeU16) {
                         const unsigned long long dot = ((unsigned long long)x0[j] << 16)
                                                      + ((unsigned long long)x2[j] << 8) + x1[j];
                         sv[j] = na + nbv[c0 + j] - 2ull * dot;
+                    } else {
+                        sv[j] = 0;
                     }
                 }
                 if (c0 + 16 > ncols) {                        // ragged last chunk: columns beyond T never win
 #pragma unroll
-                    for (uint32_t j = 0; j < 16; ++j) if (c0 + j >= ncols) sv[j] = ~val_t(0);
+                    for (uint32_t j = 0; j < 16; ++j) if (c0 + j >= ncols) sv[j] = val_t(~0ull);
                 }
 #pragma unroll
                 for (uint32_t j = 0; j < 16; ++j)
@@ -277,6 +327,7 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     for (uint32_t j = 0; j < 16; ++j)
                         if (c0 + j < ncols)
                             static_cast<val_t*>(p.s_out)[((size_t)img * p.n + n) * p.T + t0 + c0 + j] = sv[j];
+                }
                 }
             };
             uint32_t a0[16], a1[16], a2[16], b0[16], b1[16], b2[16];
@@ -297,7 +348,7 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
 #pragma unroll
             for (int c = 1; c < kChains; ++c)
                 if (best[c] < best_s || (best[c] == best_s && bcol[c] < best_c)) { best_s = best[c]; best_c = bcol[c]; }
-            if (n < p.n && best_s != ~val_t(0))
+            if (MODE != kModeTf32 && n < p.n && best_s != val_t(~0ull))
                 atomicMin(&p.keys[(size_t)img * p.n + n],
                           ((unsigned long long)best_s << key_shift(MODE)) | (unsigned long long)(t0 + best_c));
         } else {
@@ -369,9 +420,10 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     const uint32_t b_box = PAIR ? n_tile / 2 : n_tile;         // transform rows one CTA stages per K slice
 
     CUtensorMap ma0, ma1, mb0, mb1;
-    bool ok = make_map(&ma0, a.a0, a.n, g.Kp, kBlockM) && make_map(&mb0, a.b0, (uint64_t)a.n_img * g.T, g.Kp, b_box);
-    if (MODE == kModeU16)
-        ok = ok && make_map(&ma1, a.a1, a.n, g.Kp, kBlockM) && make_map(&mb1, a.b1, (uint64_t)a.n_img * g.T, g.Kp, b_box);
+    const uint64_t row_bytes = MODE == kModeTf32 ? 4ull * g.Kp : g.Kp;      // Kp counts operand elements
+    bool ok = make_map(&ma0, a.a0, a.n, row_bytes, kBlockM) && make_map(&mb0, a.b0, (uint64_t)a.n_img * g.T, row_bytes, b_box);
+    if (Cfg::planes == 2)
+        ok = ok && make_map(&ma1, a.a1, a.n, row_bytes, kBlockM) && make_map(&mb1, a.b1, (uint64_t)a.n_img * g.T, row_bytes, b_box);
     else { ma1 = ma0; mb1 = mb0; }
     if (!ok) { *why = "cuTensorMapEncodeTiled failed"; return cudaErrorInvalidValue; }
 
@@ -388,10 +440,11 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     // ring: as many stages as fit the budget, no more than there are K slices
     const uint32_t b_bytes = (b_box * kBlockK + 1023) & ~1023u;
     const uint32_t stage_bytes = Cfg::planes * (L::a_bytes + b_bytes);
-    const uint32_t stages = std::max(2u, std::min(std::min(kMaxStages, L::ring_budget / stage_bytes), g.Kp / kBlockK));
+    const uint32_t num_kb = (uint32_t)(row_bytes / kBlockK);
+    const uint32_t stages = std::max(2u, std::min(std::min(kMaxStages, L::ring_budget / stage_bytes), num_kb));
     TcParams p;
     p.anorm = a.anorm; p.bnorm = a.bnorm; p.keys = a.keys; p.s_out = a.s_out; p.status = a.status;
-    p.n = a.n; p.T = g.T; p.num_kb = g.Kp / kBlockK; p.n_tile = n_tile;
+    p.n = a.n; p.T = g.T; p.num_kb = num_kb; p.n_tile = n_tile;
     p.stages = stages; p.b_bytes = b_bytes;
     p.tail_counter = a.tail ? a.tail_counter : nullptr;
     if (a.tail) p.tail = *a.tail;
@@ -427,6 +480,16 @@ cudaError_t launch_tc_any(const Geometry& g, const DistanceArgs& a, cudaStream_t
 } // namespace
 
 cudaError_t launch_distance_f32(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why);
+
+// float32 filter pass: a0/a1 and b0/b1 are the TF32 word planes (high, low) of the operands, anorm/bnorm float
+// |.|^2, s_out [n_img][n][T] float receives the estimates; keys are not touched.  Needs Kp % 32 == 0.
+cudaError_t launch_distance_tf32(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why)
+{
+    *why = "";
+    if (a.n == 0 || a.n_img == 0) return cudaSuccess;
+    if (g.Kp % 32 != 0 || !a.s_out) { *why = "launch_distance_tf32: operand stride or output"; return cudaErrorInvalidValue; }
+    return launch_tc_any<kModeTf32>(g, a, st, why);
+}
 
 bool distance_has_tail(const Geometry& g) { return g.mode == kModeU8 || g.mode == kModeU16; }
 

@@ -14,6 +14,7 @@ namespace pinkb {
 
 // Distance modes; numbering follows pink::DataType (UtilitiesLib/DataType.h).
 enum : int { kModeF32 = 0, kModeU16 = 1, kModeU8 = 2 };
+constexpr int kModeTf32 = 3;      // internal: the tensor-core filter pass of float32 mapping (never a Geometry::mode)
 
 // Status codes a kernel may leave in the device status word.
 enum : int { kDevOk = 0, kDevTimeoutProducer = 1, kDevTimeoutMma = 2, kDevTimeoutEpilogue = 3,
@@ -60,11 +61,14 @@ struct BmuPair { unsigned long long code; unsigned long long neuron; };
 // images: [n_img][C][id][id] float.  cs/sn: [q] cos/sin of t*2*pi/R (entry 0 unused).
 // base_out (nullable): [n_img][max(q,1)][C][nd][nd] float base rotations.
 // b0/b1: operand planes [n_img*T][Kp] (u8: b0; u16: b0 = high byte, b1 = low
-// byte; f32: b0 as float).  bnorm: [n_img*T] sum of squares (u32 for u8,
-// u64 for u16, unused for f32).
+// byte; f32: b0 as float, and -- when b1 is given -- b1 / b2 the two TF32 word
+// planes of the mapping estimate: value with its low 13 mantissa bits cleared,
+// and the rest).  bnorm: [n_img*T] sum of squares (u32 for u8, u64 for u16,
+// float for f32 with planes, else unused for f32).
 // rmax (nullable): [n_img] words zeroed by the caller; receives the bit pattern of max |pixel| over each image's base rotations.
 cudaError_t launch_rotate(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
-                   float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st, uint32_t* rmax = nullptr);
+                   float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st, uint32_t* rmax = nullptr,
+                   void* b2 = nullptr);
 
 // ---- SOM operand ------------------------------------------------------------
 // som: [n][Pp] float.  a0/a1/anorm: as b0/b1/bnorm with one row per neuron.
@@ -89,6 +93,19 @@ struct DistanceArgs
 bool distance_has_tail(const Geometry& g);
 // Returns cudaSuccess or the launch / tensor-map error; *why receives a static message.
 cudaError_t launch_distance(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why);
+
+// float32 mapping as filter + exact pass (distance_tc.cu, filter_f32.cu).  launch_split_tf32 writes, for `rows`
+// operand rows of Kp floats, the two TF32 word planes (hi = the value with its low 13 mantissa bits cleared,
+// lo = value - hi, exact) and the float |row|^2.  launch_distance_tf32 fills est[n_img][n][T] with
+// max(|a|^2 + |b|^2 - 2 (ah.bh + ah.bl + al.bh), 0).  launch_refine_f32 then, per (image, neuron), keeps every
+// transform whose estimate could still be the minimum given the error bound eps * (|a|^2 + |b|^2) on both sides,
+// computes those distances exactly from the float operands (direct differences) and stores the key
+// (float bits << 32 | transform) of the first minimum; cand_count (nullable) accumulates the exact evaluations.
+cudaError_t launch_split_tf32(const float* src, uint64_t rows, uint32_t Kp, float* hi, float* lo, float* norm, cudaStream_t st);
+cudaError_t launch_distance_tf32(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why);
+cudaError_t launch_refine_f32(const Geometry& g, const float* A, const float* anorm, uint32_t n, const float* B, const float* bnorm,
+                              uint32_t n_img, const float* est, float eps, unsigned long long* keys,
+                              unsigned long long* cand_count, cudaStream_t st);
 
 // ---- update factors ----------------------------------------------------------------
 // Either the N x N table of the reference (Trainer.h:69-76), this shard's columns of it, or -- for the grid layouts,
@@ -228,6 +245,7 @@ struct StepPlan
 
 struct StepArgs
 {
+    uint32_t plain_launch;            // host only: launch without the cooperative attribute (profilers that refuse it)
     // distance phase
     void* a0; void* a1; void* anorm; uint32_t n;                       // SOM operand of this shard (rows are rewritten by the update phase)
     const void* b0; const void* b1; const void* bnorm; uint32_t b_rows; // transform operand buffer (all rows) and its row count

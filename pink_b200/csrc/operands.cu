@@ -104,7 +104,8 @@ template <int MODE>
 __global__ void __launch_bounds__(kRotThreads, 5)
 rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, uint32_t magic_nd, uint32_t magic_ed,
               const float* __restrict__ cs, const float* __restrict__ sn, float* __restrict__ base_out,
-              void* __restrict__ b0, void* __restrict__ b1, void* __restrict__ bnorm, uint32_t* __restrict__ rmax)
+              void* __restrict__ b0, void* __restrict__ b1, void* __restrict__ bnorm, uint32_t* __restrict__ rmax,
+              void* __restrict__ b2)
 {
     using stage_t = typename StageType<MODE>::type;
     extern __shared__ __align__(16) uint8_t rot_dyn[];
@@ -230,6 +231,7 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
         const uint8_t* run_plane = (j & 1) ? stage_tr : reinterpret_cast<const uint8_t*>(stage);
         // a thread's share of a row's sum of squares fits 32 bits in uint8 mode (K * 255^2 < 2^32)
         typename std::conditional<MODE == kModeU8, uint32_t, unsigned long long>::type acc = 0;
+        float facc = 0.0f;                           // float mode with planes: this thread's share of the row's sum of squares
         for (uint32_t gi = threadIdx.x; gi < groups; gi += kRotThreads) {
             const uint32_t k = gi * kGroup;
             uint32_t r = fast_div(k, magic_ed), jj = k - r * g.ed;                  // r = c * ed + i
@@ -306,24 +308,44 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
                 reinterpret_cast<uint4*>(static_cast<uint8_t*>(b0) + orow * g.Kp)[gi] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                 reinterpret_cast<uint4*>(static_cast<uint8_t*>(b1) + orow * g.Kp)[gi] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             } else {
-                reinterpret_cast<float4*>(static_cast<float*>(b0) + orow * g.Kp)[gi] =
-                    make_float4((float)val[0], (float)val[1], (float)val[2], (float)val[3]);
+                const float4 v4 = make_float4((float)val[0], (float)val[1], (float)val[2], (float)val[3]);
+                reinterpret_cast<float4*>(static_cast<float*>(b0) + orow * g.Kp)[gi] = v4;
+                if (b1) {
+                    // planes of the tensor-core estimate: the top 19 bits of every value and the (exact) rest
+                    float4 h, l;
+                    h.x = __uint_as_float(__float_as_uint(v4.x) & 0xFFFFE000u); l.x = __fsub_rn(v4.x, h.x);
+                    h.y = __uint_as_float(__float_as_uint(v4.y) & 0xFFFFE000u); l.y = __fsub_rn(v4.y, h.y);
+                    h.z = __uint_as_float(__float_as_uint(v4.z) & 0xFFFFE000u); l.z = __fsub_rn(v4.z, h.z);
+                    h.w = __uint_as_float(__float_as_uint(v4.w) & 0xFFFFE000u); l.w = __fsub_rn(v4.w, h.w);
+                    reinterpret_cast<float4*>(static_cast<float*>(b1) + orow * g.Kp)[gi] = h;
+                    reinterpret_cast<float4*>(static_cast<float*>(b2) + orow * g.Kp)[gi] = l;
+                    facc += (v4.x * v4.x + v4.y * v4.y) + (v4.z * v4.z + v4.w * v4.w);
+                }
             }
         }
         if (MODE != kModeF32) {
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
             if (lane == 0) norm_s[v][warp] = acc;
+        } else if (b1) {
+            for (int o = 16; o > 0; o >>= 1) facc += __shfl_down_sync(0xffffffffu, facc, o);
+            if (lane == 0) norm_s[v][warp] = (unsigned long long)__double_as_longlong((double)facc);
         }
     }
-    if (MODE != kModeF32) {
+    if (MODE != kModeF32 || b1) {
         __syncthreads();
         if (threadIdx.x < nv) {
             const uint32_t v = threadIdx.x, f = v / nq, j = v - f * nq;
             const size_t orow = (size_t)img_i * g.T + f * g.R + j * g.q + tq;
-            unsigned long long tot = 0;
-            for (uint32_t wv = 0; wv < kRotThreads / 32; ++wv) tot += norm_s[v][wv];
-            if (MODE == kModeU8) static_cast<uint32_t*>(bnorm)[orow] = (uint32_t)tot;
-            else static_cast<unsigned long long*>(bnorm)[orow] = tot;
+            if (MODE == kModeF32) {
+                double tot = 0.0;
+                for (uint32_t wv = 0; wv < kRotThreads / 32; ++wv) tot += __longlong_as_double((long long)norm_s[v][wv]);
+                static_cast<float*>(bnorm)[orow] = (float)tot;
+            } else {
+                unsigned long long tot = 0;
+                for (uint32_t wv = 0; wv < kRotThreads / 32; ++wv) tot += norm_s[v][wv];
+                if (MODE == kModeU8) static_cast<uint32_t*>(bnorm)[orow] = (uint32_t)tot;
+                else static_cast<unsigned long long*>(bnorm)[orow] = tot;
+            }
         }
     }
 }
@@ -407,7 +429,7 @@ constexpr size_t kRotateSmemLimit = 200 * 1024;
 
 template <int MODE>
 cudaError_t rotate_dispatch(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
-                     float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st, uint32_t* rmax)
+                     float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st, uint32_t* rmax, void* b2)
 {
     size_t smem = MODE == kModeU8 ? 2 * (((size_t)g.P + 15) & ~size_t(15)) + 3 * kStagePad
                                   : (size_t)g.P * sizeof(typename StageType<MODE>::type);
@@ -428,19 +450,20 @@ cudaError_t rotate_dispatch(const Geometry& g, const float* images, uint32_t n_i
     const uint32_t magic_nd = div_magic(g.nd), magic_ed = div_magic(g.ed);
     dim3 grid(g.q ? g.q : 1, n_img);
     rotate_kernel<MODE><<<grid, kRotThreads, smem, st>>>(g, images, use_smem, magic_nd, magic_ed, cs, sn, base_out,
-                                                         b0, b1, bnorm, rmax);
+                                                         b0, b1, bnorm, rmax, b2);
     return cudaGetLastError();
 }
 
 } // namespace
 
 cudaError_t launch_rotate(const Geometry& g, const float* images, uint32_t n_img, const float* cs, const float* sn,
-                          float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st, uint32_t* rmax)
+                          float* base_out, void* b0, void* b1, void* bnorm, cudaStream_t st, uint32_t* rmax, void* b2)
 {
     if (n_img == 0) return cudaSuccess;
-    if (g.mode == kModeU8) return rotate_dispatch<kModeU8>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st, rmax);
-    if (g.mode == kModeU16) return rotate_dispatch<kModeU16>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st, rmax);
-    return rotate_dispatch<kModeF32>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st, rmax);
+    if (g.mode == kModeU8) return rotate_dispatch<kModeU8>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st, rmax, nullptr);
+    if (g.mode == kModeU16) return rotate_dispatch<kModeU16>(g, images, n_img, cs, sn, base_out, b0, b1, bnorm, st, rmax, nullptr);
+    // float: the planes are written only when both are given (b1 alone has no meaning in this mode)
+    return rotate_dispatch<kModeF32>(g, images, n_img, cs, sn, base_out, b0, b2 ? b1 : nullptr, bnorm, st, rmax, b2);
 }
 
 cudaError_t launch_quantize_som(const Geometry& g, const float* som, uint32_t n, void* a0, void* a1, void* anorm,

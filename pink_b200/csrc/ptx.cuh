@@ -244,6 +244,41 @@ __host__ __device__ constexpr uint32_t make_idesc_u8(uint32_t m, uint32_t n)
          | ((m >> 4) << 24);    // M / 16, bits [24,29)
 }
 
+// Instruction descriptor of kind::tf32: A and B are 32-bit words read as TF32 (both K-major), float
+// accumulator, tile M x N.
+__host__ __device__ constexpr uint32_t make_idesc_tf32(uint32_t m, uint32_t n)
+{
+    return (1u << 4)            // accumulator format F32, bits [4,6)
+         | (2u << 7)            // A format: TF32, bits [7,10)
+         | (2u << 10)           // B format: TF32, bits [10,13)
+         | ((n >> 3) << 17)     // N / 8, bits [17,23)
+         | ((m >> 4) << 24);    // M / 16, bits [24,29)
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // D[tmem] (+)= A[smem] * B[smem]^T, issued by one thread.
 __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate)

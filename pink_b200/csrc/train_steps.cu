@@ -898,7 +898,7 @@ cudaError_t launch_train_steps(const Geometry& g, const StepPlan& pl, const Step
     attr[1].id = cudaLaunchAttributeCooperative;
     attr[1].val.cooperative = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 2;
+    cfg.numAttrs = a.plain_launch ? 1 : 2;       // without the attribute the caller vouches for an otherwise idle device
     *why = "train_steps_kernel launch";
     return cudaLaunchKernelExC(&cfg, fn, args);
 }

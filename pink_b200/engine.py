@@ -211,6 +211,12 @@ class Engine:
                 "update_own_us", "barrier2_wait_us")
         return dict(zip(keys, list(out)[:7]))
 
+    def map_filter_stats(self):
+        """Counters of float32 mapping's estimate + exact pass (see pink_b200_map_filter_stats)."""
+        out = (C.c_double * 4)()
+        capi.check(capi.lib.pink_b200_map_filter_stats(self._h, out))
+        return dict(zip(("pairs_estimated", "pairs_exact", "worst_estimate_error", "error_bound"), list(out)))
+
     def profile_stamps(self):
         """Raw device-timer stamps of the last profiled pass: uint64 array [steps][blocks][12]."""
         blocks, steps = C.c_uint32(), C.c_uint64()

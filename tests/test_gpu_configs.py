@@ -74,14 +74,22 @@ def test_distance_sweep(cuda, mode):
                 np.testing.assert_allclose(mat[0][n, ::step], ref_row, rtol=1e-5)
 
 
-def test_c2_float_map_at_size(cuda):
-    """20 x 20 cartesian SOM of 90 x 90 neurons, 128 x 128 images, 64 x 64 region, 360 rotations + flip, float32."""
+@pytest.mark.parametrize("filtered", [1, 0])
+def test_c2_float_map_at_size(cuda, filtered):
+    """20 x 20 cartesian SOM of 90 x 90 neurons, 128 x 128 images, 64 x 64 region, 360 rotations + flip, float32:
+    through the tensor-core estimate + exact pass (default) and through the all-pairs exact kernel."""
     N, IDIM, ND, ED, R = 400, 128, 90, 64, 360
     som = mt19937_uniform(N * ND * ND, 1234).reshape(N, 1, ND, ND)
     imgs = blob_images(3, IDIM, 1, seed=1002).reshape(3, 1, IDIM, IDIM)
-    with engine.Engine(N, 1, IDIM, ND, ED, R, True, capi.FLOAT) as eng:
+    with engine.Engine(N, 1, IDIM, ND, ED, R, True, capi.FLOAT, options={"f32_filter": filtered}) as eng:
         eng.set_som(som)
         dist, rot = eng.map(imgs)
+        stats = eng.map_filter_stats()
+    if filtered:
+        assert stats["pairs_estimated"] == 3 * N * 2 * R and 3 * N <= stats["pairs_exact"] < stats["pairs_estimated"] / 20
+        assert stats["worst_estimate_error"] < stats["error_bound"] / 2       # the assumed bound has room to spare
+    else:
+        assert stats["pairs_estimated"] == 0
     rng = np.random.default_rng(2)
     for i, img in enumerate(imgs):
         sample = np.unique(np.concatenate([rng.integers(0, N, 24), [0, N - 1, int(np.argmin(dist[i]))]]))
@@ -92,6 +100,39 @@ def test_c2_float_map_at_size(cuda):
         at_gpu = D[np.arange(len(sample)), rot[i][sample]]
         assert (at_gpu <= wd * (1 + 1e-5)).all()
         assert (rot[i][sample] == wr).mean() >= 0.9
+
+
+def test_float_map_of_a_converged_map_through_the_filter(cuda):
+    """The estimate |a|^2 + |b|^2 - 2 a.b is weakest where the distances are small against the norms: neurons that
+    are rotated copies of the mapped images plus a little noise (what a trained map looks like).  Both float paths
+    must agree with the oracle; exact copies give distance 0 at the right transform."""
+    N, IDIM, ND, ED, R = 64, 64, 44, 31, 64
+    rng = np.random.default_rng(11)
+    imgs = blob_images(4, IDIM, 1, seed=77).reshape(4, 1, IDIM, IDIM)
+    som = np.empty((N, 1, ND, ND), np.float32)
+    for n in range(N):
+        rs = O.rotation_set(imgs[n % 4][0], ND, R, True)
+        som[n, 0] = rs[(7 * n) % (2 * R)].reshape(ND, ND)
+        if n >= 8:
+            som[n] += rng.normal(0, 0.003 * (1 + n % 5), som[n].shape).astype(np.float32)
+    som = np.clip(som, 0, 1)
+    out = {}
+    for filtered in (1, 0):
+        with engine.Engine(N, 1, IDIM, ND, ED, R, True, capi.FLOAT, options={"f32_filter": filtered}) as eng:
+            eng.set_som(som)
+            out[filtered] = eng.map(imgs)
+            if filtered:
+                st = eng.map_filter_stats()
+                assert st["worst_estimate_error"] < st["error_bound"] / 2
+    for i, img in enumerate(imgs):
+        rotset = O.rotation_set(img[0], ND, R, True)
+        wd, wr, D = O.distance_f32(som, rotset, ED, full=True)
+        for filtered in (1, 0):
+            dist, rot = out[filtered][0][i], out[filtered][1][i]
+            np.testing.assert_allclose(dist, np.sqrt(wd), rtol=1e-5, atol=1e-7)
+            assert (D[np.arange(N), rot] <= wd * (1 + 1e-5) + 1e-12).all()
+        for n in range(i, 8, 4):                                   # exact copies of this image
+            assert out[1][0][i][n] == 0.0 and out[1][1][i][n] == (7 * n) % (2 * R)
 
 
 def test_c3_uint16_two_channel_training_at_size(cuda):

@@ -194,8 +194,12 @@ def test_map(cuda, case, mode):
         d, r = O.map_image(som, imgs[i], ed, R, flip, mode)
         if mode == 0:
             np.testing.assert_allclose(dist[i], d, rtol=1e-5)
-            same = rot[i] == r
-            assert same.mean() > 0.9              # float near-ties may pick a neighbouring transform
+            # the transform is the oracle's, or a float near-tie: its oracle distance within 1e-5 of the oracle minimum
+            rs = O.rotation_set(imgs[i], nd, R, flip)
+            _, _, D = O.distance_f32(som, rs, ed, full=True)
+            chosen = D[np.arange(N), rot[i]]
+            assert (chosen <= D.min(axis=1) * (1 + 1e-5)).all()
+            assert (rot[i] == r).mean() > 0.5
         else:
             assert np.array_equal(dist[i].view(np.uint32), d.view(np.uint32))
             assert np.array_equal(rot[i], r)

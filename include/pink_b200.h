@@ -326,7 +326,7 @@ int pink_b200_host_free(void* ptr);
  * cudaStream_t (NULL = default stream).  Operand layout: integer modes use
  * rows of `row_stride` bytes (a multiple of 128, zero beyond K) per plane,
  * uint16 as two planes (high bytes, low bytes); float mode uses rows of
- * `row_stride` floats (a multiple of 16, zero beyond K). */
+ * `row_stride` floats (a multiple of 32, zero beyond K). */
 
 /* Row stride (in elements) the library uses for a distance length of K elements. */
 uint32_t pink_b200_operand_stride(uint32_t K, uint32_t dist_type);

@@ -319,6 +319,43 @@ int check_status(pink_b200_ctx* c)
 
 constexpr uint32_t kRotBatch = kStepBatchMax;
 
+// float32 distances through the tensor-core estimate + exact pass: possible when the exact pass's candidate lists
+// fit shared memory (T) and the operand rows are whole 128-byte slices
+bool uses_filter(const pink_b200_ctx* c)
+{
+    return c->g.mode == kModeF32 && c->opt_f32_filter && c->g.Kp % 32 == 0 && c->g.T <= 12800;
+}
+
+// Bound of the estimate's error relative to |a|^2 + |b|^2 (derived in filter_f32.cu): 3 * K / 16 * 2^-23 + 2^-17
+float filter_eps(uint32_t K) { return (float)(3.0 * K / 16.0 * 1.1920928955078125e-7 + 7.62939453125e-6); }
+
+int ensure_filter_buffers(pink_b200_ctx* c, size_t imgs)
+{
+    const Geometry& g = c->g;
+    if (!c->d_af_hi) {
+        const size_t elems = (size_t)c->count * g.Kp;
+        CU_TRY(cudaMalloc(&c->d_af_hi, elems * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_af_lo, elems * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_af_norm, (size_t)c->count * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_filter_stats, 2 * sizeof(unsigned long long)));
+        CU_TRY(cudaMemsetAsync(c->d_filter_stats, 0, 2 * sizeof(unsigned long long), c->stream));
+        c->af_valid = false;
+    }
+    if (c->filter_imgs < imgs) {
+        free_dev(c->d_bf_hi); free_dev(c->d_bf_lo); free_dev(c->d_bf_norm); free_dev(c->d_est);
+        const size_t rows = imgs * g.T;
+        CU_TRY(cudaMalloc(&c->d_bf_hi, rows * g.Kp * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_bf_lo, rows * g.Kp * sizeof(float)));
+        // the rotation kernel writes K values per row; the padding up to Kp stays zero
+        CU_TRY(cudaMemsetAsync(c->d_bf_hi, 0, rows * g.Kp * sizeof(float), c->stream));
+        CU_TRY(cudaMemsetAsync(c->d_bf_lo, 0, rows * g.Kp * sizeof(float), c->stream));
+        CU_TRY(cudaMalloc(&c->d_bf_norm, rows * sizeof(float)));
+        CU_TRY(cudaMalloc(&c->d_est, rows * c->count * sizeof(float)));
+        c->filter_imgs = imgs;
+    }
+    return PINK_B200_OK;
+}
+
 // One training step on image `slot_img` of the transform buffers (its rotation
 // set is already there): distance + minimum over transforms, best matching
 // unit (+ exchange between ranks), neighbourhood update.
@@ -364,7 +401,29 @@ int train_step(pink_b200_ctx* c, size_t slot_img, uint32_t* bmu_slot)
     if (tail) { da.tail = &ba; da.tail_counter = c->d_nitems + 2; }
     const char* why = "";
     if (ev) CU_TRY(cudaEventRecord(ev[0], c->stream));
-    cudaError_t e = launch_distance(g, da, c->stream, &why);
+    cudaError_t e = cudaSuccess;
+    if (uses_filter(c)) {
+        // float32: estimate of every pair on the tensor cores, exact sums for the transforms it cannot rule out.
+        // The update rewrites operand rows, so the SOM's planes are rebuilt for every image.
+        const float* A = static_cast<const float*>(c->d_a0);
+        const float* B = static_cast<const float*>(c->d_b0) + row0 * g.Kp;
+        LAUNCH_TRY(launch_split_tf32(A, c->count, g.Kp, c->d_af_hi, c->d_af_lo, c->d_af_norm, c->stream));
+        LAUNCH_TRY(launch_split_tf32(B, g.T, g.Kp, c->d_bf_hi, c->d_bf_lo, c->d_bf_norm, c->stream));
+        DistanceArgs fa = da;
+        fa.a0 = c->d_af_hi; fa.a1 = c->d_af_lo; fa.anorm = c->d_af_norm;
+        fa.b0 = c->d_bf_hi; fa.b1 = c->d_bf_lo; fa.bnorm = c->d_bf_norm;
+        fa.s_out = c->d_est;
+        e = launch_distance_tf32(g, fa, c->stream, &why);
+        if (e == cudaSuccess) {
+            why = "refine_f32_kernel launch";
+            e = launch_refine_f32(g, A, c->d_af_norm, c->count, B, c->d_bf_norm, 1, c->d_est, filter_eps(g.K), c->d_keys,
+                                  c->d_filter_stats, c->stream);
+        }
+        c->filter_pairs += (unsigned long long)c->count * g.T;
+        c->launches += 3;
+    } else {
+        e = launch_distance(g, da, c->stream, &why);
+    }
     if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
     if (ev) CU_TRY(cudaEventRecord(ev[1], c->stream));
     if (!multi) {
@@ -752,6 +811,10 @@ int train_prepare(pink_b200_ctx* c, uint64_t n)
         return fail(PINK_B200_ESTATE, "an earlier device-side wait expired; the context no longer trains (read the map back or destroy it)");
     if (!c->have_som) return fail(PINK_B200_ESTATE, "pink_b200_set_som must be called before training");
     c->af_valid = false;                 // training rewrites the SOM operand: the mapping filter's planes are rebuilt on demand
+    if (uses_filter(c) && !c->use_steps) {
+        int rcf = ensure_filter_buffers(c, c->filter_imgs ? c->filter_imgs : 1);
+        if (rcf) return rcf;
+    }
     if (!c->have_factors) return fail(PINK_B200_ESTATE, "pink_b200_set_update_factors must be called before training");
     if (c->cfg.world_size > 1 && !c->comm)
         return fail(PINK_B200_ESTATE, "pink_b200_comm_init must be called before training with world_size > 1");
@@ -779,7 +842,7 @@ const char* pink_b200_version(void) { return "pink_b200 0.1 (sm_100a)"; }
 
 uint32_t pink_b200_operand_stride(uint32_t K, uint32_t dist_type)
 {
-    return dist_type == PINK_B200_FLOAT ? round_up(K, 16) : round_up(K, 128);
+    return dist_type == PINK_B200_FLOAT ? round_up(K, 32) : round_up(K, 128);
 }
 
 int pink_b200_create(const pink_b200_config* cfg, pink_b200_ctx** out)
@@ -1222,46 +1285,10 @@ int pink_b200_get_bmu_log(pink_b200_ctx* c, uint32_t* host_bmus, uint64_t n)
     return PINK_B200_OK;
 }
 
-// Bound of the estimate's error relative to |a|^2 + |b|^2 (derived in filter_f32.cu): 3 * K / 16 * 2^-23 + 2^-17
-static float filter_eps(uint32_t K) { return (float)(3.0 * K / 16.0 * 1.1920928955078125e-7 + 7.62939453125e-6); }
-
-// float32 mapping through the tensor-core filter: possible when the exact pass's candidate lists fit shared memory
-static bool map_uses_filter(const pink_b200_ctx* c)
-{
-    return c->g.mode == kModeF32 && c->opt_f32_filter && c->g.Kp % 32 == 0 && c->g.T <= 12800;
-}
-
-static int ensure_filter_buffers(pink_b200_ctx* c, size_t imgs)
-{
-    const Geometry& g = c->g;
-    if (!c->d_af_hi) {
-        const size_t elems = (size_t)c->count * g.Kp;
-        CU_TRY(cudaMalloc(&c->d_af_hi, elems * sizeof(float)));
-        CU_TRY(cudaMalloc(&c->d_af_lo, elems * sizeof(float)));
-        CU_TRY(cudaMalloc(&c->d_af_norm, (size_t)c->count * sizeof(float)));
-        CU_TRY(cudaMalloc(&c->d_filter_stats, 2 * sizeof(unsigned long long)));
-        CU_TRY(cudaMemsetAsync(c->d_filter_stats, 0, 2 * sizeof(unsigned long long), c->stream));
-        c->af_valid = false;
-    }
-    if (c->filter_imgs < imgs) {
-        free_dev(c->d_bf_hi); free_dev(c->d_bf_lo); free_dev(c->d_bf_norm); free_dev(c->d_est);
-        const size_t rows = imgs * g.T;
-        CU_TRY(cudaMalloc(&c->d_bf_hi, rows * g.Kp * sizeof(float)));
-        CU_TRY(cudaMalloc(&c->d_bf_lo, rows * g.Kp * sizeof(float)));
-        // the rotation kernel writes K values per row; the padding up to Kp stays zero
-        CU_TRY(cudaMemsetAsync(c->d_bf_hi, 0, rows * g.Kp * sizeof(float), c->stream));
-        CU_TRY(cudaMemsetAsync(c->d_bf_lo, 0, rows * g.Kp * sizeof(float), c->stream));
-        CU_TRY(cudaMalloc(&c->d_bf_norm, rows * sizeof(float)));
-        CU_TRY(cudaMalloc(&c->d_est, rows * c->count * sizeof(float)));
-        c->filter_imgs = imgs;
-    }
-    return PINK_B200_OK;
-}
-
 static int map_chunk(pink_b200_ctx* c, const float* d_images, uint32_t m, float* d_dist, uint32_t* d_rot)
 {
     const Geometry& g = c->g;
-    const bool filter = map_uses_filter(c);
+    const bool filter = uses_filter(c);
     if (filter) {
         int rc = ensure_filter_buffers(c, c->map_batch);
         if (rc) return rc;

@@ -429,6 +429,7 @@ def main():
         if world == 1:
             extras["other_configs"] = bench_other_configs(torch, local)
             extras["distance_sweep"] = bench_distance_sweep(torch)
+            extras["cli"] = bench_cli(w, pool)
             extras["reference_gpu"] = bench_reference_gpu(w, som, pool)
 
     cpu = None
@@ -554,6 +555,37 @@ def bench_map(torch, dist, barrier, rank, world, local, som4, pool4):
         out[key] = res
         eng.close()
     return out
+
+
+def bench_cli(w, pool, n_images=2048, epochs=8):
+    """The command line program on a data file (the reference's `Pink --train`): images/s of its training loop,
+    file reading included (reader thread, pinned double buffer), from the program's own progress clock."""
+    import re, subprocess, tempfile
+    from pink_b200 import build as B, files
+    if not os.path.exists(B.CLI):
+        return {"unavailable": "pink_b200/Pink is not built"}
+    n_images = min(n_images, len(pool))
+    with tempfile.TemporaryDirectory() as tmp:
+        data, som_path = os.path.join(tmp, "data.bin"), os.path.join(tmp, "som.bin")
+        files.write_data_file(data, pool[:n_images].reshape(n_images, w["image_dim"], w["image_dim"]))
+        cmd = [B.CLI, "--layout", "hexagonal" if w["som_layout"] == 1 else "cartesian", "--som-width", str(w["som_dim"]),
+               "--som-height", str(w["som_dim"]), "--numrot", str(w["rotations"]), "--neuron-dimension", str(w["neuron_dim"]),
+               "--euclidean-distance-dimension", str(w["ed_dim"]), "--euclidean-distance-type", "uint8", "--seed", "1234",
+               "--init", "random", "--num-iter", str(epochs), "--dist-func", "gaussian", str(w["sigma"]), str(w["damping"]),
+               "--input-shuffle-off", "--progress", "4", "--train", data, som_path]
+        t0 = time.perf_counter()
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        wall = time.perf_counter() - t0
+    if r.returncode != 0:
+        return {"unavailable": (r.stdout + r.stderr)[-300:]}
+    marks = re.findall(r"\] 100 % ([0-9.]+) s", r.stdout)
+    if not marks:
+        return {"unavailable": "no progress line in the program's output"}
+    loop_s = float(marks[-1])
+    return {"value": n_images * epochs / loop_s, "unit": "images/s", "images": n_images, "epochs": epochs,
+            "loop_seconds": loop_s, "process_seconds": wall,
+            "note": "Pink --train on a data file of the bench workload, all visible GPUs of the process (here one); "
+                    "loop time from the program's progress output, process time includes start-up and writing the map"}
 
 
 def bench_distance_sweep(torch):

@@ -125,7 +125,7 @@ int pink_b200_shard_range(uint32_t n_neurons, uint32_t world_size, uint32_t rank
  *                          image; g >= 2 groups of g consecutive ranks share
  *   "rotation_overlap"     1 puts the rotation kernels on a second, low-priority stream (default 0)
  *   "mma_pairs"            0 keeps the distance kernel from pairing blocks (default 1)
- *   "f32_filter"           0 maps float32 distances with the all-pairs exact kernel instead of the tensor-core
+ *   "f32_filter"           0 computes float32 distances with the all-pairs exact kernel instead of the tensor-core
  *                          estimate + exact pass (default 1)
  *   "cooperative_launch"   0 launches the persistent kernel without the cooperative attribute (default 1).  Its
  *                          blocks wait for one another, so this is only for a device with nothing else running,
@@ -274,8 +274,8 @@ int pink_b200_profile_detail(pink_b200_ctx* ctx, double out[8]);
  * *steps are always set; `out` may be NULL to ask for the sizes only. */
 int pink_b200_profile_stamps(pink_b200_ctx* ctx, uint64_t* out, uint64_t capacity, uint32_t* blocks, uint64_t* steps);
 
-/* float32 mapping runs as an estimate of all N x T distances on the tensor cores followed by exact sums for the
- * transforms the estimate cannot rule out (option "f32_filter" = 0 computes all of them exactly instead; the
+/* float32 distances (mapping and training) run as an estimate of all N x T distances on the tensor cores followed
+ * by exact sums for the transforms the estimate cannot rule out (option "f32_filter" = 0 computes all of them exactly instead; the
  * results are the same up to the summation order of the exact sums).  out[0] = pairs estimated so far,
  * out[1] = exact sums formed, out[2] = largest |estimate - exact| / (|a|^2 + |b|^2) seen among those,
  * out[3] = the error bound the selection assumes for that ratio. */

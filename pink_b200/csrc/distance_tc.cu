@@ -90,6 +90,7 @@ struct TcParams
     void* s_out;
     int* status;
     uint32_t n, T, num_kb, n_tile;
+    uint32_t swap;              // kModeTf32 only: the transforms are the tile rows (M side), the neurons its columns
     uint32_t stages, b_bytes;   // ring depth; bytes of this CTA's transform rows per plane and stage (multiple of 1024)
     uint32_t* tail_counter;     // nullable: block arrival counter (zero between launches) that enables the tail below
     BmuArgs tail;               // the last block to finish reduces the shard's keys to its record and publishes it
@@ -153,7 +154,11 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer --
         if (elect_one()) {
-            const int32_t brow = (int32_t)(img * p.T + t0 + pair_rank * b_rows);
+            // rows of the M-side map (map_a*) and of the N-side map (map_b*); swapped: the transforms of this image
+            // are the M side (a tile's rows beyond T are the next image's and are never stored)
+            const int32_t arow = (int32_t)(MODE == kModeTf32 && p.swap ? img * p.T + m0 : m0);
+            const int32_t brow = (int32_t)(MODE == kModeTf32 && p.swap ? t0 + pair_rank * b_rows
+                                                                      : img * p.T + t0 + pair_rank * b_rows);
             for (uint32_t kb = 0; kb < p.num_kb; ++kb) {
                 const uint32_t s = kb % p.stages, ph = (kb / p.stages) & 1;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1)) { report(p.status, kDevTimeoutProducer); break; }
@@ -162,18 +167,18 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                 if (PAIR) {
                     const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);      // the issuing CTA's barrier
                     mbar_expect_tx_cluster(bar, stage_tx);
-                    tma_load_2d_pair(st, &map_a0, bar, kx, (int32_t)m0);
+                    tma_load_2d_pair(st, &map_a0, bar, kx, arow);
                     tma_load_2d_pair(st + Cfg::planes * L::a_bytes, &map_b0, bar, kx, brow);
                     if (Cfg::planes == 2) {
-                        tma_load_2d_pair(st + L::a_bytes, &map_a1, bar, kx, (int32_t)m0);
+                        tma_load_2d_pair(st + L::a_bytes, &map_a1, bar, kx, arow);
                         tma_load_2d_pair(st + Cfg::planes * L::a_bytes + p.b_bytes, &map_b1, bar, kx, brow);
                     }
                 } else {
                     mbar_expect_tx(&full_bar[s], stage_tx);
-                    tma_load_2d(st, &map_a0, &full_bar[s], kx, (int32_t)m0);
+                    tma_load_2d(st, &map_a0, &full_bar[s], kx, arow);
                     tma_load_2d(st + Cfg::planes * L::a_bytes, &map_b0, &full_bar[s], kx, brow);
                     if (Cfg::planes == 2) {
-                        tma_load_2d(st + L::a_bytes, &map_a1, &full_bar[s], kx, (int32_t)m0);
+                        tma_load_2d(st + L::a_bytes, &map_a1, &full_bar[s], kx, arow);
                         tma_load_2d(st + Cfg::planes * L::a_bytes + p.b_bytes, &map_b1, &full_bar[s], kx, brow);
                     }
                 }
@@ -247,13 +252,17 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
         const uint32_t quad = warp & 3;                      // TMEM lane quadrant this warp may read
         const uint32_t row = quad * 32 + lane;
         const uint32_t n = m0 + row;
-        const uint32_t ncols = p.T > t0 ? min(p.n_tile, p.T - t0) : 0u;     // columns that are transforms of this image
+        const bool swapped = MODE == kModeTf32 && p.swap;
+        const uint32_t m_rows = swapped ? p.T : p.n, n_cols = swapped ? p.n : p.T;       // extent of the two tile sides
+        const uint32_t ncols = n_cols > t0 ? min(p.n_tile, n_cols - t0) : 0u;     // columns of this tile that exist
         for (uint32_t j = et; j < p.n_tile; j += 128) {
             val_t v = 0;
-            if (j < ncols) v = static_cast<const val_t*>(p.bnorm)[(size_t)img * p.T + t0 + j];
+            if (j < ncols) v = swapped ? static_cast<const val_t*>(p.anorm)[t0 + j]
+                                       : static_cast<const val_t*>(p.bnorm)[(size_t)img * p.T + t0 + j];
             nbv[j] = v;
         }
-        const val_t na = n < p.n ? static_cast<const val_t*>(p.anorm)[n] : val_t(0);
+        const val_t na = n >= m_rows ? val_t(0) : swapped ? static_cast<const val_t*>(p.bnorm)[(size_t)img * p.T + n]
+                                                          : static_cast<const val_t*>(p.anorm)[n];
         asm volatile("bar.sync 1, 128;" ::: "memory");      // nbv visible to the four epilogue warps
 
         constexpr int kChains = 4;
@@ -282,7 +291,18 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                 if (MODE == kModeTf32) {
                     // the estimate of every pair goes out (row-major per neuron: 64 contiguous bytes per thread
                     // and chunk); nothing is reduced here
-                    if (n < p.n) {
+                    if (swapped) {
+                        // this thread's row is a transform, the columns are neurons: a warp stores 32 consecutive
+                        // transforms of one neuron's row of the estimate matrix
+                        if (n < p.T) {
+                            float* dst = static_cast<float*>(p.s_out) + ((size_t)img * p.n + t0 + c0) * p.T + n;
+#pragma unroll
+                            for (uint32_t j = 0; j < 16; ++j)
+                                if (c0 + j < ncols)
+                                    dst[(size_t)j * p.T] = fmaxf((float)na + (float)nbv[c0 + j]
+                                                                 - 2.0f * (__uint_as_float(x0[j]) + __uint_as_float(x1[j])), 0.0f);
+                        }
+                    } else if (n < p.n) {
                         float* dst = static_cast<float*>(p.s_out) + ((size_t)img * p.n + n) * p.T + t0 + c0;
 #pragma unroll
                         for (uint32_t j = 0; j < 16; j += 4) {
@@ -392,38 +412,44 @@ distance_tc_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
 // ------------------------------------------------------------------ host side --
 
 template <int MODE, bool PAIR>
-cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why)
+cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st, const char** why, bool swap = false)
 {
     using Cfg = TcCfg<MODE, PAIR>;
     using L = SmemLayout<MODE, PAIR>;
-    // neuron tiles; CTA pairs take two consecutive ones (an odd count is padded with an empty tile)
-    uint32_t m_tiles = (a.n + kBlockM - 1) / kBlockM;
+    // The tile rows (M side, 128 per block) are the neurons and the tile columns the transforms -- or, swapped
+    // (float estimate only), the other way round.
+    const uint32_t m_extent = swap ? g.T : a.n, n_extent = swap ? a.n : g.T;
+    // row tiles; CTA pairs take two consecutive ones (an odd count is padded with an empty tile)
+    uint32_t m_tiles = (m_extent + kBlockM - 1) / kBlockM;
     if (PAIR) m_tiles = (m_tiles + 1) & ~1u;
-    // Balanced transform tiles, each a multiple of 16 columns: the fewest tiles of at most max_n
+    // Balanced column tiles, each a multiple of 16 columns: the fewest tiles of at most max_n
     // columns -- unless that leaves SMs without a block (a small neuron shard, few images): a block's
     // run time is set by the bytes it pulls through its SM, (128 + its share of n_tile) * K, so narrower
-    // tiles spread over all SMs finish sooner.  Below 32 columns the neuron tile dominates and nothing is gained.
-    uint32_t tiles = (g.T + Cfg::max_n - 1) / Cfg::max_n;
+    // tiles spread over all SMs finish sooner.  Below 32 columns the row tile dominates and nothing is gained.
+    uint32_t tiles = (n_extent + Cfg::max_n - 1) / Cfg::max_n;
     {
         static thread_local int sm_dev = -1, sms = 0;
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev != sm_dev) { cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); sm_dev = dev; }
         const uint64_t rows = (uint64_t)m_tiles * a.n_img;
-        const uint32_t most = std::max<uint32_t>(tiles, g.T / 32);
+        const uint32_t most = std::max<uint32_t>(tiles, n_extent / 32);
         if (sms > 0 && rows * tiles < (uint64_t)sms)
             tiles = (uint32_t)std::max<uint64_t>(tiles, std::min<uint64_t>(most, (uint64_t)sms / rows));   // one wave
     }
-    uint32_t n_tile = ((g.T + tiles - 1) / tiles + 15) & ~15u;
+    uint32_t n_tile = ((n_extent + tiles - 1) / tiles + 15) & ~15u;
     if (n_tile > Cfg::max_n) n_tile = Cfg::max_n;
-    const uint32_t n_tiles = (g.T + n_tile - 1) / n_tile;
-    const uint32_t b_box = PAIR ? n_tile / 2 : n_tile;         // transform rows one CTA stages per K slice
+    const uint32_t n_tiles = (n_extent + n_tile - 1) / n_tile;
+    const uint32_t b_box = PAIR ? n_tile / 2 : n_tile;         // column-side rows one CTA stages per K slice
 
     CUtensorMap ma0, ma1, mb0, mb1;
     const uint64_t row_bytes = MODE == kModeTf32 ? 4ull * g.Kp : g.Kp;      // Kp counts operand elements
-    bool ok = make_map(&ma0, a.a0, a.n, row_bytes, kBlockM) && make_map(&mb0, a.b0, (uint64_t)a.n_img * g.T, row_bytes, b_box);
+    const uint64_t som_rows = a.n, tr_rows = (uint64_t)a.n_img * g.T;
+    bool ok = swap ? make_map(&ma0, a.b0, tr_rows, row_bytes, kBlockM) && make_map(&mb0, a.a0, som_rows, row_bytes, b_box)
+                   : make_map(&ma0, a.a0, som_rows, row_bytes, kBlockM) && make_map(&mb0, a.b0, tr_rows, row_bytes, b_box);
     if (Cfg::planes == 2)
-        ok = ok && make_map(&ma1, a.a1, a.n, row_bytes, kBlockM) && make_map(&mb1, a.b1, (uint64_t)a.n_img * g.T, row_bytes, b_box);
+        ok = ok && (swap ? make_map(&ma1, a.b1, tr_rows, row_bytes, kBlockM) && make_map(&mb1, a.a1, som_rows, row_bytes, b_box)
+                         : make_map(&ma1, a.a1, som_rows, row_bytes, kBlockM) && make_map(&mb1, a.b1, tr_rows, row_bytes, b_box));
     else { ma1 = ma0; mb1 = mb0; }
     if (!ok) { *why = "cuTensorMapEncodeTiled failed"; return cudaErrorInvalidValue; }
 
@@ -444,7 +470,7 @@ cudaError_t launch_tc(const Geometry& g, const DistanceArgs& a, cudaStream_t st,
     const uint32_t stages = std::max(2u, std::min(std::min(kMaxStages, L::ring_budget / stage_bytes), num_kb));
     TcParams p;
     p.anorm = a.anorm; p.bnorm = a.bnorm; p.keys = a.keys; p.s_out = a.s_out; p.status = a.status;
-    p.n = a.n; p.T = g.T; p.num_kb = num_kb; p.n_tile = n_tile;
+    p.n = a.n; p.T = g.T; p.num_kb = num_kb; p.n_tile = n_tile; p.swap = swap ? 1u : 0u;
     p.stages = stages; p.b_bytes = b_bytes;
     p.tail_counter = a.tail ? a.tail_counter : nullptr;
     if (a.tail) p.tail = *a.tail;
@@ -488,7 +514,17 @@ cudaError_t launch_distance_tf32(const Geometry& g, const DistanceArgs& a, cudaS
     *why = "";
     if (a.n == 0 || a.n_img == 0) return cudaSuccess;
     if (g.Kp % 32 != 0 || !a.s_out) { *why = "launch_distance_tf32: operand stride or output"; return cudaErrorInvalidValue; }
-    return launch_tc_any<kModeTf32>(g, a, st, why);
+    // orientation: the one whose padded tile grid (rows to 128, or 256 for block pairs; columns to balanced tiles of
+    // at most 256, multiples of 16) computes fewer pairs that do not exist
+    auto padded = [](uint32_t m, uint32_t n) -> uint64_t {
+        const uint32_t mp = m > kBlockM ? (m + 2 * kBlockM - 1) / (2 * kBlockM) * (2 * kBlockM) : kBlockM;
+        const uint32_t tiles = (n + 255) / 256, nt = (((n + tiles - 1) / tiles) + 15) & ~15u;
+        return (uint64_t)mp * ((n + nt - 1) / nt) * nt;
+    };
+    const bool swap = padded(g.T, a.n) < padded(a.n, g.T);
+    const uint32_t m_extent = swap ? g.T : a.n;
+    if (m_extent > kBlockM && !a.single_cta) return launch_tc<kModeTf32, true>(g, a, st, why, swap);
+    return launch_tc<kModeTf32, false>(g, a, st, why, swap);
 }
 
 bool distance_has_tail(const Geometry& g) { return g.mode == kModeU8 || g.mode == kModeU16; }

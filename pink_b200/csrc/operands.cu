@@ -138,6 +138,10 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
             pyc[i] = __fmul_rn(py, ca);
         }
         const uint32_t idm1 = g.id - 1;
+        // When the rotated neuron window lies strictly inside the image for every angle (half its diagonal plus a
+        // margin of half a pixel within half the image), no source position is out of range and no +1 tap falls
+        // outside: the range test and the clamps below are identities and are left out.
+        const bool all_inside = __fadd_rn(__fmul_rn((float)(g.nd - 1), 0.70710678f), 0.5f) <= sc;
         for (uint32_t row = warp; row < rows; row += kRotThreads / 32) {
             const uint32_t c = fast_div(row, magic_nd), x = row - c * g.nd;
             const float* plane = img + (size_t)c * g.id * g.id;
@@ -150,6 +154,22 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
                 float v;
                 if (tq == 0) {                                     // block-uniform
                     v = resize_pixel(plane, g.id, g.nd, x, y);
+                } else if (all_inside) {                           // uniform over the launch
+                    const float sx = __fadd_rn(__fsub_rn(xc, ys), sc);
+                    const float sy = __fadd_rn(__fadd_rn(xs, yc), sc);
+                    const float tx = __fadd_rz(sx, 8388608.0f), ty = __fadd_rz(sy, 8388608.0f);
+                    const uint32_t ix = __float_as_uint(tx) & 0x7FFFFFu, iy = __float_as_uint(ty) & 0x7FFFFFu;
+                    const float rx = __fsub_rn(sx, __fsub_rn(tx, 8388608.0f));
+                    const float ry = __fsub_rn(sy, __fsub_rn(ty, 8388608.0f));
+                    const float cx = __fsub_rn(1.0f, rx), cy = __fsub_rn(1.0f, ry);
+                    const float* r0 = plane + (ix * g.id + iy);
+                    const float* r1 = r0 + g.id;
+                    const float p00 = __ldg(r0), p01 = __ldg(r0 + 1), p10 = __ldg(r1), p11 = __ldg(r1 + 1);
+                    const float t00 = __fmul_rn(__fmul_rn(cx, cy), p00);
+                    const float t01 = __fmul_rn(__fmul_rn(cx, ry), p01);
+                    const float t10 = __fmul_rn(__fmul_rn(rx, cy), p10);
+                    const float t11 = __fmul_rn(__fmul_rn(rx, ry), p11);
+                    v = __fadd_rn(__fadd_rn(__fadd_rn(t00, t01), t10), t11);
                 } else {
                     // inverse rotation and bilinear taps; every product and sum rounded
                     // separately, in the order of src/ImageProcessingLib/rotate.h:37-63

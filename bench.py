@@ -430,6 +430,7 @@ def main():
             extras["other_configs"] = bench_other_configs(torch, local)
             extras["distance_sweep"] = bench_distance_sweep(torch)
             extras["cli"] = bench_cli(w, pool)
+            extras["python_api"] = bench_python_api(w, som, pool)
             extras["reference_gpu"] = bench_reference_gpu(w, som, pool)
 
     cpu = None
@@ -586,6 +587,34 @@ def bench_cli(w, pool, n_images=2048, epochs=8):
             "loop_seconds": loop_s, "process_seconds": wall,
             "note": "Pink --train on a data file of the bench workload, all visible GPUs of the process (here one); "
                     "loop time from the program's progress output, process time includes start-up and writing the map"}
+
+
+def bench_python_api(w, som, pool, n_images=2048):
+    """The reference's Python usage (python/pink/train.py): one Trainer call per image from a Python loop, then
+    update_som(); through the compiled module pink_b200._pink."""
+    try:
+        from pink_b200 import _pink as pink
+    except ImportError as ex:
+        return {"unavailable": "pink_b200._pink is not built: %s" % ex}
+    N = som_size(w)
+    n_images = min(n_images, len(pool))
+    images = pool[:n_images].reshape(n_images, w["image_dim"], w["image_dim"])
+    hexa = w["som_layout"] == 1
+    shape = (N, w["neuron_dim"], w["neuron_dim"]) if hexa else (w["som_dim"], w["som_dim"], w["neuron_dim"], w["neuron_dim"])
+    som_obj = pink.SOM(np.ascontiguousarray(som.reshape(shape)), som_layout="hexagonal-2d" if hexa else "cartesian-2d")
+    trainer = pink.Trainer(som_obj, pink.GaussianFunctor(w["sigma"], w["damping"]), number_of_rotations=w["rotations"],
+                           use_flip=bool(w["flip"]), euclidean_distance_dim=w["ed_dim"],
+                           euclidean_distance_type=pink.DataType.UINT8)
+    for i in range(32):                              # context creation and warm-up
+        trainer(pink.Data(images[i]))
+    trainer.update_som()
+    t0 = time.perf_counter()
+    for i in range(n_images):
+        trainer(pink.Data(images[i]))
+    trainer.update_som()
+    dt = time.perf_counter() - t0
+    return {"value": n_images / dt, "unit": "images/s", "images": n_images,
+            "note": "for i: trainer(pink.Data(image[i])); then trainer.update_som() -- wall clock of the Python loop"}
 
 
 def bench_distance_sweep(torch):

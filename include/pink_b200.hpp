@@ -277,19 +277,24 @@ public:
                                 ? distribution_function(distance[i]) : 0.0f;
     }
 
+    /// Nothing of a training step can be observed before update_som(), so the images are collected and handed to
+    /// the device sixteen at a time: whole batches of steps run in one launch.
     void operator () (Data<DataLayout, float> const& data)
     {
         const bool first = m_session.get() == nullptr;
         pink_b200_ctx* ctx = m_session.context(data, m_som.get_data_pointer());
         if (first) detail::check(pink_b200_set_update_lut(ctx, m_grid[0], m_grid[1], m_grid[2], m_grid[3], m_update_factors.data(),
                                                           static_cast<uint32_t>(m_update_factors.size())));
-        detail::check(pink_b200_train(ctx, data.get_data_pointer(), 1));
+        const float* px = data.get_data_pointer();
+        m_pending.insert(m_pending.end(), px, px + data.size());
+        if (++m_n_pending == 16) flush();
     }
 
     /// copy the trained map from the device into the SOM object
     void update_som()
     {
         if (!m_session.get()) return;
+        flush();
         detail::check(pink_b200_get_som(m_session.get(), m_som.get_data_pointer()));
         detail::check(pink_b200_get_update_counts(m_session.get(), m_update_info.data()));
     }
@@ -298,9 +303,22 @@ public:
     auto get_update_info() const { return m_update_info; }
 
 private:
+    /// the collected images, in order (the library has taken them out of the buffer when the call returns)
+    void flush()
+    {
+        if (m_n_pending == 0) return;
+        const uint32_t n = m_n_pending;
+        m_n_pending = 0;
+        const int rc = pink_b200_train(m_session.get(), m_pending.data(), n);
+        m_pending.clear();
+        detail::check(rc);
+    }
+
     SOMType& m_som;
     detail::Session<SOMLayout, DataLayout> m_session;
     std::array<uint32_t, 4> m_grid{};
+    std::vector<float> m_pending;               // images given to operator() that have not gone to the device yet
+    uint32_t m_n_pending = 0;
     std::vector<float> m_update_factors;        // one factor per distance class of the grid
     std::vector<uint32_t> m_update_info;
 };

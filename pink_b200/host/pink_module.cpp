@@ -220,10 +220,14 @@ public:
         }
     }
 
+    // One image (src/pink/DynamicTrainer.h:110-120).  Nothing of a training step can be observed before
+    // update_som() / get_update_info(), so the images are collected and handed to the device kDefer at a time:
+    // whole batches of steps run in one launch instead of one launch sequence per image.
     void call(const Data& data)
     {
         prepare(data.shape);
-        check(pink_b200_train(m_session.ctx(), data.data.data(), 1));
+        m_pending.insert(m_pending.end(), data.data.begin(), data.data.end());
+        if (++m_n_pending == kDefer) flush();
     }
 
     // many images in one call: (n, id, id) or (n, C, id, id)
@@ -232,6 +236,7 @@ public:
         if (images.ndim() < 3) throw pink_error("images must have shape (n, id, id) or (n, C, id, id)");
         std::vector<uint32_t> shape(images.shape() + 1, images.shape() + images.ndim());
         prepare(shape);
+        flush();
         check(pink_b200_train(m_session.ctx(), images.data(), (uint64_t)images.shape(0)));
     }
 
@@ -239,6 +244,7 @@ public:
     void update_som()
     {
         if (!m_session.ctx()) return;
+        flush();
         check(pink_b200_synchronize(m_session.ctx()));
         check(pink_b200_get_som(m_session.ctx(), m_session.som().data.data()));
     }
@@ -247,11 +253,27 @@ public:
     {
         py::array_t<uint32_t> out((ssize_t)m_session.som().n_neurons);
         std::memset(out.mutable_data(), 0, out.size() * sizeof(uint32_t));
-        if (m_session.ctx()) check(pink_b200_get_update_counts(m_session.ctx(), out.mutable_data()));
+        if (m_session.ctx()) {
+            flush();
+            check(pink_b200_get_update_counts(m_session.ctx(), out.mutable_data()));
+        }
         return out;
     }
 
 private:
+    static constexpr uint32_t kDefer = 16;          // images collected before they go to the device
+
+    // the collected images, in order (pink_b200_train has taken them out of the buffer when it returns: pageable memory)
+    void flush()
+    {
+        if (m_n_pending == 0) return;
+        const uint32_t n = m_n_pending;
+        m_n_pending = 0;
+        const int rc = pink_b200_train(m_session.ctx(), m_pending.data(), n);
+        m_pending.clear();
+        check(rc);
+    }
+
     void prepare(const std::vector<uint32_t>& image_shape)
     {
         if (m_session.open(image_shape)) {
@@ -262,6 +284,8 @@ private:
     }
     Session m_session;
     std::vector<float> m_factors;
+    std::vector<float> m_pending;                   // images given to call() that have not gone to the device yet
+    uint32_t m_n_pending = 0;
 };
 
 class Mapper

@@ -224,17 +224,35 @@ class Trainer(_Common):
         s = self._som
         self._eng.set_update_lut(s._layout, s._dim0, s._dim1, self._lut)
 
+    _DEFER = 16          # images collected before they go to the device
+
     def __call__(self, data):
-        self._engine(data).train(np.asarray(data))
+        """One image.  Nothing of a training step can be observed before update_som() / get_update_info(), so the
+        images are collected and handed to the device _DEFER at a time: whole batches of steps run in one launch."""
+        self._engine(data)
+        pending = self.__dict__.setdefault("_pending", [])
+        pending.append(np.array(data, dtype=np.float32, copy=True))
+        if len(pending) == self._DEFER:
+            self._flush()
+
+    def _flush(self):
+        pending = self.__dict__.get("_pending")
+        if pending:
+            images = np.stack(pending)
+            pending.clear()
+            self._eng.train(images)
 
     def train(self, images):
         """Sequential training steps over an array of images (n, id, id) or (n, C, id, id) in one call."""
         images = np.ascontiguousarray(images, dtype=np.float32)
-        self._engine(images[0]).train(images)
+        self._engine(images[0])
+        self._flush()
+        self._eng.train(images)
 
     def update_som(self):
         """Copies the trained weights into the SOM's storage (Trainer.h:306-309)."""
         if self._eng is not None:
+            self._flush()
             self._eng.synchronize()
             flat = np.asarray(self._som).reshape(self._som.number_of_neurons, -1)
             self._eng.get_som(flat)
@@ -243,6 +261,7 @@ class Trainer(_Common):
         """Number of times each neuron was the best matching unit (TrainerCommon::get_update_info)."""
         if self._eng is None:
             return np.zeros(self._som.number_of_neurons, np.uint32)
+        self._flush()
         return self._eng.update_counts()
 
 

@@ -149,6 +149,28 @@ def test_dynamic_trainer_layouts_like_train_py(cuda, pink, layout, shape):
     assert trainer.get_update_info().sum() == 5
 
 
+def test_images_given_one_by_one_equal_one_batch(cuda, pink):
+    """Trainer.__call__ collects images and hands them to the device in batches; the map after update_som() is the
+    one a single train() call over the same images gives, whatever the number of images (more than one batch,
+    not a whole number of them) and with a train() call in between."""
+    rng = np.random.default_rng(8)
+    som0 = rng.random((4, 4, 12, 12), dtype=np.float32)
+    imgs = rng.random((37, 16, 16), dtype=np.float32)
+    a, b = pink.SOM(som0), pink.SOM(som0)
+    ta = pink.Trainer(a, pink.GaussianFunctor(1.1, 0.3), number_of_rotations=8, euclidean_distance_dim=8)
+    tb = pink.Trainer(b, pink.GaussianFunctor(1.1, 0.3), number_of_rotations=8, euclidean_distance_dim=8)
+    for i in range(20):
+        ta(pink.Data(imgs[i]))
+    ta.train(imgs[20:30])
+    for i in range(30, 37):
+        ta(pink.Data(imgs[i]))
+    assert ta.get_update_info().sum() == 37
+    ta.update_som()
+    tb.train(imgs)
+    tb.update_som()
+    assert np.array_equal(np.array(a).view(np.uint32), np.array(b).view(np.uint32))
+
+
 def test_python_callable_distribution_function(cuda, pink):
     """Any Python callable works as distribution_function (pybind11/functional.h in the reference)."""
     som0 = np.random.default_rng(1).random((3, 3, 8, 8), dtype=np.float32)

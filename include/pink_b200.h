@@ -125,8 +125,6 @@ int pink_b200_shard_range(uint32_t n_neurons, uint32_t world_size, uint32_t rank
  *                          image; g >= 2 groups of g consecutive ranks share
  *   "rotation_overlap"     1 puts the rotation kernels on a second, low-priority stream (default 0)
  *   "mma_pairs"            0 keeps the distance kernel from pairing blocks (default 1)
- *   "map_overlap"          0 keeps mapping on one stream; 1 (default) rotates the next batch of images on a second
- *                          stream beside the distance kernels of the current one
  *   "f32_filter"           0 computes float32 distances with the all-pairs exact kernel instead of the tensor-core
  *                          estimate + exact pass (default 1)
  *   "cooperative_launch"   0 launches the persistent kernel without the cooperative attribute (default 1).  Its

@@ -232,12 +232,6 @@ struct pink_b200_ctx
     int opt_mma_pairs = 1;
     int opt_cooperative = 1;          // 0: persistent kernel launched without the cooperative attribute
     int opt_f32_filter = 1;           // float32 mapping: tensor-core estimate + exact pass where the geometry allows it
-    int opt_map_overlap = 1;          // mapping: rotation of the next batch on a second stream beside the distances of this one
-    // mapping pipeline: the transform buffers hold two batches (slots); the rotation of batch k + 1 runs on map_rot_stream
-    // while the distance kernels of batch k run on the context's stream
-    cudaStream_t map_rot_stream = nullptr;
-    cudaEvent_t map_rotated[2] = { nullptr, nullptr }, map_mapped[2] = { nullptr, nullptr }, map_entry = nullptr;
-    uint64_t map_chunks = 0;          // batches mapped so far (slot = parity)
     // float32 mapping filter: TF32 word planes and float norms of the SOM operand (valid while the SOM is unchanged)
     // and of one mapping batch of transforms, the estimate matrix and the pass's counters
     float* d_af_hi = nullptr; float* d_af_lo = nullptr; float* d_af_norm = nullptr; bool af_valid = false;
@@ -712,9 +706,8 @@ int setup_peer_exchange(pink_b200_ctx* c)
         group = c->opt_rotation_sharing >= 2 ? (uint32_t)std::min<long>(c->opt_rotation_sharing, W) : std::min<uint32_t>(W, 2);
     mine.share = group;
     if (mine.share) {
-        // (sized for mapping too -- two batches -- so that the buffers the peers have mapped are never reallocated)
-        const size_t imgs = std::max<size_t>(3 * kRotBatch, 2 * (size_t)c->map_batch);
-        int rc0 = ensure_transform_buffers(c, imgs, base_fits_smem(c->g) ? 3 * kRotBatch : imgs);
+        const size_t imgs = std::max<size_t>(3 * kRotBatch, c->map_batch);
+        int rc0 = ensure_transform_buffers(c, imgs, 3 * kRotBatch);
         if (rc0) return rc0;
         CU_TRY(cudaMalloc(&c->d_rotflag, 3 * W * sizeof(unsigned long long)));
         CU_TRY(cudaMemsetAsync(c->d_rotflag, 0, 3 * W * sizeof(unsigned long long), c->stream));
@@ -1002,9 +995,6 @@ int pink_b200_destroy(pink_b200_ctx* c)
     free_dev(c->d_som); free_dev(c->d_a0); free_dev(c->d_a1); free_dev(c->d_anorm);
     free_dev(c->d_cs); free_dev(c->d_sn); free_dev(c->d_factors); free_dev(c->d_coords); free_dev(c->d_lut); free_dev(c->d_base);
     free_dev(c->d_b0); free_dev(c->d_b1); free_dev(c->d_bnorm); free_dev(c->d_keys);
-    if (c->map_rot_stream) cudaStreamDestroy(c->map_rot_stream);
-    for (int i = 0; i < 2; ++i) { if (c->map_rotated[i]) cudaEventDestroy(c->map_rotated[i]); if (c->map_mapped[i]) cudaEventDestroy(c->map_mapped[i]); }
-    if (c->map_entry) cudaEventDestroy(c->map_entry);
     free_dev(c->d_af_hi); free_dev(c->d_af_lo); free_dev(c->d_af_norm); free_dev(c->d_bf_hi); free_dev(c->d_bf_lo);
     free_dev(c->d_bf_norm); free_dev(c->d_est); free_dev(c->d_filter_stats);
     free_dev(c->d_items); free_dev(c->d_nitems); free_dev(c->d_stats); free_dev(c->d_wrange); free_dev(c->d_rmax);
@@ -1074,8 +1064,6 @@ int pink_b200_set_option(pink_b200_ctx* c, const char* name, long long value)
         }
     } else if (key == "mma_pairs") {
         c->opt_mma_pairs = value != 0;
-    } else if (key == "map_overlap") {
-        c->opt_map_overlap = value != 0;
     } else if (key == "f32_filter") {
         c->opt_f32_filter = value != 0;
     } else if (key == "cooperative_launch") {
@@ -1297,96 +1285,50 @@ int pink_b200_get_bmu_log(pink_b200_ctx* c, uint32_t* host_bmus, uint64_t n)
     return PINK_B200_OK;
 }
 
-// Streams and events of the mapping pipeline, and transform buffers for two batches.
-static int map_prepare(pink_b200_ctx* c)
-{
-    if (!c->map_rot_stream) {
-        CU_TRY(cudaStreamCreateWithFlags(&c->map_rot_stream, cudaStreamNonBlocking));
-        for (int i = 0; i < 2; ++i) {
-            CU_TRY(cudaEventCreateWithFlags(&c->map_rotated[i], cudaEventDisableTiming));
-            CU_TRY(cudaEventCreateWithFlags(&c->map_mapped[i], cudaEventDisableTiming));
-        }
-        CU_TRY(cudaEventCreateWithFlags(&c->map_entry, cudaEventDisableTiming));
-    }
-    const size_t imgs = 2 * (size_t)c->map_batch;
-    int rc = ensure_transform_buffers(c, imgs, base_fits_smem(c->g) ? 0 : imgs);
-    if (rc) return rc;
-    if (uses_filter(c)) rc = ensure_filter_buffers(c, imgs);
-    return rc;
-}
-
-// One batch of m <= map_batch images: rotation set on the rotation stream into the batch's slot of the transform
-// buffers, distances + minimum + square root on the context's stream.  Consecutive batches alternate between the two
-// slots, so that the rotation of the next batch (issue-bound, small blocks) shares the SMs with the distance
-// kernels of this one (bound by operand traffic and the tensor pipe, one large block per SM).  `images_ready`: event
-// after which d_images may be read (nullable: they are ready in stream order of the context's stream).
-static int map_chunk(pink_b200_ctx* c, const float* d_images, uint32_t m, float* d_dist, uint32_t* d_rot, cudaEvent_t images_ready)
+static int map_chunk(pink_b200_ctx* c, const float* d_images, uint32_t m, float* d_dist, uint32_t* d_rot)
 {
     const Geometry& g = c->g;
     const bool filter = uses_filter(c);
-    const uint32_t slot = (uint32_t)(c->map_chunks++ & 1);
-    const size_t img0 = (size_t)slot * c->map_batch, row0 = img0 * g.T;
-    const size_t esz = g.mode == kModeF32 ? 4 : 1;
-    cudaStream_t rs = c->opt_map_overlap ? c->map_rot_stream : c->stream;
-    uint8_t* b0 = static_cast<uint8_t*>(c->d_b0) + row0 * g.Kp * esz;
-    uint8_t* b1 = c->d_b1 ? static_cast<uint8_t*>(c->d_b1) + row0 * g.Kp * esz : nullptr;
-    uint8_t* bnorm = static_cast<uint8_t*>(c->d_bnorm) + row0 * (g.mode == kModeU16 ? 8 : 4);
-    float* base = base_fits_smem(g) ? nullptr : c->d_base + img0 * (g.q ? g.q : 1) * (size_t)g.P;
-    unsigned long long* keys = c->d_keys + img0 * c->count;
-    float* bf_hi = filter ? c->d_bf_hi + row0 * g.Kp : nullptr;
-    float* bf_lo = filter ? c->d_bf_lo + row0 * g.Kp : nullptr;
-    float* bf_norm = filter ? c->d_bf_norm + row0 : nullptr;
-    float* est = filter ? c->d_est + row0 * c->count : nullptr;
-
-    if (rs != c->stream) {
-        // the slot's buffers are free once the batch before last is mapped; the images are there in stream order of
-        // the context's stream (or after images_ready)
-        CU_TRY(cudaStreamWaitEvent(rs, c->map_mapped[slot], 0));
-        if (images_ready) CU_TRY(cudaStreamWaitEvent(rs, images_ready, 0));
-        else {
-            CU_TRY(cudaEventRecord(c->map_entry, c->stream));
-            CU_TRY(cudaStreamWaitEvent(rs, c->map_entry, 0));
-        }
+    if (filter) {
+        int rc = ensure_filter_buffers(c, c->map_batch);
+        if (rc) return rc;
+        // the rotation kernel also writes the estimate's TF32 planes and norms of the transforms
+        LAUNCH_TRY(launch_rotate(g, d_images, m, c->d_cs, c->d_sn, base_fits_smem(g) ? nullptr : c->d_base, c->d_b0, c->d_bf_hi,
+                                 c->d_bf_norm, c->stream, nullptr, c->d_bf_lo));
+    } else {
+        LAUNCH_TRY(launch_rotate(g, d_images, m, c->d_cs, c->d_sn, base_fits_smem(g) ? nullptr : c->d_base, c->d_b0, c->d_b1, c->d_bnorm, c->stream));
     }
-    if (filter)     // the rotation kernel also writes the estimate's TF32 planes and norms of the transforms
-        LAUNCH_TRY(launch_rotate(g, d_images, m, c->d_cs, c->d_sn, base, b0, bf_hi, bf_norm, rs, nullptr, bf_lo));
-    else
-        LAUNCH_TRY(launch_rotate(g, d_images, m, c->d_cs, c->d_sn, base, b0, b1, bnorm, rs));
-    if (rs != c->stream) {
-        CU_TRY(cudaEventRecord(c->map_rotated[slot], rs));
-        CU_TRY(cudaStreamWaitEvent(c->stream, c->map_rotated[slot], 0));
-    }
-
     DistanceArgs da{};
     da.a0 = c->d_a0; da.a1 = c->d_a1; da.anorm = c->d_anorm; da.n = c->count;
-    da.b0 = b0; da.b1 = b1; da.bnorm = bnorm; da.n_img = m;
-    da.keys = keys; da.s_out = nullptr; da.status = c->d_status; da.single_cta = !c->opt_mma_pairs;
+    da.b0 = c->d_b0; da.b1 = c->d_b1; da.bnorm = c->d_bnorm; da.n_img = m;
+    da.keys = c->d_keys; da.s_out = nullptr; da.status = c->d_status; da.single_cta = !c->opt_mma_pairs;
     const char* why = "";
     if (filter) {
         // estimate of every pair on the tensor cores, then exact sums for the transforms it cannot rule out
         const float* A = static_cast<const float*>(c->d_a0);
-        const float* B = reinterpret_cast<const float*>(b0);
+        const float* B = static_cast<const float*>(c->d_b0);
         if (!c->af_valid) {
             LAUNCH_TRY(launch_split_tf32(A, c->count, g.Kp, c->d_af_hi, c->d_af_lo, c->d_af_norm, c->stream));
             c->af_valid = true;
             c->launches += 1;
         }
         da.a0 = c->d_af_hi; da.a1 = c->d_af_lo; da.anorm = c->d_af_norm;
-        da.b0 = bf_hi; da.b1 = bf_lo; da.bnorm = bf_norm;
-        da.s_out = est;
+        da.b0 = c->d_bf_hi; da.b1 = c->d_bf_lo; da.bnorm = c->d_bf_norm;
+        da.s_out = c->d_est;
         cudaError_t e = launch_distance_tf32(g, da, c->stream, &why);
         if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
-        LAUNCH_TRY(launch_refine_f32(g, A, c->d_af_norm, c->count, B, bf_norm, m, est, filter_eps(g.K), keys,
+        const float eps = filter_eps(g.K);
+        LAUNCH_TRY(launch_refine_f32(g, A, c->d_af_norm, c->count, B, c->d_bf_norm, m, c->d_est, eps, c->d_keys,
                                      c->d_filter_stats, c->stream));
         c->filter_pairs += (unsigned long long)m * c->count * g.T;
-        c->launches += 1;                 // the exact pass
-    } else {
-        cudaError_t e = launch_distance(g, da, c->stream, &why);
-        if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
+        LAUNCH_TRY(launch_map_finalize(g, c->d_keys, m, c->count, d_dist, d_rot, c->stream));
+        c->launches += 4;                 // rotation set, estimate, exact pass, epilogue
+        return PINK_B200_OK;
     }
-    LAUNCH_TRY(launch_map_finalize(g, keys, m, c->count, d_dist, d_rot, c->stream));
-    if (rs != c->stream) CU_TRY(cudaEventRecord(c->map_mapped[slot], c->stream));
-    c->launches += 3;                 // rotation set, distance (estimate), epilogue
+    cudaError_t e = launch_distance(g, da, c->stream, &why);
+    if (e != cudaSuccess) return fail(PINK_B200_ECUDA, std::string(why) + ": " + cudaGetErrorString(e));
+    LAUNCH_TRY(launch_map_finalize(g, c->d_keys, m, c->count, d_dist, d_rot, c->stream));
+    c->launches += 3;                 // rotation set, distance, epilogue
     return PINK_B200_OK;
 }
 
@@ -1413,11 +1355,11 @@ int pink_b200_map_device(pink_b200_ctx* c, const float* dev_images, uint64_t n, 
     if (!c || ((!dev_images || !dev_dist || !dev_rot) && n)) return fail(PINK_B200_EINVAL, "null argument");
     if (!c->have_som) return fail(PINK_B200_ESTATE, "pink_b200_set_som must be called before mapping");
     CU_TRY(cudaSetDevice(c->cfg.device));
-    int rc = map_prepare(c);
+    int rc = ensure_transform_buffers(c, c->map_batch, base_fits_smem(c->g) ? 0 : c->map_batch);
     if (rc) return rc;
     for (uint64_t done = 0; done < n;) {
         const uint32_t m = (uint32_t)(n - done < c->map_batch ? n - done : c->map_batch);
-        rc = map_chunk(c, dev_images + done * c->image_size(), m, dev_dist + done * c->count, dev_rot + done * c->count, nullptr);
+        rc = map_chunk(c, dev_images + done * c->image_size(), m, dev_dist + done * c->count, dev_rot + done * c->count);
         if (rc) return rc;
         done += m;
     }
@@ -1431,7 +1373,7 @@ int pink_b200_map(pink_b200_ctx* c, const float* host_images, uint64_t n, float*
     if (!c->have_som) return fail(PINK_B200_ESTATE, "pink_b200_set_som must be called before mapping");
     CU_TRY(cudaSetDevice(c->cfg.device));
     const size_t B = c->map_batch, isz = c->image_size();
-    int rc = map_prepare(c);
+    int rc = ensure_transform_buffers(c, B, base_fits_smem(c->g) ? 0 : B);
     if (rc) return rc;
     rc = ensure_image_staging(c, B > c->train_batch ? B : c->train_batch);
     if (rc) return rc;
@@ -1454,7 +1396,7 @@ int pink_b200_map(pink_b200_ctx* c, const float* host_images, uint64_t n, float*
                                cudaMemcpyHostToDevice, c->copy_stream));
         CU_TRY(cudaEventRecord(c->copied[buf], c->copy_stream));
         CU_TRY(cudaStreamWaitEvent(c->stream, c->copied[buf], 0));
-        rc = map_chunk(c, c->d_images[buf], m, dd, dr, c->copied[buf]);
+        rc = map_chunk(c, c->d_images[buf], m, dd, dr);
         if (rc) return rc;
         CU_TRY(cudaMemcpyAsync(host_dist + done * c->count, dd, (size_t)m * c->count * sizeof(float),
                                cudaMemcpyDeviceToHost, c->stream));
@@ -1472,7 +1414,6 @@ int pink_b200_synchronize(pink_b200_ctx* c)
     CU_TRY(cudaSetDevice(c->cfg.device));
     CU_TRY(cudaStreamSynchronize(c->copy_stream));
     CU_TRY(cudaStreamSynchronize(c->rot_stream));
-    if (c->map_rot_stream) CU_TRY(cudaStreamSynchronize(c->map_rot_stream));
     return check_status(c);
 }
 

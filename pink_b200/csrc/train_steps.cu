@@ -266,17 +266,15 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                     const uint32_t mu = item % pl.m_units, nt = item / pl.m_units;
                     const int32_t m0 = (int32_t)((PAIR ? 2 * mu + pair_rank : mu) * kBlockM);
                     const int32_t brow = (int32_t)(a.b_row0 + img * g.T + nt * pl.n_tile + pair_rank * b_rows);
-                    // Tiles that share neuron rows (or transform rows) run at the same time on other SMs.  Each starts
-                    // its walk over K at a different slice, so that they do not all ask the same L2 lines for the same
-                    // bytes at the same moment; integer accumulation does not depend on the order.
-                    const uint32_t k_first = (uint32_t)(((uint64_t)item * num_kb) / n_items);
+                    // All tiles walk K in the same order from the same slice: the tiles that share neuron rows (or
+                    // transform rows) run at the same time on other SMs and then ask for the same L2 lines at about the
+                    // same moment, which is cheaper for the L2 than the same requests spread in time (measured both ways).
                     for (uint32_t kb = 0; kb < num_kb; ++kb) {
                         const uint32_t it = (img * my_items + k) * num_kb + kb;
                         const uint32_t s = it % pl.ring_stages, ph = (it / pl.ring_stages) & 1;
                         if (!step_wait(&sh.empty_bar[s], ph ^ 1, sh, a.status)) { step_fail(sh, a.status, kDevTimeoutProducer); break; }
                         uint8_t* st = region + s * ring_stage_bytes;
-                        const uint32_t kb_at = kb + k_first < num_kb ? kb + k_first : kb + k_first - num_kb;
-                        const int32_t kx = (int32_t)(kb_at * kBlockK);
+                        const int32_t kx = (int32_t)(kb * kBlockK);
                         if (PAIR) {
                             const uint32_t bar = map_to_cta(smem_u32(&sh.full_bar[s]), 0);     // the issuing block's barrier
                             mbar_expect_tx_cluster(bar, stage_tx);

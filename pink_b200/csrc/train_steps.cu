@@ -669,6 +669,9 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                         aw += sw; ab += sb;
                     }
                 }
+                // this thread's stores into the stage before the producer's bulk store reads it (asynchronous proxy);
+                // issued here so that its latency overlaps the barrier and the operand pass below, which only read
+                if (diff_bits != 0u) fence_async_smem();
                 {
                     const bool warp_changed = __any_sync(0xffffffffu, diff_bits != 0u);
                     lo_i = __reduce_min_sync(0xffffffffu, lo_i);
@@ -709,10 +712,15 @@ train_steps_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_cons
                             }
                         }
                     }
-                    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
-                    if (lane == 0) sh.norm_s[s][cwarp] = acc;
+                    if (MODE == kModeU8) {
+                        // at most 16 squares below 2^16 per thread: the warp's sum fits 32 bits, one reduction instruction
+                        const uint32_t wsum = __reduce_add_sync(0xffffffffu, (uint32_t)acc);
+                        if (lane == 0) sh.norm_s[s][cwarp] = wsum;
+                    } else {
+                        for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+                        if (lane == 0) sh.norm_s[s][cwarp] = acc;
+                    }
                 }
-                if (plane_changed) fence_async_smem();        // this thread's stage writes before the producer's bulk store
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh.upd_done[s]);
             }

@@ -112,3 +112,12 @@ def test_shard_ranges_partition_the_som(N, W):
     assert nxt == N
     with pytest.raises(capi.PinkError):
         engine.shard_range(3, 4, 0)
+
+
+def test_bench_reads_tracked_profile_figures():
+    """bench.py quotes DRAM traffic from the tracked ncu summary (lines `key = value`); the keys it asks for exist."""
+    import bench
+    assert bench.tracked_figure("train_steps_kernel_u8_c4.txt", "dram_bytes_per_image") > 1e6
+    assert bench.tracked_figure("train_steps_kernel_u8_c4.txt", "moved_bytes_per_image") > 1e6
+    assert bench.tracked_figure("train_steps_kernel_u8_c4.txt", "no_such_key") is None
+    assert bench.tracked_figure("no_such_file.txt", "x") is None

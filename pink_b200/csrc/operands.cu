@@ -138,10 +138,11 @@ rotate_kernel(Geometry g, const float* __restrict__ images, uint32_t use_smem, u
             pyc[i] = __fmul_rn(py, ca);
         }
         const uint32_t idm1 = g.id - 1;
-        // When the rotated neuron window lies strictly inside the image for every angle (half its diagonal plus a
-        // margin of half a pixel within half the image), no source position is out of range and no +1 tap falls
-        // outside: the range test and the clamps below are identities and are left out.
-        const bool all_inside = __fadd_rn(__fmul_rn((float)(g.nd - 1), 0.70710678f), 0.5f) <= sc;
+        // When the rotated neuron window lies strictly inside the image for every angle (half its diagonal, plus a
+        // margin far above the rounding of the positions, within half the image), every source position s satisfies
+        // 0 <= s < id - 1: none is out of range and no +1 tap falls outside, so the range test and the clamps below
+        // are identities and are left out.
+        const bool all_inside = __fadd_rn(__fmul_rn((float)(g.nd - 1), 0.70710678f), 0.01f) <= sc;
         for (uint32_t row = warp; row < rows; row += kRotThreads / 32) {
             const uint32_t c = fast_div(row, magic_nd), x = row - c * g.nd;
             const float* plane = img + (size_t)c * g.id * g.id;
